@@ -1,0 +1,122 @@
+/*
+ * subcuber_b200 -- C ABI of the Blackwell (sm_100a) Strassen-Winograd GEMM backend.
+ *
+ * Two groups of entry points:
+ *
+ *  1. `run_<kernel>`: the benchmark-driver ABI of the reference project.  Signature, argument meaning,
+ *     ownership and error behaviour are those of `extern "C" int run_<kernel>(KernelRunnerBuffers, ...)`
+ *     in the reference (src/cuda/kernel_runner.cpp:27-32, src/cuda/kernel_runner_support.cuh:16-21,48-178,
+ *     544-578): a, b, d are DEVICE pointers owned by the caller, packed row-major (lda = k, ldb = n,
+ *     ldd = n); c may be NULL and is never read (beta = 0); the callee allocates and frees its own
+ *     workspace; D = A * B; *avg_ms is the mean over `iterations` timed runs after `warmup_iterations`
+ *     untimed ones, measured with CUDA events on streams[0].  Return 0 on success; otherwise one of the
+ *     SB200_ERR_* codes below (same meaning as the reference's int(cutlass::Status)), an int(cudaError_t),
+ *     10000 + cublasStatus_t for the cuBLAS rows (src/cuda/cublas_runner.cpp:37-39), or a device status
+ *     code >= 100 when a kernel gave up on a bounded wait.  No exception crosses the boundary.
+ *     Only streams[0] is used: products that the reference spreads over 7 or 49 streams run inside one
+ *     persistent kernel here.  split_k_slices must be 1.
+ *
+ *  2. `sb200_*`: the operator itself (one GEMM, asynchronous on a stream), for callers that manage
+ *     their own buffers, and a host-buffer convenience call.
+ */
+#ifndef SUBCUBER_B200_H_
+#define SUBCUBER_B200_H_
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* reference: src/cuda/kernel_runner_support.cuh:16-21 */
+typedef struct KernelRunnerBuffers {
+  const void* a;
+  const void* b;
+  const void* c;
+  void* d;
+} KernelRunnerBuffers;
+
+/* Opaque CUDA stream handle (cudaStream_t) without requiring cuda_runtime.h in C callers. */
+typedef struct CUstream_st* sb200_stream_t;
+
+enum {
+  SB200_OK = 0,
+  SB200_ERR_MISALIGNED_OPERAND = 1, /* a row of an operand or quadrant does not start on 16 bytes   */
+  SB200_ERR_INVALID_PROBLEM = 4,    /* non-positive or (level >= 1) odd sizes, NULL operand         */
+  SB200_ERR_NOT_SUPPORTED = 5,      /* unknown kernel / dtype / split_k_slices != 1                 */
+  SB200_ERR_WORKSPACE_NULL = 6,     /* workspace missing, too small or not 256-byte aligned         */
+  SB200_ERR_INTERNAL = 7,
+  SB200_ERR_NO_KERNEL = 8,          /* kernel name not in the registry                              */
+  SB200_STATUS_PRODUCER_TIMEOUT = 101, /* device: a bounded wait gave up (role in the code)        */
+  SB200_STATUS_MMA_TIMEOUT = 102,
+  SB200_STATUS_EPILOGUE_TIMEOUT = 103,
+  SB200_STATUS_PRESUM_TIMEOUT = 104
+};
+
+/* ---- group 1: kernel_runner ABI (reference: src/cuda/kernel_runner.cpp:27-32) --------------------- */
+#define SB200_DECLARE_RUN(name)                                                                          \
+  int name(KernelRunnerBuffers buffers, int m, int n, int k, int warmup_iterations, int iterations,    \
+           sb200_stream_t* streams, int num_streams, int split_k_slices, float* avg_ms)
+
+/* Level 0 (plain GEMM on tcgen05); registry rows analogous to the reference's *_cutlass_* kernels
+ * (src/cuda/kernel_runner.cpp:127-137). */
+SB200_DECLARE_RUN(run_blackwell_f16_cubic_128x256);
+SB200_DECLARE_RUN(run_blackwell_f16_cubic_128x128);
+SB200_DECLARE_RUN(run_blackwell_f32_cubic_128x256); /* fp32 storage, TF32 tensor-core math */
+SB200_DECLARE_RUN(run_blackwell_f32_cubic_128x128);
+/* Level 1, presums formed in shared memory each k-step ("FUSED_IN_SUM" variants of the reference,
+ * src/cuda/kernel_runner.cpp:148,150,161,164,179). */
+SB200_DECLARE_RUN(run_blackwell_f16_sw_fused_presum);
+SB200_DECLARE_RUN(run_blackwell_f32_sw_fused_presum);
+/* Level 1, presums written to a workspace by the launch that computes M0 and M1 ("PRESUM" /
+ * interleaved variants of the reference, src/cuda/kernel_runner.cpp:140-141,144-145,151-152). */
+SB200_DECLARE_RUN(run_blackwell_f16_sw_interleaved_presum);
+SB200_DECLARE_RUN(run_blackwell_f32_sw_interleaved_presum);
+/* cuBLAS baselines behind the same ABI (reference: src/cuda/cublas_runner.cpp:151-175); the tf32 row is
+ * an addition: the reference's f32 row is CUBLAS_COMPUTE_32F_PEDANTIC (cublas_runner.cpp:14). */
+SB200_DECLARE_RUN(run_cublas_f16);
+SB200_DECLARE_RUN(run_cublas_f32);
+SB200_DECLARE_RUN(run_cublas_f64);
+SB200_DECLARE_RUN(run_cublas_tf32);
+/* cuBLASLt baselines (reference: src/cuda/cublaslt_runner.cpp:42-272). */
+SB200_DECLARE_RUN(run_cublaslt_f16);
+SB200_DECLARE_RUN(run_cublaslt_f32);
+SB200_DECLARE_RUN(run_cublaslt_f64);
+
+/* Registry: the rows a driver lists (reference: `KernelEntry kKernels[]`, src/cuda/kernel_runner.cpp:99-181). */
+typedef SB200_DECLARE_RUN((*sb200_run_fn));
+typedef struct sb200_kernel_entry {
+  const char* name;
+  const char* arch;  /* "blackwell" */
+  const char* dtype; /* "f16" | "f32" | "f64" */
+  int strassen_level;
+  sb200_run_fn run;
+} sb200_kernel_entry;
+int sb200_num_kernels(void);
+const sb200_kernel_entry* sb200_kernel(int index);
+
+/* ---- group 2: the operator (reference: device::StrassenGemm life cycle can_implement /
+ *      get_workspace_size / initialize / run, include/cutlass/gemm/device/strassen_gemm.h:538-1117) -- */
+
+/* 0 if `kernel` (a registry name without the "run_" prefix, e.g. "blackwell_f16_sw_interleaved_presum")
+ * can run m x n x k, else an error code. */
+int sb200_gemm_can_implement(const char* kernel, int m, int n, int k);
+/* Bytes of device workspace one call needs (0 on unknown kernel). */
+size_t sb200_gemm_workspace_bytes(const char* kernel, int m, int n, int k);
+/* Enqueue D = A * B on `stream` (device pointers, packed row-major).  Asynchronous.  `workspace` must be
+ * 256-byte aligned device memory of at least sb200_gemm_workspace_bytes().  Allocates nothing. */
+int sb200_gemm(const char* kernel, const void* a, const void* b, void* d, int m, int n, int k, void* workspace,
+               size_t workspace_bytes, sb200_stream_t stream);
+/* Synchronise `stream` and return the device status word of the last sb200_gemm on `workspace`
+ * (0 = every bounded wait was satisfied). */
+int sb200_gemm_status(void* workspace, sb200_stream_t stream);
+/* Kernel launches one sb200_gemm call makes for this kernel name. */
+int sb200_gemm_launches(const char* kernel);
+/* Host-buffer convenience: copies A and B to the device, runs, copies D back, synchronously.
+ * Allocates and frees device memory inside the call. */
+int sb200_gemm_host(const char* kernel, const void* a_host, const void* b_host, void* d_host, int m, int n, int k);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SUBCUBER_B200_H_ */

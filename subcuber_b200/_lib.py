@@ -1,0 +1,60 @@
+"""ctypes loader for libsubcuber_b200.so (the C ABI declared in include/subcuber_b200.h).
+
+The library is the product: there is no Python or CPU fallback.  If the shared object is missing it is
+built with nvcc; if that is impossible the import fails with an error that says so.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libsubcuber_b200.so")
+
+
+class KernelRunnerBuffers(C.Structure):
+    """Mirror of `struct KernelRunnerBuffers` (reference: src/cuda/kernel_runner_support.cuh:16-21)."""
+
+    _fields_ = [("a", C.c_void_p), ("b", C.c_void_p), ("c", C.c_void_p), ("d", C.c_void_p)]
+
+
+RUN_ARGTYPES = [KernelRunnerBuffers, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_void_p), C.c_int,
+                C.c_int, C.POINTER(C.c_float)]
+RUN_FN = C.CFUNCTYPE(C.c_int, *RUN_ARGTYPES)
+
+
+class KernelEntry(C.Structure):
+    """Mirror of `sb200_kernel_entry` (reference: `struct KernelEntry`, src/cuda/kernel_runner.cpp:99-105)."""
+
+    _fields_ = [("name", C.c_char_p), ("arch", C.c_char_p), ("dtype", C.c_char_p), ("strassen_level", C.c_int),
+                ("run", RUN_FN)]
+
+
+_lib = None
+
+
+def load(build_if_missing: bool = True) -> C.CDLL:
+    """Load the CUDA library, building it first when the .so is absent.  Raises if neither works."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        if not build_if_missing:
+            raise RuntimeError(f"{LIB_PATH} is missing: run `python -m subcuber_b200.build`")
+        from . import build as _build
+
+        _build.build()
+    lib = C.CDLL(LIB_PATH)
+    lib.sb200_num_kernels.restype = C.c_int
+    lib.sb200_kernel.restype = C.POINTER(KernelEntry)
+    lib.sb200_kernel.argtypes = [C.c_int]
+    lib.sb200_gemm_can_implement.argtypes = [C.c_char_p, C.c_int, C.c_int, C.c_int]
+    lib.sb200_gemm_workspace_bytes.restype = C.c_size_t
+    lib.sb200_gemm_workspace_bytes.argtypes = [C.c_char_p, C.c_int, C.c_int, C.c_int]
+    lib.sb200_gemm.argtypes = [C.c_char_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p,
+                               C.c_size_t, C.c_void_p]
+    lib.sb200_gemm_status.argtypes = [C.c_void_p, C.c_void_p]
+    lib.sb200_gemm_launches.argtypes = [C.c_char_p]
+    lib.sb200_gemm_host.argtypes = [C.c_char_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int]
+    _lib = lib
+    return lib

@@ -1,0 +1,364 @@
+// extern "C" boundary of the library: the reference benchmark driver's `run_<kernel>` entry points
+// (src/cuda/kernel_runner.cpp:27-32 in the reference project), the kernel registry and the `sb200_*` operator calls.
+#include <cublasLt.h>
+#include <cublas_v2.h>
+#include <cuda_runtime.h>
+#include <string.h>
+
+#include "../../include/subcuber_b200.h"
+#include "sw_host.h"
+
+namespace {
+
+using sb200::DType;
+using sb200::GemmArgs;
+using sb200::Variant;
+
+struct KernelDesc {
+  const char* name;
+  const char* dtype;
+  int level;
+  DType dt;
+  Variant variant;
+  int bn;
+};
+
+const KernelDesc kDescs[] = {
+    {"blackwell_f16_cubic_128x256", "f16", 0, sb200::kF16, sb200::kCubic, 256},
+    {"blackwell_f16_cubic_128x128", "f16", 0, sb200::kF16, sb200::kCubic, 128},
+    {"blackwell_f32_cubic_128x256", "f32", 0, sb200::kF32, sb200::kCubic, 256},
+    {"blackwell_f32_cubic_128x128", "f32", 0, sb200::kF32, sb200::kCubic, 128},
+    {"blackwell_f16_sw_fused_presum", "f16", 1, sb200::kF16, sb200::kFusedPresum, 256},
+    {"blackwell_f32_sw_fused_presum", "f32", 1, sb200::kF32, sb200::kFusedPresum, 256},
+    {"blackwell_f16_sw_interleaved_presum", "f16", 1, sb200::kF16, sb200::kInterleavedPresum, 256},
+    {"blackwell_f32_sw_interleaved_presum", "f32", 1, sb200::kF32, sb200::kInterleavedPresum, 256},
+};
+constexpr int kNumDescs = sizeof(kDescs) / sizeof(kDescs[0]);
+
+const KernelDesc* find_desc(const char* name) {
+  if (!name) return nullptr;
+  for (int i = 0; i < kNumDescs; ++i)
+    if (strcmp(kDescs[i].name, name) == 0) return &kDescs[i];
+  return nullptr;
+}
+
+GemmArgs make_args(const KernelDesc& d, const void* a, const void* b, void* out, int m, int n, int k) {
+  GemmArgs g;
+  memset(&g, 0, sizeof(g));
+  g.dtype = d.dt;
+  g.variant = d.variant;
+  g.m = m;
+  g.n = n;
+  g.k = k;
+  g.a = a;
+  g.b = b;
+  g.d = out;
+  g.bn = d.bn;
+  g.sm_limit = 0;
+  return g;
+}
+
+// Timing harness of one registry row: the shape of kernel_runner_run_cutlass2 in the reference
+// (src/cuda/kernel_runner_support.cuh:48-178): check, allocate workspace, warm up, time `iterations` runs with
+// CUDA events, free.  Events are recorded on the stream the kernels run on.
+int run_registry_kernel(const char* name, KernelRunnerBuffers buf, int m, int n, int k, int warmup, int iterations,
+                        sb200_stream_t* streams, int num_streams, int split_k, float* avg_ms) {
+  const KernelDesc* d = find_desc(name);
+  if (!d) return SB200_ERR_NO_KERNEL;
+  if (split_k != 1) return SB200_ERR_NOT_SUPPORTED;
+  if (iterations <= 0 || warmup < 0 || !avg_ms) return SB200_ERR_INVALID_PROBLEM;
+  GemmArgs g = make_args(*d, buf.a, buf.b, buf.d, m, n, k);
+  int rc = sb200::can_implement(g);
+  if (rc) return rc;
+  cudaStream_t stream = (streams && num_streams > 0) ? reinterpret_cast<cudaStream_t>(streams[0]) : nullptr;
+  const size_t ws_bytes = sb200::workspace_bytes(g);
+  void* ws = nullptr;
+  cudaError_t ce = cudaMalloc(&ws, ws_bytes);
+  if (ce != cudaSuccess) return static_cast<int>(ce);
+  cudaEvent_t start = nullptr, stop = nullptr;
+  auto cleanup = [&]() {
+    if (start) cudaEventDestroy(start);
+    if (stop) cudaEventDestroy(stop);
+    cudaFree(ws);
+  };
+  for (int i = 0; i < warmup; ++i) {
+    rc = sb200::run(g, ws, ws_bytes, stream);
+    if (rc) { cleanup(); return rc; }
+  }
+  rc = sb200::read_status(ws, stream);
+  if (rc) { cleanup(); return rc; }
+  if ((ce = cudaEventCreate(&start)) != cudaSuccess || (ce = cudaEventCreate(&stop)) != cudaSuccess ||
+      (ce = cudaEventRecord(start, stream)) != cudaSuccess) {
+    cleanup();
+    return static_cast<int>(ce);
+  }
+  for (int i = 0; i < iterations; ++i) {
+    rc = sb200::run(g, ws, ws_bytes, stream);
+    if (rc) { cleanup(); return rc; }
+  }
+  if ((ce = cudaEventRecord(stop, stream)) != cudaSuccess || (ce = cudaEventSynchronize(stop)) != cudaSuccess) {
+    cleanup();
+    return static_cast<int>(ce);
+  }
+  float ms = 0.f;
+  if ((ce = cudaEventElapsedTime(&ms, start, stop)) != cudaSuccess) { cleanup(); return static_cast<int>(ce); }
+  rc = sb200::read_status(ws, stream);
+  cleanup();
+  if (rc) return rc;
+  *avg_ms = ms / static_cast<float>(iterations);
+  return 0;
+}
+
+// ------------------------------------------------------------------------------------------- cuBLAS rows
+int cublas_err(cublasStatus_t s) { return s == CUBLAS_STATUS_SUCCESS ? 0 : 10000 + static_cast<int>(s); }
+
+struct BlasType {
+  cudaDataType_t data;
+  cublasComputeType_t compute;
+  cublasMath_t math;
+  cublasGemmAlgo_t algo;
+  bool f64;
+};
+// f16 / f32 / f64 rows use the reference's settings (src/cuda/cublas_runner.cpp:9-35).
+const BlasType kBlasF16 = {CUDA_R_16F, CUBLAS_COMPUTE_32F_FAST_16F, CUBLAS_TENSOR_OP_MATH, CUBLAS_GEMM_DEFAULT_TENSOR_OP, false};
+const BlasType kBlasF32 = {CUDA_R_32F, CUBLAS_COMPUTE_32F_PEDANTIC, CUBLAS_DEFAULT_MATH, CUBLAS_GEMM_DEFAULT, false};
+const BlasType kBlasF64 = {CUDA_R_64F, CUBLAS_COMPUTE_64F_PEDANTIC, CUBLAS_DEFAULT_MATH, CUBLAS_GEMM_DEFAULT, true};
+const BlasType kBlasTF32 = {CUDA_R_32F, CUBLAS_COMPUTE_32F_FAST_TF32, CUBLAS_TF32_TENSOR_OP_MATH, CUBLAS_GEMM_DEFAULT_TENSOR_OP, false};
+
+template <typename Launch>
+int time_launches(Launch launch, cudaStream_t stream, int warmup, int iterations, float* avg_ms) {
+  int rc;
+  for (int i = 0; i < warmup; ++i)
+    if ((rc = launch())) return rc;
+  cudaError_t ce = cudaStreamSynchronize(stream);
+  if (ce != cudaSuccess) return static_cast<int>(ce);
+  cudaEvent_t start = nullptr, stop = nullptr;
+  if ((ce = cudaEventCreate(&start)) != cudaSuccess) return static_cast<int>(ce);
+  if ((ce = cudaEventCreate(&stop)) != cudaSuccess) { cudaEventDestroy(start); return static_cast<int>(ce); }
+  auto done = [&](int code) { cudaEventDestroy(start); cudaEventDestroy(stop); return code; };
+  if ((ce = cudaEventRecord(start, stream)) != cudaSuccess) return done(static_cast<int>(ce));
+  for (int i = 0; i < iterations; ++i)
+    if ((rc = launch())) return done(rc);
+  if ((ce = cudaEventRecord(stop, stream)) != cudaSuccess) return done(static_cast<int>(ce));
+  if ((ce = cudaEventSynchronize(stop)) != cudaSuccess) return done(static_cast<int>(ce));
+  float ms = 0.f;
+  if ((ce = cudaEventElapsedTime(&ms, start, stop)) != cudaSuccess) return done(static_cast<int>(ce));
+  *avg_ms = ms / static_cast<float>(iterations);
+  return done(0);
+}
+
+// Row-major D = A * B through column-major cuBLAS by swapping the operands
+// (reference: src/cuda/cublas_runner.cpp:81-90).
+int run_cublas(const BlasType& t, KernelRunnerBuffers buf, int m, int n, int k, int warmup, int iterations,
+               sb200_stream_t* streams, int num_streams, float* avg_ms) {
+  if (m <= 0 || n <= 0 || k <= 0 || iterations <= 0 || warmup < 0 || !avg_ms) return SB200_ERR_INVALID_PROBLEM;
+  cudaStream_t stream = (streams && num_streams > 0) ? reinterpret_cast<cudaStream_t>(streams[0]) : nullptr;
+  cublasHandle_t h = nullptr;
+  cublasStatus_t s = cublasCreate(&h);
+  if (s != CUBLAS_STATUS_SUCCESS) return cublas_err(s);
+  int rc = 0;
+  if ((s = cublasSetStream(h, stream)) != CUBLAS_STATUS_SUCCESS || (s = cublasSetMathMode(h, t.math)) != CUBLAS_STATUS_SUCCESS) {
+    cublasDestroy(h);
+    return cublas_err(s);
+  }
+  float alpha_f = 1.f, beta_f = 0.f;
+  double alpha_d = 1.0, beta_d = 0.0;
+  const void* alpha = t.f64 ? static_cast<const void*>(&alpha_d) : static_cast<const void*>(&alpha_f);
+  const void* beta = t.f64 ? static_cast<const void*>(&beta_d) : static_cast<const void*>(&beta_f);
+  auto launch = [&]() {
+    return cublas_err(cublasGemmEx(h, CUBLAS_OP_N, CUBLAS_OP_N, n, m, k, alpha, buf.b, t.data, n, buf.a, t.data, k, beta,
+                                   buf.d, t.data, n, t.compute, t.algo));
+  };
+  rc = time_launches(launch, stream, warmup, iterations, avg_ms);
+  cublasDestroy(h);
+  return rc;
+}
+
+// cuBLASLt with row-order layouts, one heuristic result and a 32 MiB workspace
+// (reference: src/cuda/cublaslt_runner.cpp:59,74-187).
+int run_cublaslt(const BlasType& t, KernelRunnerBuffers buf, int m, int n, int k, int warmup, int iterations,
+                 sb200_stream_t* streams, int num_streams, float* avg_ms) {
+  if (m <= 0 || n <= 0 || k <= 0 || iterations <= 0 || warmup < 0 || !avg_ms) return SB200_ERR_INVALID_PROBLEM;
+  cudaStream_t stream = (streams && num_streams > 0) ? reinterpret_cast<cudaStream_t>(streams[0]) : nullptr;
+  cublasLtHandle_t h = nullptr;
+  cublasLtMatmulDesc_t desc = nullptr;
+  cublasLtMatrixLayout_t la = nullptr, lb = nullptr, lc = nullptr;
+  cublasLtMatmulPreference_t pref = nullptr;
+  void* ws = nullptr;
+  const size_t ws_bytes = size_t(32) << 20;
+  auto cleanup = [&]() {
+    if (ws) cudaFree(ws);
+    if (pref) cublasLtMatmulPreferenceDestroy(pref);
+    if (lc) cublasLtMatrixLayoutDestroy(lc);
+    if (lb) cublasLtMatrixLayoutDestroy(lb);
+    if (la) cublasLtMatrixLayoutDestroy(la);
+    if (desc) cublasLtMatmulDescDestroy(desc);
+    if (h) cublasLtDestroy(h);
+  };
+  cublasStatus_t s;
+#define LT_CHECK(call)                      \
+  if ((s = (call)) != CUBLAS_STATUS_SUCCESS) { \
+    cleanup();                              \
+    return cublas_err(s);                   \
+  }
+  LT_CHECK(cublasLtCreate(&h));
+  LT_CHECK(cublasLtMatmulDescCreate(&desc, t.compute, t.f64 ? CUDA_R_64F : CUDA_R_32F));
+  cublasOperation_t op = CUBLAS_OP_N;
+  LT_CHECK(cublasLtMatmulDescSetAttribute(desc, CUBLASLT_MATMUL_DESC_TRANSA, &op, sizeof(op)));
+  LT_CHECK(cublasLtMatmulDescSetAttribute(desc, CUBLASLT_MATMUL_DESC_TRANSB, &op, sizeof(op)));
+  LT_CHECK(cublasLtMatrixLayoutCreate(&la, t.data, m, k, k));
+  LT_CHECK(cublasLtMatrixLayoutCreate(&lb, t.data, k, n, n));
+  LT_CHECK(cublasLtMatrixLayoutCreate(&lc, t.data, m, n, n));
+  cublasLtOrder_t order = CUBLASLT_ORDER_ROW;
+  LT_CHECK(cublasLtMatrixLayoutSetAttribute(la, CUBLASLT_MATRIX_LAYOUT_ORDER, &order, sizeof(order)));
+  LT_CHECK(cublasLtMatrixLayoutSetAttribute(lb, CUBLASLT_MATRIX_LAYOUT_ORDER, &order, sizeof(order)));
+  LT_CHECK(cublasLtMatrixLayoutSetAttribute(lc, CUBLASLT_MATRIX_LAYOUT_ORDER, &order, sizeof(order)));
+  LT_CHECK(cublasLtMatmulPreferenceCreate(&pref));
+  LT_CHECK(cublasLtMatmulPreferenceSetAttribute(pref, CUBLASLT_MATMUL_PREF_MAX_WORKSPACE_BYTES, &ws_bytes, sizeof(ws_bytes)));
+  cudaError_t ce = cudaMalloc(&ws, ws_bytes);
+  if (ce != cudaSuccess) { cleanup(); return static_cast<int>(ce); }
+  cublasLtMatmulHeuristicResult_t heur;
+  memset(&heur, 0, sizeof(heur));
+  int found = 0;
+  LT_CHECK(cublasLtMatmulAlgoGetHeuristic(h, desc, la, lb, lc, lc, pref, 1, &heur, &found));
+  if (found == 0) { cleanup(); return cublas_err(CUBLAS_STATUS_NOT_SUPPORTED); }
+#undef LT_CHECK
+  float alpha_f = 1.f, beta_f = 0.f;
+  double alpha_d = 1.0, beta_d = 0.0;
+  const void* alpha = t.f64 ? static_cast<const void*>(&alpha_d) : static_cast<const void*>(&alpha_f);
+  const void* beta = t.f64 ? static_cast<const void*>(&beta_d) : static_cast<const void*>(&beta_f);
+  auto launch = [&]() {
+    return cublas_err(cublasLtMatmul(h, desc, alpha, buf.a, la, buf.b, lb, beta, buf.d, lc, buf.d, lc, &heur.algo, ws,
+                                     ws_bytes, stream));
+  };
+  int rc = time_launches(launch, stream, warmup, iterations, avg_ms);
+  cleanup();
+  return rc;
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------------------------------- exports
+#define SB200_DEFINE_RUN(kernel)                                                                              \
+  extern "C" int run_##kernel(KernelRunnerBuffers buffers, int m, int n, int k, int warmup_iterations,        \
+                              int iterations, sb200_stream_t* streams, int num_streams, int split_k_slices,   \
+                              float* avg_ms) {                                                                \
+    return run_registry_kernel(#kernel, buffers, m, n, k, warmup_iterations, iterations, streams, num_streams, \
+                               split_k_slices, avg_ms);                                                       \
+  }
+
+SB200_DEFINE_RUN(blackwell_f16_cubic_128x256)
+SB200_DEFINE_RUN(blackwell_f16_cubic_128x128)
+SB200_DEFINE_RUN(blackwell_f32_cubic_128x256)
+SB200_DEFINE_RUN(blackwell_f32_cubic_128x128)
+SB200_DEFINE_RUN(blackwell_f16_sw_fused_presum)
+SB200_DEFINE_RUN(blackwell_f32_sw_fused_presum)
+SB200_DEFINE_RUN(blackwell_f16_sw_interleaved_presum)
+SB200_DEFINE_RUN(blackwell_f32_sw_interleaved_presum)
+
+#define SB200_DEFINE_BLAS(fn, impl, type)                                                                      \
+  extern "C" int fn(KernelRunnerBuffers buffers, int m, int n, int k, int warmup_iterations, int iterations,   \
+                    sb200_stream_t* streams, int num_streams, int, float* avg_ms) {                            \
+    return impl(type, buffers, m, n, k, warmup_iterations, iterations, streams, num_streams, avg_ms);          \
+  }
+SB200_DEFINE_BLAS(run_cublas_f16, run_cublas, kBlasF16)
+SB200_DEFINE_BLAS(run_cublas_f32, run_cublas, kBlasF32)
+SB200_DEFINE_BLAS(run_cublas_f64, run_cublas, kBlasF64)
+SB200_DEFINE_BLAS(run_cublas_tf32, run_cublas, kBlasTF32)
+SB200_DEFINE_BLAS(run_cublaslt_f16, run_cublaslt, kBlasF16)
+SB200_DEFINE_BLAS(run_cublaslt_f32, run_cublaslt, kBlasF32)
+SB200_DEFINE_BLAS(run_cublaslt_f64, run_cublaslt, kBlasF64)
+
+static const sb200_kernel_entry kRegistry[] = {
+    {"cublas_f32", "blackwell", "f32", 0, run_cublas_f32},
+    {"cublas_f16", "blackwell", "f16", 0, run_cublas_f16},
+    {"cublas_f64", "blackwell", "f64", 0, run_cublas_f64},
+    {"cublas_tf32", "blackwell", "f32", 0, run_cublas_tf32},
+    {"cublaslt_f32", "blackwell", "f32", 0, run_cublaslt_f32},
+    {"cublaslt_f16", "blackwell", "f16", 0, run_cublaslt_f16},
+    {"cublaslt_f64", "blackwell", "f64", 0, run_cublaslt_f64},
+    {"blackwell_f16_cubic_128x256", "blackwell", "f16", 0, run_blackwell_f16_cubic_128x256},
+    {"blackwell_f16_cubic_128x128", "blackwell", "f16", 0, run_blackwell_f16_cubic_128x128},
+    {"blackwell_f32_cubic_128x256", "blackwell", "f32", 0, run_blackwell_f32_cubic_128x256},
+    {"blackwell_f32_cubic_128x128", "blackwell", "f32", 0, run_blackwell_f32_cubic_128x128},
+    {"blackwell_f16_sw_fused_presum", "blackwell", "f16", 1, run_blackwell_f16_sw_fused_presum},
+    {"blackwell_f32_sw_fused_presum", "blackwell", "f32", 1, run_blackwell_f32_sw_fused_presum},
+    {"blackwell_f16_sw_interleaved_presum", "blackwell", "f16", 1, run_blackwell_f16_sw_interleaved_presum},
+    {"blackwell_f32_sw_interleaved_presum", "blackwell", "f32", 1, run_blackwell_f32_sw_interleaved_presum},
+};
+
+extern "C" int sb200_num_kernels(void) { return static_cast<int>(sizeof(kRegistry) / sizeof(kRegistry[0])); }
+extern "C" const sb200_kernel_entry* sb200_kernel(int index) {
+  return (index >= 0 && index < sb200_num_kernels()) ? &kRegistry[index] : nullptr;
+}
+
+extern "C" int sb200_gemm_can_implement(const char* kernel, int m, int n, int k) {
+  const KernelDesc* d = find_desc(kernel);
+  if (!d) return SB200_ERR_NO_KERNEL;
+  // operand pointers are checked by sb200_gemm; use aligned placeholders here
+  GemmArgs g = make_args(*d, reinterpret_cast<const void*>(256), reinterpret_cast<const void*>(256),
+                         reinterpret_cast<void*>(256), m, n, k);
+  return sb200::can_implement(g);
+}
+
+extern "C" size_t sb200_gemm_workspace_bytes(const char* kernel, int m, int n, int k) {
+  const KernelDesc* d = find_desc(kernel);
+  if (!d || m <= 0 || n <= 0 || k <= 0) return 0;
+  GemmArgs g = make_args(*d, nullptr, nullptr, nullptr, m, n, k);
+  return sb200::workspace_bytes(g);
+}
+
+extern "C" int sb200_gemm(const char* kernel, const void* a, const void* b, void* d_out, int m, int n, int k,
+                          void* workspace, size_t workspace_bytes, sb200_stream_t stream) {
+  const KernelDesc* d = find_desc(kernel);
+  if (!d) return SB200_ERR_NO_KERNEL;
+  GemmArgs g = make_args(*d, a, b, d_out, m, n, k);
+  return sb200::run(g, workspace, workspace_bytes, reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" int sb200_gemm_status(void* workspace, sb200_stream_t stream) {
+  if (!workspace) return SB200_ERR_WORKSPACE_NULL;
+  return sb200::read_status(workspace, reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" int sb200_gemm_launches(const char* kernel) {
+  const KernelDesc* d = find_desc(kernel);
+  if (!d) return 0;
+  GemmArgs g = make_args(*d, nullptr, nullptr, nullptr, 2, 2, 2);
+  return sb200::launches_per_run(g);
+}
+
+extern "C" int sb200_gemm_host(const char* kernel, const void* a_host, const void* b_host, void* d_host, int m, int n,
+                               int k) {
+  const KernelDesc* d = find_desc(kernel);
+  if (!d) return SB200_ERR_NO_KERNEL;
+  if (!a_host || !b_host || !d_host || m <= 0 || n <= 0 || k <= 0) return SB200_ERR_INVALID_PROBLEM;
+  const size_t es = d->dt == sb200::kF16 ? 2 : 4;
+  const size_t a_bytes = size_t(m) * k * es, b_bytes = size_t(k) * n * es, d_bytes = size_t(m) * n * es;
+  void *da = nullptr, *db = nullptr, *dd = nullptr, *ws = nullptr;
+  int rc = 0;
+  cudaError_t ce = cudaSuccess;
+  auto cleanup = [&]() { cudaFree(da); cudaFree(db); cudaFree(dd); cudaFree(ws); };
+  if ((ce = cudaMalloc(&da, a_bytes)) != cudaSuccess || (ce = cudaMalloc(&db, b_bytes)) != cudaSuccess ||
+      (ce = cudaMalloc(&dd, d_bytes)) != cudaSuccess) {
+    cleanup();
+    return static_cast<int>(ce);
+  }
+  GemmArgs g = make_args(*d, da, db, dd, m, n, k);
+  if ((rc = sb200::can_implement(g))) { cleanup(); return rc; }
+  const size_t ws_bytes = sb200::workspace_bytes(g);
+  if ((ce = cudaMalloc(&ws, ws_bytes)) != cudaSuccess) { cleanup(); return static_cast<int>(ce); }
+  if ((ce = cudaMemcpyAsync(da, a_host, a_bytes, cudaMemcpyHostToDevice, nullptr)) != cudaSuccess ||
+      (ce = cudaMemcpyAsync(db, b_host, b_bytes, cudaMemcpyHostToDevice, nullptr)) != cudaSuccess) {
+    cleanup();
+    return static_cast<int>(ce);
+  }
+  if ((rc = sb200::run(g, ws, ws_bytes, nullptr))) { cleanup(); return rc; }
+  if ((ce = cudaMemcpyAsync(d_host, dd, d_bytes, cudaMemcpyDeviceToHost, nullptr)) != cudaSuccess) {
+    cleanup();
+    return static_cast<int>(ce);
+  }
+  rc = sb200::read_status(ws, nullptr);
+  cleanup();
+  return rc;
+}

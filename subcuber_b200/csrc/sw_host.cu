@@ -1,0 +1,239 @@
+// Host-side operator: checks, workspace layout, tensor maps, launches.  See sw_host.h.
+#include "sw_host.h"
+
+#include <cuda.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include "sw_kernel.cuh"
+#include "sw_programs.h"
+
+namespace sb200 {
+namespace {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// 2-D row-major view -> tensor map with a [box_rows x 128 bytes] box and 128-byte swizzle.
+int make_tmap(CUtensorMap* m, int esize, const View& v, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return kErrInternal;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(v.cols), static_cast<cuuint64_t>(v.rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(v.ld) * esize};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / esize), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMapDataType dt = esize == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  CUresult r = fn(m, dt, 2, const_cast<void*>(v.ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? kOk : kErrInternal;
+}
+
+inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+inline int esize_of(DType t) { return t == kF16 ? 2 : 4; }
+
+struct Layout {
+  int esize, bn, level;
+  int mq, nq, kq;          // extents of one operand/output block (level 0: the whole matrix)
+  int tiles_m, tiles_n, num_k;
+  size_t off_status, off_pa, off_pb, off_ws[SB200_NUM_WS], total;
+};
+
+Layout make_layout(const GemmArgs& a) {
+  Layout L;
+  memset(&L, 0, sizeof(L));
+  L.esize = esize_of(a.dtype);
+  L.bn = a.bn == 128 ? 128 : 256;
+  L.level = a.variant == kCubic ? 0 : 1;
+  int div = L.level ? 2 : 1;
+  L.mq = a.m / div;
+  L.nq = a.n / div;
+  L.kq = a.k / div;
+  L.tiles_m = ceil_div(L.mq, 128);
+  L.tiles_n = ceil_div(L.nq, L.bn);
+  L.num_k = ceil_div(L.kq, 128 / L.esize);
+  size_t off = 0;
+  L.off_status = off;
+  off += 256;
+  if (a.variant == kInterleavedPresum) {
+    L.off_pa = off;
+    off = align_up(off + size_t(4) * L.mq * L.kq * L.esize, 256);
+    L.off_pb = off;
+    off = align_up(off + size_t(4) * L.kq * L.nq * L.esize, 256);
+  }
+  int nws = a.variant == kCubic ? 0 : 2;
+  size_t tile_bytes = size_t(128) * L.bn * sizeof(float);
+  for (int i = 0; i < nws; ++i) {
+    L.off_ws[i] = off;
+    off = align_up(off + size_t(L.tiles_m) * L.tiles_n * tile_bytes, 256);
+  }
+  L.total = off;
+  return L;
+}
+
+template <typename Cfg>
+int launch(const KernelParams& p, int grid, cudaStream_t stream) {
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(sw_tile_program_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr_done = true;
+  }
+  sw_tile_program_kernel<Cfg><<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+template <int ESIZE, int BN>
+int launch_mode(int mode, const KernelParams& p, int grid, cudaStream_t stream) {
+  constexpr int STAGES = (BN == 256) ? 4 : 6;
+  switch (mode) {
+    case kPresumNone: return launch<KernelConfig<ESIZE, BN, STAGES, kPresumNone>>(p, grid, stream);
+    case kPresumFeed: return launch<KernelConfig<ESIZE, BN, STAGES, kPresumFeed>>(p, grid, stream);
+    case kPresumJob: return launch<KernelConfig<ESIZE, BN, STAGES, kPresumJob>>(p, grid, stream);
+  }
+  return kErrInternal;
+}
+
+int launch_any(int esize, int bn, int mode, const KernelParams& p, int grid, cudaStream_t stream) {
+  if (esize == 2 && bn == 256) return launch_mode<2, 256>(mode, p, grid, stream);
+  if (esize == 2 && bn == 128) return launch_mode<2, 128>(mode, p, grid, stream);
+  if (esize == 4 && bn == 256) return launch_mode<4, 256>(mode, p, grid, stream);
+  if (esize == 4 && bn == 128) return launch_mode<4, 128>(mode, p, grid, stream);
+  return kErrNotSupported;
+}
+
+int sm_count() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return n;
+}
+
+}  // namespace
+
+int can_implement(const GemmArgs& a) {
+  if (a.m <= 0 || a.n <= 0 || a.k <= 0 || !a.a || !a.b || !a.d) return kErrInvalidProblem;
+  if (a.dtype != kF16 && a.dtype != kF32) return kErrNotSupported;
+  if (a.bn != 0 && a.bn != 128 && a.bn != 256) return kErrNotSupported;
+  const int es = esize_of(a.dtype);
+  const int vec = 16 / es;  // elements per 16 bytes
+  const int div = a.variant == kCubic ? 1 : 2;
+  if (div == 2 && ((a.m % 2) || (a.n % 2) || (a.k % 2))) return kErrInvalidProblem;
+  // every quadrant row must start on a 16-byte boundary (TMA base/stride rule, vector loads and stores)
+  if ((a.k / div) % vec || (a.n / div) % vec) return kErrMisalignedOperand;
+  if ((reinterpret_cast<uintptr_t>(a.a) | reinterpret_cast<uintptr_t>(a.b) | reinterpret_cast<uintptr_t>(a.d)) & 15)
+    return kErrMisalignedOperand;
+  return kOk;
+}
+
+size_t workspace_bytes(const GemmArgs& a) { return make_layout(a).total; }
+
+int launches_per_run(const GemmArgs& a) { return a.variant == kInterleavedPresum ? 2 : 1; }
+
+int run(const GemmArgs& a, void* workspace, size_t workspace_size, cudaStream_t stream) {
+  int rc = can_implement(a);
+  if (rc) return rc;
+  const Layout L = make_layout(a);
+  if (!workspace) return kErrWorkspaceNull;
+  if (workspace_size < L.total || (reinterpret_cast<uintptr_t>(workspace) & 255)) return kErrWorkspaceNull;
+  char* wsb = static_cast<char*>(workspace);
+  const int es = L.esize;
+
+  KernelParams p;
+  memset(&p, 0, sizeof(p));
+  p.status = reinterpret_cast<int*>(wsb + L.off_status);
+  cudaError_t ce = cudaMemsetAsync(p.status, 0, 256, stream);
+  if (ce != cudaSuccess) return static_cast<int>(ce);
+
+  const char* A = static_cast<const char*>(a.a);
+  const char* B = static_cast<const char*>(a.b);
+  char* D = static_cast<char*>(a.d);
+  const long long lda = a.k, ldb = a.n, ldd = a.n;
+  if (L.level == 0) {
+    for (int v = 0; v < 8; ++v) p.view[v] = View{A, lda, a.m, a.k};
+    for (int v = 8; v < 16; ++v) p.view[v] = View{B, ldb, a.k, a.n};
+    p.out[0] = D;
+  } else {
+    for (int q = 0; q < 4; ++q) {
+      p.view[SB200_VIEW_A0 + q] = View{A + ((q >> 1) * L.mq * lda + (q & 1) * L.kq) * es, lda, L.mq, L.kq};
+      p.view[SB200_VIEW_B0 + q] = View{B + ((q >> 1) * L.kq * ldb + (q & 1) * L.nq) * es, ldb, L.kq, L.nq};
+      p.out[q] = D + ((q >> 1) * L.mq * ldd + (q & 1) * L.nq) * es;
+      if (a.variant == kInterleavedPresum) {
+        p.view[SB200_VIEW_PA0 + q] =
+            View{wsb + L.off_pa + size_t(q) * L.mq * L.kq * es, static_cast<long long>(L.kq), L.mq, L.kq};
+        p.view[SB200_VIEW_PB0 + q] =
+            View{wsb + L.off_pb + size_t(q) * L.kq * L.nq * es, static_cast<long long>(L.nq), L.kq, L.nq};
+      } else {
+        p.view[SB200_VIEW_PA0 + q] = p.view[SB200_VIEW_A0 + q];
+        p.view[SB200_VIEW_PB0 + q] = p.view[SB200_VIEW_B0 + q];
+      }
+    }
+  }
+  for (int v = 0; v < 8; ++v)
+    if ((rc = make_tmap(&p.tmap[v], es, p.view[v], 128))) return rc;
+  for (int v = 8; v < 16; ++v)
+    if ((rc = make_tmap(&p.tmap[v], es, p.view[v], 128 / es))) return rc;
+  p.ldo = ldd;
+  p.out_rows = L.mq;
+  p.out_cols = L.nq;
+  for (int i = 0; i < SB200_NUM_WS; ++i) p.ws[i] = reinterpret_cast<float*>(wsb + L.off_ws[i]);
+  p.tiles_m = L.tiles_m;
+  p.tiles_n = L.tiles_n;
+  p.num_k = L.num_k;
+  p.band = 8;
+  if (const char* dbg = getenv("SB200_DEBUG_FLAGS")) p.debug_flags = atoi(dbg);
+  p.job_pa = wsb + L.off_pa;
+  p.job_pb = wsb + L.off_pb;
+  p.job_mq = L.mq;
+  p.job_nq = L.nq;
+  p.job_kq = L.kq;
+
+  int grid = L.tiles_m * L.tiles_n;
+  int cap = a.sm_limit > 0 ? a.sm_limit : sm_count();
+  if (grid > cap) grid = cap;
+
+  switch (a.variant) {
+    case kCubic:
+      p.prog = programs::level0();
+      return launch_any(es, L.bn, kPresumNone, p, grid, stream);
+    case kFusedPresum:
+      p.prog = programs::level1_full(true);
+      return launch_any(es, L.bn, kPresumFeed, p, grid, stream);
+    case kInterleavedPresum:
+      p.prog = programs::level1_first();
+      rc = launch_any(es, L.bn, kPresumJob, p, grid, stream);
+      if (rc) return rc;
+      p.prog = programs::level1_second();
+      return launch_any(es, L.bn, kPresumNone, p, grid, stream);
+  }
+  return kErrNotSupported;
+}
+
+int read_status(void* workspace, cudaStream_t stream) {
+  int st = 0;
+  cudaError_t e = cudaMemcpyAsync(&st, workspace, sizeof(int), cudaMemcpyDeviceToHost, stream);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  e = cudaStreamSynchronize(stream);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  return st;
+}
+
+}  // namespace sb200

@@ -1,0 +1,54 @@
+// Host-side operator for the Blackwell Strassen-Winograd GEMM path: argument checks, workspace carving,
+// tensor-map construction and launches.  It stands where the reference project has its device-level
+// operators (include/cutlass/gemm/device/strassen_gemm.h:277-1217 `StrassenGemm`: can_implement /
+// get_workspace_size / initialize / run) and mirrors their four-step life cycle.
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+
+namespace sb200 {
+
+enum DType { kF16 = 0, kF32 = 1, kF64 = 2 };  // kF32: fp32 storage, TF32 tensor-core math, fp32 accumulate
+
+enum Variant {
+  kCubic = 0,             // level 0, plain GEMM
+  kFusedPresum = 1,       // level 1, one launch, presums formed in shared memory by the presum warps
+  kInterleavedPresum = 2, // level 1, two launches, presums materialised by the first launch's presum warps
+};
+
+// Error codes returned across the C ABI.  Small values keep the meaning of the reference's
+// `int(cutlass::Status)` returns (kernel_runner_support.cuh:44-46); CUDA errors are passed through as
+// `int(cudaError_t)` exactly as the reference does (:107,116); device-side status codes are >= 100.
+enum Error {
+  kOk = 0,
+  kErrMisalignedOperand = 1,
+  kErrInvalidProblem = 4,
+  kErrNotSupported = 5,
+  kErrWorkspaceNull = 6,
+  kErrInternal = 7,
+};
+
+struct GemmArgs {
+  DType dtype;
+  Variant variant;
+  int m, n, k;
+  const void* a;  // m x k row-major, lda = k
+  const void* b;  // k x n row-major, ldb = n
+  void* d;        // m x n row-major, ldd = n;  D = A * B
+  int bn;         // tile width: 256 (default when 0) or 128
+  int sm_limit;   // CTAs to launch at most (0: one per SM of the current device)
+};
+
+// 0 when the kernels can run this problem, else an Error.
+int can_implement(const GemmArgs& args);
+// Bytes of device workspace `run` needs (status word, presum buffers, fp32 hand-off tiles).
+size_t workspace_bytes(const GemmArgs& args);
+// Enqueue the GEMM on `stream`.  `workspace` must hold workspace_bytes(args) and be 256-byte aligned.
+// Asynchronous: returns launch errors only; device-side aborts are read with `read_status`.
+int run(const GemmArgs& args, void* workspace, size_t workspace_size, cudaStream_t stream);
+// Synchronises `stream` and returns the device status word of the last `run` on that workspace.
+int read_status(void* workspace, cudaStream_t stream);
+// Launches of this library's kernels made by the last `run` with these args (for launch accounting).
+int launches_per_run(const GemmArgs& args);
+
+}  // namespace sb200

@@ -1,0 +1,576 @@
+// Persistent, warp-specialised tile-program GEMM kernel for sm_100a.
+//
+// One CTA per SM walks a static list of output tiles.  For every tile it interprets a tile program
+// (tile_program.h): a sequence of half-size products (level 1: the seven Strassen-Winograd products of
+// src/algos/strassen_winograd_level1.py:16-42 in the reference project; level 0: one product) and a
+// sequence of epilogue steps that apply the postsums and write C.  It replaces, for this path, the
+// reference's per-CTA kernel (include/cutlass/gemm/kernel/strassen_gemm.h:419-1460), its multistage
+// mainloop with presum (gemm/threadblock/strassen_mma_multistage.h), its postsum epilogues
+// (epilogue/threadblock/strassen_epilogue.h, strassen_interim_epilogue.h) and the cross-kernel
+// PostsumSemaphore: products that feed one output tile run back to back in ONE CTA and hand their
+// accumulators over inside tensor memory, so no cross-CTA flag exists.
+//
+// Warp roles (one CTA = 6 or 10 warps):
+//   warp 0      TMA producer: non-multicast tiled bulk loads of single-term operands into the stage ring
+//   warp 1      MMA issuer: tcgen05.mma (kind::f16 or kind::tf32, fp32 accumulators in TMEM), one thread
+//   warps 2-5   epilogue: tcgen05.ld -> registers -> postsum -> vectorised global stores
+//   warps 6-9   presum warps (modes FEED and JOB only)
+//                 FEED: form multi-term operand tiles S/T = +-X +-Y ... in shared memory, in the swizzled
+//                       layout the MMA reads, straight from the raw quadrant values (one rounding)
+//                 JOB : materialise the eight presums into a global workspace while the MMA pipeline of the
+//                       same launch computes the products that need no presum (the reference's
+//                       "interleaved presum", strassen_mma_multistage.h:1536-1726)
+//
+// Shared-memory stage (48 KiB at BN = 256): A tile 128 rows x 128 B (K-major, 128B swizzle) followed by the
+// B tile as BN*ESIZE/128 blocks of [BK rows x 128 B] (N-major, 128B swizzle), exactly as TMA deposits them.
+#pragma once
+#include "ptx.cuh"
+#include "tile_program.h"
+
+namespace sb200 {
+
+enum PresumMode { kPresumNone = 0, kPresumFeed = 1, kPresumJob = 2 };
+
+enum StatusCode {
+  kStatusOk = 0,
+  kStatusProducerTimeout = 101,
+  kStatusMmaTimeout = 102,
+  kStatusEpilogueTimeout = 103,
+  kStatusPresumTimeout = 104,
+};
+
+struct View {
+  const void* ptr;  // first element of the view
+  long long ld;     // leading dimension in elements
+  int rows;         // extent of the slow dimension
+  int cols;         // extent of the contiguous dimension
+};
+
+struct KernelParams {
+  CUtensorMap tmap[SB200_NUM_VIEWS];
+  View view[SB200_NUM_VIEWS];
+  void* out[4];       // output quadrant base pointers (level 0: out[0] = D)
+  long long ldo;      // leading dimension of the output in elements
+  int out_rows;       // rows of one output quadrant
+  int out_cols;       // columns of one output quadrant
+  float* ws[SB200_NUM_WS];  // fp32 hand-off buffers, tile-contiguous: [tile id][BN/32][128][32]
+  int tiles_m, tiles_n;     // tile grid over one output quadrant
+  int num_k;                // k-steps per product
+  int band;                 // raster band height in tiles
+  int* status;              // device status word, 0 = ok
+  int debug_flags;          // measurement aids: bit 0 = issue no MMA, bit 1 = issue no TMA load (results are garbage)
+  // presum job (mode JOB): pa = S1,S2,A02,A1S2 packed [4][mq][kq]; pb = B10,B31,S3,S3B2 packed [4][kq][nq]
+  void* job_pa;
+  void* job_pb;
+  int job_mq, job_nq, job_kq;
+  sb200_program_t prog;
+};
+
+template <int ESIZE_, int BN_, int STAGES_, int MODE_>
+struct KernelConfig {
+  static constexpr int ESIZE = ESIZE_;            // operand element size: 2 (f16) or 4 (f32 storage, tf32 math)
+  static constexpr int BM = 128;
+  static constexpr int BN = BN_;
+  static constexpr int BK = 128 / ESIZE;          // elements per 128-byte swizzle row
+  static constexpr int STAGES = STAGES_;
+  static constexpr int MODE = MODE_;
+  static constexpr int UMMA_K = 32 / ESIZE;
+  static constexpr int KSUB = BK / UMMA_K;        // MMAs per stage (4)
+  static constexpr int A_BYTES = BM * 128;
+  static constexpr int NBLK = BN * ESIZE / 128;   // 128-byte-wide column blocks of the B tile
+  static constexpr int BLK_BYTES = BK * 128;
+  static constexpr int B_BYTES = NBLK * BLK_BYTES;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int SLOTS = 512 / BN;
+  static constexpr int TMEM_COLS = 512;
+  static constexpr int PRESUM_WARPS = (MODE == kPresumNone) ? 0 : 4;
+  static constexpr int THREADS = (6 + PRESUM_WARPS) * 32;
+  static constexpr int BAR_BYTES = 1024;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // +1024: manual alignment slack
+  static constexpr uint32_t FMT = (ESIZE == 2) ? 0u : 2u;
+};
+
+struct TileCoord {
+  int i, j, id;
+};
+
+__device__ __forceinline__ TileCoord tile_of(int w, int tiles_m, int tiles_n, int band) {
+  int per_band = band * tiles_n;
+  int b = w / per_band;
+  int r = w - b * per_band;
+  int rows_in_band = min(band, tiles_m - b * band);
+  TileCoord t;
+  t.i = b * band + (r % rows_in_band);
+  t.j = r / rows_in_band;
+  t.id = t.i * tiles_n + t.j;
+  return t;
+}
+
+__device__ __forceinline__ void raise_abort(const KernelParams& p, volatile int* abort_flag, int code) {
+  *abort_flag = 1;
+  atomicCAS(p.status, 0, code);
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Presum arithmetic on one 16-byte vector per term.  Terms are combined left to right in fp32 (fp16
+// operands) or fp32 (f32 operands) and rounded once, which is the reference oracle's convention
+// (src/cuda/strassen_reference_l1.cuh:68-85).
+template <int ESIZE>
+struct VecAcc;
+
+template <>
+struct VecAcc<2> {
+  float v[8];
+  __device__ __forceinline__ void set(uint4 x, int c) {
+    const __half2* h = reinterpret_cast<const __half2*>(&x);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      float2 f = __half22float2(h[q]);
+      v[2 * q] = c > 0 ? f.x : -f.x;
+      v[2 * q + 1] = c > 0 ? f.y : -f.y;
+    }
+  }
+  __device__ __forceinline__ void add(uint4 x, int c) {
+    const __half2* h = reinterpret_cast<const __half2*>(&x);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      float2 f = __half22float2(h[q]);
+      v[2 * q] = c > 0 ? __fadd_rn(v[2 * q], f.x) : __fsub_rn(v[2 * q], f.x);
+      v[2 * q + 1] = c > 0 ? __fadd_rn(v[2 * q + 1], f.y) : __fsub_rn(v[2 * q + 1], f.y);
+    }
+  }
+  __device__ __forceinline__ uint4 pack() const {
+    uint4 o;
+    __half2* h = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) h[q] = __floats2half2_rn(v[2 * q], v[2 * q + 1]);
+    return o;
+  }
+};
+
+template <>
+struct VecAcc<4> {
+  float v[4];
+  __device__ __forceinline__ void set(uint4 x, int c) {
+    const float* f = reinterpret_cast<const float*>(&x);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) v[q] = c > 0 ? f[q] : -f[q];
+  }
+  __device__ __forceinline__ void add(uint4 x, int c) {
+    const float* f = reinterpret_cast<const float*>(&x);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) v[q] = c > 0 ? __fadd_rn(v[q], f[q]) : __fsub_rn(v[q], f[q]);
+  }
+  __device__ __forceinline__ uint4 pack() const {
+    uint4 o;
+    float* f = reinterpret_cast<float*>(&o);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) f[q] = v[q];
+    return o;
+  }
+};
+
+// Combine the terms of `op` for the tile whose slow-dimension origin is `row0` and whose contiguous-dimension
+// origin is `col0` (both in elements of the operand views) and write it into the stage buffer.
+//   ROWS          rows of the tile in shared memory (A: 128 tile rows; B: BK k-rows)
+//   VEC_PER_ROW   16-byte vectors per tile row (A: 8; B: BN*ESIZE/16)
+//   block stride  bytes between 128-byte-wide column blocks (A: unused; B: BK*128)
+template <int ESIZE, int ROWS, int VEC_PER_ROW, int NTHREADS>
+__device__ __forceinline__ void build_operand_tile(uint32_t smem_tile, uint32_t blk_bytes, const sb200_operand_t& op,
+                                                   const View* views, int row0, int col0, int tid) {
+  constexpr int EPV = 16 / ESIZE;  // elements per vector
+  constexpr int TOTAL = ROWS * VEC_PER_ROW;
+  const int nterms = op.nterms;
+#pragma unroll 2
+  for (int v = tid; v < TOTAL; v += NTHREADS) {
+    int r = v / VEC_PER_ROW;
+    int cv = v - r * VEC_PER_ROW;
+    int grow = row0 + r;
+    int gcol = col0 + cv * EPV;
+    uint4 x[SB200_MAX_TERMS];
+#pragma unroll
+    for (int t = 0; t < SB200_MAX_TERMS; ++t) {
+      x[t] = make_uint4(0u, 0u, 0u, 0u);
+      if (t < nterms) {
+        const View& vw = views[op.view[t]];
+        if (grow < vw.rows && gcol < vw.cols) {
+          const char* src = static_cast<const char*>(vw.ptr) + (static_cast<long long>(grow) * vw.ld + gcol) * ESIZE;
+          x[t] = ptx::ldg_nc_v4(src);
+        }
+      }
+    }
+    VecAcc<ESIZE> acc;
+    acc.set(x[0], op.coef[0]);
+#pragma unroll
+    for (int t = 1; t < SB200_MAX_TERMS; ++t)
+      if (t < nterms) acc.add(x[t], op.coef[t]);
+    int blk = cv >> 3;
+    int ch = cv & 7;
+    uint32_t dst = smem_tile + blk * blk_bytes + r * 128 + ((ch ^ (r & 7)) << 4);
+    ptx::sts_v4(dst, acc.pack());
+  }
+}
+
+// Global presum job: every presum thread of the grid takes 16-byte vector positions of the quadrant space in a
+// grid-stride loop; per position it reads the four raw quadrant vectors and writes the four presums.
+template <int ESIZE>
+__device__ __forceinline__ void presum_job(const KernelParams& p, int gtid, int gthreads) {
+  constexpr int EPV = 16 / ESIZE;
+  // A side: S1 = A2 + A3, S2 = S1 - A0, A02 = A0 - A2, A1S2 = A1 - S2
+  {
+    const int vec_per_row = p.job_kq / EPV;
+    const long long total = static_cast<long long>(p.job_mq) * vec_per_row;
+    const long long q = static_cast<long long>(p.job_mq) * p.job_kq;  // elements per presum matrix
+    const View a0 = p.view[SB200_VIEW_A0 + 0], a1 = p.view[SB200_VIEW_A0 + 1], a2 = p.view[SB200_VIEW_A0 + 2],
+               a3 = p.view[SB200_VIEW_A0 + 3];
+    char* out = static_cast<char*>(p.job_pa);
+    for (long long v = gtid; v < total; v += gthreads) {
+      int r = static_cast<int>(v / vec_per_row);
+      int c = static_cast<int>(v - static_cast<long long>(r) * vec_per_row) * EPV;
+      uint4 x0 = ptx::ldg_nc_v4(static_cast<const char*>(a0.ptr) + (r * a0.ld + c) * ESIZE);
+      uint4 x1 = ptx::ldg_nc_v4(static_cast<const char*>(a1.ptr) + (r * a1.ld + c) * ESIZE);
+      uint4 x2 = ptx::ldg_nc_v4(static_cast<const char*>(a2.ptr) + (r * a2.ld + c) * ESIZE);
+      uint4 x3 = ptx::ldg_nc_v4(static_cast<const char*>(a3.ptr) + (r * a3.ld + c) * ESIZE);
+      long long o = (static_cast<long long>(r) * p.job_kq + c) * ESIZE;
+      VecAcc<ESIZE> s;
+      s.set(x2, 1); s.add(x3, 1);                                   // S1
+      *reinterpret_cast<uint4*>(out + 0 * q * ESIZE + o) = s.pack();
+      s.add(x0, -1);                                                // S2 = S1 - A0 (unrounded S1)
+      *reinterpret_cast<uint4*>(out + 1 * q * ESIZE + o) = s.pack();
+      VecAcc<ESIZE> t;
+      t.set(x0, 1); t.add(x2, -1);                                  // A02
+      *reinterpret_cast<uint4*>(out + 2 * q * ESIZE + o) = t.pack();
+      // A1S2 = A1 - S2 with the unrounded S2: -(S2) + A1
+      VecAcc<ESIZE> u;
+      u.set(x2, -1); u.add(x3, -1); u.add(x0, 1); u.add(x1, 1);
+      *reinterpret_cast<uint4*>(out + 3 * q * ESIZE + o) = u.pack();
+    }
+  }
+  // B side: B10 = B1 - B0, B31 = B3 - B1, S3 = B31 + B0, S3B2 = S3 - B2
+  {
+    const int vec_per_row = p.job_nq / EPV;
+    const long long total = static_cast<long long>(p.job_kq) * vec_per_row;
+    const long long q = static_cast<long long>(p.job_kq) * p.job_nq;
+    const View b0 = p.view[SB200_VIEW_B0 + 0], b1 = p.view[SB200_VIEW_B0 + 1], b2 = p.view[SB200_VIEW_B0 + 2],
+               b3 = p.view[SB200_VIEW_B0 + 3];
+    char* out = static_cast<char*>(p.job_pb);
+    for (long long v = gtid; v < total; v += gthreads) {
+      int r = static_cast<int>(v / vec_per_row);
+      int c = static_cast<int>(v - static_cast<long long>(r) * vec_per_row) * EPV;
+      uint4 x0 = ptx::ldg_nc_v4(static_cast<const char*>(b0.ptr) + (r * b0.ld + c) * ESIZE);
+      uint4 x1 = ptx::ldg_nc_v4(static_cast<const char*>(b1.ptr) + (r * b1.ld + c) * ESIZE);
+      uint4 x2 = ptx::ldg_nc_v4(static_cast<const char*>(b2.ptr) + (r * b2.ld + c) * ESIZE);
+      uint4 x3 = ptx::ldg_nc_v4(static_cast<const char*>(b3.ptr) + (r * b3.ld + c) * ESIZE);
+      long long o = (static_cast<long long>(r) * p.job_nq + c) * ESIZE;
+      VecAcc<ESIZE> s;
+      s.set(x1, 1); s.add(x0, -1);                                  // B10
+      *reinterpret_cast<uint4*>(out + 0 * q * ESIZE + o) = s.pack();
+      VecAcc<ESIZE> t;
+      t.set(x3, 1); t.add(x1, -1);                                  // B31
+      *reinterpret_cast<uint4*>(out + 1 * q * ESIZE + o) = t.pack();
+      t.add(x0, 1);                                                 // S3 = B31 + B0 (unrounded B31)
+      *reinterpret_cast<uint4*>(out + 2 * q * ESIZE + o) = t.pack();
+      t.add(x2, -1);                                                // S3B2 = S3 - B2 (unrounded S3)
+      *reinterpret_cast<uint4*>(out + 3 * q * ESIZE + o) = t.pack();
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------
+template <typename Cfg>
+__global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_kernel(const __grid_constant__ KernelParams p) {
+  constexpr int ESIZE = Cfg::ESIZE;
+  constexpr int BN = Cfg::BN;
+  constexpr int BK = Cfg::BK;
+  constexpr int STAGES = Cfg::STAGES;
+  constexpr int SLOTS = Cfg::SLOTS;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* bar_base = smem + STAGES * Cfg::STAGE_BYTES;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(bar_base);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* slot_full = empty_bar + STAGES;
+  uint64_t* slot_free = slot_full + SLOTS;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(slot_free + SLOTS);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int total_tiles = p.tiles_m * p.tiles_n;
+  const int nproducts = p.prog.nproducts;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      ptx::mbar_init(&full_bar[s], 1 + (Cfg::MODE == kPresumFeed ? Cfg::PRESUM_WARPS : 0));
+      ptx::mbar_init(&empty_bar[s], 1);
+    }
+    for (int s = 0; s < SLOTS; ++s) {
+      ptx::mbar_init(&slot_full[s], 1);
+      ptx::mbar_init(&slot_free[s], 4);
+    }
+    ptx::fence_mbar_init();
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(tmem_holder, Cfg::TMEM_COLS);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      for (int v = 0; v < SB200_NUM_VIEWS; ++v) ptx::prefetch_tmap(&p.tmap[v]);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; ok && w < total_tiles; w += gridDim.x) {
+        const TileCoord tile = tile_of(w, p.tiles_m, p.tiles_n, p.band);
+        for (int ps = 0; ok && ps < nproducts; ++ps) {
+          const sb200_product_t& pr = p.prog.product[ps];
+          const bool a_tma = pr.a.nterms == 1;
+          const bool b_tma = pr.b.nterms == 1;
+          const uint32_t tx = (a_tma ? Cfg::A_BYTES : 0) + (b_tma ? Cfg::B_BYTES : 0);
+          const CUtensorMap* ma = &p.tmap[pr.a.view[0]];
+          const CUtensorMap* mb = &p.tmap[pr.b.view[0]];
+          for (int kk = 0; kk < p.num_k; ++kk) {
+            if (!ptx::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) {
+              raise_abort(p, abort_flag, kStatusProducerTimeout);
+              ok = false;
+              break;
+            }
+            uint8_t* sa = smem + stage * Cfg::STAGE_BYTES;
+            uint8_t* sb = sa + Cfg::A_BYTES;
+            const bool no_load = (p.debug_flags & 2) != 0;
+            if (tx && !no_load) ptx::mbar_arrive_expect_tx(&full_bar[stage], tx);
+            else ptx::mbar_arrive(&full_bar[stage]);
+            if (no_load) {
+              if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+              continue;
+            }
+            if (a_tma) ptx::tma_load_2d(sa, ma, &full_bar[stage], kk * BK, tile.i * Cfg::BM);
+            if (b_tma) {
+#pragma unroll
+              for (int nb = 0; nb < Cfg::NBLK; ++nb)
+                ptx::tma_load_2d(sb + nb * Cfg::BLK_BYTES, mb, &full_bar[stage], tile.j * BN + nb * BK, kk * BK);
+            }
+            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t free_bits = 0;
+      uint32_t iter = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; ok && w < total_tiles; w += gridDim.x, ++iter) {
+        const uint32_t sx = p.prog.alternate_slots ? (iter & 1u) : 0u;
+        for (int ps = 0; ok && ps < nproducts; ++ps) {
+          const sb200_product_t& pr = p.prog.product[ps];
+          const uint32_t slot = pr.slot ^ sx;
+          if (pr.wait_free) {
+            if (!ptx::mbar_wait(&slot_free[slot], ((free_bits >> slot) & 1u) ^ 1u, abort_flag)) {
+              raise_abort(p, abort_flag, kStatusMmaTimeout);
+              ok = false;
+              break;
+            }
+            free_bits ^= (1u << slot);
+            ptx::tc_fence_after_sync();
+          }
+          const uint32_t idesc = ptx::umma_idesc(Cfg::FMT, Cfg::BM, BN, pr.negate != 0);
+          const uint32_t tmem_d = tmem_base + slot * BN;
+          for (int kk = 0; kk < p.num_k; ++kk) {
+            if (!ptx::mbar_wait(&full_bar[stage], phase, abort_flag)) {
+              raise_abort(p, abort_flag, kStatusMmaTimeout);
+              ok = false;
+              break;
+            }
+            ptx::tc_fence_after_sync();
+            const uint32_t a_addr = ptx::smem_u32(smem + stage * Cfg::STAGE_BYTES);
+            const uint32_t b_addr = a_addr + Cfg::A_BYTES;
+#pragma unroll
+            for (int ks = 0; ks < Cfg::KSUB && !(p.debug_flags & 1); ++ks) {
+              const uint64_t adesc = ptx::umma_desc_sw128(a_addr + ks * 32, 16, 1024);
+              const uint64_t bdesc = ptx::umma_desc_sw128(b_addr + ks * Cfg::UMMA_K * 128, Cfg::BLK_BYTES, 1024);
+              const uint32_t acc = (kk > 0 || ks > 0 || pr.accumulate) ? 1u : 0u;
+              if (ESIZE == 2) ptx::umma_f16(tmem_d, adesc, bdesc, idesc, acc);
+              else ptx::umma_tf32(tmem_d, adesc, bdesc, idesc, acc);
+            }
+            ptx::umma_commit(&empty_bar[stage]);
+            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          }
+          if (ok && pr.commit) ptx::umma_commit(&slot_full[slot]);
+        }
+      }
+    }
+  } else if (warp < 6) {
+    // ------------------------------------------------------------------ epilogue warps
+    const int quarter = warp & 3;            // TMEM lane quarter this warp may read
+    const int row = quarter * 32 + lane;     // row of the tile owned by this thread
+    uint32_t full_bits = 0;
+    uint32_t iter = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; ok && w < total_tiles; w += gridDim.x, ++iter) {
+      const TileCoord tile = tile_of(w, p.tiles_m, p.tiles_n, p.band);
+      const uint32_t sx = p.prog.alternate_slots ? (iter & 1u) : 0u;
+      for (int es = 0; ok && es < p.prog.nepilogues; ++es) {
+        const sb200_epilogue_t& ep = p.prog.epilogue[es];
+        for (int s = 0; s < SLOTS; ++s) {
+          if ((ep.wait_full_mask >> s) & 1u) {
+            const uint32_t slot = s ^ sx;
+            bool got = ptx::mbar_wait(&slot_full[slot], (full_bits >> slot) & 1u, abort_flag);
+            got = __all_sync(0xffffffffu, got);
+            if (!got) {
+              if (lane == 0) raise_abort(p, abort_flag, kStatusEpilogueTimeout);
+              ok = false;
+              break;
+            }
+            full_bits ^= (1u << slot);
+          }
+        }
+        if (!ok) break;
+        ptx::tc_fence_after_sync();
+        const long long tile_off = static_cast<long long>(tile.id) * (128 * BN);
+        const int grow = tile.i * 128 + row;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[SB200_MAX_SLOT_TERMS][32];
+#pragma unroll
+          for (int t = 0; t < SB200_MAX_SLOT_TERMS; ++t) {
+            if (t < ep.nslots) {
+              const uint32_t slot = ep.slot[t] ^ sx;
+              ptx::tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + slot * BN + c * 32, r[t]);
+            }
+          }
+          float acc[32];
+          // fp32 workspace sources first (their latency overlaps the TMEM loads)
+#pragma unroll
+          for (int q = 0; q < 32; ++q) acc[q] = 0.f;
+          for (int t = 0; t < ep.nsrc; ++t) {
+            const float4* src = reinterpret_cast<const float4*>(p.ws[ep.src[t]] + tile_off + (c * 128 + row) * 32);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              float4 f = src[q];
+              acc[4 * q + 0] += f.x;
+              acc[4 * q + 1] += f.y;
+              acc[4 * q + 2] += f.z;
+              acc[4 * q + 3] += f.w;
+            }
+          }
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int t = 0; t < SB200_MAX_SLOT_TERMS; ++t) {
+            if (t < ep.nslots) {
+              if (ep.slot_sign[t] > 0) {
+#pragma unroll
+                for (int q = 0; q < 32; ++q) acc[q] += __uint_as_float(r[t][q]);
+              } else {
+#pragma unroll
+                for (int q = 0; q < 32; ++q) acc[q] -= __uint_as_float(r[t][q]);
+              }
+            }
+          }
+          if (ep.dst_kind == 1) {
+            float4* dst = reinterpret_cast<float4*>(p.ws[ep.dst] + tile_off + (c * 128 + row) * 32);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) dst[q] = make_float4(acc[4 * q], acc[4 * q + 1], acc[4 * q + 2], acc[4 * q + 3]);
+          } else if (grow < p.out_rows) {
+            const int gcol = tile.j * BN + c * 32;
+            char* dst = static_cast<char*>(p.out[ep.dst]) + (static_cast<long long>(grow) * p.ldo + gcol) * ESIZE;
+            if (ESIZE == 2) {
+#pragma unroll
+              for (int g = 0; g < 4; ++g) {
+                if (gcol + g * 8 < p.out_cols) {
+                  uint4 o;
+                  __half2* h = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+                  for (int q = 0; q < 4; ++q) h[q] = __floats2half2_rn(acc[g * 8 + 2 * q], acc[g * 8 + 2 * q + 1]);
+                  *reinterpret_cast<uint4*>(dst + g * 16) = o;
+                }
+              }
+            } else {
+#pragma unroll
+              for (int g = 0; g < 8; ++g) {
+                if (gcol + g * 4 < p.out_cols) {
+                  *reinterpret_cast<float4*>(dst + g * 16) =
+                      make_float4(acc[g * 4], acc[g * 4 + 1], acc[g * 4 + 2], acc[g * 4 + 3]);
+                }
+              }
+            }
+          }
+        }
+        ptx::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) {
+          for (int s = 0; s < SLOTS; ++s)
+            if ((ep.release_mask >> s) & 1u) ptx::mbar_arrive(&slot_free[s ^ sx]);
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ presum warps
+    if (Cfg::MODE == kPresumFeed) {
+      const int ptid = threadIdx.x - 6 * 32;
+      constexpr int PT = Cfg::PRESUM_WARPS * 32;
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; ok && w < total_tiles; w += gridDim.x) {
+        const TileCoord tile = tile_of(w, p.tiles_m, p.tiles_n, p.band);
+        for (int ps = 0; ok && ps < nproducts; ++ps) {
+          const sb200_product_t& pr = p.prog.product[ps];
+          const bool a_mt = pr.a.nterms > 1;
+          const bool b_mt = pr.b.nterms > 1;
+          for (int kk = 0; kk < p.num_k; ++kk) {
+            bool got = ptx::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag);
+            got = __all_sync(0xffffffffu, got);
+            if (!got) {
+              if (lane == 0) raise_abort(p, abort_flag, kStatusPresumTimeout);
+              ok = false;
+              break;
+            }
+            const uint32_t sa = ptx::smem_u32(smem + stage * Cfg::STAGE_BYTES);
+            const uint32_t sb = sa + Cfg::A_BYTES;
+            if (a_mt)
+              build_operand_tile<ESIZE, Cfg::BM, 8, PT>(sa, 0u, pr.a, p.view, tile.i * Cfg::BM, kk * BK, ptid);
+            if (b_mt)
+              build_operand_tile<ESIZE, BK, BN * ESIZE / 16, PT>(sb, Cfg::BLK_BYTES, pr.b, p.view, kk * BK, tile.j * BN,
+                                                                  ptid);
+            if (a_mt || b_mt) ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&full_bar[stage]);
+            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          }
+        }
+      }
+    } else if (Cfg::MODE == kPresumJob) {
+      const int ptid = threadIdx.x - 6 * 32;
+      constexpr int PT = Cfg::PRESUM_WARPS * 32;
+      presum_job<ESIZE>(p, blockIdx.x * PT + ptid, gridDim.x * PT);
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    // give copies that are still in flight a bounded time to land before the shared memory is released
+    uint64_t t0 = ptx::globaltimer_ns();
+    while (ptx::globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+}  // namespace sb200

@@ -1,0 +1,153 @@
+// Hand-checked tile programs for level 0 and level 1 (2 TMEM slots of 256 columns, or 4 of 128).
+//
+// The arithmetic contract is the reference project's src/algos/strassen_winograd_level1.py:16-42:
+//   S1=A2+A3  S2=S1-A0  A02=A0-A2  A1S2=A1-S2      B10=B1-B0  B31=B3-B1  S3=B31+B0  S3B2=S3-B2
+//   M0=A0*B0  M1=A1*B2  M2=S2*S3   M3=A02*B31  M4=S1*B10  M5=A1S2*B3  M6=A3*S3B2
+//   C0=M0+M1  C1=M0+M2+M4+M5       C2=M0+M2+M3-M6         C3=M0+M2+M3+M4
+// The same tables are produced by the Python front end (subcuber_b200/emit.py); tests compare the two.
+#pragma once
+#include <string.h>
+
+#include "tile_program.h"
+
+namespace sb200 {
+namespace programs {
+
+enum { A0 = 0, A1 = 1, A2 = 2, A3 = 3, PS1 = 4, PS2 = 5, PA02 = 6, PA1S2 = 7,
+       B0 = 8, B1 = 9, B2 = 10, B3 = 11, PB10 = 12, PB31 = 13, PS3 = 14, PS3B2 = 15 };
+
+inline sb200_operand_t term1(int v) {
+  sb200_operand_t o;
+  memset(&o, 0, sizeof(o));
+  o.nterms = 1;
+  o.view[0] = (int8_t)v;
+  o.coef[0] = 1;
+  return o;
+}
+inline sb200_operand_t terms(int n, const int* v, const int* c) {
+  sb200_operand_t o;
+  memset(&o, 0, sizeof(o));
+  o.nterms = (int8_t)n;
+  for (int i = 0; i < n; ++i) {
+    o.view[i] = (int8_t)v[i];
+    o.coef[i] = (int8_t)c[i];
+  }
+  return o;
+}
+// On-the-fly operand combinations, term order chosen so that left-to-right evaluation reproduces the
+// reference oracle's expression tree (strassen_reference_l1.cuh:68-75) bit for bit.
+inline sb200_operand_t fly_S1() { int v[] = {A2, A3}; int c[] = {1, 1}; return terms(2, v, c); }
+inline sb200_operand_t fly_S2() { int v[] = {A2, A3, A0}; int c[] = {1, 1, -1}; return terms(3, v, c); }
+inline sb200_operand_t fly_A02() { int v[] = {A0, A2}; int c[] = {1, -1}; return terms(2, v, c); }
+inline sb200_operand_t fly_A1S2() { int v[] = {A2, A3, A0, A1}; int c[] = {-1, -1, 1, 1}; return terms(4, v, c); }
+inline sb200_operand_t fly_B10() { int v[] = {B1, B0}; int c[] = {1, -1}; return terms(2, v, c); }
+inline sb200_operand_t fly_B31() { int v[] = {B3, B1}; int c[] = {1, -1}; return terms(2, v, c); }
+inline sb200_operand_t fly_S3() { int v[] = {B3, B1, B0}; int c[] = {1, -1, 1}; return terms(3, v, c); }
+inline sb200_operand_t fly_S3B2() { int v[] = {B3, B1, B0, B2}; int c[] = {1, -1, 1, -1}; return terms(4, v, c); }
+
+inline void add_product(sb200_program_t& pg, sb200_operand_t a, sb200_operand_t b, int slot, int accumulate, int negate,
+                        int wait_free, int commit) {
+  sb200_product_t& p = pg.product[pg.nproducts++];
+  memset(&p, 0, sizeof(p));
+  p.a = a;
+  p.b = b;
+  p.slot = (uint8_t)slot;
+  p.accumulate = (uint8_t)accumulate;
+  p.negate = (uint8_t)negate;
+  p.wait_free = (uint8_t)wait_free;
+  p.commit = (uint8_t)commit;
+  if (a.nterms > 1 || b.nterms > 1) pg.needs_feed = 1;
+}
+
+// slots/signs: up to 3 (slot, sign) pairs; srcs: up to 2 workspace ids; masks are bit sets of slot ids.
+inline void add_epilogue(sb200_program_t& pg, int nslots, const int* slots, const int* signs, int nsrc, const int* srcs,
+                         int wait_mask, int release_mask, int dst_kind, int dst) {
+  sb200_epilogue_t& e = pg.epilogue[pg.nepilogues];
+  memset(&e, 0, sizeof(e));
+  e.nslots = (uint8_t)nslots;
+  for (int i = 0; i < nslots; ++i) {
+    e.slot[i] = (uint8_t)slots[i];
+    e.slot_sign[i] = (int8_t)signs[i];
+  }
+  e.nsrc = (uint8_t)nsrc;
+  for (int i = 0; i < nsrc; ++i) e.src[i] = (uint8_t)srcs[i];
+  e.wait_full_mask = (uint8_t)wait_mask;
+  e.release_mask = (uint8_t)release_mask;
+  e.dst_kind = (uint8_t)dst_kind;
+  e.dst = (uint8_t)dst;
+  pg.epilogue_after[pg.nepilogues] = (uint8_t)(pg.nproducts - 1);
+  pg.nepilogues++;
+}
+
+enum { P = 0, Q = 1, mP = 1, mQ = 2 };
+enum { WS_M0 = 0, WS_M4 = 1 };
+
+// Level 0: one product per tile, the two (or four) slots used alternately so that the epilogue of tile t
+// overlaps the mainloop of tile t+1.
+inline sb200_program_t level0() {
+  sb200_program_t pg;
+  memset(&pg, 0, sizeof(pg));
+  pg.alternate_slots = 1;
+  add_product(pg, term1(A0), term1(B0), P, 0, 0, 1, 1);
+  int s[] = {P}, g[] = {1};
+  add_epilogue(pg, 1, s, g, 0, nullptr, mP, mP, 0, 0);
+  return pg;
+}
+
+// Level 1, all seven products of a tile in one CTA.  `fly` selects where multi-quadrant operands come from:
+//   fly = true  : formed on the fly in shared memory by the presum warps (no workspace for operands)
+//   fly = false : read from the materialised presum workspace by TMA (views 4..7 and 12..15)
+// One fp32 hand-off tile (M4) goes through the workspace; everything else stays in tensor memory.
+inline sb200_program_t level1_full(bool fly) {
+  sb200_program_t pg;
+  memset(&pg, 0, sizeof(pg));
+  const int sP[] = {P}, sQ[] = {Q}, sPQ[] = {P, Q}, pos1[] = {1}, pos2[] = {1, 1};
+  const int srcM4[] = {WS_M4};
+  add_product(pg, term1(A1), term1(B2), Q, 0, 0, 1, 1);                                       // Q  = M1
+  add_product(pg, term1(A0), term1(B0), P, 0, 0, 1, 1);                                       // P  = M0
+  add_epilogue(pg, 2, sPQ, pos2, 0, nullptr, mP | mQ, mP | mQ, 0, 0);                         // C0 = P + Q
+  add_product(pg, fly ? fly_S1() : term1(PS1), fly ? fly_B10() : term1(PB10), Q, 0, 0, 1, 1); // Q  = M4
+  add_product(pg, fly ? fly_S2() : term1(PS2), fly ? fly_S3() : term1(PS3), P, 1, 0, 1, 1);   // P += M2  (U)
+  add_epilogue(pg, 1, sQ, pos1, 0, nullptr, mQ, mQ, 1, WS_M4);                                // ws[M4] = Q
+  add_product(pg, fly ? fly_A1S2() : term1(PA1S2), term1(B3), Q, 1, 0, 1, 1);                 // Q += M5
+  add_epilogue(pg, 2, sPQ, pos2, 0, nullptr, mP | mQ, mP | mQ, 0, 1);                         // C1 = U + M4 + M5
+  add_product(pg, fly ? fly_A02() : term1(PA02), fly ? fly_B31() : term1(PB31), P, 1, 0, 1, 1); // P += M3 (V2)
+  add_epilogue(pg, 1, sP, pos1, 1, srcM4, mP, mP, 0, 3);                                      // C3 = V2 + M4
+  add_product(pg, term1(A3), fly ? fly_S3B2() : term1(PS3B2), P, 1, 1, 1, 1);                 // P -= M6
+  add_epilogue(pg, 1, sP, pos1, 0, nullptr, mP, mP, 0, 2);                                    // C2 = V2 - M6
+  return pg;
+}
+
+// Level 1 with interleaved presum, launch 1 of 2: the two products that need no presum; M0 is also handed
+// to launch 2 through the fp32 workspace.  The presum warps of this launch materialise the eight presums.
+inline sb200_program_t level1_first() {
+  sb200_program_t pg;
+  memset(&pg, 0, sizeof(pg));
+  const int sP[] = {P}, sPQ[] = {P, Q}, pos1[] = {1}, pos2[] = {1, 1};
+  add_product(pg, term1(A0), term1(B0), P, 0, 0, 1, 1);                // P = M0
+  add_product(pg, term1(A1), term1(B2), Q, 0, 0, 1, 1);                // Q = M1
+  add_epilogue(pg, 1, sP, pos1, 0, nullptr, mP, 0, 1, WS_M0);          // ws[M0] = P   (overlaps M1)
+  add_epilogue(pg, 2, sPQ, pos2, 0, nullptr, mQ, mP | mQ, 0, 0);       // C0 = P + Q
+  return pg;
+}
+
+// Launch 2 of 2: the five products that read presums from the workspace through TMA.
+inline sb200_program_t level1_second() {
+  sb200_program_t pg;
+  memset(&pg, 0, sizeof(pg));
+  const int sP[] = {P}, sQ[] = {Q}, sPQ[] = {P, Q}, pos1[] = {1}, pos2[] = {1, 1};
+  const int srcM0[] = {WS_M0}, srcM0M4[] = {WS_M0, WS_M4};
+  add_product(pg, term1(PS1), term1(PB10), Q, 0, 0, 1, 1);             // Q  = M4
+  add_product(pg, term1(PS2), term1(PS3), P, 0, 0, 1, 1);              // P  = M2
+  add_epilogue(pg, 1, sQ, pos1, 0, nullptr, mQ, mQ, 1, WS_M4);         // ws[M4] = Q   (overlaps M2)
+  add_product(pg, term1(PA1S2), term1(B3), Q, 1, 0, 1, 1);             // Q += M5
+  add_epilogue(pg, 2, sPQ, pos2, 1, srcM0, mP | mQ, mP | mQ, 0, 1);    // C1 = M0 + M2 + M4 + M5
+  add_product(pg, term1(PA02), term1(PB31), P, 1, 0, 1, 1);            // P += M3
+  add_epilogue(pg, 1, sP, pos1, 2, srcM0M4, mP, mP, 0, 3);             // C3 = M0 + M2 + M3 + M4
+  add_product(pg, term1(A3), term1(PS3B2), P, 1, 1, 1, 1);             // P -= M6
+  add_epilogue(pg, 1, sP, pos1, 1, srcM0, mP, mP, 0, 2);               // C2 = M0 + M2 + M3 - M6
+  return pg;
+}
+
+}  // namespace programs
+}  // namespace sb200

@@ -1,0 +1,183 @@
+"""Python mirror of the reference benchmark driver's kernel interface.
+
+`kernels()` lists the registry rows (reference: `kKernels[]`, src/cuda/kernel_runner.cpp:107-181);
+`run_kernel` calls one row through its `run_<kernel>` C entry point exactly as the reference driver does
+(src/cuda/kernel_runner.cpp:319); `gemm` is the operator call (one asynchronous GEMM on the current stream).
+All compute happens in the CUDA library; tensors are torch CUDA tensors used as device buffers only.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import List, Optional
+
+import torch
+
+from . import _lib
+
+ERROR_NAMES = {
+    0: "ok",
+    1: "misaligned operand",
+    4: "invalid problem",
+    5: "not supported",
+    6: "workspace null / too small / misaligned",
+    7: "internal error",
+    8: "no such kernel",
+    101: "device: producer wait timed out",
+    102: "device: mma wait timed out",
+    103: "device: epilogue wait timed out",
+    104: "device: presum wait timed out",
+}
+
+TORCH_DTYPE = {"f16": torch.float16, "f32": torch.float32, "f64": torch.float64}
+
+
+class KernelError(RuntimeError):
+    def __init__(self, kernel: str, code: int):
+        self.kernel, self.code = kernel, code
+        super().__init__(f"{kernel}: error {code} ({ERROR_NAMES.get(code, 'CUDA/cuBLAS error')})")
+
+
+@dataclass(frozen=True)
+class KernelInfo:
+    name: str
+    arch: str
+    dtype: str
+    strassen_level: int
+    index: int
+
+
+def normalize_arch(arch: str) -> str:
+    """Reference aliases (src/cuda/kernel_runner.cpp:190-196) plus the Blackwell ones."""
+    arch = arch.lower()
+    if arch in ("sm70", "70", "compute_70"):
+        return "volta"
+    if arch in ("sm80", "80", "compute_80"):
+        return "ampere"
+    if arch in ("sm90", "sm90a", "90", "90a", "compute_90a"):
+        return "hopper"
+    if arch in ("sm100", "sm100a", "100", "100a", "compute_100a", "b200"):
+        return "blackwell"
+    return arch
+
+
+def normalize_dtype(dtype: str) -> str:
+    """Reference aliases (src/cuda/kernel_runner.cpp:198-204)."""
+    dtype = dtype.lower()
+    if dtype in ("float", "fp32", "s"):
+        return "f32"
+    if dtype in ("half", "fp16", "h"):
+        return "f16"
+    if dtype in ("double", "fp64", "d"):
+        return "f64"
+    return dtype
+
+
+def kernels(dtype: Optional[str] = None, level: Optional[int] = None, regex: Optional[str] = None) -> List[KernelInfo]:
+    import re
+
+    lib = _lib.load()
+    out = []
+    for i in range(lib.sb200_num_kernels()):
+        e = lib.sb200_kernel(i).contents
+        info = KernelInfo(e.name.decode(), e.arch.decode(), e.dtype.decode(), int(e.strassen_level), i)
+        if dtype is not None and info.dtype != normalize_dtype(dtype):
+            continue
+        if level is not None and info.strassen_level != level:
+            continue
+        if regex is not None and not re.search(regex, info.name):
+            continue
+        out.append(info)
+    return out
+
+
+def _check_inputs(a: torch.Tensor, b: torch.Tensor):
+    if not (a.is_cuda and b.is_cuda):
+        raise ValueError("operands must be CUDA tensors: this backend has no CPU path")
+    if a.dim() != 2 or b.dim() != 2 or a.shape[1] != b.shape[0]:
+        raise ValueError("expected A (m x k) and B (k x n)")
+    if not (a.is_contiguous() and b.is_contiguous()):
+        raise ValueError("operands must be packed row-major")
+    if a.dtype != b.dtype:
+        raise ValueError("A and B must have the same dtype")
+
+
+def run_kernel(name: str, a: torch.Tensor, b: torch.Tensor, d: Optional[torch.Tensor] = None, warmup: int = 1,
+               iterations: int = 1, split_k: int = 1, stream: Optional[torch.cuda.Stream] = None):
+    """Call `run_<name>` through the C ABI.  Returns (d, avg_ms).  Raises KernelError on a nonzero return."""
+    lib = _lib.load()
+    _check_inputs(a, b)
+    m, k = a.shape
+    n = b.shape[1]
+    if d is None:
+        d = torch.zeros((m, n), dtype=a.dtype, device=a.device)
+    fn = getattr(lib, "run_" + name, None)
+    if fn is None:
+        raise KernelError(name, 8)
+    fn.argtypes = _lib.RUN_ARGTYPES
+    fn.restype = C.c_int
+    s = stream if stream is not None else torch.cuda.current_stream(a.device)
+    streams = (C.c_void_p * 1)(C.c_void_p(s.cuda_stream))
+    avg = C.c_float(0.0)
+    buf = _lib.KernelRunnerBuffers(a.data_ptr(), b.data_ptr(), None, d.data_ptr())
+    with torch.cuda.device(a.device):
+        rc = fn(buf, m, n, k, warmup, iterations, streams, 1, split_k, C.byref(avg))
+    if rc != 0:
+        raise KernelError(name, rc)
+    return d, float(avg.value)
+
+
+class Workspace:
+    """Device workspace for `gemm`, sized for one (kernel, m, n, k); reusable across calls of that shape."""
+
+    def __init__(self, kernel: str, m: int, n: int, k: int, device):
+        lib = _lib.load()
+        rc = lib.sb200_gemm_can_implement(kernel.encode(), m, n, k)
+        if rc != 0:
+            raise KernelError(kernel, rc)
+        self.nbytes = int(lib.sb200_gemm_workspace_bytes(kernel.encode(), m, n, k))
+        self.buf = torch.empty(self.nbytes + 256, dtype=torch.uint8, device=device)
+        off = (-self.buf.data_ptr()) % 256
+        self.ptr = self.buf.data_ptr() + off
+        self.key = (kernel, m, n, k)
+
+
+def gemm(kernel: str, a: torch.Tensor, b: torch.Tensor, d: Optional[torch.Tensor] = None,
+         workspace: Optional[Workspace] = None, check: bool = True) -> torch.Tensor:
+    """D = A @ B with the named kernel, asynchronous on the current stream (synchronises only if `check`)."""
+    lib = _lib.load()
+    _check_inputs(a, b)
+    m, k = a.shape
+    n = b.shape[1]
+    if d is None:
+        d = torch.empty((m, n), dtype=a.dtype, device=a.device)
+    if workspace is None or workspace.key != (kernel, m, n, k):
+        workspace = Workspace(kernel, m, n, k, a.device)
+    s = torch.cuda.current_stream(a.device).cuda_stream
+    with torch.cuda.device(a.device):
+        rc = lib.sb200_gemm(kernel.encode(), a.data_ptr(), b.data_ptr(), d.data_ptr(), m, n, k, workspace.ptr,
+                            workspace.nbytes, s)
+        if rc != 0:
+            raise KernelError(kernel, rc)
+        if check:
+            rc = lib.sb200_gemm_status(workspace.ptr, s)
+            if rc != 0:
+                raise KernelError(kernel, rc)
+    return d
+
+
+def gemm_host(kernel: str, a, b):
+    """End-to-end call on HOST arrays (numpy): copies in, runs on the GPU, copies D back."""
+    import numpy as np
+
+    lib = _lib.load()
+    a = np.ascontiguousarray(a)
+    b = np.ascontiguousarray(b)
+    m, k = a.shape
+    n = b.shape[1]
+    d = np.empty((m, n), dtype=a.dtype)
+    rc = lib.sb200_gemm_host(kernel.encode(), a.ctypes.data_as(C.c_void_p), b.ctypes.data_as(C.c_void_p),
+                             d.ctypes.data_as(C.c_void_p), m, n, k)
+    if rc != 0:
+        raise KernelError(kernel, rc)
+    return d
