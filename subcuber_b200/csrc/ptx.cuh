@@ -120,14 +120,17 @@ __device__ __forceinline__ void tmem_ld_wait() {
 // ---------------------------------------------------------------- UMMA
 // Shared-memory matrix descriptor, 128-byte swizzle, sm_100 format:
 //   [0,14) start address >> 4 | [16,30) leading byte offset >> 4 | [32,46) stride byte offset >> 4
-//   [46,48) version = 1 | [61,64) layout type (2 = SWIZZLE_128B)
-__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+//   [46,48) version = 1 | [61,64) layout type: 2 = SWIZZLE_128B (16-byte chunks XOR row & 7);
+//   1 = SWIZZLE_128B with 32-byte atoms (32-byte chunks XOR row & 3), the only swizzled layout the
+//   tensor core accepts for an MN-major operand of 32-bit elements.
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes,
+                                                    uint32_t layout_type = 2) {
   uint64_t d = 0;
   d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
   d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
   d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
   d |= 1ull << 46;
-  d |= 2ull << 61;
+  d |= static_cast<uint64_t>(layout_type) << 61;
   return d;
 }
 

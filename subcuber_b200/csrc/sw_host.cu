@@ -29,7 +29,7 @@ EncodeTiledFn encode_fn() {
 }
 
 // 2-D row-major view -> tensor map with a [box_rows x 128 bytes] box and 128-byte swizzle.
-int make_tmap(CUtensorMap* m, int esize, const View& v, int box_rows) {
+int make_tmap(CUtensorMap* m, int esize, const View& v, int box_rows, CUtensorMapSwizzle swizzle) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return kErrInternal;
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(v.cols), static_cast<cuuint64_t>(v.rows)};
@@ -38,7 +38,7 @@ int make_tmap(CUtensorMap* m, int esize, const View& v, int box_rows) {
   cuuint32_t estr[2] = {1, 1};
   CUtensorMapDataType dt = esize == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
   CUresult r = fn(m, dt, 2, const_cast<void*>(v.ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                  swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? kOk : kErrInternal;
 }
 
@@ -188,9 +188,11 @@ int run(const GemmArgs& a, void* workspace, size_t workspace_size, cudaStream_t 
     }
   }
   for (int v = 0; v < 8; ++v)
-    if ((rc = make_tmap(&p.tmap[v], es, p.view[v], 128))) return rc;
+    if ((rc = make_tmap(&p.tmap[v], es, p.view[v], 128, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+  // B tiles of 32-bit elements are deposited with 32-byte swizzle atoms (see KernelConfig::B_SWZ32)
+  const CUtensorMapSwizzle b_swz = es == 4 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B;
   for (int v = 8; v < 16; ++v)
-    if ((rc = make_tmap(&p.tmap[v], es, p.view[v], 128 / es))) return rc;
+    if ((rc = make_tmap(&p.tmap[v], es, p.view[v], 128 / es, b_swz))) return rc;
   p.ldo = ldd;
   p.out_rows = L.mq;
   p.out_cols = L.nq;

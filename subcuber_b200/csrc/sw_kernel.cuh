@@ -88,6 +88,11 @@ struct KernelConfig {
   static constexpr int BAR_BYTES = 1024;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // +1024: manual alignment slack
   static constexpr uint32_t FMT = (ESIZE == 2) ? 0u : 2u;
+  // B tile (N contiguous): 16-bit elements use the plain 128-byte swizzle with 8-row groups; 32-bit elements
+  // must use the 128-byte swizzle with 32-byte atoms, whose pattern repeats every 4 rows.
+  static constexpr bool B_SWZ32 = (ESIZE == 4);
+  static constexpr uint32_t B_LAYOUT_TYPE = B_SWZ32 ? 1u : 2u;
+  static constexpr uint32_t B_SBO = B_SWZ32 ? 512u : 1024u;
 };
 
 struct TileCoord {
@@ -175,7 +180,8 @@ struct VecAcc<4> {
 //   ROWS          rows of the tile in shared memory (A: 128 tile rows; B: BK k-rows)
 //   VEC_PER_ROW   16-byte vectors per tile row (A: 8; B: BN*ESIZE/16)
 //   block stride  bytes between 128-byte-wide column blocks (A: unused; B: BK*128)
-template <int ESIZE, int ROWS, int VEC_PER_ROW, int NTHREADS>
+//   SWZ32         false: 16-byte chunk index XOR (row & 7); true: 32-byte chunk index XOR (row & 3)
+template <int ESIZE, int ROWS, int VEC_PER_ROW, int NTHREADS, bool SWZ32>
 __device__ __forceinline__ void build_operand_tile(uint32_t smem_tile, uint32_t blk_bytes, const sb200_operand_t& op,
                                                    const View* views, int row0, int col0, int tid) {
   constexpr int EPV = 16 / ESIZE;  // elements per vector
@@ -206,7 +212,8 @@ __device__ __forceinline__ void build_operand_tile(uint32_t smem_tile, uint32_t 
       if (t < nterms) acc.add(x[t], op.coef[t]);
     int blk = cv >> 3;
     int ch = cv & 7;
-    uint32_t dst = smem_tile + blk * blk_bytes + r * 128 + ((ch ^ (r & 7)) << 4);
+    const int sch = SWZ32 ? ((((ch >> 1) ^ (r & 3)) << 1) | (ch & 1)) : (ch ^ (r & 7));
+    uint32_t dst = smem_tile + blk * blk_bytes + r * 128 + (sch << 4);
     ptx::sts_v4(dst, acc.pack());
   }
 }
@@ -399,7 +406,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_kernel(const 
 #pragma unroll
             for (int ks = 0; ks < Cfg::KSUB && !(p.debug_flags & 1); ++ks) {
               const uint64_t adesc = ptx::umma_desc_sw128(a_addr + ks * 32, 16, 1024);
-              const uint64_t bdesc = ptx::umma_desc_sw128(b_addr + ks * Cfg::UMMA_K * 128, Cfg::BLK_BYTES, 1024);
+              const uint64_t bdesc =
+                  ptx::umma_desc_sw128(b_addr + ks * Cfg::UMMA_K * 128, Cfg::BLK_BYTES, Cfg::B_SBO, Cfg::B_LAYOUT_TYPE);
               const uint32_t acc = (kk > 0 || ks > 0 || pr.accumulate) ? 1u : 0u;
               if (ESIZE == 2) ptx::umma_f16(tmem_d, adesc, bdesc, idesc, acc);
               else ptx::umma_tf32(tmem_d, adesc, bdesc, idesc, acc);
@@ -540,9 +548,9 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_kernel(const 
             const uint32_t sa = ptx::smem_u32(smem + stage * Cfg::STAGE_BYTES);
             const uint32_t sb = sa + Cfg::A_BYTES;
             if (a_mt)
-              build_operand_tile<ESIZE, Cfg::BM, 8, PT>(sa, 0u, pr.a, p.view, tile.i * Cfg::BM, kk * BK, ptid);
+              build_operand_tile<ESIZE, Cfg::BM, 8, PT, false>(sa, 0u, pr.a, p.view, tile.i * Cfg::BM, kk * BK, ptid);
             if (b_mt)
-              build_operand_tile<ESIZE, BK, BN * ESIZE / 16, PT>(sb, Cfg::BLK_BYTES, pr.b, p.view, kk * BK, tile.j * BN,
+              build_operand_tile<ESIZE, BK, BN * ESIZE / 16, PT, Cfg::B_SWZ32>(sb, Cfg::BLK_BYTES, pr.b, p.view, kk * BK, tile.j * BN,
                                                                   ptid);
             if (a_mt || b_mt) ptx::fence_proxy_async_smem();
             __syncwarp();
