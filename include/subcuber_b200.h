@@ -116,6 +116,46 @@ int sb200_gemm_launches(const char* kernel);
  * Allocates and frees device memory inside the call. */
 int sb200_gemm_host(const char* kernel, const void* a_host, const void* b_host, void* d_host, int m, int n, int k);
 
+
+/* Byte offsets of the parts of the workspace of (kernel, m, n, k).  presum_a holds S1,S2,A02,A1S2 packed
+ * [4][mq][kq] and presum_b holds B10,B31,S3,S3B2 packed [4][kq][nq] in the operand type (interleaved-presum
+ * kernels only: the counterpart of the reference's presum workspace, strassen_gemm.h:653-657); handoff[i] are
+ * fp32 tile-contiguous buffers. */
+typedef struct sb200_workspace_layout {
+  size_t status, presum_a, presum_b, handoff[4], total;
+  int mq, nq, kq, tiles_m, tiles_n, bn;
+} sb200_workspace_layout;
+int sb200_gemm_workspace_layout(const char* kernel, int m, int n, int k, sb200_workspace_layout* out);
+
+/* Like sb200_gemm, but synchronises and reports the device time of each kernel launch of the call
+ * (CUDA events on `stream`); launch_ms must have room for 3 floats. */
+int sb200_gemm_timed(const char* kernel, const void* a, const void* b, void* d, int m, int n, int k, void* workspace,
+                     size_t workspace_bytes, sb200_stream_t stream, float* launch_ms, int* num_launches);
+
+/* Per-launch device timing inside a caller's own timed loop: sb200_gemm_events is sb200_gemm that also records
+ * launches+1 CUDA events of `list`, starting at `first_index`, before the first and after every kernel launch. */
+typedef struct sb200_event_list sb200_event_list;
+sb200_event_list* sb200_events_create(int count);
+void sb200_events_destroy(sb200_event_list* list);
+int sb200_events_elapsed_ms(sb200_event_list* list, int first, int second, float* ms);
+int sb200_gemm_events(const char* kernel, const void* a, const void* b, void* d, int m, int n, int k, void* workspace,
+                      size_t workspace_bytes, sb200_stream_t stream, sb200_event_list* list, int first_index);
+
+/* The tile program tables the kernels interpret (csrc/tile_program.h), for inspection and tests.
+ * which: "level0" | "level1_full_fly" | "level1_full_ws" | "level1_first" | "level1_second". */
+int sb200_tile_program(const char* which, void* out, size_t out_bytes);
+size_t sb200_tile_program_bytes(void);
+
+/* Seeded synthetic inputs, bit-identical on host and device for dist 0 and 2 (dist 1 uses libm / device
+ * math and agrees to rounding).  dtype: 0 f16, 1 f32, 2 f64.  dist: 0 uniform[-1,1), 1 normal(0,1),
+ * 2 the reference harness' value set (multiples of 0.25 in [-4,4] for f16, [-16,16] otherwise;
+ * tests/base_test.cuh:248-262 in the reference).  Element i takes Philox4x32-10(key = seed,
+ * counter = (i, subsequence)); by convention A uses subsequence 0 and B subsequence 1. */
+int sb200_fill_device(int dtype, int dist, unsigned long long seed, unsigned subsequence, void* device_ptr,
+                      unsigned long long count, sb200_stream_t stream);
+int sb200_fill_host(int dtype, int dist, unsigned long long seed, unsigned subsequence, void* host_ptr,
+                    unsigned long long count);
+
 #ifdef __cplusplus
 }
 #endif

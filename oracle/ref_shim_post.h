@@ -6,17 +6,21 @@
 
 typedef _Float16 ref_half;
 
+// rows [ref_row_begin, ref_row_end) of the thread grid are replayed (whole grid by default); a bounded row
+// range is what the benchmark's CPU-reference arm times, since every output element is an independent thread.
+static int ref_row_begin = 0, ref_row_end = -1;
+
 template <typename F>
 static void ref_for_each_element(int M, int N, F body) {
-#pragma omp parallel for schedule(dynamic, 1)
-  for (int i = 0; i < M; ++i) {
+  const int i0 = ref_row_begin, i1 = (ref_row_end < 0 || ref_row_end > M) ? M : ref_row_end;
+  const long long first = (long long)i0 * N, last = (long long)i1 * N;
+#pragma omp parallel for schedule(dynamic, 64)
+  for (long long e = first; e < last; ++e) {
     blockDim.x = blockDim.y = blockDim.z = 1;
     threadIdx.x = threadIdx.y = threadIdx.z = 0;
-    blockIdx.x = (unsigned)i;
-    for (int j = 0; j < N; ++j) {
-      blockIdx.y = (unsigned)j;
-      body();
-    }
+    blockIdx.x = (unsigned)(e / N);
+    blockIdx.y = (unsigned)(e % N);
+    body();
   }
 }
 
@@ -50,6 +54,18 @@ extern "C" int ref_sw_gemm(int dtype, int level, int M, int N, int K, double alp
     case 2: ref_run<double, double, double>(level, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc); return 0;
   }
   return 1;
+}
+
+// Same, restricted to C rows [row_begin, row_end): the other rows of C are left untouched.
+extern "C" int ref_sw_gemm_rows(int dtype, int level, int M, int N, int K, double alpha, const void *A, int lda,
+                                const void *B, int ldb, double beta, void *C, int ldc, int row_begin, int row_end) {
+  if (row_begin < 0 || row_end > M || row_begin >= row_end) return 1;
+  ref_row_begin = row_begin;
+  ref_row_end = row_end;
+  int rc = ref_sw_gemm(dtype, level, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc);
+  ref_row_begin = 0;
+  ref_row_end = -1;
+  return rc;
 }
 
 // The reference's presum dump (src/cuda/strassen_reference_l1.cuh:119-183) for ONE output column pair

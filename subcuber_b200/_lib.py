@@ -30,6 +30,14 @@ class KernelEntry(C.Structure):
                 ("run", RUN_FN)]
 
 
+class WorkspaceLayout(C.Structure):
+    """Mirror of `sb200_workspace_layout`."""
+
+    _fields_ = [("status", C.c_size_t), ("presum_a", C.c_size_t), ("presum_b", C.c_size_t),
+                ("handoff", C.c_size_t * 4), ("total", C.c_size_t), ("mq", C.c_int), ("nq", C.c_int),
+                ("kq", C.c_int), ("tiles_m", C.c_int), ("tiles_n", C.c_int), ("bn", C.c_int)]
+
+
 _lib = None
 
 
@@ -56,5 +64,19 @@ def load(build_if_missing: bool = True) -> C.CDLL:
     lib.sb200_gemm_status.argtypes = [C.c_void_p, C.c_void_p]
     lib.sb200_gemm_launches.argtypes = [C.c_char_p]
     lib.sb200_gemm_host.argtypes = [C.c_char_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int]
+    lib.sb200_gemm_workspace_layout.argtypes = [C.c_char_p, C.c_int, C.c_int, C.c_int, C.POINTER(WorkspaceLayout)]
+    lib.sb200_gemm_timed.argtypes = [C.c_char_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
+                                     C.c_void_p, C.c_size_t, C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_int)]
+    lib.sb200_tile_program.argtypes = [C.c_char_p, C.c_void_p, C.c_size_t]
+    lib.sb200_tile_program_bytes.restype = C.c_size_t
+    lib.sb200_fill_device.argtypes = [C.c_int, C.c_int, C.c_ulonglong, C.c_uint, C.c_void_p, C.c_ulonglong, C.c_void_p]
+    lib.sb200_fill_host.argtypes = [C.c_int, C.c_int, C.c_ulonglong, C.c_uint, C.c_void_p, C.c_ulonglong]
+    lib.sb200_events_create.restype = C.c_void_p
+    lib.sb200_events_create.argtypes = [C.c_int]
+    lib.sb200_events_destroy.restype = None
+    lib.sb200_events_destroy.argtypes = [C.c_void_p]
+    lib.sb200_events_elapsed_ms.argtypes = [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_float)]
+    lib.sb200_gemm_events.argtypes = [C.c_char_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
+                                      C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_int]
     _lib = lib
     return lib

@@ -24,7 +24,7 @@ NVCC_FLAGS = [
     "-Xcompiler", "-fPIC",
 ]
 
-LIB_SOURCES = ["sw_host.cu", "abi.cu"]
+LIB_SOURCES = ["sw_host.cu", "abi.cu", "fill.cu"]
 RUNNER_SOURCES = ["kernel_runner.cpp"]
 
 
@@ -69,7 +69,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
                 cmd.insert(2, "-v")
             subprocess.run(cmd, check=True)
             objs.append(obj)
-        cmd = [nvcc, "-shared", "-o", LIB, *objs, "-L" + libdir, "-lcublas", "-lcublasLt", "-lcudart",
+        cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-o", LIB, *objs, "-L" + libdir, "-lcublas", "-lcublasLt", "-lcudart",
                "-Xlinker", "-rpath=" + libdir]
         subprocess.run(cmd, check=True)
     runner_srcs = [os.path.join(CSRC, s) for s in RUNNER_SOURCES if os.path.exists(os.path.join(CSRC, s))]

@@ -7,6 +7,7 @@
 
 #include "../../include/subcuber_b200.h"
 #include "sw_host.h"
+#include "sw_programs.h"
 
 namespace {
 
@@ -361,4 +362,108 @@ extern "C" int sb200_gemm_host(const char* kernel, const void* a_host, const voi
   rc = sb200::read_status(ws, nullptr);
   cleanup();
   return rc;
+}
+
+extern "C" int sb200_gemm_workspace_layout(const char* kernel, int m, int n, int k, sb200_workspace_layout* out) {
+  const KernelDesc* d = find_desc(kernel);
+  if (!d) return SB200_ERR_NO_KERNEL;
+  if (!out || m <= 0 || n <= 0 || k <= 0) return SB200_ERR_INVALID_PROBLEM;
+  GemmArgs g = make_args(*d, nullptr, nullptr, nullptr, m, n, k);
+  const sb200::WorkspaceLayout w = sb200::workspace_layout(g);
+  out->status = w.status;
+  out->presum_a = w.presum_a;
+  out->presum_b = w.presum_b;
+  for (int i = 0; i < 4; ++i) out->handoff[i] = w.handoff[i];
+  out->total = w.total;
+  out->mq = w.mq; out->nq = w.nq; out->kq = w.kq;
+  out->tiles_m = w.tiles_m; out->tiles_n = w.tiles_n; out->bn = w.bn;
+  return 0;
+}
+
+extern "C" int sb200_gemm_timed(const char* kernel, const void* a, const void* b, void* d_out, int m, int n, int k,
+                                void* workspace, size_t workspace_bytes, sb200_stream_t stream, float* launch_ms,
+                                int* num_launches) {
+  const KernelDesc* d = find_desc(kernel);
+  if (!d) return SB200_ERR_NO_KERNEL;
+  if (!launch_ms || !num_launches) return SB200_ERR_INVALID_PROBLEM;
+  GemmArgs g = make_args(*d, a, b, d_out, m, n, k);
+  const int nl = sb200::launches_per_run(g);
+  cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr};
+  cudaError_t ce = cudaSuccess;
+  for (int i = 0; i <= nl; ++i)
+    if ((ce = cudaEventCreate(&ev[i])) != cudaSuccess) break;
+  int rc = static_cast<int>(ce);
+  if (!rc) {
+    g.events = ev;
+    rc = sb200::run(g, workspace, workspace_bytes, reinterpret_cast<cudaStream_t>(stream));
+  }
+  if (!rc) rc = sb200::read_status(workspace, reinterpret_cast<cudaStream_t>(stream));
+  if (!rc) {
+    for (int i = 0; i < nl; ++i)
+      if ((ce = cudaEventElapsedTime(&launch_ms[i], ev[i], ev[i + 1])) != cudaSuccess) rc = static_cast<int>(ce);
+    *num_launches = nl;
+  }
+  for (int i = 0; i < 4; ++i)
+    if (ev[i]) cudaEventDestroy(ev[i]);
+  return rc;
+}
+
+extern "C" int sb200_tile_program(const char* which, void* out, size_t out_bytes) {
+  if (!which || !out || out_bytes < sizeof(sb200_program_t)) return SB200_ERR_INVALID_PROBLEM;
+  sb200_program_t pg;
+  if (strcmp(which, "level0") == 0) pg = sb200::programs::level0();
+  else if (strcmp(which, "level1_full_fly") == 0) pg = sb200::programs::level1_full(true);
+  else if (strcmp(which, "level1_full_ws") == 0) pg = sb200::programs::level1_full(false);
+  else if (strcmp(which, "level1_first") == 0) pg = sb200::programs::level1_first();
+  else if (strcmp(which, "level1_second") == 0) pg = sb200::programs::level1_second();
+  else return SB200_ERR_NO_KERNEL;
+  memcpy(out, &pg, sizeof(pg));
+  return 0;
+}
+
+extern "C" size_t sb200_tile_program_bytes(void) { return sizeof(sb200_program_t); }
+
+// ---- event lists: per-launch device timing inside a caller's timed loop -------------------------------
+struct sb200_event_list {
+  int count;
+  cudaEvent_t* ev;
+};
+
+extern "C" sb200_event_list* sb200_events_create(int count) {
+  if (count <= 0) return nullptr;
+  sb200_event_list* l = new sb200_event_list;
+  l->count = count;
+  l->ev = new cudaEvent_t[count];
+  for (int i = 0; i < count; ++i) {
+    if (cudaEventCreate(&l->ev[i]) != cudaSuccess) {
+      for (int j = 0; j < i; ++j) cudaEventDestroy(l->ev[j]);
+      delete[] l->ev;
+      delete l;
+      return nullptr;
+    }
+  }
+  return l;
+}
+
+extern "C" void sb200_events_destroy(sb200_event_list* l) {
+  if (!l) return;
+  for (int i = 0; i < l->count; ++i) cudaEventDestroy(l->ev[i]);
+  delete[] l->ev;
+  delete l;
+}
+
+extern "C" int sb200_events_elapsed_ms(sb200_event_list* l, int first, int second, float* ms) {
+  if (!l || !ms || first < 0 || second < 0 || first >= l->count || second >= l->count) return SB200_ERR_INVALID_PROBLEM;
+  return static_cast<int>(cudaEventElapsedTime(ms, l->ev[first], l->ev[second]));
+}
+
+extern "C" int sb200_gemm_events(const char* kernel, const void* a, const void* b, void* d_out, int m, int n, int k,
+                                 void* workspace, size_t workspace_bytes, sb200_stream_t stream, sb200_event_list* l,
+                                 int first_index) {
+  const KernelDesc* d = find_desc(kernel);
+  if (!d) return SB200_ERR_NO_KERNEL;
+  GemmArgs g = make_args(*d, a, b, d_out, m, n, k);
+  if (!l || first_index < 0 || first_index + sb200::launches_per_run(g) + 1 > l->count) return SB200_ERR_INVALID_PROBLEM;
+  g.events = l->ev + first_index;
+  return sb200::run(g, workspace, workspace_bytes, reinterpret_cast<cudaStream_t>(stream));
 }

@@ -146,6 +146,20 @@ int can_implement(const GemmArgs& a) {
 
 size_t workspace_bytes(const GemmArgs& a) { return make_layout(a).total; }
 
+WorkspaceLayout workspace_layout(const GemmArgs& a) {
+  const Layout L = make_layout(a);
+  WorkspaceLayout w;
+  memset(&w, 0, sizeof(w));
+  w.status = L.off_status;
+  w.presum_a = L.off_pa;
+  w.presum_b = L.off_pb;
+  for (int i = 0; i < SB200_NUM_WS; ++i) w.handoff[i] = L.off_ws[i];
+  w.total = L.total;
+  w.mq = L.mq; w.nq = L.nq; w.kq = L.kq;
+  w.tiles_m = L.tiles_m; w.tiles_n = L.tiles_n; w.bn = L.bn;
+  return w;
+}
+
 int launches_per_run(const GemmArgs& a) { return a.variant == kInterleavedPresum ? 2 : 1; }
 
 int run(const GemmArgs& a, void* workspace, size_t workspace_size, cudaStream_t stream) {
@@ -212,21 +226,34 @@ int run(const GemmArgs& a, void* workspace, size_t workspace_size, cudaStream_t 
   int cap = a.sm_limit > 0 ? a.sm_limit : sm_count();
   if (grid > cap) grid = cap;
 
+  int nev = 0;
+  auto mark = [&]() -> int {
+    if (!a.events) return 0;
+    return static_cast<int>(cudaEventRecord(a.events[nev++], stream));
+  };
+  if ((rc = mark())) return rc;
   switch (a.variant) {
     case kCubic:
       p.prog = programs::level0();
-      return launch_any(es, L.bn, kPresumNone, p, grid, stream);
+      rc = launch_any(es, L.bn, kPresumNone, p, grid, stream);
+      break;
     case kFusedPresum:
       p.prog = programs::level1_full(true);
-      return launch_any(es, L.bn, kPresumFeed, p, grid, stream);
+      rc = launch_any(es, L.bn, kPresumFeed, p, grid, stream);
+      break;
     case kInterleavedPresum:
       p.prog = programs::level1_first();
       rc = launch_any(es, L.bn, kPresumJob, p, grid, stream);
       if (rc) return rc;
+      if ((rc = mark())) return rc;
       p.prog = programs::level1_second();
-      return launch_any(es, L.bn, kPresumNone, p, grid, stream);
+      rc = launch_any(es, L.bn, kPresumNone, p, grid, stream);
+      break;
+    default:
+      return kErrNotSupported;
   }
-  return kErrNotSupported;
+  if (rc) return rc;
+  return mark();
 }
 
 int read_status(void* workspace, cudaStream_t stream) {

@@ -37,7 +37,15 @@ struct GemmArgs {
   void* d;        // m x n row-major, ldd = n;  D = A * B
   int bn;         // tile width: 256 (default when 0) or 128
   int sm_limit;   // CTAs to launch at most (0: one per SM of the current device)
+  cudaEvent_t* events;  // optional: launches_per_run()+1 events, recorded before the first and after each launch
 };
+
+// Byte offsets of the parts of the workspace (tests read the presum buffers through this).
+struct WorkspaceLayout {
+  size_t status, presum_a, presum_b, handoff[4], total;
+  int mq, nq, kq, tiles_m, tiles_n, bn;
+};
+WorkspaceLayout workspace_layout(const GemmArgs& args);
 
 // 0 when the kernels can run this problem, else an Error.
 int can_implement(const GemmArgs& args);

@@ -1,0 +1,294 @@
+"""Parity of the CUDA path with the CPU oracle, through the C ABI, on a B200.
+
+Tolerances follow the reference harness (tests/base_test.cuh:85-117 in the reference project): an element
+passes if abs <= tol_abs OR rel <= tol_rel; f32: 1e-4 / 1e-4, f16: abs 4 (level 1), rel 1e-2.  On the harness'
+own value set (multiples of 0.25) every partial sum is exactly representable, so the comparison there is
+BIT-EXACT.  On uniform[-1,1) inputs the gate is the one the path's specification states: relative Frobenius
+error against an fp64 product no worse than 1.5x the error of the reference's own level-1 routine (the CPU
+oracle at the harness' types) on the same inputs.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+L1_F16 = ["blackwell_f16_sw_interleaved_presum", "blackwell_f16_sw_fused_presum"]
+L1_F32 = ["blackwell_f32_sw_interleaved_presum", "blackwell_f32_sw_fused_presum"]
+L0_F16 = ["blackwell_f16_cubic_128x256", "blackwell_f16_cubic_128x128"]
+L0_F32 = ["blackwell_f32_cubic_128x256", "blackwell_f32_cubic_128x128"]
+
+
+def _dt(kernel):
+    return "f16" if "_f16_" in kernel else "f32"
+
+
+def _level(kernel):
+    return 0 if "cubic" in kernel else 1
+
+
+def _run(kernel, a_np, b_np, device):
+    import torch
+
+    from subcuber_b200 import runner
+
+    a = torch.from_numpy(a_np).to(device)
+    b = torch.from_numpy(b_np).to(device)
+    d = torch.full((a.shape[0], b.shape[1]), float("nan"), dtype=a.dtype, device=device)
+    runner.gemm(kernel, a, b, d)
+    torch.cuda.synchronize()
+    return d.cpu().numpy()
+
+
+def _rel_fro(x, truth):
+    return float(np.linalg.norm(x.astype(np.float64) - truth) / np.linalg.norm(truth))
+
+
+# --------------------------------------------------------------------------------------------- bit-exact
+SMALL_SHAPES = [(256, 512, 128), (384, 768, 320), (272, 528, 144), (2, 16, 16), (130, 48, 80), (1024, 1024, 1024)]
+
+
+@pytest.mark.parametrize("kernel", L0_F16 + L0_F32 + L1_F16 + L1_F32)
+@pytest.mark.parametrize("shape", SMALL_SHAPES)
+def test_bit_exact_on_harness_values(kernel, shape, oracle, cuda_device):
+    from subcuber_b200 import inputs
+
+    m, n, k = shape
+    dt = _dt(kernel)
+    a, b = inputs.operands(dt, "harness", m, n, k, seed=m + n + k)
+    got = _run(kernel, a, b, cuda_device)
+    want = oracle.sw_gemm(dt, _level(kernel), a, b)
+    assert not np.isnan(got).any()
+    assert np.array_equal(got, want), f"{np.count_nonzero(got != want)} elements differ from the oracle"
+    truth = a.astype(np.float64) @ b.astype(np.float64)
+    if dt == "f32":
+        assert np.array_equal(got.astype(np.float64), truth)
+
+
+@pytest.mark.parametrize("kernel", L1_F16 + L1_F32)
+@pytest.mark.parametrize("shape", [(2048, 2048, 2048), (6144, 2560, 2048), (2048, 4096, 6144)])
+def test_bit_exact_on_harness_values_reference_shapes(kernel, shape, oracle, cuda_device):
+    """Shapes of the reference's own gtest lists (tests/f32_strassen_winograd_tile.cu:22-34), row-sampled."""
+    from subcuber_b200 import inputs
+
+    m, n, k = shape
+    dt = _dt(kernel)
+    a, b = inputs.operands(dt, "harness", m, n, k, seed=3)
+    got = _run(kernel, a, b, cuda_device)
+    rows = np.array([0, 1, 127, 128, m // 4 + 5, m // 2 - 1], dtype=np.int32)
+    want = oracle.sw_gemm(dt, 1, a, b, rows=rows)
+    for r in rows:
+        assert np.array_equal(got[r], want[r]) and np.array_equal(got[r + m // 2], want[r + m // 2])
+    # whole-matrix check that does not depend on the size: sum of all elements = colsum(A) . rowsum(B)
+    if dt == "f32":
+        total = float(a.astype(np.float64).sum(axis=0) @ b.astype(np.float64).sum(axis=1))
+        assert float(got.astype(np.float64).sum()) == total
+
+
+# ------------------------------------------------------------------------------------- presum workspace
+@pytest.mark.parametrize("kernel", ["blackwell_f16_sw_interleaved_presum", "blackwell_f32_sw_interleaved_presum"])
+@pytest.mark.parametrize("shape", [(256, 512, 128), (272, 528, 144), (1024, 768, 512)])
+def test_presum_workspace_bit_exact(kernel, shape, oracle, lib, cuda_device):
+    """The eight presums the first launch materialises equal the oracle's, bit for bit, on uniform inputs."""
+    import torch
+
+    from subcuber_b200 import _lib as L
+    from subcuber_b200 import inputs, runner
+
+    m, n, k = shape
+    dt = _dt(kernel)
+    a_np, b_np = inputs.operands(dt, "uniform1", m, n, k, seed=21)
+    a = torch.from_numpy(a_np).to(cuda_device)
+    b = torch.from_numpy(b_np).to(cuda_device)
+    ws = runner.Workspace(kernel, m, n, k, cuda_device)
+    runner.gemm(kernel, a, b, workspace=ws)
+    torch.cuda.synchronize()
+    lay = L.WorkspaceLayout()
+    assert lib.sb200_gemm_workspace_layout(kernel.encode(), m, n, k, C.byref(lay)) == 0
+    off = ws.ptr - ws.buf.data_ptr()
+    raw = ws.buf.cpu().numpy()
+    npd = oracle.NP_DTYPE[dt]
+    es = np.dtype(npd).itemsize
+    pa = raw[off + lay.presum_a: off + lay.presum_a + 4 * lay.mq * lay.kq * es].view(npd).reshape(4, lay.mq, lay.kq)
+    pb = raw[off + lay.presum_b: off + lay.presum_b + 4 * lay.kq * lay.nq * es].view(npd).reshape(4, lay.kq, lay.nq)
+    want_a, want_b = oracle.sw_presums(dt, a_np, b_np)
+    assert np.array_equal(pa, want_a)
+    assert np.array_equal(pb, want_b)
+
+
+# ------------------------------------------------------------------------------------------ tolerances
+def _harness_tol(dt, level):
+    if dt == "f16":
+        return (4.0 if level == 1 else 7.0), 1e-2
+    return 1e-4, 1e-4
+
+
+@pytest.mark.parametrize("kernel", L1_F16 + L0_F16)
+@pytest.mark.parametrize("shape", [(512, 512, 512), (1024, 1024, 1024), (1536, 640, 1152)])
+def test_uniform_inputs_f16(kernel, shape, oracle, cuda_device):
+    from subcuber_b200 import inputs
+
+    m, n, k = shape
+    a, b = inputs.operands("f16", "uniform1", m, n, k, seed=5)
+    got = _run(kernel, a, b, cuda_device)
+    truth = a.astype(np.float64) @ b.astype(np.float64)
+    level = _level(kernel)
+    ref = oracle.sw_gemm("f16", level, a, b)
+    err, ref_err = _rel_fro(got, truth), _rel_fro(ref, truth)
+    assert err <= 1.5 * ref_err, f"rel. Frobenius error {err:.3e} vs reference routine {ref_err:.3e}"
+    tol_abs, tol_rel = _harness_tol("f16", max(level, 1))
+    diff = np.abs(got.astype(np.float64) - ref.astype(np.float64))
+    ok = (diff <= tol_abs) | (diff <= tol_rel * np.abs(ref.astype(np.float64)))
+    assert ok.all()
+    if level == 0:
+        assert np.allclose(got.astype(np.float64), truth, rtol=1e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("kernel", L1_F32 + L0_F32)
+@pytest.mark.parametrize("dist", ["uniform1", "normal"])
+def test_uniform_inputs_tf32(kernel, dist, oracle, cuda_device):
+    """fp32 storage with TF32 tensor-core math: the reference has no TF32 oracle; the CPU model rounds every
+    multiplicand to TF32 (error ~ 2^-11 per operand, zero mean).  The tensor core reads the upper 19 bits,
+    i.e. truncates (error up to 2^-10 per operand, one sign), so the bound is 4x that model's error, and the
+    result must also sit within TF32 distance of the fp64 product."""
+    from subcuber_b200 import inputs
+
+    m, n, k = 1024, 768, 1280
+    a, b = inputs.operands("f32", dist, m, n, k, seed=8)
+    got = _run(kernel, a, b, cuda_device)
+    truth = a.astype(np.float64) @ b.astype(np.float64)
+    model = oracle.sw_gemm("tf32", _level(kernel), a, b)
+    err, model_err = _rel_fro(got, truth), _rel_fro(model, truth)
+    assert err <= 4.0 * model_err + 1e-6, f"{err:.3e} vs TF32 model {model_err:.3e}"
+    assert err < 3e-3
+
+
+# ----------------------------------------------------------------------------------------- full size
+@pytest.mark.parametrize("kernel,size", [("blackwell_f16_sw_interleaved_presum", 8192),
+                                         ("blackwell_f16_cubic_128x256", 8192),
+                                         ("blackwell_f32_sw_interleaved_presum", 4096)])
+def test_full_size_properties(kernel, size, oracle, cuda_device):
+    """The benchmark workload itself (f16, level 1, 8192^3): sampled rows against fp64 and against the
+    reference routine, plus the checksum identity sum(C) = colsum(A) . rowsum(B) over the whole matrix."""
+    import torch
+
+    from subcuber_b200 import inputs, runner
+
+    dt = _dt(kernel)
+    a = inputs.fill_device(dt, "uniform1", (size, size), 1, 0, cuda_device)
+    b = inputs.fill_device(dt, "uniform1", (size, size), 1, 1, cuda_device)
+    d = runner.gemm(kernel, a, b)
+    torch.cuda.synchronize()
+    total_dev = float(d.double().sum())
+    total = float(a.double().sum(dim=0) @ b.double().sum(dim=1))
+    scale = float((a.double().abs().sum(dim=0) @ b.double().abs().sum(dim=1)))
+    assert abs(total_dev - total) <= 2e-5 * scale
+    a_np, b_np = a.cpu().numpy(), b.cpu().numpy()
+    rows = np.array([0, 77, size // 4, size // 2 - 1], dtype=np.int32)
+    all_rows = np.concatenate([rows, rows + size // 2])
+    truth = oracle.truth_rows(dt, a_np, b_np, all_rows)
+    got = d[torch.from_numpy(all_rows).long().to(cuda_device)].cpu().numpy()
+    if dt == "f16":
+        level = _level(kernel)
+        ref = oracle.sw_gemm("f16", level, a_np, b_np, rows=(rows if level else all_rows))[all_rows]
+        err, ref_err = _rel_fro(got, truth), _rel_fro(ref, truth)
+        assert err <= 1.5 * ref_err, f"{err:.3e} vs reference routine {ref_err:.3e}"
+    else:
+        assert _rel_fro(got, truth) < 3e-3
+
+
+def test_level0_agrees_with_cublas(cuda_device):
+    import torch
+
+    from subcuber_b200 import inputs, runner
+
+    a = inputs.fill_device("f16", "uniform1", (2048, 1024), 2, 0, cuda_device)
+    b = inputs.fill_device("f16", "uniform1", (1024, 3072), 2, 1, cuda_device)
+    d_blas, ms_blas = runner.run_kernel("cublas_f16", a, b, warmup=1, iterations=2)
+    d_ours, ms_ours = runner.run_kernel("blackwell_f16_cubic_128x256", a, b, warmup=1, iterations=2)
+    assert ms_blas > 0 and ms_ours > 0
+    torch.cuda.synchronize()
+    diff = (d_blas.double() - d_ours.double()).abs().max().item()
+    assert diff <= 0.07  # both round an fp32 sum of 1024 products to fp16 (values up to ~64: ulp 0.03)
+
+
+# --------------------------------------------------------------------------------------- ABI behaviour
+def test_run_entry_point_error_codes(cuda_device):
+    import torch
+
+    from subcuber_b200 import runner
+
+    a = torch.zeros((255, 128), dtype=torch.float16, device=cuda_device)
+    b = torch.zeros((128, 256), dtype=torch.float16, device=cuda_device)
+    with pytest.raises(runner.KernelError) as e:
+        runner.run_kernel("blackwell_f16_sw_interleaved_presum", a, b)
+    assert e.value.code == 4
+    a = torch.zeros((256, 128), dtype=torch.float16, device=cuda_device)
+    with pytest.raises(runner.KernelError) as e:
+        runner.run_kernel("blackwell_f16_sw_interleaved_presum", a, b, split_k=2)
+    assert e.value.code == 5
+    b = torch.zeros((128, 264), dtype=torch.float16, device=cuda_device)  # quadrant rows start at 8 mod 16 bytes
+    with pytest.raises(runner.KernelError) as e:
+        runner.run_kernel("blackwell_f16_sw_interleaved_presum", a, b)
+    assert e.value.code == 1
+
+
+def test_workspace_checks(lib, cuda_device):
+    import torch
+
+    a = torch.zeros((256, 128), dtype=torch.float16, device=cuda_device)
+    b = torch.zeros((128, 256), dtype=torch.float16, device=cuda_device)
+    d = torch.zeros((256, 256), dtype=torch.float16, device=cuda_device)
+    name = b"blackwell_f16_sw_interleaved_presum"
+    assert lib.sb200_gemm(name, a.data_ptr(), b.data_ptr(), d.data_ptr(), 256, 256, 128, None, 0, None) == 6
+    need = lib.sb200_gemm_workspace_bytes(name, 256, 256, 128)
+    ws = torch.empty(need + 512, dtype=torch.uint8, device=cuda_device)
+    base = ws.data_ptr() + ((-ws.data_ptr()) % 256)
+    assert lib.sb200_gemm(name, a.data_ptr(), b.data_ptr(), d.data_ptr(), 256, 256, 128, base, need - 1, None) == 6
+    assert lib.sb200_gemm(name, a.data_ptr(), b.data_ptr(), d.data_ptr(), 256, 256, 128, base + 16, need, None) == 6
+    assert lib.sb200_gemm(name, a.data_ptr(), b.data_ptr(), d.data_ptr(), 256, 256, 128, base, need, None) == 0
+    assert lib.sb200_gemm_status(base, None) == 0
+
+
+def test_host_buffer_call_and_determinism(oracle, cuda_device):
+    from subcuber_b200 import inputs, runner
+
+    a, b = inputs.operands("f16", "uniform1", 512, 768, 384, seed=4)
+    d1 = runner.gemm_host("blackwell_f16_sw_interleaved_presum", a, b)
+    d2 = _run("blackwell_f16_sw_interleaved_presum", a, b, cuda_device)
+    d3 = _run("blackwell_f16_sw_interleaved_presum", a, b, cuda_device)
+    assert np.array_equal(d1, d2) and np.array_equal(d2, d3)
+    # the on-the-fly presum variant forms the same operands but chains its accumulators in another order
+    d4 = _run("blackwell_f16_sw_fused_presum", a, b, cuda_device)
+    assert np.allclose(d2.astype(np.float64), d4.astype(np.float64), rtol=2e-3, atol=2e-2)
+
+
+@pytest.mark.parametrize("dt", ["f16", "f32", "f64"])
+@pytest.mark.parametrize("dist", ["uniform1", "harness", "normal"])
+def test_device_fill_matches_host_fill(dt, dist, cuda_device):
+    from subcuber_b200 import inputs
+
+    h = inputs.fill_host(dt, dist, (257, 129), seed=6, subsequence=1)
+    d = inputs.fill_device(dt, dist, (257, 129), seed=6, subsequence=1, device=cuda_device).cpu().numpy()
+    if dist == "normal":
+        assert np.allclose(h.astype(np.float64), d.astype(np.float64), rtol=2e-3, atol=2e-3)
+    else:
+        assert np.array_equal(h, d)
+
+
+def test_timed_call_reports_every_launch(lib, cuda_device):
+    import torch
+
+    from subcuber_b200 import inputs, runner
+
+    a = inputs.fill_device("f16", "uniform1", (1024, 1024), 1, 0, cuda_device)
+    b = inputs.fill_device("f16", "uniform1", (1024, 1024), 1, 1, cuda_device)
+    d = torch.empty((1024, 1024), dtype=torch.float16, device=cuda_device)
+    name = "blackwell_f16_sw_interleaved_presum"
+    ws = runner.Workspace(name, 1024, 1024, 1024, cuda_device)
+    ms = (C.c_float * 3)()
+    nl = C.c_int(0)
+    rc = lib.sb200_gemm_timed(name.encode(), a.data_ptr(), b.data_ptr(), d.data_ptr(), 1024, 1024, 1024, ws.ptr,
+                              ws.nbytes, None, ms, C.byref(nl))
+    assert rc == 0 and nl.value == 2 and ms[0] > 0 and ms[1] > 0

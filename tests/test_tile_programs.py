@@ -1,0 +1,56 @@
+"""Tile-program tables compiled into the library: protocol and algebra, checked symbolically on the CPU."""
+import ctypes as C
+
+import pytest
+
+from subcuber_b200 import tile_program as tp
+
+
+def test_struct_mirror_matches_header(lib):
+    assert lib.sb200_tile_program_bytes() == C.sizeof(tp.Program)
+
+
+def test_level0(lib):
+    pg = tp.from_library("level0")
+    assert pg.nproducts == 1 and pg.alternate_slots == 1 and pg.needs_feed == 0
+    tp.check_program(pg, level=0, nslots=2, tiles=5)
+    tp.check_program(pg, level=0, nslots=4, tiles=5)
+
+
+@pytest.mark.parametrize("which,feed", [("level1_full_fly", 1), ("level1_full_ws", 0)])
+def test_level1_single_launch(lib, which, feed):
+    pg = tp.from_library(which)
+    assert pg.nproducts == 7 and pg.needs_feed == feed
+    res = tp.check_program(pg, level=1, nslots=2, tiles=4)
+    assert sorted(res["outputs"]) == [0, 1, 2, 3]
+
+
+def test_level1_two_launches(lib):
+    first = tp.from_library("level1_first")
+    second = tp.from_library("level1_second")
+    assert first.nproducts == 2 and second.nproducts == 5
+    assert first.needs_feed == 0 and second.needs_feed == 0
+    r1 = tp.check_program(first, level=1, nslots=2, expect=[0], tiles=4)
+    assert 0 in r1["ws"]  # M0 handed to the second launch
+    r2 = tp.check_program(second, level=1, nslots=2, ws_in=r1["ws"], expect=[1, 2, 3], tiles=4)
+    assert sorted(r2["outputs"]) == [1, 2, 3]
+
+
+def test_second_launch_needs_the_handoff(lib):
+    with pytest.raises(tp.ProgramError):
+        tp.check_program(tp.from_library("level1_second"), level=1, nslots=2, expect=[1, 2, 3])
+
+
+def test_checker_rejects_broken_tables(lib):
+    pg = tp.from_library("level1_full_ws")
+    pg.product[3].negate = 1  # flips the sign of one product
+    with pytest.raises(tp.ProgramError):
+        tp.check_program(pg, level=1)
+    pg = tp.from_library("level1_full_ws")
+    pg.product[4].wait_free = 0  # writes a slot the epilogue still owns
+    with pytest.raises(tp.ProgramError):
+        tp.check_program(pg, level=1)
+    pg = tp.from_library("level1_full_ws")
+    pg.epilogue[1].release_mask = 0  # never gives the slot back
+    with pytest.raises(tp.ProgramError):
+        tp.check_program(pg, level=1)
