@@ -117,6 +117,29 @@ int sb200_gemm_launches(const char* kernel);
 int sb200_gemm_host(const char* kernel, const void* a_host, const void* b_host, void* d_host, int m, int n, int k);
 
 
+/* D = A * B (f16, Strassen-Winograd level 1, the "blackwell_f16_sw_interleaved_presum" kernels) for callers
+ * that are not allowed to allocate device memory: a serving process whose memory pool owns the whole GPU, a
+ * latency-critical loop that cannot take the device-wide synchronisation cudaMalloc/cudaFree imply, a plugin
+ * host that grants libraries no allocation rights.  No counterpart in the reference project, whose operators
+ * always allocate their workspace per call (src/cuda/kernel_runner_support.cuh:90-91).
+ *
+ * The scratch memory the kernels need lives in a fixed array of SB200_STATIC_SCRATCH_BYTES inside the library,
+ * resident on every GPU that uses this call until the process exits.  The call itself performs no cudaMalloc,
+ * cudaFree or other allocating call.  Limits:
+ *  - the problem's scratch (sb200_gemm_workspace_bytes of that kernel) must fit, else SB200_ERR_SCRATCH_TOO_LARGE
+ *    is returned and nothing runs (32 MiB covers m = n = k = 2048; 3072^3 already needs 54 MiB);
+ *  - one array per GPU, shared by all calls and never cleared between them except for what must start at zero
+ *    (the status block, cleared on `stream` by every call): calls whose kernels could overlap on the GPU race on
+ *    it, so order them on one stream (or otherwise serialise them);
+ *  - the first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
+ *    current) and loads the kernels: make that first call before starting any stream capture.
+ * a, b, d: device pointers, packed row-major.  wait != 0: synchronise `stream` and return the device status word
+ * (0 = ok); wait == 0: return after the launches are enqueued. */
+#define SB200_STATIC_SCRATCH_BYTES (32u << 20)
+#define SB200_ERR_SCRATCH_TOO_LARGE 9
+int sb200_gemm_f16_sw_static_scratch(const void* a, const void* b, void* d, int m, int n, int k,
+                                     sb200_stream_t stream, int wait);
+
 /* Byte offsets of the parts of the workspace of (kernel, m, n, k).  presum_a holds S1,S2,A02,A1S2 packed
  * [4][mq][kq] and presum_b holds B10,B31,S3,S3B2 packed [4][kq][nq] in the operand type (interleaved-presum
  * kernels only: the counterpart of the reference's presum workspace, strassen_gemm.h:653-657); handoff[i] are

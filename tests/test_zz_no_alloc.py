@@ -1,0 +1,67 @@
+"""The allocation-free entry point (`sb200_gemm_f16_sw_static_scratch`) against the ordinary one.
+
+For callers that may not allocate device memory (a process whose pool owns the GPU, a loop that cannot afford
+the device-wide synchronisation of cudaMalloc/cudaFree) the library keeps the level-1 kernels' scratch in a fixed
+32 MiB array of its own.  The test calls the entry point through the C ABI twice in a row, with different operands
+and shapes, so the second call starts from the scratch the first one left behind, and compares each result with
+the output of `sb200_gemm` on a caller-provided workspace: same kernels, same operands, so the outputs must be
+identical bit for bit.  It also checks that a problem whose scratch does not fit is refused before anything runs.
+This file sorts last so that a run that stops at the first failure has already run every other test.
+"""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+KERNEL = "blackwell_f16_sw_interleaved_presum"
+ERR_SCRATCH_TOO_LARGE = 9
+
+
+def _both(lib, cuda_device, m, n, k, seed):
+    import torch
+
+    from subcuber_b200 import inputs, runner
+
+    a = inputs.fill_device("f16", "uniform1", (m, k), seed, 0, cuda_device)
+    b = inputs.fill_device("f16", "uniform1", (k, n), seed, 1, cuda_device)
+    want = runner.gemm(KERNEL, a, b)
+    got = torch.full((m, n), float("nan"), dtype=torch.float16, device=cuda_device)
+    stream = torch.cuda.current_stream(cuda_device).cuda_stream
+    with torch.cuda.device(cuda_device):
+        rc = lib.sb200_gemm_f16_sw_static_scratch(a.data_ptr(), b.data_ptr(), got.data_ptr(), m, n, k, stream, 1)
+    assert rc == 0, f"entry point returned {rc}"
+    torch.cuda.synchronize()
+    return got.cpu().numpy(), want.cpu().numpy()
+
+
+def test_static_scratch_matches_workspace_path_twice_in_a_row(lib, cuda_device):
+    got1, want1 = _both(lib, cuda_device, 1024, 1536, 512, seed=31)
+    assert not np.isnan(got1).any()
+    assert np.array_equal(got1, want1)
+    # second call: other operands, other shape, scratch still holds the first call's presums and hand-off tiles
+    got2, want2 = _both(lib, cuda_device, 2048, 768, 1280, seed=32)
+    assert not np.isnan(got2).any()
+    assert np.array_equal(got2, want2)
+    truth = None  # the ordinary path is itself checked against the oracle elsewhere; one sanity check here
+    from subcuber_b200 import inputs
+
+    a, b = inputs.operands("f16", "uniform1", 2048, 768, 1280, seed=32)
+    truth = a[:4].astype(np.float64) @ b.astype(np.float64)
+    assert np.allclose(got2[:4].astype(np.float64), truth, rtol=1e-2, atol=0.05)
+
+
+def test_static_scratch_rejects_what_does_not_fit(lib, cuda_device):
+    import torch
+
+    m = n = k = 4096  # needs 96 MiB of scratch, the array holds 32 MiB
+    a = torch.zeros((m, k), dtype=torch.float16, device=cuda_device)
+    b = torch.zeros((k, n), dtype=torch.float16, device=cuda_device)
+    d = torch.full((m, n), 7.0, dtype=torch.float16, device=cuda_device)
+    with torch.cuda.device(cuda_device):
+        rc = lib.sb200_gemm_f16_sw_static_scratch(a.data_ptr(), b.data_ptr(), d.data_ptr(), m, n, k, None, 1)
+    assert rc == ERR_SCRATCH_TOO_LARGE
+    torch.cuda.synchronize()
+    assert float(d.min()) == 7.0 and float(d.max()) == 7.0  # nothing ran
+    with torch.cuda.device(cuda_device):
+        rc = lib.sb200_gemm_f16_sw_static_scratch(a.data_ptr(), b.data_ptr(), d.data_ptr(), 1023, 1024, 1024, None, 1)
+    assert rc == 4  # the ordinary argument checks still apply
