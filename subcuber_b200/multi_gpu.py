@@ -1,0 +1,107 @@
+"""Multi-GPU plan for one box: C (and A) split into slabs, B replicated by an all-gather.
+
+The reference project is single-GPU (device 0 only, src/cuda/kernel_runner_support.cuh:312 there); this module is
+the one exchange step the path needs when it runs on 2, 4 or 8 GPUs of a box.  One process per GPU.  GPU r owns the
+row slab A[r] (M/P rows) and produces the same rows of C with an independent local Strassen-Winograd GEMM on an
+(M/P) x N x K problem.  Every GPU needs all of B: B starts row-sharded (K/P contiguous rows per GPU, contiguous in
+row-major) and is replicated into each GPU's own memory by an NCCL all-gather over NVLink; the kernels then read
+local memory only (plain, non-multicast TMA).  When N is much larger than M the symmetric column plan (B column
+slabs local, A replicated) moves fewer bytes; `plan` picks between them.
+
+Everything here is host logic and runs on CPU with the gloo backend too (tests/test_multi_gpu_cpu.py).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def row_shard(rows: int, world: int, rank: int) -> Tuple[int, int]:
+    """[begin, end) of the contiguous block of `rows` owned by `rank`; earlier ranks take the remainder."""
+    if world <= 0 or not (0 <= rank < world) or rows < 0:
+        raise ValueError("bad shard request")
+    base, rem = divmod(rows, world)
+    begin = rank * base + min(rank, rem)
+    return begin, begin + base + (1 if rank < rem else 0)
+
+
+@dataclass(frozen=True)
+class SlabPlan:
+    kind: str            # "row": A/C row slabs, B replicated; "col": B/C column slabs, A replicated; "replica"
+    world: int
+    m: int
+    n: int
+    k: int
+    local_m: int         # shape of the local GEMM
+    local_n: int
+    exchange_bytes: int  # bytes each GPU receives per GEMM
+
+    def describe(self) -> str:
+        return (f"{self.kind} slabs x{self.world}: local {self.local_m}x{self.local_n}x{self.k}, "
+                f"{self.exchange_bytes / 2**20:.0f} MiB received per GPU")
+
+
+def plan(m: int, n: int, k: int, world: int, esize: int, level: int = 1, tile_m: int = 128, tile_n: int = 256) -> SlabPlan:
+    """Choose the slab direction: the one whose replicated operand is smaller, provided the local problem still
+    splits into quadrants whose rows start on 16 bytes and is not smaller than one tile program per GPU."""
+    if world == 1:
+        return SlabPlan("row", 1, m, n, k, m, n, 0)
+    div = 1 << level
+    vec = 16 // esize
+    candidates: List[SlabPlan] = []
+    if m % world == 0 and (m // world) % div == 0 and (m // world) // div >= tile_m:
+        candidates.append(SlabPlan("row", world, m, n, k, m // world, n, (world - 1) * k * n * esize // world))
+    if n % world == 0 and (n // world) % (div * vec) == 0 and (n // world) // div >= tile_n:
+        candidates.append(SlabPlan("col", world, m, n, k, m, n // world, (world - 1) * m * k * esize // world))
+    if not candidates:
+        # slabs would be too thin to fill a GPU: run independent replicas instead (no exchange)
+        return SlabPlan("replica", world, m, n, k, m, n, 0)
+    return min(candidates, key=lambda p: p.exchange_bytes)
+
+
+def all_gather_rows(full: torch.Tensor, shard: torch.Tensor, world: int, group=None) -> None:
+    """Replicate a row-sharded matrix: `full` (rows x cols, this rank's own memory) receives every rank's `shard`.
+
+    Equal shards go through one all_gather_into_tensor (a single NCCL kernel writing straight into `full`); ragged
+    shards fall back to a list all-gather.
+    """
+    rows = full.shape[0]
+    if rows % world == 0 and shard.shape[0] == rows // world:
+        try:
+            dist.all_gather_into_tensor(full, shard, group=group)
+            return
+        except (RuntimeError, NotImplementedError):
+            pass  # backend without the fused form (older gloo): use the list form below
+    parts = []
+    for r in range(world):
+        b, e = row_shard(rows, world, r)
+        parts.append(full[b:e])
+    if all(p.shape == parts[0].shape for p in parts):
+        dist.all_gather(parts, shard, group=group)
+    else:
+        # ragged: pad to the largest shard
+        big = max(p.shape[0] for p in parts)
+        padded = torch.zeros((big,) + tuple(shard.shape[1:]), dtype=shard.dtype, device=shard.device)
+        padded[: shard.shape[0]] = shard
+        bufs = [torch.empty_like(padded) for _ in range(world)]
+        dist.all_gather(bufs, padded, group=group)
+        for p, buf in zip(parts, bufs):
+            p.copy_(buf[: p.shape[0]])
+
+
+def slab_gemm(a_slab: torch.Tensor, b_shard: torch.Tensor, k: int, world: int, rank: int,
+              local_gemm: Callable[[torch.Tensor, torch.Tensor], torch.Tensor],
+              b_full: Optional[torch.Tensor] = None, group=None) -> torch.Tensor:
+    """Row-slab plan, one step: all-gather B, then the local GEMM on this rank's rows of A.  Returns this rank's
+    rows of C.  `local_gemm` is `runner.gemm` bound to a kernel on a GPU; tests pass a CPU stand-in."""
+    n = b_shard.shape[1]
+    if b_full is None:
+        b_full = torch.empty((k, n), dtype=b_shard.dtype, device=b_shard.device)
+    if world > 1:
+        all_gather_rows(b_full, b_shard, world, group)
+    else:
+        b_full.copy_(b_shard)
+    return local_gemm(a_slab, b_full)

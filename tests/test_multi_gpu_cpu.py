@@ -1,0 +1,88 @@
+"""Host logic of the multi-GPU slab plan, run as 2 gloo ranks on CPU (no GPU, no NCCL)."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from subcuber_b200 import multi_gpu
+
+
+def test_row_shard_covers_everything():
+    for rows, world in ((8192, 8), (10, 4), (7, 2), (3, 4)):
+        spans = [multi_gpu.row_shard(rows, world, r) for r in range(world)]
+        assert spans[0][0] == 0 and spans[-1][1] == rows
+        assert all(spans[i][1] == spans[i + 1][0] for i in range(world - 1))
+        sizes = [e - b for b, e in spans]
+        assert max(sizes) - min(sizes) <= 1
+    with pytest.raises(ValueError):
+        multi_gpu.row_shard(8, 2, 2)
+
+
+def test_plan_picks_the_cheaper_direction():
+    p = multi_gpu.plan(16384, 16384, 16384, 8, esize=2, level=2)
+    assert p.kind in ("row", "col") and p.local_m * p.local_n == 16384 * 16384 // 8
+    assert p.exchange_bytes == 7 * 16384 * 16384 * 2 // 8
+    # K-heavy rectangular config: M=16384 N=8192 K=32768 -> B (1 GiB at f32) is smaller than A (2 GiB): row slabs
+    p = multi_gpu.plan(16384, 8192, 32768, 8, esize=4, level=2)
+    assert p.kind == "row" and (p.local_m, p.local_n) == (2048, 8192)
+    assert p.exchange_bytes == 7 * 32768 * 8192 * 4 // 8
+    # wide problem: A is the smaller operand -> column slabs
+    p = multi_gpu.plan(2048, 65536, 4096, 8, esize=2, level=1)
+    assert p.kind == "col" and (p.local_m, p.local_n) == (2048, 8192)
+    # too small to slab: replicas
+    assert multi_gpu.plan(512, 512, 512, 8, esize=2, level=1).kind == "replica"
+    assert multi_gpu.plan(4096, 4096, 4096, 1, esize=2).exchange_bytes == 0
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, k, n, m_per_rank, ragged, out):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        g = torch.Generator().manual_seed(7)
+        b_all = torch.randint(-3, 4, (k, n), generator=g).float()
+        a_all = torch.randint(-3, 4, (m_per_rank * world, k), generator=g).float()
+        b0, b1 = multi_gpu.row_shard(k, world, rank)
+        a_slab = a_all[rank * m_per_rank:(rank + 1) * m_per_rank].contiguous()
+        calls = []
+
+        def local_gemm(a, b):
+            calls.append((tuple(a.shape), tuple(b.shape)))
+            return a @ b
+
+        c_slab = multi_gpu.slab_gemm(a_slab, b_all[b0:b1].contiguous(), k, world, rank, local_gemm)
+        want = (a_all @ b_all)[rank * m_per_rank:(rank + 1) * m_per_rank]
+        ok = torch.equal(c_slab, want) and calls == [((m_per_rank, k), (k, n))]
+        # the gathered B must be the whole matrix on every rank
+        full = torch.empty((k, n))
+        multi_gpu.all_gather_rows(full, b_all[b0:b1].contiguous(), world)
+        ok = ok and torch.equal(full, b_all)
+        out.put((rank, bool(ok)))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("k,ragged", [(64, False), (67, True)])
+def test_slab_gemm_two_gloo_ranks(k, ragged):
+    world = 2
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, k, 24, 16, ragged, out)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    results = dict(out.get(timeout=10) for _ in range(world))
+    assert results == {0: True, 1: True}
