@@ -72,6 +72,13 @@ SB200_DECLARE_RUN(run_blackwell_f32_sw_fused_presum);
  * interleaved variants of the reference, src/cuda/kernel_runner.cpp:140-141,144-145,151-152). */
 SB200_DECLARE_RUN(run_blackwell_f16_sw_interleaved_presum);
 SB200_DECLARE_RUN(run_blackwell_f32_sw_interleaved_presum);
+/* CTA-pair variants: 256 x 256 tiles computed by two SMs with tcgen05.mma.cta_group::2 (each SM loads half of B). */
+SB200_DECLARE_RUN(run_blackwell_f16_cubic_2sm_256x256);
+SB200_DECLARE_RUN(run_blackwell_f32_cubic_2sm_256x256);
+SB200_DECLARE_RUN(run_blackwell_f16_sw_fused_presum_2sm);
+SB200_DECLARE_RUN(run_blackwell_f32_sw_fused_presum_2sm);
+SB200_DECLARE_RUN(run_blackwell_f16_sw_interleaved_presum_2sm);
+SB200_DECLARE_RUN(run_blackwell_f32_sw_interleaved_presum_2sm);
 /* cuBLAS baselines behind the same ABI (reference: src/cuda/cublas_runner.cpp:151-175); the tf32 row is
  * an addition: the reference's f32 row is CUBLAS_COMPUTE_32F_PEDANTIC (cublas_runner.cpp:14). */
 SB200_DECLARE_RUN(run_cublas_f16);

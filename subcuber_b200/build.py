@@ -64,6 +64,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
         for src in sources:
             obj = os.path.join(CSRC, src.rsplit(".", 1)[0] + ".o")
             cmd = [nvcc, *NVCC_FLAGS, "-c", os.path.join(CSRC, src), "-o", obj]
+            if os.environ.get("SB200_PROFILE"):  # tuning aid: compile the in-kernel cycle counters in
+                cmd.insert(1, "-DSB200_PROFILE")
             if verbose:
                 cmd.insert(1, "-Xptxas")
                 cmd.insert(2, "-v")

@@ -22,17 +22,24 @@ struct KernelDesc {
   DType dt;
   Variant variant;
   int bn;
+  int pair;
 };
 
 const KernelDesc kDescs[] = {
-    {"blackwell_f16_cubic_128x256", "f16", 0, sb200::kF16, sb200::kCubic, 256},
-    {"blackwell_f16_cubic_128x128", "f16", 0, sb200::kF16, sb200::kCubic, 128},
-    {"blackwell_f32_cubic_128x256", "f32", 0, sb200::kF32, sb200::kCubic, 256},
-    {"blackwell_f32_cubic_128x128", "f32", 0, sb200::kF32, sb200::kCubic, 128},
-    {"blackwell_f16_sw_fused_presum", "f16", 1, sb200::kF16, sb200::kFusedPresum, 256},
-    {"blackwell_f32_sw_fused_presum", "f32", 1, sb200::kF32, sb200::kFusedPresum, 256},
-    {"blackwell_f16_sw_interleaved_presum", "f16", 1, sb200::kF16, sb200::kInterleavedPresum, 256},
-    {"blackwell_f32_sw_interleaved_presum", "f32", 1, sb200::kF32, sb200::kInterleavedPresum, 256},
+    {"blackwell_f16_cubic_128x256", "f16", 0, sb200::kF16, sb200::kCubic, 256, 0},
+    {"blackwell_f16_cubic_128x128", "f16", 0, sb200::kF16, sb200::kCubic, 128, 0},
+    {"blackwell_f32_cubic_128x256", "f32", 0, sb200::kF32, sb200::kCubic, 256, 0},
+    {"blackwell_f32_cubic_128x128", "f32", 0, sb200::kF32, sb200::kCubic, 128, 0},
+    {"blackwell_f16_sw_fused_presum", "f16", 1, sb200::kF16, sb200::kFusedPresum, 256, 0},
+    {"blackwell_f32_sw_fused_presum", "f32", 1, sb200::kF32, sb200::kFusedPresum, 256, 0},
+    {"blackwell_f16_sw_interleaved_presum", "f16", 1, sb200::kF16, sb200::kInterleavedPresum, 256, 0},
+    {"blackwell_f32_sw_interleaved_presum", "f32", 1, sb200::kF32, sb200::kInterleavedPresum, 256, 0},
+    {"blackwell_f16_cubic_2sm_256x256", "f16", 0, sb200::kF16, sb200::kCubic, 256, 1},
+    {"blackwell_f32_cubic_2sm_256x256", "f32", 0, sb200::kF32, sb200::kCubic, 256, 1},
+    {"blackwell_f16_sw_fused_presum_2sm", "f16", 1, sb200::kF16, sb200::kFusedPresum, 256, 1},
+    {"blackwell_f32_sw_fused_presum_2sm", "f32", 1, sb200::kF32, sb200::kFusedPresum, 256, 1},
+    {"blackwell_f16_sw_interleaved_presum_2sm", "f16", 1, sb200::kF16, sb200::kInterleavedPresum, 256, 1},
+    {"blackwell_f32_sw_interleaved_presum_2sm", "f32", 1, sb200::kF32, sb200::kInterleavedPresum, 256, 1},
 };
 constexpr int kNumDescs = sizeof(kDescs) / sizeof(kDescs[0]);
 
@@ -55,6 +62,7 @@ GemmArgs make_args(const KernelDesc& d, const void* a, const void* b, void* out,
   g.b = b;
   g.d = out;
   g.bn = d.bn;
+  g.pair = d.pair;
   g.sm_limit = 0;
   return g;
 }
@@ -256,6 +264,12 @@ SB200_DEFINE_RUN(blackwell_f16_sw_fused_presum)
 SB200_DEFINE_RUN(blackwell_f32_sw_fused_presum)
 SB200_DEFINE_RUN(blackwell_f16_sw_interleaved_presum)
 SB200_DEFINE_RUN(blackwell_f32_sw_interleaved_presum)
+SB200_DEFINE_RUN(blackwell_f16_cubic_2sm_256x256)
+SB200_DEFINE_RUN(blackwell_f32_cubic_2sm_256x256)
+SB200_DEFINE_RUN(blackwell_f16_sw_fused_presum_2sm)
+SB200_DEFINE_RUN(blackwell_f32_sw_fused_presum_2sm)
+SB200_DEFINE_RUN(blackwell_f16_sw_interleaved_presum_2sm)
+SB200_DEFINE_RUN(blackwell_f32_sw_interleaved_presum_2sm)
 
 #define SB200_DEFINE_BLAS(fn, impl, type)                                                                      \
   extern "C" int fn(KernelRunnerBuffers buffers, int m, int n, int k, int warmup_iterations, int iterations,   \
@@ -286,6 +300,12 @@ static const sb200_kernel_entry kRegistry[] = {
     {"blackwell_f32_sw_fused_presum", "blackwell", "f32", 1, run_blackwell_f32_sw_fused_presum},
     {"blackwell_f16_sw_interleaved_presum", "blackwell", "f16", 1, run_blackwell_f16_sw_interleaved_presum},
     {"blackwell_f32_sw_interleaved_presum", "blackwell", "f32", 1, run_blackwell_f32_sw_interleaved_presum},
+    {"blackwell_f16_cubic_2sm_256x256", "blackwell", "f16", 0, run_blackwell_f16_cubic_2sm_256x256},
+    {"blackwell_f32_cubic_2sm_256x256", "blackwell", "f32", 0, run_blackwell_f32_cubic_2sm_256x256},
+    {"blackwell_f16_sw_fused_presum_2sm", "blackwell", "f16", 1, run_blackwell_f16_sw_fused_presum_2sm},
+    {"blackwell_f32_sw_fused_presum_2sm", "blackwell", "f32", 1, run_blackwell_f32_sw_fused_presum_2sm},
+    {"blackwell_f16_sw_interleaved_presum_2sm", "blackwell", "f16", 1, run_blackwell_f16_sw_interleaved_presum_2sm},
+    {"blackwell_f32_sw_interleaved_presum_2sm", "blackwell", "f32", 1, run_blackwell_f32_sw_interleaved_presum_2sm},
 };
 
 extern "C" int sb200_num_kernels(void) { return static_cast<int>(sizeof(kRegistry) / sizeof(kRegistry[0])); }

@@ -3,10 +3,12 @@
 
 #include <cuda.h>
 #include <stdint.h>
+#include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
 
 #include "sw_kernel.cuh"
+#include "sw_kernel_pair.cuh"
 #include "sw_programs.h"
 
 namespace sb200 {
@@ -63,7 +65,7 @@ Layout make_layout(const GemmArgs& a) {
   L.mq = a.m / div;
   L.nq = a.n / div;
   L.kq = a.k / div;
-  L.tiles_m = ceil_div(L.mq, 128);
+  L.tiles_m = ceil_div(L.mq, a.pair ? 256 : 128);
   L.tiles_n = ceil_div(L.nq, L.bn);
   L.num_k = ceil_div(L.kq, 128 / L.esize);
   size_t off = 0;
@@ -79,7 +81,7 @@ Layout make_layout(const GemmArgs& a) {
   size_t tile_bytes = size_t(128) * L.bn * sizeof(float);
   for (int i = 0; i < nws; ++i) {
     L.off_ws[i] = off;
-    off = align_up(off + size_t(L.tiles_m) * L.tiles_n * tile_bytes, 256);
+    off = align_up(off + size_t(L.tiles_m) * L.tiles_n * (a.pair ? 2 : 1) * tile_bytes, 256);
   }
   L.total = off;
   return L;
@@ -109,12 +111,53 @@ int launch_mode(int mode, const KernelParams& p, int grid, cudaStream_t stream) 
   return kErrInternal;
 }
 
+int launch_any(int esize, int bn, int mode, const KernelParams& p, int grid, cudaStream_t stream);
+int launch_any_pair(int esize, int mode, const KernelParams& p, int pairs, cudaStream_t stream);
+
 int launch_any(int esize, int bn, int mode, const KernelParams& p, int grid, cudaStream_t stream) {
+  if (bn < 0) return launch_any_pair(esize, mode, p, grid, stream);
   if (esize == 2 && bn == 256) return launch_mode<2, 256>(mode, p, grid, stream);
   if (esize == 2 && bn == 128) return launch_mode<2, 128>(mode, p, grid, stream);
   if (esize == 4 && bn == 256) return launch_mode<4, 256>(mode, p, grid, stream);
   if (esize == 4 && bn == 128) return launch_mode<4, 128>(mode, p, grid, stream);
   return kErrNotSupported;
+}
+
+template <typename Cfg>
+int launch_pair(const KernelParams& p, int pairs, cudaStream_t stream) {
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(sw_tile_program_pair_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr_done = true;
+  }
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(2 * pairs, 1, 1);
+  cfg.blockDim = dim3(Cfg::THREADS, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return static_cast<int>(cudaLaunchKernelEx(&cfg, sw_tile_program_pair_kernel<Cfg>, p));
+}
+
+template <int ESIZE>
+int launch_pair_mode(int mode, const KernelParams& p, int pairs, cudaStream_t stream) {
+  constexpr int STAGES = 6;
+  if (mode == kPresumNone && getenv("SB200_STAGES7")) return launch_pair<PairConfig<ESIZE, 7, kPresumNone>>(p, pairs, stream);
+  switch (mode) {
+    case kPresumNone: return launch_pair<PairConfig<ESIZE, STAGES, kPresumNone>>(p, pairs, stream);
+    case kPresumFeed: return launch_pair<PairConfig<ESIZE, STAGES, kPresumFeed>>(p, pairs, stream);
+    case kPresumJob: return launch_pair<PairConfig<ESIZE, STAGES, kPresumJob>>(p, pairs, stream);
+  }
+  return kErrInternal;
 }
 
 int sm_count() {
@@ -127,12 +170,19 @@ int sm_count() {
   return n;
 }
 
+int launch_any_pair(int esize, int mode, const KernelParams& p, int pairs, cudaStream_t stream) {
+  if (esize == 2) return launch_pair_mode<2>(mode, p, pairs, stream);
+  if (esize == 4) return launch_pair_mode<4>(mode, p, pairs, stream);
+  return kErrNotSupported;
+}
+
 }  // namespace
 
 int can_implement(const GemmArgs& a) {
   if (a.m <= 0 || a.n <= 0 || a.k <= 0 || !a.a || !a.b || !a.d) return kErrInvalidProblem;
   if (a.dtype != kF16 && a.dtype != kF32) return kErrNotSupported;
   if (a.bn != 0 && a.bn != 128 && a.bn != 256) return kErrNotSupported;
+  if (a.pair && a.bn == 128) return kErrNotSupported;
   const int es = esize_of(a.dtype);
   const int vec = 16 / es;  // elements per 16 bytes
   const int div = a.variant == kCubic ? 1 : 2;
@@ -215,6 +265,30 @@ int run(const GemmArgs& a, void* workspace, size_t workspace_size, cudaStream_t 
   p.tiles_n = L.tiles_n;
   p.num_k = L.num_k;
   p.band = 8;
+  if (getenv("SB200_PROF")) {
+    // measurement aid: per-CTA cycle counters of the CTA-pair kernels, printed by the next call
+    static long long* prof_dev = nullptr;
+    static long long prof_host[8 * 256];
+    if (!prof_dev) {
+      cudaMalloc(&prof_dev, sizeof(prof_host));
+    } else {
+      cudaDeviceSynchronize();
+      cudaMemcpy(prof_host, prof_dev, sizeof(prof_host), cudaMemcpyDeviceToHost);
+      double sum[8] = {0};
+      int n = 0;
+      for (int c = 0; c < 148; c += 2, ++n)
+        for (int i = 0; i < 8; ++i) sum[i] += double(prof_host[c * 8 + i]);
+      double psum3 = 0, psum4 = 0, e5 = 0, e6 = 0;
+      for (int c = 1; c < 148; c += 2) { psum3 += double(prof_host[c * 8 + 3]); psum4 += double(prof_host[c * 8 + 4]); e5 += double(prof_host[c * 8 + 5]); e6 += double(prof_host[c * 8 + 6]); }
+      fprintf(stderr, "[prof] leader mma thread: total %.0f = wait_full %.0f + wait_free %.0f + issue %.0f + commit %.0f + rest | producer A: wait_empty %.0f issue %.0f total %.0f\n",
+              sum[0] / n, sum[1] / n, sum[2] / n, sum[5] / n, sum[6] / n, sum[3] / n, sum[7] / n, sum[4] / n);
+      (void)psum3; (void)psum4; (void)e5; (void)e6;
+    }
+    cudaMemset(prof_dev, 0, sizeof(prof_host));
+    p.prof = prof_dev;
+  }
+  if (const char* pf = getenv("SB200_PREFETCH")) p.prefetch_dist = atoi(pf);
+  if (const char* bd = getenv("SB200_BAND")) p.band = atoi(bd) > 0 ? atoi(bd) : 8;
   if (const char* dbg = getenv("SB200_DEBUG_FLAGS")) p.debug_flags = atoi(dbg);
   p.job_pa = wsb + L.off_pa;
   p.job_pb = wsb + L.off_pb;
@@ -224,7 +298,9 @@ int run(const GemmArgs& a, void* workspace, size_t workspace_size, cudaStream_t 
 
   int grid = L.tiles_m * L.tiles_n;
   int cap = a.sm_limit > 0 ? a.sm_limit : sm_count();
+  if (a.pair) cap /= 2;  // one pair per two SMs
   if (grid > cap) grid = cap;
+  const int bn_sel = a.pair ? -1 : L.bn;  // -1 routes launch_any to the CTA-pair kernels (grid = pairs)
 
   int nev = 0;
   auto mark = [&]() -> int {
@@ -235,19 +311,19 @@ int run(const GemmArgs& a, void* workspace, size_t workspace_size, cudaStream_t 
   switch (a.variant) {
     case kCubic:
       p.prog = programs::level0();
-      rc = launch_any(es, L.bn, kPresumNone, p, grid, stream);
+      rc = launch_any(es, bn_sel, kPresumNone, p, grid, stream);
       break;
     case kFusedPresum:
       p.prog = programs::level1_full(true);
-      rc = launch_any(es, L.bn, kPresumFeed, p, grid, stream);
+      rc = launch_any(es, bn_sel, kPresumFeed, p, grid, stream);
       break;
     case kInterleavedPresum:
       p.prog = programs::level1_first();
-      rc = launch_any(es, L.bn, kPresumJob, p, grid, stream);
+      rc = launch_any(es, bn_sel, kPresumJob, p, grid, stream);
       if (rc) return rc;
       if ((rc = mark())) return rc;
       p.prog = programs::level1_second();
-      rc = launch_any(es, L.bn, kPresumNone, p, grid, stream);
+      rc = launch_any(es, bn_sel, kPresumNone, p, grid, stream);
       break;
     default:
       return kErrNotSupported;

@@ -36,6 +36,7 @@ struct GemmArgs {
   const void* b;  // k x n row-major, ldb = n
   void* d;        // m x n row-major, ldd = n;  D = A * B
   int bn;         // tile width: 256 (default when 0) or 128
+  int pair;       // 1: CTA-pair kernels (256 x 256 tiles on two SMs, cta_group::2); requires bn == 256
   int sm_limit;   // CTAs to launch at most (0: one per SM of the current device)
   cudaEvent_t* events;  // optional: launches_per_run()+1 events, recorded before the first and after each launch
 };

@@ -26,6 +26,7 @@
 #pragma once
 #include "ptx.cuh"
 #include "tile_program.h"
+#include "epilogue.cuh"
 
 namespace sb200 {
 
@@ -59,6 +60,8 @@ struct KernelParams {
   int band;                 // raster band height in tiles
   int* status;              // device status word, 0 = ok
   int debug_flags;          // measurement aids: bit 0 = issue no MMA, bit 1 = issue no TMA load (results are garbage)
+  int prefetch_dist;        // > 0: the producer asks L2 for the operand tiles this many k-steps ahead
+  long long* prof;          // measurement aid (CTA-pair kernels): 8 cycle counters per CTA, or null
   // presum job (mode JOB): pa = S1,S2,A02,A1S2 packed [4][mq][kq]; pb = B10,B31,S3,S3B2 packed [4][kq][nq]
   void* job_pa;
   void* job_pb;
@@ -86,7 +89,7 @@ struct KernelConfig {
   static constexpr int PRESUM_WARPS = (MODE == kPresumNone) ? 0 : 4;
   static constexpr int THREADS = (6 + PRESUM_WARPS) * 32;
   static constexpr int BAR_BYTES = 1024;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // +1024: manual alignment slack
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + kStagingBytes + 1024;  // +1024: manual alignment slack
   static constexpr uint32_t FMT = (ESIZE == 2) ? 0u : 2u;
   // B tile (N contiguous): 16-bit elements use the plain 128-byte swizzle with 8-row groups; 32-bit elements
   // must use the 128-byte swizzle with 32-byte atoms, whose pattern repeats every 4 rows.
@@ -301,6 +304,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_kernel(const 
   uint64_t* slot_free = slot_full + SLOTS;
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(slot_free + SLOTS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  const uint32_t staging = ptx::smem_u32(bar_base + Cfg::BAR_BYTES);  // epilogue staging rows (epilogue.cuh)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -422,7 +426,6 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_kernel(const 
   } else if (warp < 6) {
     // ------------------------------------------------------------------ epilogue warps
     const int quarter = warp & 3;            // TMEM lane quarter this warp may read
-    const int row = quarter * 32 + lane;     // row of the tile owned by this thread
     uint32_t full_bits = 0;
     uint32_t iter = 0;
     bool ok = true;
@@ -447,74 +450,9 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_kernel(const 
         if (!ok) break;
         ptx::tc_fence_after_sync();
         const long long tile_off = static_cast<long long>(tile.id) * (128 * BN);
-        const int grow = tile.i * 128 + row;
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t r[SB200_MAX_SLOT_TERMS][32];
-#pragma unroll
-          for (int t = 0; t < SB200_MAX_SLOT_TERMS; ++t) {
-            if (t < ep.nslots) {
-              const uint32_t slot = ep.slot[t] ^ sx;
-              ptx::tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + slot * BN + c * 32, r[t]);
-            }
-          }
-          float acc[32];
-          // fp32 workspace sources first (their latency overlaps the TMEM loads)
-#pragma unroll
-          for (int q = 0; q < 32; ++q) acc[q] = 0.f;
-          for (int t = 0; t < ep.nsrc; ++t) {
-            const float4* src = reinterpret_cast<const float4*>(p.ws[ep.src[t]] + tile_off + (c * 128 + row) * 32);
-#pragma unroll
-            for (int q = 0; q < 8; ++q) {
-              float4 f = src[q];
-              acc[4 * q + 0] += f.x;
-              acc[4 * q + 1] += f.y;
-              acc[4 * q + 2] += f.z;
-              acc[4 * q + 3] += f.w;
-            }
-          }
-          ptx::tmem_ld_wait();
-#pragma unroll
-          for (int t = 0; t < SB200_MAX_SLOT_TERMS; ++t) {
-            if (t < ep.nslots) {
-              if (ep.slot_sign[t] > 0) {
-#pragma unroll
-                for (int q = 0; q < 32; ++q) acc[q] += __uint_as_float(r[t][q]);
-              } else {
-#pragma unroll
-                for (int q = 0; q < 32; ++q) acc[q] -= __uint_as_float(r[t][q]);
-              }
-            }
-          }
-          if (ep.dst_kind == 1) {
-            float4* dst = reinterpret_cast<float4*>(p.ws[ep.dst] + tile_off + (c * 128 + row) * 32);
-#pragma unroll
-            for (int q = 0; q < 8; ++q) dst[q] = make_float4(acc[4 * q], acc[4 * q + 1], acc[4 * q + 2], acc[4 * q + 3]);
-          } else if (grow < p.out_rows) {
-            const int gcol = tile.j * BN + c * 32;
-            char* dst = static_cast<char*>(p.out[ep.dst]) + (static_cast<long long>(grow) * p.ldo + gcol) * ESIZE;
-            if (ESIZE == 2) {
-#pragma unroll
-              for (int g = 0; g < 4; ++g) {
-                if (gcol + g * 8 < p.out_cols) {
-                  uint4 o;
-                  __half2* h = reinterpret_cast<__half2*>(&o);
-#pragma unroll
-                  for (int q = 0; q < 4; ++q) h[q] = __floats2half2_rn(acc[g * 8 + 2 * q], acc[g * 8 + 2 * q + 1]);
-                  *reinterpret_cast<uint4*>(dst + g * 16) = o;
-                }
-              }
-            } else {
-#pragma unroll
-              for (int g = 0; g < 8; ++g) {
-                if (gcol + g * 4 < p.out_cols) {
-                  *reinterpret_cast<float4*>(dst + g * 16) =
-                      make_float4(acc[g * 4], acc[g * 4 + 1], acc[g * 4 + 2], acc[g * 4 + 3]);
-                }
-              }
-            }
-          }
-        }
+        if (!(p.debug_flags & 32))  // bit 5: measurement aid, skip the epilogue body
+          epilogue_body<ESIZE, BN>(p.out, p.ldo, p.out_rows, p.out_cols, p.ws, ep, sx, tmem_base, quarter, lane, tile_off,
+                                   tile.i * 128, tile.j * BN, staging + (warp - 2) * kStagingWarpBytes);
         ptx::tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) {

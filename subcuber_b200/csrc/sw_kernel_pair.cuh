@@ -1,0 +1,351 @@
+// CTA-pair variant of the tile-program kernel: two CTAs of a 2-CTA cluster (two SMs) compute one 256 x 256 output
+// tile with `tcgen05.mma.cta_group::2`.  Each CTA keeps its own 128 rows of A and its own 128 columns of B in
+// shared memory and its own 128 rows of every accumulator in tensor memory; the tensor cores of both SMs read
+// both halves of B.  Per MMA step a CTA therefore loads 32 KiB instead of 48 KiB (B traffic per SM halves), which
+// is the sm_100 replacement for cluster-multicast loads and needs none: every TMA load here is a plain tiled load
+// into the issuing CTA's own shared memory.
+//
+// Roles are those of sw_kernel.cuh, with these pair rules:
+//   * both CTAs run a TMA producer for their own halves; the bytes of both are reported to the LEADER's (cluster
+//     rank 0) full barrier, which the leader's producer arms with the pair's total;
+//   * only the leader issues MMAs; its commits arrive on the stage-empty and slot-full barriers of BOTH CTAs;
+//   * both CTAs run epilogue warps on their own TMEM half and return slot credits to the leader's slot-free barrier;
+//   * in FEED mode the presum warps of both CTAs write their own shared memory and arrive on the leader's barrier.
+#pragma once
+#include "sw_kernel.cuh"
+
+// Cycle counters for tuning are compiled in only with -DSB200_PROFILE; otherwise they cost nothing.
+#ifdef SB200_PROFILE
+#define SB200_CLOCK() clock64()
+#else
+#define SB200_CLOCK() 0ll
+#endif
+
+namespace sb200 {
+
+template <int ESIZE_, int STAGES_, int MODE_>
+struct PairConfig {
+  static constexpr int ESIZE = ESIZE_;
+  static constexpr int BM = 128;                  // rows per CTA
+  static constexpr int PAIR_M = 256;              // rows per pair tile
+  static constexpr int BN = 256;                  // columns per pair tile = accumulator columns per CTA
+  static constexpr int BN_CTA = 128;              // columns of B held by each CTA
+  static constexpr int BK = 128 / ESIZE;
+  static constexpr int STAGES = STAGES_;
+  static constexpr int MODE = MODE_;
+  static constexpr int UMMA_K = 32 / ESIZE;
+  static constexpr int KSUB = BK / UMMA_K;
+  static constexpr int A_BYTES = BM * 128;
+  static constexpr int NBLK = BN_CTA * ESIZE / 128;
+  static constexpr int BLK_BYTES = BK * 128;
+  static constexpr int B_BYTES = NBLK * BLK_BYTES;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int SLOTS = 2;
+  static constexpr int TMEM_COLS = 512;
+  static constexpr int PRESUM_WARPS = (MODE == kPresumNone) ? 0 : 4;
+  static constexpr int THREADS = (7 + PRESUM_WARPS) * 32;  // warps 0-5 as in sw_kernel.cuh, warp 6 = B producer
+  static constexpr int BAR_BYTES = 1024;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + kStagingBytes + 1024;
+  static constexpr uint32_t FMT = (ESIZE == 2) ? 0u : 2u;
+  static constexpr bool B_SWZ32 = (ESIZE == 4);
+  static constexpr uint32_t B_LAYOUT_TYPE = B_SWZ32 ? 1u : 2u;
+  static constexpr uint32_t B_SBO = B_SWZ32 ? 512u : 1024u;
+};
+
+template <typename Cfg>
+__global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(const __grid_constant__ KernelParams p) {
+  constexpr int ESIZE = Cfg::ESIZE;
+  constexpr int BN = Cfg::BN;
+  constexpr int BK = Cfg::BK;
+  constexpr int STAGES = Cfg::STAGES;
+  constexpr int SLOTS = Cfg::SLOTS;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* bar_base = smem + STAGES * Cfg::STAGE_BYTES;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(bar_base);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* slot_full = empty_bar + STAGES;
+  uint64_t* slot_free = slot_full + SLOTS;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(slot_free + SLOTS);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  const uint32_t staging = ptx::smem_u32(bar_base + Cfg::BAR_BYTES);  // epilogue staging rows (epilogue.cuh)
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = ptx::cluster_ctarank();   // 0 = leader
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+  const int total_tiles = p.tiles_m * p.tiles_n;  // pair tiles
+  const int nproducts = p.prog.nproducts;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      // leader's full barrier: its own producer + (FEED) the presum warps of both CTAs
+      ptx::mbar_init(&full_bar[s], 1 + (Cfg::MODE == kPresumFeed ? 2 * Cfg::PRESUM_WARPS : 0));
+      ptx::mbar_init(&empty_bar[s], 1);
+    }
+    for (int s = 0; s < SLOTS; ++s) {
+      ptx::mbar_init(&slot_full[s], 1);
+      ptx::mbar_init(&slot_free[s], 8);  // 4 epilogue warps of each CTA
+    }
+    ptx::fence_mbar_init();
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc_pair(tmem_holder, Cfg::TMEM_COLS);
+    ptx::tmem_relinquish_pair();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::cluster_sync_all();  // both CTAs' barriers are initialised before anyone signals across the pair
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0 || warp == 6) {
+    // ------------------------------------------------------------------ TMA producers (both CTAs)
+    // Two single-thread producers share the work so that neither's instruction stream limits the load rate:
+    // warp 0 loads the A tiles and (leader only) arms the full barrier with the pair's byte total,
+    // warp 6 loads the B tiles.  Both wait on the same stage-empty barrier.
+    if (lane == 0) {
+      const bool is_a = (warp == 0);
+      if (is_a)
+        for (int v = 0; v < SB200_NUM_VIEWS; ++v) ptx::prefetch_tmap(&p.tmap[v]);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      const long long pt0 = SB200_CLOCK();
+      long long pw_empty = 0, pw_issue = 0;
+      for (int w = pair; ok && w < total_tiles; w += num_pairs) {
+        const TileCoord tile = tile_of(w, p.tiles_m, p.tiles_n, p.band);
+        const int row0 = tile.i * Cfg::PAIR_M + static_cast<int>(rank) * Cfg::BM;
+        const int col0 = tile.j * BN + static_cast<int>(rank) * Cfg::BN_CTA;
+        for (int ps = 0; ok && ps < nproducts; ++ps) {
+          const sb200_product_t& pr = p.prog.product[ps];
+          const bool a_tma = pr.a.nterms == 1;
+          const bool b_tma = pr.b.nterms == 1;
+          const uint32_t tx = 2u * ((a_tma ? Cfg::A_BYTES : 0) + (b_tma ? Cfg::B_BYTES : 0));  // both CTAs' bytes
+          const CUtensorMap* ma = &p.tmap[pr.a.view[0]];
+          const CUtensorMap* mb = &p.tmap[pr.b.view[0]];
+          const bool no_load_all = (p.debug_flags & 2) != 0;
+          for (int kk = 0; kk < p.num_k; ++kk) {
+            const long long tw = SB200_CLOCK();
+            if (!ptx::mbar_wait_cluster(&empty_bar[stage], phase ^ 1u, abort_flag)) {
+              raise_abort(p, abort_flag, kStatusProducerTimeout);
+              ok = false;
+              break;
+            }
+            const long long tw2 = SB200_CLOCK();
+            pw_empty += tw2 - tw;
+            uint8_t* sa = smem + stage * Cfg::STAGE_BYTES;
+            uint8_t* sb = sa + Cfg::A_BYTES;
+            // measurement aids: bit 1 = never load; bit 3 = load only while the ring fills for the first time
+            const bool no_load = no_load_all || ((p.debug_flags & 8) != 0 && (w != pair || ps > 0 || kk >= STAGES));
+            if (is_a) {
+              if (rank == 0) {
+                if (tx && !no_load) ptx::mbar_arrive_expect_tx(&full_bar[stage], tx);
+                else ptx::mbar_arrive(&full_bar[stage]);
+              }
+              if (a_tma && !no_load) ptx::tma_load_2d_pair(sa, ma, &full_bar[stage], kk * BK, row0);
+            } else if (b_tma && !no_load) {
+#pragma unroll
+              for (int nb = 0; nb < Cfg::NBLK; ++nb)
+                ptx::tma_load_2d_pair(sb + nb * Cfg::BLK_BYTES, mb, &full_bar[stage], col0 + nb * BK, kk * BK);
+            }
+            pw_issue += SB200_CLOCK() - tw2;
+            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          }
+        }
+      }
+      if (p.prof && is_a) {
+        p.prof[blockIdx.x * 8 + 7] = pw_issue;
+        p.prof[blockIdx.x * 8 + 3] = pw_empty;
+        p.prof[blockIdx.x * 8 + 4] = SB200_CLOCK() - pt0;
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (lane == 0 && rank == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t free_bits = 0;
+      uint32_t iter = 0;
+      bool ok = true;
+      const long long mt0 = SB200_CLOCK();
+      long long mw_full = 0, mw_free = 0, mw_issue = 0;
+      const long long mw_commit = 0;
+      for (int w = pair; ok && w < total_tiles; w += num_pairs, ++iter) {
+        const uint32_t sx = p.prog.alternate_slots ? (iter & 1u) : 0u;
+        for (int ps = 0; ok && ps < nproducts; ++ps) {
+          const sb200_product_t& pr = p.prog.product[ps];
+          const uint32_t slot = pr.slot ^ sx;
+          if (pr.wait_free) {
+            const long long tw = SB200_CLOCK();
+            if (!ptx::mbar_wait_cluster(&slot_free[slot], ((free_bits >> slot) & 1u) ^ 1u, abort_flag)) {
+              raise_abort(p, abort_flag, kStatusMmaTimeout);
+              ok = false;
+              break;
+            }
+            mw_free += SB200_CLOCK() - tw;
+            free_bits ^= (1u << slot);
+            ptx::tc_fence_after_sync();
+          }
+          const uint32_t idesc = ptx::umma_idesc(Cfg::FMT, Cfg::PAIR_M, BN, pr.negate != 0);
+          const uint32_t tmem_d = tmem_base + slot * BN;
+          const bool skip_mma = (p.debug_flags & 1) != 0;
+          // descriptors differ between stages and k-substeps only in the start-address field (low word, 16-byte units)
+          const uint64_t adesc0 = ptx::umma_desc_sw128(ptx::smem_u32(smem), 16, 1024);
+          const uint64_t bdesc0 =
+              ptx::umma_desc_sw128(ptx::smem_u32(smem) + Cfg::A_BYTES, Cfg::BLK_BYTES, Cfg::B_SBO, Cfg::B_LAYOUT_TYPE);
+          // k-steps are taken two at a time: both full-barrier waits first, then 4 MMAs + stage release for each.
+          // (Measured on B200: with one wait per 4 MMAs the tensor pipe idles ~48 cycles per k-step; with the
+          // waits of two k-steps issued back to back ahead of their 8 MMAs it does not.)
+          for (int kk = 0; kk < p.num_k; kk += 2) {
+            const int group = (kk + 1 < p.num_k) ? 2 : 1;
+            int s_w = stage;
+            uint32_t ph_w = phase;
+            const long long tw = SB200_CLOCK();
+            for (int g = 0; g < group; ++g) {
+              if (!ptx::mbar_wait_cluster(&full_bar[s_w], ph_w, abort_flag)) {
+                raise_abort(p, abort_flag, kStatusMmaTimeout);
+                ok = false;
+                break;
+              }
+              if (++s_w == STAGES) { s_w = 0; ph_w ^= 1u; }
+            }
+            if (!ok) break;
+            mw_full += SB200_CLOCK() - tw;
+            const long long ti0 = SB200_CLOCK();
+            for (int g = 0; g < group; ++g) {
+              const uint64_t adesc_s = adesc0 + static_cast<uint64_t>((stage * Cfg::STAGE_BYTES) >> 4);
+              const uint64_t bdesc_s = bdesc0 + static_cast<uint64_t>((stage * Cfg::STAGE_BYTES) >> 4);
+              if (!skip_mma) {
+#pragma unroll
+                for (int ks = 0; ks < Cfg::KSUB; ++ks) {
+                  const uint64_t adesc = adesc_s + static_cast<uint64_t>((ks * 32) >> 4);
+                  const uint64_t bdesc = bdesc_s + static_cast<uint64_t>((ks * Cfg::UMMA_K * 128) >> 4);
+                  const uint32_t acc = (kk + g > 0 || ks > 0 || pr.accumulate) ? 1u : 0u;
+                  if (ESIZE == 2) ptx::umma_f16_pair(tmem_d, adesc, bdesc, idesc, acc);
+                  else ptx::umma_tf32_pair(tmem_d, adesc, bdesc, idesc, acc);
+                }
+              }
+              ptx::umma_commit_pair(&empty_bar[stage], 3);
+              if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            }
+            mw_issue += SB200_CLOCK() - ti0;
+          }
+          if (ok && pr.commit) ptx::umma_commit_pair(&slot_full[slot], 3);
+        }
+      }
+      if (p.prof) {
+        p.prof[blockIdx.x * 8 + 0] = SB200_CLOCK() - mt0;
+        p.prof[blockIdx.x * 8 + 1] = mw_full;
+        p.prof[blockIdx.x * 8 + 2] = mw_free;
+        p.prof[blockIdx.x * 8 + 5] = mw_issue;
+        p.prof[blockIdx.x * 8 + 6] = mw_commit;
+      }
+    }
+  } else if (warp < 6) {
+    // ------------------------------------------------------------------ epilogue warps (both CTAs, own TMEM half)
+    const int quarter = warp & 3;
+    uint32_t full_bits = 0;
+    uint32_t iter = 0;
+    bool ok = true;
+    const long long et0 = SB200_CLOCK();
+    long long ew_full = 0;
+    for (int w = pair; ok && w < total_tiles; w += num_pairs, ++iter) {
+      const TileCoord tile = tile_of(w, p.tiles_m, p.tiles_n, p.band);
+      const uint32_t sx = p.prog.alternate_slots ? (iter & 1u) : 0u;
+      for (int es = 0; ok && es < p.prog.nepilogues; ++es) {
+        const sb200_epilogue_t& ep = p.prog.epilogue[es];
+        for (int s0 = 0; s0 < SLOTS; ++s0) {
+          if ((ep.wait_full_mask >> s0) & 1u) {
+            const uint32_t s = s0 ^ sx;
+            const long long tw = SB200_CLOCK();
+            bool got = ptx::mbar_wait_cluster(&slot_full[s], (full_bits >> s) & 1u, abort_flag);
+            ew_full += SB200_CLOCK() - tw;
+            got = __all_sync(0xffffffffu, got);
+            if (!got) {
+              if (lane == 0) raise_abort(p, abort_flag, kStatusEpilogueTimeout);
+              ok = false;
+              break;
+            }
+            full_bits ^= (1u << s);
+          }
+        }
+        if (!ok) break;
+        ptx::tc_fence_after_sync();
+        const long long tile_off = (static_cast<long long>(tile.id) * 2 + rank) * (128 * BN);
+        if (!(p.debug_flags & 32))  // bit 5: measurement aid, skip the epilogue body
+          epilogue_body<ESIZE, BN>(p.out, p.ldo, p.out_rows, p.out_cols, p.ws, ep, sx, tmem_base, quarter, lane, tile_off,
+                                   tile.i * Cfg::PAIR_M + static_cast<int>(rank) * Cfg::BM, tile.j * BN, staging + (warp - 2) * kStagingWarpBytes);
+        ptx::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) {
+          for (int s = 0; s < SLOTS; ++s)
+            if ((ep.release_mask >> s) & 1u) ptx::mbar_arrive_cluster(&slot_free[s ^ sx], 0);
+        }
+      }
+    }
+    (void)ew_full;
+    (void)et0;
+  } else if (warp >= 7) {
+    // ------------------------------------------------------------------ presum warps (both CTAs)
+    if (Cfg::MODE == kPresumFeed) {
+      const int ptid = threadIdx.x - 7 * 32;
+      constexpr int PT = Cfg::PRESUM_WARPS * 32;
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int w = pair; ok && w < total_tiles; w += num_pairs) {
+        const TileCoord tile = tile_of(w, p.tiles_m, p.tiles_n, p.band);
+        const int row0 = tile.i * Cfg::PAIR_M + static_cast<int>(rank) * Cfg::BM;
+        const int col0 = tile.j * BN + static_cast<int>(rank) * Cfg::BN_CTA;
+        for (int ps = 0; ok && ps < nproducts; ++ps) {
+          const sb200_product_t& pr = p.prog.product[ps];
+          const bool a_mt = pr.a.nterms > 1;
+          const bool b_mt = pr.b.nterms > 1;
+          for (int kk = 0; kk < p.num_k; ++kk) {
+            bool got = ptx::mbar_wait_cluster(&empty_bar[stage], phase ^ 1u, abort_flag);
+            got = __all_sync(0xffffffffu, got);
+            if (!got) {
+              if (lane == 0) raise_abort(p, abort_flag, kStatusPresumTimeout);
+              ok = false;
+              break;
+            }
+            const uint32_t sa = ptx::smem_u32(smem + stage * Cfg::STAGE_BYTES);
+            const uint32_t sb = sa + Cfg::A_BYTES;
+            if (a_mt) build_operand_tile<ESIZE, Cfg::BM, 8, PT, false>(sa, 0u, pr.a, p.view, row0, kk * BK, ptid);
+            if (b_mt)
+              build_operand_tile<ESIZE, BK, Cfg::BN_CTA * ESIZE / 16, PT, Cfg::B_SWZ32>(sb, Cfg::BLK_BYTES, pr.b, p.view,
+                                                                                        kk * BK, col0, ptid);
+            if (a_mt || b_mt) ptx::fence_proxy_async_all();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive_cluster(&full_bar[stage], 0);
+            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          }
+        }
+      }
+    } else if (Cfg::MODE == kPresumJob) {
+      const int ptid = threadIdx.x - 7 * 32;
+      constexpr int PT = Cfg::PRESUM_WARPS * 32;
+      presum_job<ESIZE>(p, blockIdx.x * PT + ptid, gridDim.x * PT);
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    uint64_t t0 = ptx::globaltimer_ns();
+    while (ptx::globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+  }
+  // neither CTA may leave (and release its shared memory and barriers) while its peer can still signal into it
+  ptx::cluster_sync_all();
+  if (warp == 1) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc_pair(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+}  // namespace sb200
