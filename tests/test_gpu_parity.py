@@ -14,10 +14,12 @@ import pytest
 
 pytestmark = pytest.mark.gpu
 
-L1_F16 = ["blackwell_f16_sw_interleaved_presum", "blackwell_f16_sw_fused_presum"]
-L1_F32 = ["blackwell_f32_sw_interleaved_presum", "blackwell_f32_sw_fused_presum"]
-L0_F16 = ["blackwell_f16_cubic_128x256", "blackwell_f16_cubic_128x128"]
-L0_F32 = ["blackwell_f32_cubic_128x256", "blackwell_f32_cubic_128x128"]
+L1_F16 = ["blackwell_f16_sw_interleaved_presum", "blackwell_f16_sw_fused_presum",
+          "blackwell_f16_sw_interleaved_presum_2sm", "blackwell_f16_sw_fused_presum_2sm"]
+L1_F32 = ["blackwell_f32_sw_interleaved_presum", "blackwell_f32_sw_fused_presum",
+          "blackwell_f32_sw_interleaved_presum_2sm", "blackwell_f32_sw_fused_presum_2sm"]
+L0_F16 = ["blackwell_f16_cubic_128x256", "blackwell_f16_cubic_128x128", "blackwell_f16_cubic_2sm_256x256"]
+L0_F32 = ["blackwell_f32_cubic_128x256", "blackwell_f32_cubic_128x128", "blackwell_f32_cubic_2sm_256x256"]
 
 
 def _dt(kernel):
@@ -87,7 +89,8 @@ def test_bit_exact_on_harness_values_reference_shapes(kernel, shape, oracle, cud
 
 
 # ------------------------------------------------------------------------------------- presum workspace
-@pytest.mark.parametrize("kernel", ["blackwell_f16_sw_interleaved_presum", "blackwell_f32_sw_interleaved_presum"])
+@pytest.mark.parametrize("kernel", ["blackwell_f16_sw_interleaved_presum", "blackwell_f32_sw_interleaved_presum",
+                                    "blackwell_f16_sw_interleaved_presum_2sm"])
 @pytest.mark.parametrize("shape", [(256, 512, 128), (272, 528, 144), (1024, 768, 512)])
 def test_presum_workspace_bit_exact(kernel, shape, oracle, lib, cuda_device):
     """The eight presums the first launch materialises equal the oracle's, bit for bit, on uniform inputs."""
@@ -166,6 +169,7 @@ def test_uniform_inputs_tf32(kernel, dist, oracle, cuda_device):
 
 # ----------------------------------------------------------------------------------------- full size
 @pytest.mark.parametrize("kernel,size", [("blackwell_f16_sw_interleaved_presum", 8192),
+                                         ("blackwell_f16_sw_interleaved_presum_2sm", 8192),
                                          ("blackwell_f16_cubic_128x256", 8192),
                                          ("blackwell_f32_sw_interleaved_presum", 4096)])
 def test_full_size_properties(kernel, size, oracle, cuda_device):
