@@ -26,7 +26,7 @@ constexpr int kStagingBytes = 4 * kStagingWarpBytes;
 
 struct KernelParams;
 
-template <int ESIZE, int BN>
+template <int ESIZE, int BN, int NSRC_MAX>
 __device__ __forceinline__ void epilogue_body(void* const* out, long long ldo, int out_rows, int out_cols,
                                               float* const* ws, const sb200_epilogue_t& ep, uint32_t sx,
                                               uint32_t tmem_base, int quarter, int lane, long long tile_off,
@@ -34,13 +34,13 @@ __device__ __forceinline__ void epilogue_body(void* const* out, long long ldo, i
   constexpr int NCHUNK = BN / 32;
   const int row = quarter * 32 + lane;
   const int nsrc = ep.nsrc;
-  const float4* srcp[SB200_MAX_SRC_TERMS];
+  const float4* srcp[NSRC_MAX];
 #pragma unroll
-  for (int t = 0; t < SB200_MAX_SRC_TERMS; ++t)
+  for (int t = 0; t < NSRC_MAX; ++t)
     srcp[t] = (t < nsrc) ? reinterpret_cast<const float4*>(ws[ep.src[t]] + tile_off) + row : nullptr;
-  float4 nxt[SB200_MAX_SRC_TERMS][8];
+  float4 nxt[NSRC_MAX][8];
 #pragma unroll
-  for (int t = 0; t < SB200_MAX_SRC_TERMS; ++t)
+  for (int t = 0; t < NSRC_MAX; ++t)
     if (t < nsrc) {
 #pragma unroll
       for (int q = 0; q < 8; ++q) nxt[t][q] = srcp[t][q * 128];
@@ -54,7 +54,7 @@ __device__ __forceinline__ void epilogue_body(void* const* out, long long ldo, i
 #pragma unroll
     for (int q = 0; q < 32; ++q) acc[q] = 0.f;
 #pragma unroll
-    for (int t = 0; t < SB200_MAX_SRC_TERMS; ++t)
+    for (int t = 0; t < NSRC_MAX; ++t)
       if (t < nsrc) {
 #pragma unroll
         for (int q = 0; q < 8; ++q) {
@@ -66,7 +66,7 @@ __device__ __forceinline__ void epilogue_body(void* const* out, long long ldo, i
       }
     if (c + 1 < NCHUNK) {
 #pragma unroll
-      for (int t = 0; t < SB200_MAX_SRC_TERMS; ++t)
+      for (int t = 0; t < NSRC_MAX; ++t)
         if (t < nsrc) {
 #pragma unroll
           for (int q = 0; q < 8; ++q) nxt[t][q] = srcp[t][((c + 1) * 8 + q) * 128];

@@ -77,7 +77,7 @@ Layout make_layout(const GemmArgs& a) {
     L.off_pb = off;
     off = align_up(off + size_t(4) * L.kq * L.nq * L.esize, 256);
   }
-  int nws = a.variant == kCubic ? 0 : 2;
+  int nws = a.variant == kCubic ? 0 : (a.variant == kInterleavedPresum ? 4 : 2);
   size_t tile_bytes = size_t(128) * L.bn * sizeof(float);
   for (int i = 0; i < nws; ++i) {
     L.off_ws[i] = off;
@@ -322,7 +322,7 @@ int run(const GemmArgs& a, void* workspace, size_t workspace_size, cudaStream_t 
       rc = launch_any(es, bn_sel, kPresumJob, p, grid, stream);
       if (rc) return rc;
       if ((rc = mark())) return rc;
-      p.prog = programs::level1_second();
+      p.prog = getenv("SB200_L1_PLAIN") ? programs::level1_second() : programs::level1_second_taps();
       rc = launch_any(es, bn_sel, kPresumNone, p, grid, stream);
       break;
     default:

@@ -33,6 +33,9 @@ struct PairConfig {
   static constexpr int BK = 128 / ESIZE;
   static constexpr int STAGES = STAGES_;
   static constexpr int MODE = MODE_;
+  // fp32 hand-off tiles an epilogue step may sum: only the kernels without presum warps (which have the register
+  // budget for it) run programs with more than one
+  static constexpr int NSRC_MAX = MODE_ == 0 ? SB200_MAX_SRC_TERMS : 1;
   static constexpr int UMMA_K = 32 / ESIZE;
   static constexpr int KSUB = BK / UMMA_K;
   static constexpr int A_BYTES = BM * 128;
@@ -277,7 +280,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
         ptx::tc_fence_after_sync();
         const long long tile_off = (static_cast<long long>(tile.id) * 2 + rank) * (128 * BN);
         if (!(p.debug_flags & 32))  // bit 5: measurement aid, skip the epilogue body
-          epilogue_body<ESIZE, BN>(p.out, p.ldo, p.out_rows, p.out_cols, p.ws, ep, sx, tmem_base, quarter, lane, tile_off,
+          epilogue_body<ESIZE, BN, Cfg::NSRC_MAX>(p.out, p.ldo, p.out_rows, p.out_cols, p.ws, ep, sx, tmem_base, quarter, lane, tile_off,
                                    tile.i * Cfg::PAIR_M + static_cast<int>(rank) * Cfg::BM, tile.j * BN, staging + (warp - 2) * kStagingWarpBytes);
         ptx::tc_fence_before_sync();
         __syncwarp();

@@ -80,7 +80,7 @@ inline void add_epilogue(sb200_program_t& pg, int nslots, const int* slots, cons
 }
 
 enum { P = 0, Q = 1, mP = 1, mQ = 2 };
-enum { WS_M0 = 0, WS_M4 = 1 };
+enum { WS_M0 = 0, WS_M4 = 1, WS_U = 2, WS_V = 3 };
 
 // Level 0: one product per tile, the two (or four) slots used alternately so that the epilogue of tile t
 // overlaps the mainloop of tile t+1.
@@ -146,6 +146,29 @@ inline sb200_program_t level1_second() {
   add_epilogue(pg, 1, sP, pos1, 2, srcM0M4, mP, mP, 0, 3);             // C3 = M0 + M2 + M3 + M4
   add_product(pg, term1(A3), term1(PS3B2), P, 1, 1, 1, 1);             // P -= M6
   add_epilogue(pg, 1, sP, pos1, 1, srcM0, mP, mP, 0, 2);               // C2 = M0 + M2 + M3 - M6
+  return pg;
+}
+
+// Launch 2 of 2, variant with short taps: whenever the next product must wait for an epilogue step, that step is
+// only a copy of a slot into an fp32 hand-off tile (no global reads); the sums that need hand-off tiles from
+// global memory (C1, C3) run afterwards while the MMA pipeline is already on the next product.
+//   hand-offs: M4, U = M2, V = M2 + M3  (M0 comes from launch 1)
+inline sb200_program_t level1_second_taps() {
+  sb200_program_t pg;
+  memset(&pg, 0, sizeof(pg));
+  const int sP[] = {P}, sQ[] = {Q}, pos1[] = {1};
+  const int srcC1[] = {WS_M0, WS_U, WS_M4}, srcC3[] = {WS_M0, WS_V, WS_M4}, srcM0[] = {WS_M0};
+  add_product(pg, term1(PS1), term1(PB10), Q, 0, 0, 1, 1);             // Q  = M4
+  add_product(pg, term1(PS2), term1(PS3), P, 0, 0, 1, 1);              // P  = M2
+  add_epilogue(pg, 1, sQ, pos1, 0, nullptr, mQ, mQ, 1, WS_M4);         // ws[M4] = Q        (overlaps M2)
+  add_epilogue(pg, 1, sP, pos1, 0, nullptr, mP, mP, 1, WS_U);          // ws[U]  = P        (overlaps M5)
+  add_product(pg, term1(PA1S2), term1(B3), Q, 0, 0, 1, 1);             // Q  = M5
+  add_product(pg, term1(PA02), term1(PB31), P, 1, 0, 1, 1);            // P += M3
+  add_epilogue(pg, 1, sQ, pos1, 3, srcC1, mQ, mQ, 0, 1);               // C1 = M0 + U + M4 + Q   (overlaps M3)
+  add_epilogue(pg, 1, sP, pos1, 0, nullptr, mP, mP, 1, WS_V);          // ws[V]  = P        (short tap before M6)
+  add_product(pg, term1(A3), term1(PS3B2), P, 1, 1, 1, 1);             // P -= M6
+  add_epilogue(pg, 0, nullptr, nullptr, 3, srcC3, 0, 0, 0, 3);         // C3 = M0 + V + M4      (overlaps M6)
+  add_epilogue(pg, 1, sP, pos1, 1, srcM0, mP, mP, 0, 2);               // C2 = M0 + P
   return pg;
 }
 

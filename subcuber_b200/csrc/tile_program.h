@@ -22,7 +22,7 @@
 #define SB200_MAX_PRODUCTS 8
 #define SB200_MAX_EPILOGUES 8
 #define SB200_MAX_SLOT_TERMS 3
-#define SB200_MAX_SRC_TERMS 2
+#define SB200_MAX_SRC_TERMS 3
 #define SB200_NUM_VIEWS 16
 #define SB200_NUM_WS 4
 
@@ -64,7 +64,7 @@ typedef struct {
   uint8_t src[SB200_MAX_SRC_TERMS];
   uint8_t dst_kind;        // 0: output quadrant `dst` in the output type; 1: fp32 workspace buffer `dst`
   uint8_t dst;
-  uint8_t pad[3];
+  uint8_t pad[2];
 } sb200_epilogue_t;
 
 typedef struct {

@@ -22,7 +22,7 @@ from .dsl import BinOp, Matrix, expand_terms
 QUADRANT_VIEW = {"a0": 0, "a1": 1, "a2": 2, "a3": 3, "b0": 8, "b1": 9, "b2": 10, "b3": 11}
 PRESUM_VIEW = {"s1": 4, "s2": 5, "a02": 6, "a1s2": 7, "b10": 12, "b31": 13, "s3": 14, "s3b2": 15}
 P, Q = 0, 1
-WS_M0, WS_M4 = 0, 1
+WS_M0, WS_M4, WS_U, WS_V = 0, 1, 2, 3
 
 
 # ------------------------------------------------------------------------------------------- algebra from the DSL
@@ -150,6 +150,22 @@ def level1_second_program(ms) -> tp.Program:
     return b.pg
 
 
+def level1_second_taps_program(ms) -> tp.Program:
+    """Launch 2 with short taps: a product never waits for an epilogue step that reads global memory.  Hand-offs:
+    m4, u = m2, v = m2 + m3 (and m0 from launch 1); c1 and c3 are summed from hand-offs off the critical path."""
+    b = ProgramBuilder(_products_by_name(ms), fly=False)
+    b.product("m4", Q).product("m2", P)
+    b.epilogue([Q], [], wait=[Q], release=[Q], dst_kind=1, dst=WS_M4)
+    b.epilogue([P], [], wait=[P], release=[P], dst_kind=1, dst=WS_U)
+    b.product("m5", Q).product("m3", P, accumulate=1)
+    b.epilogue([Q], [WS_M0, WS_U, WS_M4], wait=[Q], release=[Q], dst_kind=0, dst=1)  # c1 = m0 + m2 + m4 + m5
+    b.epilogue([P], [], wait=[P], release=[P], dst_kind=1, dst=WS_V)
+    b.product("m6", P, accumulate=1, negate=1)
+    b.epilogue([], [WS_M0, WS_V, WS_M4], wait=[], release=[], dst_kind=0, dst=3)     # c3 = m0 + m2 + m3 + m4
+    b.epilogue([P], [WS_M0], wait=[P], release=[P], dst_kind=0, dst=2)               # c2 = m0 + m2 + m3 - m6
+    return b.pg
+
+
 def all_programs() -> Dict[str, tp.Program]:
     """The named tables, generated from the DSL (names as in `sb200_tile_program`)."""
     from .algos.strassen_winograd_level1 import strassen_winograd
@@ -161,6 +177,7 @@ def all_programs() -> Dict[str, tp.Program]:
         "level1_full_ws": level1_full_program(ms, fly=False),
         "level1_first": level1_first_program(ms),
         "level1_second": level1_second_program(ms),
+        "level1_second_taps": level1_second_taps_program(ms),
     }
 
 
@@ -176,10 +193,11 @@ def verify_programs(programs: Dict[str, tp.Program]) -> None:
         for q in range(4):
             assert np.array_equal(got[q], want[q]), (name, q)
     r1 = tp.check_program(programs["level1_first"], level=1, expect=[0])
-    r2 = tp.check_program(programs["level1_second"], level=1, ws_in=r1["ws"], expect=[1, 2, 3])
     assert np.array_equal(r1["outputs"][0], want[0])
-    for q in (1, 2, 3):
-        assert np.array_equal(r2["outputs"][q], want[q]), q
+    for name in ("level1_second", "level1_second_taps"):
+        r2 = tp.check_program(programs[name], level=1, ws_in=r1["ws"], expect=[1, 2, 3])
+        for q in (1, 2, 3):
+            assert np.array_equal(r2["outputs"][q], want[q]), (name, q)
 
 
 # --------------------------------------------------------------------------------------------- schedule -> plan
@@ -202,7 +220,7 @@ def plan_for_schedule(schedule: list, level: int, mnk: Tuple[int, int, int], dty
         plan = {"level": 1, "kernel": f"blackwell_{dtype}_sw_interleaved_presum_2sm",
                 "launches": [{"program": "level1_first", "products": ["m0", "m1"],
                               "presum": "materialised by the presum warps of this launch"},
-                             {"program": "level1_second", "products": ["m4", "m2", "m5", "m3", "m6"],
+                             {"program": "level1_second_taps", "products": ["m4", "m2", "m5", "m3", "m6"],
                               "presum": "read from the workspace by TMA"}]}
     plan["mnk"] = [m, n, k]
     if level > 1:

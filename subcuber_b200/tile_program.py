@@ -22,7 +22,7 @@ MAX_TERMS = 4
 MAX_PRODUCTS = 8
 MAX_EPILOGUES = 8
 MAX_SLOT_TERMS = 3
-MAX_SRC_TERMS = 2
+MAX_SRC_TERMS = 3
 
 VIEW_NAMES = ["A0", "A1", "A2", "A3", "S1", "S2", "A02", "A1S2", "B0", "B1", "B2", "B3", "B10", "B31", "S3", "S3B2"]
 # coefficient vectors of every view over (A0..A3) or (B0..B3):
@@ -48,7 +48,7 @@ class Epilogue(C.Structure):
     _fields_ = [("nslots", C.c_uint8), ("slot", C.c_uint8 * MAX_SLOT_TERMS), ("slot_sign", C.c_int8 * MAX_SLOT_TERMS),
                 ("wait_full_mask", C.c_uint8), ("release_mask", C.c_uint8), ("nsrc", C.c_uint8),
                 ("src", C.c_uint8 * MAX_SRC_TERMS), ("dst_kind", C.c_uint8), ("dst", C.c_uint8),
-                ("pad", C.c_uint8 * 3)]
+                ("pad", C.c_uint8 * 2)]
 
 
 class Program(C.Structure):

@@ -36,6 +36,16 @@ def test_level1_two_launches(lib):
     assert sorted(r2["outputs"]) == [1, 2, 3]
 
 
+def test_level1_second_launch_with_short_taps(lib):
+    first = tp.from_library("level1_first")
+    taps = tp.from_library("level1_second_taps")
+    r1 = tp.check_program(first, level=1, nslots=2, expect=[0], tiles=3)
+    r2 = tp.check_program(taps, level=1, nslots=2, ws_in=r1["ws"], expect=[1, 2, 3], tiles=5)
+    assert sorted(r2["outputs"]) == [1, 2, 3] and sorted(r2["ws"]) == [0, 1, 2, 3]
+    # every step a product waits on is a pure slot-to-hand-off copy or a final sum of one slot: none reads two slots
+    assert all(taps.epilogue[i].nslots <= 1 for i in range(taps.nepilogues))
+
+
 def test_second_launch_needs_the_handoff(lib):
     with pytest.raises(tp.ProgramError):
         tp.check_program(tp.from_library("level1_second"), level=1, nslots=2, expect=[1, 2, 3])
