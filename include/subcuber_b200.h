@@ -79,6 +79,13 @@ SB200_DECLARE_RUN(run_blackwell_f16_sw_fused_presum_2sm);
 SB200_DECLARE_RUN(run_blackwell_f32_sw_fused_presum_2sm);
 SB200_DECLARE_RUN(run_blackwell_f16_sw_interleaved_presum_2sm);
 SB200_DECLARE_RUN(run_blackwell_f32_sw_interleaved_presum_2sm);
+/* Level 2 (49 products): seven level-1 interleaved-presum groups over half-size operands, 14 launches, chained through
+ * fp32 buffers.  Stands where the reference has StrassenGemmLevel2 (include/cutlass/gemm/device/strassen_gemm.h:
+ * 1300-2008) behind its "*_level_2" runner entries. */
+SB200_DECLARE_RUN(run_blackwell_f16_sw_level2);
+SB200_DECLARE_RUN(run_blackwell_f32_sw_level2);
+SB200_DECLARE_RUN(run_blackwell_f16_sw_level2_2sm);
+SB200_DECLARE_RUN(run_blackwell_f32_sw_level2_2sm);
 /* cuBLAS baselines behind the same ABI (reference: src/cuda/cublas_runner.cpp:151-175); the tf32 row is
  * an addition: the reference's f32 row is CUBLAS_COMPUTE_32F_PEDANTIC (cublas_runner.cpp:14). */
 SB200_DECLARE_RUN(run_cublas_f16);
@@ -158,7 +165,8 @@ typedef struct sb200_workspace_layout {
 int sb200_gemm_workspace_layout(const char* kernel, int m, int n, int k, sb200_workspace_layout* out);
 
 /* Like sb200_gemm, but synchronises and reports the device time of each kernel launch of the call
- * (CUDA events on `stream`); launch_ms must have room for 3 floats. */
+ * (CUDA events on `stream`); launch_ms must have room for SB200_MAX_LAUNCHES floats. */
+#define SB200_MAX_LAUNCHES 16
 int sb200_gemm_timed(const char* kernel, const void* a, const void* b, void* d, int m, int n, int k, void* workspace,
                      size_t workspace_bytes, sb200_stream_t stream, float* launch_ms, int* num_launches);
 
@@ -172,7 +180,8 @@ int sb200_gemm_events(const char* kernel, const void* a, const void* b, void* d,
                       size_t workspace_bytes, sb200_stream_t stream, sb200_event_list* list, int first_index);
 
 /* The tile program tables the kernels interpret (csrc/tile_program.h), for inspection and tests.
- * which: "level0" | "level1_full_fly" | "level1_full_ws" | "level1_first" | "level1_second". */
+ * which: "level0" | "level1_full_fly" | "level1_full_ws" | "level1_first" | "level1_second" | "level1_second_taps" |
+ * "level2_<child>_launch<1|2>" with child in m0, m1, m2, m4, m5, m3, m6. */
 int sb200_tile_program(const char* which, void* out, size_t out_bytes);
 size_t sb200_tile_program_bytes(void);
 

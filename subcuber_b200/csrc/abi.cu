@@ -40,6 +40,10 @@ const KernelDesc kDescs[] = {
     {"blackwell_f32_sw_fused_presum_2sm", "f32", 1, sb200::kF32, sb200::kFusedPresum, 256, 1},
     {"blackwell_f16_sw_interleaved_presum_2sm", "f16", 1, sb200::kF16, sb200::kInterleavedPresum, 256, 1},
     {"blackwell_f32_sw_interleaved_presum_2sm", "f32", 1, sb200::kF32, sb200::kInterleavedPresum, 256, 1},
+    {"blackwell_f16_sw_level2", "f16", 2, sb200::kF16, sb200::kInterleavedLevel2, 256, 0},
+    {"blackwell_f32_sw_level2", "f32", 2, sb200::kF32, sb200::kInterleavedLevel2, 256, 0},
+    {"blackwell_f16_sw_level2_2sm", "f16", 2, sb200::kF16, sb200::kInterleavedLevel2, 256, 1},
+    {"blackwell_f32_sw_level2_2sm", "f32", 2, sb200::kF32, sb200::kInterleavedLevel2, 256, 1},
 };
 constexpr int kNumDescs = sizeof(kDescs) / sizeof(kDescs[0]);
 
@@ -270,6 +274,10 @@ SB200_DEFINE_RUN(blackwell_f16_sw_fused_presum_2sm)
 SB200_DEFINE_RUN(blackwell_f32_sw_fused_presum_2sm)
 SB200_DEFINE_RUN(blackwell_f16_sw_interleaved_presum_2sm)
 SB200_DEFINE_RUN(blackwell_f32_sw_interleaved_presum_2sm)
+SB200_DEFINE_RUN(blackwell_f16_sw_level2)
+SB200_DEFINE_RUN(blackwell_f32_sw_level2)
+SB200_DEFINE_RUN(blackwell_f16_sw_level2_2sm)
+SB200_DEFINE_RUN(blackwell_f32_sw_level2_2sm)
 
 #define SB200_DEFINE_BLAS(fn, impl, type)                                                                      \
   extern "C" int fn(KernelRunnerBuffers buffers, int m, int n, int k, int warmup_iterations, int iterations,   \
@@ -306,6 +314,10 @@ static const sb200_kernel_entry kRegistry[] = {
     {"blackwell_f32_sw_fused_presum_2sm", "blackwell", "f32", 1, run_blackwell_f32_sw_fused_presum_2sm},
     {"blackwell_f16_sw_interleaved_presum_2sm", "blackwell", "f16", 1, run_blackwell_f16_sw_interleaved_presum_2sm},
     {"blackwell_f32_sw_interleaved_presum_2sm", "blackwell", "f32", 1, run_blackwell_f32_sw_interleaved_presum_2sm},
+    {"blackwell_f16_sw_level2", "blackwell", "f16", 2, run_blackwell_f16_sw_level2},
+    {"blackwell_f32_sw_level2", "blackwell", "f32", 2, run_blackwell_f32_sw_level2},
+    {"blackwell_f16_sw_level2_2sm", "blackwell", "f16", 2, run_blackwell_f16_sw_level2_2sm},
+    {"blackwell_f32_sw_level2_2sm", "blackwell", "f32", 2, run_blackwell_f32_sw_level2_2sm},
 };
 
 extern "C" int sb200_num_kernels(void) { return static_cast<int>(sizeof(kRegistry) / sizeof(kRegistry[0])); }
@@ -408,7 +420,9 @@ extern "C" int sb200_gemm_timed(const char* kernel, const void* a, const void* b
   if (!launch_ms || !num_launches) return SB200_ERR_INVALID_PROBLEM;
   GemmArgs g = make_args(*d, a, b, d_out, m, n, k);
   const int nl = sb200::launches_per_run(g);
-  cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr};
+  cudaEvent_t ev[SB200_MAX_LAUNCHES + 1];
+  memset(ev, 0, sizeof(ev));
+  if (nl > SB200_MAX_LAUNCHES) return SB200_ERR_INTERNAL;
   cudaError_t ce = cudaSuccess;
   for (int i = 0; i <= nl; ++i)
     if ((ce = cudaEventCreate(&ev[i])) != cudaSuccess) break;
@@ -423,7 +437,7 @@ extern "C" int sb200_gemm_timed(const char* kernel, const void* a, const void* b
       if ((ce = cudaEventElapsedTime(&launch_ms[i], ev[i], ev[i + 1])) != cudaSuccess) rc = static_cast<int>(ce);
     *num_launches = nl;
   }
-  for (int i = 0; i < 4; ++i)
+  for (int i = 0; i <= SB200_MAX_LAUNCHES; ++i)
     if (ev[i]) cudaEventDestroy(ev[i]);
   return rc;
 }
@@ -437,6 +451,21 @@ extern "C" int sb200_tile_program(const char* which, void* out, size_t out_bytes
   else if (strcmp(which, "level1_first") == 0) pg = sb200::programs::level1_first();
   else if (strcmp(which, "level1_second") == 0) pg = sb200::programs::level1_second();
   else if (strcmp(which, "level1_second_taps") == 0) pg = sb200::programs::level1_second_taps();
+  else if (strncmp(which, "level2_", 7) == 0) {
+    // "level2_<child>_launch<1|2>", child = m0, m1, m2, m4, m5, m3, m6 (execution order)
+    const sb200::programs::Level2Child* ch = sb200::programs::level2_children();
+    int found = -1, launch = 0;
+    for (int c = 0; c < 7 && found < 0; ++c) {
+      const size_t len = strlen(ch[c].name);
+      if (strncmp(which + 7, ch[c].name, len) == 0 && strncmp(which + 7 + len, "_launch", 7) == 0) {
+        found = c;
+        launch = which[7 + len + 7] - '0';
+      }
+    }
+    if (found < 0 || (launch != 1 && launch != 2)) return SB200_ERR_NO_KERNEL;
+    pg = sb200::programs::link_outer(launch == 1 ? sb200::programs::level1_first() : sb200::programs::level1_second_taps(),
+                                     ch[found].link, launch);
+  }
   else return SB200_ERR_NO_KERNEL;
   memcpy(out, &pg, sizeof(pg));
   return 0;

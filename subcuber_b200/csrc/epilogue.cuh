@@ -3,7 +3,8 @@
 // One call handles one epilogue step of a tile program for one warp: the warp owns 32 rows (one TMEM lane
 // quarter) of the CTA's 128-row accumulator and walks the BN columns in chunks of 32.  Per chunk it
 //   1. sums the fp32 hand-off tiles the step lists (loaded one chunk AHEAD, so their latency overlaps the work on
-//      the current chunk),
+//      the current chunk; the first chunk is requested BEFORE the warp waits for the step's TMEM slots, so it
+//      overlaps the product that is still running),
 //   2. adds / subtracts the TMEM slots (tcgen05.ld 32 lanes x 32 columns),
 //   3. writes either an fp32 hand-off tile or the output in the output type.
 //
@@ -26,11 +27,14 @@ constexpr int kStagingBytes = 4 * kStagingWarpBytes;
 
 struct KernelParams;
 
-template <int ESIZE, int BN, int NSRC_MAX>
-__device__ __forceinline__ void epilogue_body(void* const* out, long long ldo, int out_rows, int out_cols,
+// `wait_slots()` blocks until the slots in ep.wait_full_mask are ready and returns false when the wait was given up.
+template <int ESIZE, int BN, int NSRC_MAX, typename WaitFn>
+__device__ __forceinline__ bool epilogue_body(void* const* out, long long ldo, int out_rows, int out_cols,
                                               float* const* ws, const sb200_epilogue_t& ep, uint32_t sx,
                                               uint32_t tmem_base, int quarter, int lane, long long tile_off,
-                                              int grow_tile, int gcol_tile, uint32_t staging_warp) {
+                                              int grow_tile, int gcol_tile, uint32_t staging_warp, bool skip_body,
+                                              WaitFn wait_slots) {
+  if (skip_body) return wait_slots();  // measurement aid
   constexpr int NCHUNK = BN / 32;
   const int row = quarter * 32 + lane;
   const int nsrc = ep.nsrc;
@@ -47,6 +51,7 @@ __device__ __forceinline__ void epilogue_body(void* const* out, long long ldo, i
     }
   float4* dstp = (ep.dst_kind == 1) ? reinterpret_cast<float4*>(ws[ep.dst] + tile_off) + row : nullptr;
   char* outp = (ep.dst_kind == 1) ? nullptr : static_cast<char*>(out[ep.dst]);
+  if (!wait_slots()) return false;
 
 #pragma unroll 1
   for (int c = 0; c < NCHUNK; ++c) {
@@ -140,6 +145,7 @@ __device__ __forceinline__ void epilogue_body(void* const* out, long long ldo, i
       __syncwarp();
     }
   }
+  return true;
 }
 
 }  // namespace sb200

@@ -44,24 +44,47 @@ int make_tmap(CUtensorMap* m, int esize, const View& v, int box_rows, CUtensorMa
   return r == CUDA_SUCCESS ? kOk : kErrInternal;
 }
 
+// Row-major B view as a 3-D tensor [128-byte column block][row][block index] (the block stride is 128 bytes), so
+// that ONE load deposits `nblk` column blocks of `box_rows` rows, each in the canonical swizzled layout, back to
+// back.  Needs a column count that is a whole number of blocks: a partial last block would be read past the row end.
+int make_tmap_b_blocked(CUtensorMap* m, int esize, const View& v, int box_rows, int nblk, CUtensorMapSwizzle swizzle) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return kErrInternal;
+  const int blk = 128 / esize;
+  cuuint64_t dims[3] = {static_cast<cuuint64_t>(blk), static_cast<cuuint64_t>(v.rows),
+                        static_cast<cuuint64_t>(v.cols / blk)};
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(v.ld) * esize, 128};
+  cuuint32_t box[3] = {static_cast<cuuint32_t>(blk), static_cast<cuuint32_t>(box_rows), static_cast<cuuint32_t>(nblk)};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUtensorMapDataType dt = esize == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  CUresult r = fn(m, dt, 3, const_cast<void*>(v.ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? kOk : kErrInternal;
+}
+
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 inline int esize_of(DType t) { return t == kF16 ? 2 : 4; }
 
 struct Layout {
   int esize, bn, level;
-  int mq, nq, kq;          // extents of one operand/output block (level 0: the whole matrix)
+  int mq, nq, kq;          // extents of one operand/output block of the innermost level (level 0: the whole matrix)
   int tiles_m, tiles_n, num_k;
-  size_t off_status, off_pa, off_pb, off_ws[SB200_NUM_WS], total;
+  size_t off_status, off_pa, off_pb, off_ws[4], total;
+  // level 2 only: outer presums [4][m/2][k/2], [4][k/2][n/2] and three outer chain buffers (fp32, tile-contiguous,
+  // four inner quadrants each)
+  size_t off_opa, off_opb, off_x[3], quadrant_floats;
 };
+
+int level_of(Variant v) { return v == kCubic ? 0 : (v == kInterleavedLevel2 ? 2 : 1); }
 
 Layout make_layout(const GemmArgs& a) {
   Layout L;
   memset(&L, 0, sizeof(L));
   L.esize = esize_of(a.dtype);
   L.bn = a.bn == 128 ? 128 : 256;
-  L.level = a.variant == kCubic ? 0 : 1;
-  int div = L.level ? 2 : 1;
+  L.level = level_of(a.variant);
+  const int div = 1 << L.level;
   L.mq = a.m / div;
   L.nq = a.n / div;
   L.kq = a.k / div;
@@ -71,18 +94,31 @@ Layout make_layout(const GemmArgs& a) {
   size_t off = 0;
   L.off_status = off;
   off += 256;
-  if (a.variant == kInterleavedPresum) {
+  if (L.level == 2) {
+    L.off_opa = off;
+    off = align_up(off + size_t(4) * (2 * L.mq) * (2 * L.kq) * L.esize, 256);
+    L.off_opb = off;
+    off = align_up(off + size_t(4) * (2 * L.kq) * (2 * L.nq) * L.esize, 256);
+  }
+  if (a.variant == kInterleavedPresum || L.level == 2) {
     L.off_pa = off;
     off = align_up(off + size_t(4) * L.mq * L.kq * L.esize, 256);
     L.off_pb = off;
     off = align_up(off + size_t(4) * L.kq * L.nq * L.esize, 256);
   }
-  int nws = a.variant == kCubic ? 0 : (a.variant == kInterleavedPresum ? 4 : 2);
-  size_t tile_bytes = size_t(128) * L.bn * sizeof(float);
+  const int nws = a.variant == kCubic ? 0 : (a.variant == kFusedPresum ? 2 : 4);
+  const size_t tile_bytes = size_t(128) * L.bn * sizeof(float);
+  const size_t quadrant_bytes = size_t(L.tiles_m) * L.tiles_n * (a.pair ? 2 : 1) * tile_bytes;
+  L.quadrant_floats = quadrant_bytes / sizeof(float);
   for (int i = 0; i < nws; ++i) {
     L.off_ws[i] = off;
-    off = align_up(off + size_t(L.tiles_m) * L.tiles_n * (a.pair ? 2 : 1) * tile_bytes, 256);
+    off = align_up(off + quadrant_bytes, 256);
   }
+  if (L.level == 2)
+    for (int i = 0; i < 3; ++i) {
+      L.off_x[i] = off;
+      off = align_up(off + 4 * quadrant_bytes, 256);
+    }
   L.total = off;
   return L;
 }
@@ -151,7 +187,6 @@ int launch_pair(const KernelParams& p, int pairs, cudaStream_t stream) {
 template <int ESIZE>
 int launch_pair_mode(int mode, const KernelParams& p, int pairs, cudaStream_t stream) {
   constexpr int STAGES = 6;
-  if (mode == kPresumNone && getenv("SB200_STAGES7")) return launch_pair<PairConfig<ESIZE, 7, kPresumNone>>(p, pairs, stream);
   switch (mode) {
     case kPresumNone: return launch_pair<PairConfig<ESIZE, STAGES, kPresumNone>>(p, pairs, stream);
     case kPresumFeed: return launch_pair<PairConfig<ESIZE, STAGES, kPresumFeed>>(p, pairs, stream);
@@ -185,9 +220,9 @@ int can_implement(const GemmArgs& a) {
   if (a.pair && a.bn == 128) return kErrNotSupported;
   const int es = esize_of(a.dtype);
   const int vec = 16 / es;  // elements per 16 bytes
-  const int div = a.variant == kCubic ? 1 : 2;
-  if (div == 2 && ((a.m % 2) || (a.n % 2) || (a.k % 2))) return kErrInvalidProblem;
-  // every quadrant row must start on a 16-byte boundary (TMA base/stride rule, vector loads and stores)
+  const int div = 1 << level_of(a.variant);
+  if ((a.m % div) || (a.n % div) || (a.k % div)) return kErrInvalidProblem;
+  // every block row must start on a 16-byte boundary (TMA base/stride rule, vector loads and stores)
   if ((a.k / div) % vec || (a.n / div) % vec) return kErrMisalignedOperand;
   if ((reinterpret_cast<uintptr_t>(a.a) | reinterpret_cast<uintptr_t>(a.b) | reinterpret_cast<uintptr_t>(a.d)) & 15)
     return kErrMisalignedOperand;
@@ -203,48 +238,67 @@ WorkspaceLayout workspace_layout(const GemmArgs& a) {
   w.status = L.off_status;
   w.presum_a = L.off_pa;
   w.presum_b = L.off_pb;
-  for (int i = 0; i < SB200_NUM_WS; ++i) w.handoff[i] = L.off_ws[i];
+  for (int i = 0; i < 4; ++i) w.handoff[i] = L.off_ws[i];
   w.total = L.total;
   w.mq = L.mq; w.nq = L.nq; w.kq = L.kq;
   w.tiles_m = L.tiles_m; w.tiles_n = L.tiles_n; w.bn = L.bn;
   return w;
 }
 
-int launches_per_run(const GemmArgs& a) { return a.variant == kInterleavedPresum ? 2 : 1; }
+int launches_per_run(const GemmArgs& a) {
+  return a.variant == kInterleavedLevel2 ? 14 : (a.variant == kInterleavedPresum ? 2 : 1);
+}
 
-int run(const GemmArgs& a, void* workspace, size_t workspace_size, cudaStream_t stream) {
-  int rc = can_implement(a);
-  if (rc) return rc;
-  const Layout L = make_layout(a);
-  if (!workspace) return kErrWorkspaceNull;
-  if (workspace_size < L.total || (reinterpret_cast<uintptr_t>(workspace) & 255)) return kErrWorkspaceNull;
-  char* wsb = static_cast<char*>(workspace);
-  const int es = L.esize;
+namespace {
 
+// One launch group over (A, B) -> D with quadrant extents (mq, nq, kq): level 0 (whole matrices, one launch), level 1
+// fused (one launch) or level 1 interleaved (two launches), optionally tied into an outer recursion step.
+struct LaunchSpec {
+  Variant variant;
+  int es, bn, pair, grid;
+  View a, b;                 // whole operands of this group
+  int mq, nq, kq;            // extents of one block (level 0: of the whole problem)
+  int tiles_m, tiles_n, num_k;
+  char* out;                 // output matrix in the output type (2mq x 2nq, or mq x nq at level 0), or null
+  long long ldo;
+  char* presum_a;            // [4][mq][kq], interleaved only
+  char* presum_b;            // [4][kq][nq]
+  float* ws_inner[4];
+  size_t quadrant_floats;    // floats per output quadrant in an outer chain buffer
+  float* outer_dst;          // outer chain buffers ([4 quadrants][tiles][tile]) or null
+  float* outer_src;
+  float* outer_src2;
+  float* extra_dst;
+  programs::OuterLink link;
+  bool linked;
+  PresumSideJob more_jobs[2];  // presum jobs of the level above, run by launch 1's presum warps
+  int n_more_jobs;
+  int* status;
+};
+
+template <typename MarkFn>
+int launch_group(const LaunchSpec& s, cudaStream_t stream, MarkFn mark) {
   KernelParams p;
   memset(&p, 0, sizeof(p));
-  p.status = reinterpret_cast<int*>(wsb + L.off_status);
-  cudaError_t ce = cudaMemsetAsync(p.status, 0, 256, stream);
-  if (ce != cudaSuccess) return static_cast<int>(ce);
-
-  const char* A = static_cast<const char*>(a.a);
-  const char* B = static_cast<const char*>(a.b);
-  char* D = static_cast<char*>(a.d);
-  const long long lda = a.k, ldb = a.n, ldd = a.n;
-  if (L.level == 0) {
-    for (int v = 0; v < 8; ++v) p.view[v] = View{A, lda, a.m, a.k};
-    for (int v = 8; v < 16; ++v) p.view[v] = View{B, ldb, a.k, a.n};
-    p.out[0] = D;
+  p.status = s.status;
+  const int es = s.es;
+  const char* A = static_cast<const char*>(s.a.ptr);
+  const char* B = static_cast<const char*>(s.b.ptr);
+  int rc;
+  if (s.variant == kCubic) {
+    for (int v = 0; v < 8; ++v) p.view[v] = s.a;
+    for (int v = 8; v < 16; ++v) p.view[v] = s.b;
+    p.out[0] = s.out;
   } else {
     for (int q = 0; q < 4; ++q) {
-      p.view[SB200_VIEW_A0 + q] = View{A + ((q >> 1) * L.mq * lda + (q & 1) * L.kq) * es, lda, L.mq, L.kq};
-      p.view[SB200_VIEW_B0 + q] = View{B + ((q >> 1) * L.kq * ldb + (q & 1) * L.nq) * es, ldb, L.kq, L.nq};
-      p.out[q] = D + ((q >> 1) * L.mq * ldd + (q & 1) * L.nq) * es;
-      if (a.variant == kInterleavedPresum) {
+      p.view[SB200_VIEW_A0 + q] = View{A + ((q >> 1) * s.mq * s.a.ld + (q & 1) * s.kq) * es, s.a.ld, s.mq, s.kq};
+      p.view[SB200_VIEW_B0 + q] = View{B + ((q >> 1) * s.kq * s.b.ld + (q & 1) * s.nq) * es, s.b.ld, s.kq, s.nq};
+      p.out[q] = s.out ? s.out + ((q >> 1) * s.mq * s.ldo + (q & 1) * s.nq) * es : nullptr;
+      if (s.variant == kInterleavedPresum) {
         p.view[SB200_VIEW_PA0 + q] =
-            View{wsb + L.off_pa + size_t(q) * L.mq * L.kq * es, static_cast<long long>(L.kq), L.mq, L.kq};
+            View{s.presum_a + size_t(q) * s.mq * s.kq * es, static_cast<long long>(s.kq), s.mq, s.kq};
         p.view[SB200_VIEW_PB0 + q] =
-            View{wsb + L.off_pb + size_t(q) * L.kq * L.nq * es, static_cast<long long>(L.nq), L.kq, L.nq};
+            View{s.presum_b + size_t(q) * s.kq * s.nq * es, static_cast<long long>(s.nq), s.kq, s.nq};
       } else {
         p.view[SB200_VIEW_PA0 + q] = p.view[SB200_VIEW_A0 + q];
         p.view[SB200_VIEW_PB0 + q] = p.view[SB200_VIEW_B0 + q];
@@ -255,18 +309,35 @@ int run(const GemmArgs& a, void* workspace, size_t workspace_size, cudaStream_t 
     if ((rc = make_tmap(&p.tmap[v], es, p.view[v], 128, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   // B tiles of 32-bit elements are deposited with 32-byte swizzle atoms (see KernelConfig::B_SWZ32)
   const CUtensorMapSwizzle b_swz = es == 4 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B;
-  for (int v = 8; v < 16; ++v)
-    if ((rc = make_tmap(&p.tmap[v], es, p.view[v], 128 / es, b_swz))) return rc;
-  p.ldo = ldd;
-  p.out_rows = L.mq;
-  p.out_cols = L.nq;
-  for (int i = 0; i < SB200_NUM_WS; ++i) p.ws[i] = reinterpret_cast<float*>(wsb + L.off_ws[i]);
-  p.tiles_m = L.tiles_m;
-  p.tiles_n = L.tiles_n;
-  p.num_k = L.num_k;
+  // column blocks of B one CTA loads per k-step: BN (1-CTA kernels) or BN / 2 (CTA pairs) columns of 128 bytes each
+  const int b_nblk = (s.pair ? 128 : s.bn) * es / 128;
+  p.b_blocked = (p.view[SB200_VIEW_B0].cols % (128 / es) == 0) ? 1 : 0;
+  for (int v = 8; v < 16; ++v) {
+    rc = p.b_blocked ? make_tmap_b_blocked(&p.tmap[v], es, p.view[v], 128 / es, b_nblk, b_swz)
+                     : make_tmap(&p.tmap[v], es, p.view[v], 128 / es, b_swz);
+    if (rc) return rc;
+  }
+  p.ldo = s.ldo;
+  p.out_rows = s.mq;
+  p.out_cols = s.nq;
+  for (int i = 0; i < 4; ++i) p.ws[SB200_WS_INNER + i] = s.ws_inner[i];
+  for (int q = 0; q < 4; ++q) {
+    const size_t o = size_t(q) * s.quadrant_floats;
+    p.ws[SB200_WS_OUTER_DST + q] = s.outer_dst ? s.outer_dst + o : nullptr;
+    p.ws[SB200_WS_OUTER_SRC + q] = s.outer_src ? s.outer_src + o : nullptr;
+    p.ws[SB200_WS_OUTER_SRC2 + q] = s.outer_src2 ? s.outer_src2 + o : nullptr;
+    p.ws[SB200_WS_EXTRA_DST + q] = s.extra_dst ? s.extra_dst + o : nullptr;
+  }
+  p.tiles_m = s.tiles_m;
+  p.tiles_n = s.tiles_n;
+  p.num_k = s.num_k;
   p.band = 8;
+  if (const char* bd = getenv("SB200_BAND")) p.band = atoi(bd) > 0 ? atoi(bd) : 8;
+  if (const char* dbg = getenv("SB200_DEBUG_FLAGS")) p.debug_flags = atoi(dbg);
+  if (const char* pf = getenv("SB200_PREFETCH")) p.prefetch_dist = atoi(pf);
   if (getenv("SB200_PROF")) {
-    // measurement aid: per-CTA cycle counters of the CTA-pair kernels, printed by the next call
+    // measurement aid: per-CTA cycle counters of the CTA-pair kernels (library built with SB200_PROFILE), printed by
+    // the next call
     static long long* prof_dev = nullptr;
     static long long prof_host[8 * 256];
     if (!prof_dev) {
@@ -278,58 +349,153 @@ int run(const GemmArgs& a, void* workspace, size_t workspace_size, cudaStream_t 
       int n = 0;
       for (int c = 0; c < 148; c += 2, ++n)
         for (int i = 0; i < 8; ++i) sum[i] += double(prof_host[c * 8 + i]);
-      double psum3 = 0, psum4 = 0, e5 = 0, e6 = 0;
-      for (int c = 1; c < 148; c += 2) { psum3 += double(prof_host[c * 8 + 3]); psum4 += double(prof_host[c * 8 + 4]); e5 += double(prof_host[c * 8 + 5]); e6 += double(prof_host[c * 8 + 6]); }
-      fprintf(stderr, "[prof] leader mma thread: total %.0f = wait_full %.0f + wait_free %.0f + issue %.0f + commit %.0f + rest | producer A: wait_empty %.0f issue %.0f total %.0f\n",
-              sum[0] / n, sum[1] / n, sum[2] / n, sum[5] / n, sum[6] / n, sum[3] / n, sum[7] / n, sum[4] / n);
-      (void)psum3; (void)psum4; (void)e5; (void)e6;
+      fprintf(stderr, "[prof] leader mma thread: total %.0f = wait_full %.0f + wait_free %.0f + issue %.0f + rest | "
+              "producer: wait_empty %.0f issue %.0f total %.0f\n",
+              sum[0] / n, sum[1] / n, sum[2] / n, sum[5] / n, sum[3] / n, sum[7] / n, sum[4] / n);
     }
     cudaMemset(prof_dev, 0, sizeof(prof_host));
     p.prof = prof_dev;
   }
-  if (const char* pf = getenv("SB200_PREFETCH")) p.prefetch_dist = atoi(pf);
-  if (const char* bd = getenv("SB200_BAND")) p.band = atoi(bd) > 0 ? atoi(bd) : 8;
-  if (const char* dbg = getenv("SB200_DEBUG_FLAGS")) p.debug_flags = atoi(dbg);
-  p.job_pa = wsb + L.off_pa;
-  p.job_pb = wsb + L.off_pb;
-  p.job_mq = L.mq;
-  p.job_nq = L.nq;
-  p.job_kq = L.kq;
+  if (s.variant == kInterleavedPresum) {
+    p.njobs = 2;
+    for (int q = 0; q < 4; ++q) {
+      p.job[0].src[q] = p.view[SB200_VIEW_A0 + q].ptr;
+      p.job[1].src[q] = p.view[SB200_VIEW_B0 + q].ptr;
+    }
+    p.job[0].ld = s.a.ld; p.job[0].dst = s.presum_a; p.job[0].rows = s.mq; p.job[0].cols = s.kq; p.job[0].side = 0;
+    p.job[1].ld = s.b.ld; p.job[1].dst = s.presum_b; p.job[1].rows = s.kq; p.job[1].cols = s.nq; p.job[1].side = 1;
+    for (int j = 0; j < s.n_more_jobs; ++j) p.job[p.njobs++] = s.more_jobs[j];
+  }
+  const int bn_sel = s.pair ? -1 : s.bn;  // -1 routes launch_any to the CTA-pair kernels (grid = pairs)
+  switch (s.variant) {
+    case kCubic:
+      p.prog = programs::level0();
+      rc = launch_any(es, bn_sel, kPresumNone, p, s.grid, stream);
+      break;
+    case kFusedPresum:
+      p.prog = programs::level1_full(true);
+      rc = launch_any(es, bn_sel, kPresumFeed, p, s.grid, stream);
+      break;
+    case kInterleavedPresum: {
+      const sb200_program_t first = programs::level1_first();
+      const sb200_program_t second =
+          getenv("SB200_L1_PLAIN") && !s.linked ? programs::level1_second() : programs::level1_second_taps();
+      p.prog = s.linked ? programs::link_outer(first, s.link, 1) : first;
+      rc = launch_any(es, bn_sel, kPresumJob, p, s.grid, stream);
+      if (rc) return rc;
+      if ((rc = mark())) return rc;
+      p.prog = s.linked ? programs::link_outer(second, s.link, 2) : second;
+      p.njobs = 0;
+      rc = launch_any(es, bn_sel, kPresumNone, p, s.grid, stream);
+      break;
+    }
+    default:
+      return kErrNotSupported;
+  }
+  if (rc) return rc;
+  return mark();
+}
 
-  int grid = L.tiles_m * L.tiles_n;
-  int cap = a.sm_limit > 0 ? a.sm_limit : sm_count();
-  if (a.pair) cap /= 2;  // one pair per two SMs
-  if (grid > cap) grid = cap;
-  const int bn_sel = a.pair ? -1 : L.bn;  // -1 routes launch_any to the CTA-pair kernels (grid = pairs)
+}  // namespace
+
+int run(const GemmArgs& a, void* workspace, size_t workspace_size, cudaStream_t stream) {
+  int rc = can_implement(a);
+  if (rc) return rc;
+  const Layout L = make_layout(a);
+  if (!workspace) return kErrWorkspaceNull;
+  if (workspace_size < L.total || (reinterpret_cast<uintptr_t>(workspace) & 255)) return kErrWorkspaceNull;
+  char* wsb = static_cast<char*>(workspace);
+  const int es = L.esize;
+
+  int* status = reinterpret_cast<int*>(wsb + L.off_status);
+  cudaError_t ce = cudaMemsetAsync(status, 0, 256, stream);
+  if (ce != cudaSuccess) return static_cast<int>(ce);
 
   int nev = 0;
   auto mark = [&]() -> int {
     if (!a.events) return 0;
     return static_cast<int>(cudaEventRecord(a.events[nev++], stream));
   };
+
+  LaunchSpec s;
+  memset(&s, 0, sizeof(s));
+  s.es = es;
+  s.bn = L.bn;
+  s.pair = a.pair;
+  s.grid = L.tiles_m * L.tiles_n;
+  int cap = a.sm_limit > 0 ? a.sm_limit : sm_count();
+  if (a.pair) cap /= 2;  // one pair per two SMs
+  if (s.grid > cap) s.grid = cap;
+  s.mq = L.mq; s.nq = L.nq; s.kq = L.kq;
+  s.tiles_m = L.tiles_m; s.tiles_n = L.tiles_n; s.num_k = L.num_k;
+  s.presum_a = wsb + L.off_pa;
+  s.presum_b = wsb + L.off_pb;
+  for (int i = 0; i < 4; ++i) s.ws_inner[i] = reinterpret_cast<float*>(wsb + L.off_ws[i]);
+  s.quadrant_floats = L.quadrant_floats;
+  s.status = status;
+
   if ((rc = mark())) return rc;
-  switch (a.variant) {
-    case kCubic:
-      p.prog = programs::level0();
-      rc = launch_any(es, bn_sel, kPresumNone, p, grid, stream);
-      break;
-    case kFusedPresum:
-      p.prog = programs::level1_full(true);
-      rc = launch_any(es, bn_sel, kPresumFeed, p, grid, stream);
-      break;
-    case kInterleavedPresum:
-      p.prog = programs::level1_first();
-      rc = launch_any(es, bn_sel, kPresumJob, p, grid, stream);
-      if (rc) return rc;
-      if ((rc = mark())) return rc;
-      p.prog = getenv("SB200_L1_PLAIN") ? programs::level1_second() : programs::level1_second_taps();
-      rc = launch_any(es, bn_sel, kPresumNone, p, grid, stream);
-      break;
-    default:
-      return kErrNotSupported;
+  if (L.level < 2) {
+    s.variant = a.variant;
+    s.a = View{a.a, static_cast<long long>(a.k), a.m, a.k};
+    s.b = View{a.b, static_cast<long long>(a.n), a.k, a.n};
+    s.out = static_cast<char*>(a.d);
+    s.ldo = a.n;
+    return launch_group(s, stream, mark);
   }
-  if (rc) return rc;
-  return mark();
+
+  // ---- level 2: seven level-1 groups over half-size operands (the reference's StrassenGemmLevel2 wires seven
+  // child operators the same way, include/cutlass/gemm/device/strassen_gemm.h:1300-2008), chained through three
+  // fp32 buffers instead of interim matrices in the output type.
+  const int mh = 2 * L.mq, nh = 2 * L.nq, kh = 2 * L.kq;
+  const char* A = static_cast<const char*>(a.a);
+  const char* B = static_cast<const char*>(a.b);
+  char* D = static_cast<char*>(a.d);
+  const long long lda = a.k, ldb = a.n, ldd = a.n;
+  char* opa = wsb + L.off_opa;
+  char* opb = wsb + L.off_opb;
+  float* X[3];
+  for (int i = 0; i < 3; ++i) X[i] = reinterpret_cast<float*>(wsb + L.off_x[i]);
+  auto operand_a = [&](int code) -> View {
+    if (code < 4) return View{A + ((code >> 1) * mh * lda + (code & 1) * kh) * es, lda, mh, kh};
+    return View{opa + size_t(code - 4) * mh * kh * es, static_cast<long long>(kh), mh, kh};
+  };
+  auto operand_b = [&](int code) -> View {
+    if (code < 4) return View{B + ((code >> 1) * kh * ldb + (code & 1) * nh) * es, ldb, kh, nh};
+    return View{opb + size_t(code - 4) * kh * nh * es, static_cast<long long>(nh), kh, nh};
+  };
+  const programs::Level2Child* children = programs::level2_children();
+  s.variant = kInterleavedPresum;
+  s.linked = true;
+  for (int c = 0; c < 7; ++c) {
+    const programs::Level2Child& ch = children[c];
+    s.a = operand_a(ch.a);
+    s.b = operand_b(ch.b);
+    s.link = ch.link;
+    s.out = ch.out_quadrant >= 0 ? D + ((ch.out_quadrant >> 1) * mh * ldd + (ch.out_quadrant & 1) * nh) * es : nullptr;
+    s.ldo = ldd;
+    s.outer_dst = ch.dst >= 0 ? X[ch.dst] : nullptr;
+    s.outer_src = ch.src >= 0 ? X[ch.src] : nullptr;
+    s.outer_src2 = ch.src2 >= 0 ? X[ch.src2] : nullptr;
+    s.extra_dst = ch.extra_dst >= 0 ? X[ch.extra_dst] : nullptr;
+    // The outer presums are formed by the presum warps of the first two groups, which read only raw quadrants: the A
+    // side rides on m0's first launch, the B side on m1's; the first group that reads them (m2) starts afterwards.
+    s.n_more_jobs = 0;
+    if (c < 2) {
+      PresumSideJob& j = s.more_jobs[0];
+      for (int q = 0; q < 4; ++q)
+        j.src[q] = c == 0 ? static_cast<const void*>(A + ((q >> 1) * mh * lda + (q & 1) * kh) * es)
+                          : static_cast<const void*>(B + ((q >> 1) * kh * ldb + (q & 1) * nh) * es);
+      j.ld = c == 0 ? lda : ldb;
+      j.dst = c == 0 ? opa : opb;
+      j.rows = c == 0 ? mh : kh;
+      j.cols = c == 0 ? kh : nh;
+      j.side = c;
+      s.n_more_jobs = 1;
+    }
+    if ((rc = launch_group(s, stream, mark))) return rc;
+  }
+  return kOk;
 }
 
 int read_status(void* workspace, cudaStream_t stream) {

@@ -14,7 +14,9 @@
 //   warp 0      TMA producer: non-multicast tiled bulk loads of single-term operands into the stage ring
 //   warp 1      MMA issuer: tcgen05.mma (kind::f16 or kind::tf32, fp32 accumulators in TMEM), one thread
 //   warps 2-5   epilogue: tcgen05.ld -> registers -> postsum -> vectorised global stores
-//   warps 6-9   presum warps (modes FEED and JOB only)
+//   warps 6-7   two more TMA producers: the three take the k-steps in turn (loads of one warp complete one after
+//               the other, about 240 ns apiece on B200 whatever their size; loads of different warps overlap)
+//   warps 8-11  presum warps (modes FEED and JOB only)
 //                 FEED: form multi-term operand tiles S/T = +-X +-Y ... in shared memory, in the swizzled
 //                       layout the MMA reads, straight from the raw quadrant values (one rounding)
 //                 JOB : materialise the eight presums into a global workspace while the MMA pipeline of the
@@ -47,6 +49,17 @@ struct View {
   int cols;         // extent of the contiguous dimension
 };
 
+// One presum job: the four combinations of one operand's quadrants, written as four packed matrices.
+//   side 0 (A): S1, S2, A02, A1S2      side 1 (B): B10, B31, S3, S3B2
+struct PresumSideJob {
+  const void* src[4];  // quadrant base pointers, row-major with a common leading dimension
+  long long ld;        // in elements
+  void* dst;           // [4][rows][cols], packed
+  int rows, cols;      // extent of one quadrant
+  int side;
+};
+constexpr int SB200_MAX_JOBS = 4;
+
 struct KernelParams {
   CUtensorMap tmap[SB200_NUM_VIEWS];
   View view[SB200_NUM_VIEWS];
@@ -58,14 +71,14 @@ struct KernelParams {
   int tiles_m, tiles_n;     // tile grid over one output quadrant
   int num_k;                // k-steps per product
   int band;                 // raster band height in tiles
+  int b_blocked;            // 1: the B tensor maps are 3-D [128-byte column block][row][block]: one load per B tile
   int* status;              // device status word, 0 = ok
   int debug_flags;          // measurement aids: bit 0 = issue no MMA, bit 1 = issue no TMA load (results are garbage)
   int prefetch_dist;        // > 0: the producer asks L2 for the operand tiles this many k-steps ahead
   long long* prof;          // measurement aid (CTA-pair kernels): 8 cycle counters per CTA, or null
-  // presum job (mode JOB): pa = S1,S2,A02,A1S2 packed [4][mq][kq]; pb = B10,B31,S3,S3B2 packed [4][kq][nq]
-  void* job_pa;
-  void* job_pb;
-  int job_mq, job_nq, job_kq;
+  // presum jobs (mode JOB), run by the presum warps of the whole grid one after the other
+  int njobs;
+  PresumSideJob job[SB200_MAX_JOBS];
   sb200_program_t prog;
 };
 
@@ -90,7 +103,8 @@ struct KernelConfig {
   static constexpr int SLOTS = 512 / BN;
   static constexpr int TMEM_COLS = 512;
   static constexpr int PRESUM_WARPS = (MODE == kPresumNone) ? 0 : 4;
-  static constexpr int THREADS = (6 + PRESUM_WARPS) * 32;
+  static constexpr int FIRST_PRESUM_WARP = 8;
+  static constexpr int THREADS = (FIRST_PRESUM_WARP + PRESUM_WARPS) * 32;
   static constexpr int BAR_BYTES = 1024;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + kStagingBytes + 1024;  // +1024: manual alignment slack
   static constexpr uint32_t FMT = (ESIZE == 2) ? 0u : 2u;
@@ -100,6 +114,9 @@ struct KernelConfig {
   static constexpr uint32_t B_LAYOUT_TYPE = B_SWZ32 ? 1u : 2u;
   static constexpr uint32_t B_SBO = B_SWZ32 ? 512u : 1024u;
 };
+
+// k-steps whose full-barrier waits the MMA issuer of the CTA-pair kernels batches (at most the number of stages)
+constexpr int kWaitGroup = 3;
 
 struct TileCoord {
   int i, j, id;
@@ -224,69 +241,61 @@ __device__ __forceinline__ void build_operand_tile(uint32_t smem_tile, uint32_t 
   }
 }
 
-// Global presum job: every presum thread of the grid takes 16-byte vector positions of the quadrant space in a
-// grid-stride loop; per position it reads the four raw quadrant vectors and writes the four presums.
+// Global presum jobs: every presum thread of the grid takes 16-byte vector positions of a quadrant in a grid-stride
+// loop; per position it reads the four raw quadrant vectors and writes the four combinations of that side.
+// Sums are formed from the raw values left to right in fp32 and rounded once (VecAcc).
 template <int ESIZE>
-__device__ __forceinline__ void presum_job(const KernelParams& p, int gtid, int gthreads) {
+__device__ __forceinline__ void presum_side_job(const PresumSideJob& j, int gtid, int gthreads) {
   constexpr int EPV = 16 / ESIZE;
-  // A side: S1 = A2 + A3, S2 = S1 - A0, A02 = A0 - A2, A1S2 = A1 - S2
-  {
-    const int vec_per_row = p.job_kq / EPV;
-    const long long total = static_cast<long long>(p.job_mq) * vec_per_row;
-    const long long q = static_cast<long long>(p.job_mq) * p.job_kq;  // elements per presum matrix
-    const View a0 = p.view[SB200_VIEW_A0 + 0], a1 = p.view[SB200_VIEW_A0 + 1], a2 = p.view[SB200_VIEW_A0 + 2],
-               a3 = p.view[SB200_VIEW_A0 + 3];
-    char* out = static_cast<char*>(p.job_pa);
-    for (long long v = gtid; v < total; v += gthreads) {
-      int r = static_cast<int>(v / vec_per_row);
-      int c = static_cast<int>(v - static_cast<long long>(r) * vec_per_row) * EPV;
-      uint4 x0 = ptx::ldg_nc_v4(static_cast<const char*>(a0.ptr) + (r * a0.ld + c) * ESIZE);
-      uint4 x1 = ptx::ldg_nc_v4(static_cast<const char*>(a1.ptr) + (r * a1.ld + c) * ESIZE);
-      uint4 x2 = ptx::ldg_nc_v4(static_cast<const char*>(a2.ptr) + (r * a2.ld + c) * ESIZE);
-      uint4 x3 = ptx::ldg_nc_v4(static_cast<const char*>(a3.ptr) + (r * a3.ld + c) * ESIZE);
-      long long o = (static_cast<long long>(r) * p.job_kq + c) * ESIZE;
+  const int vec_per_row = j.cols / EPV;
+  const long long total = static_cast<long long>(j.rows) * vec_per_row;
+  const long long q = static_cast<long long>(j.rows) * j.cols * ESIZE;  // bytes per result matrix
+  const char* s0 = static_cast<const char*>(j.src[0]);
+  const char* s1 = static_cast<const char*>(j.src[1]);
+  const char* s2 = static_cast<const char*>(j.src[2]);
+  const char* s3 = static_cast<const char*>(j.src[3]);
+  char* out = static_cast<char*>(j.dst);
+  for (long long v = gtid; v < total; v += gthreads) {
+    const int r = static_cast<int>(v / vec_per_row);
+    const int c = static_cast<int>(v - static_cast<long long>(r) * vec_per_row) * EPV;
+    const long long in = (r * j.ld + c) * ESIZE;
+    const uint4 x0 = ptx::ldg_nc_v4(s0 + in);
+    const uint4 x1 = ptx::ldg_nc_v4(s1 + in);
+    const uint4 x2 = ptx::ldg_nc_v4(s2 + in);
+    const uint4 x3 = ptx::ldg_nc_v4(s3 + in);
+    const long long o = (static_cast<long long>(r) * j.cols + c) * ESIZE;
+    if (j.side == 0) {
+      // A side: S1 = A2 + A3, S2 = S1 - A0, A02 = A0 - A2, A1S2 = A1 - S2
       VecAcc<ESIZE> s;
       s.set(x2, 1); s.add(x3, 1);                                   // S1
-      *reinterpret_cast<uint4*>(out + 0 * q * ESIZE + o) = s.pack();
+      *reinterpret_cast<uint4*>(out + 0 * q + o) = s.pack();
       s.add(x0, -1);                                                // S2 = S1 - A0 (unrounded S1)
-      *reinterpret_cast<uint4*>(out + 1 * q * ESIZE + o) = s.pack();
+      *reinterpret_cast<uint4*>(out + 1 * q + o) = s.pack();
       VecAcc<ESIZE> t;
       t.set(x0, 1); t.add(x2, -1);                                  // A02
-      *reinterpret_cast<uint4*>(out + 2 * q * ESIZE + o) = t.pack();
-      // A1S2 = A1 - S2 with the unrounded S2: -(S2) + A1
-      VecAcc<ESIZE> u;
+      *reinterpret_cast<uint4*>(out + 2 * q + o) = t.pack();
+      VecAcc<ESIZE> u;                                              // A1S2 = A1 - S2 with the unrounded S2
       u.set(x2, -1); u.add(x3, -1); u.add(x0, 1); u.add(x1, 1);
-      *reinterpret_cast<uint4*>(out + 3 * q * ESIZE + o) = u.pack();
-    }
-  }
-  // B side: B10 = B1 - B0, B31 = B3 - B1, S3 = B31 + B0, S3B2 = S3 - B2
-  {
-    const int vec_per_row = p.job_nq / EPV;
-    const long long total = static_cast<long long>(p.job_kq) * vec_per_row;
-    const long long q = static_cast<long long>(p.job_kq) * p.job_nq;
-    const View b0 = p.view[SB200_VIEW_B0 + 0], b1 = p.view[SB200_VIEW_B0 + 1], b2 = p.view[SB200_VIEW_B0 + 2],
-               b3 = p.view[SB200_VIEW_B0 + 3];
-    char* out = static_cast<char*>(p.job_pb);
-    for (long long v = gtid; v < total; v += gthreads) {
-      int r = static_cast<int>(v / vec_per_row);
-      int c = static_cast<int>(v - static_cast<long long>(r) * vec_per_row) * EPV;
-      uint4 x0 = ptx::ldg_nc_v4(static_cast<const char*>(b0.ptr) + (r * b0.ld + c) * ESIZE);
-      uint4 x1 = ptx::ldg_nc_v4(static_cast<const char*>(b1.ptr) + (r * b1.ld + c) * ESIZE);
-      uint4 x2 = ptx::ldg_nc_v4(static_cast<const char*>(b2.ptr) + (r * b2.ld + c) * ESIZE);
-      uint4 x3 = ptx::ldg_nc_v4(static_cast<const char*>(b3.ptr) + (r * b3.ld + c) * ESIZE);
-      long long o = (static_cast<long long>(r) * p.job_nq + c) * ESIZE;
+      *reinterpret_cast<uint4*>(out + 3 * q + o) = u.pack();
+    } else {
+      // B side: B10 = B1 - B0, B31 = B3 - B1, S3 = B31 + B0, S3B2 = S3 - B2
       VecAcc<ESIZE> s;
       s.set(x1, 1); s.add(x0, -1);                                  // B10
-      *reinterpret_cast<uint4*>(out + 0 * q * ESIZE + o) = s.pack();
+      *reinterpret_cast<uint4*>(out + 0 * q + o) = s.pack();
       VecAcc<ESIZE> t;
       t.set(x3, 1); t.add(x1, -1);                                  // B31
-      *reinterpret_cast<uint4*>(out + 1 * q * ESIZE + o) = t.pack();
+      *reinterpret_cast<uint4*>(out + 1 * q + o) = t.pack();
       t.add(x0, 1);                                                 // S3 = B31 + B0 (unrounded B31)
-      *reinterpret_cast<uint4*>(out + 2 * q * ESIZE + o) = t.pack();
+      *reinterpret_cast<uint4*>(out + 2 * q + o) = t.pack();
       t.add(x2, -1);                                                // S3B2 = S3 - B2 (unrounded S3)
-      *reinterpret_cast<uint4*>(out + 3 * q * ESIZE + o) = t.pack();
+      *reinterpret_cast<uint4*>(out + 3 * q + o) = t.pack();
     }
   }
+}
+
+template <int ESIZE>
+__device__ __forceinline__ void presum_job(const KernelParams& p, int gtid, int gthreads) {
+  for (int j = 0; j < p.njobs; ++j) presum_side_job<ESIZE>(p.job[j], gtid, gthreads);
 }
 
 // ---------------------------------------------------------------------------------------------------
@@ -335,10 +344,13 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_kernel(const 
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_holder;
 
-  if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer
+  if (warp == 0 || (warp >= 6 && warp < Cfg::FIRST_PRESUM_WARP)) {
+    // ------------------------------------------------------------------ TMA producers (take the k-steps in turn)
     if (lane == 0) {
-      for (int v = 0; v < SB200_NUM_VIEWS; ++v) ptx::prefetch_tmap(&p.tmap[v]);
+      const uint32_t my_turn = (warp == 0) ? 0u : static_cast<uint32_t>(warp - 5);
+      uint32_t turn = 0;
+      if (warp == 0)
+        for (int v = 0; v < SB200_NUM_VIEWS; ++v) ptx::prefetch_tmap(&p.tmap[v]);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -352,6 +364,12 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_kernel(const 
           const CUtensorMap* ma = &p.tmap[pr.a.view[0]];
           const CUtensorMap* mb = &p.tmap[pr.b.view[0]];
           for (int kk = 0; kk < p.num_k; ++kk) {
+            const bool mine = (turn == my_turn);
+            if (++turn == 3u) turn = 0;
+            if (!mine) {
+              if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+              continue;
+            }
             if (!ptx::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) {
               raise_abort(p, abort_flag, kStatusProducerTimeout);
               ok = false;
@@ -368,9 +386,13 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_kernel(const 
             }
             if (a_tma) ptx::tma_load_2d(sa, ma, &full_bar[stage], kk * BK, tile.i * Cfg::BM);
             if (b_tma) {
+              if (p.b_blocked) {
+                ptx::tma_load_3d(sb, mb, &full_bar[stage], 0, kk * BK, tile.j * Cfg::NBLK);
+              } else {
 #pragma unroll
-              for (int nb = 0; nb < Cfg::NBLK; ++nb)
-                ptx::tma_load_2d(sb + nb * Cfg::BLK_BYTES, mb, &full_bar[stage], tile.j * BN + nb * BK, kk * BK);
+                for (int nb = 0; nb < Cfg::NBLK; ++nb)
+                  ptx::tma_load_2d(sb + nb * Cfg::BLK_BYTES, mb, &full_bar[stage], tile.j * BN + nb * BK, kk * BK);
+              }
             }
             if (++stage == STAGES) { stage = 0; phase ^= 1u; }
           }
@@ -401,26 +423,39 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_kernel(const 
           }
           const uint32_t idesc = ptx::umma_idesc(Cfg::FMT, Cfg::BM, BN, pr.negate != 0);
           const uint32_t tmem_d = tmem_base + slot * BN;
-          for (int kk = 0; kk < p.num_k; ++kk) {
-            if (!ptx::mbar_wait(&full_bar[stage], phase, abort_flag)) {
-              raise_abort(p, abort_flag, kStatusMmaTimeout);
-              ok = false;
-              break;
+          // k-steps could be taken several at a time as in the CTA-pair kernels, but with only four 48 KiB stages
+          // that costs more ring latency than it saves (measured: groups of 3 give 1007 instead of 1293 TFLOPS at
+          // 8192^3 f16), so the group is one k-step here
+          constexpr int kGroup = 1;
+          for (int kk = 0; kk < p.num_k; kk += kGroup) {
+            const int group = min(kGroup, p.num_k - kk);
+            int s_w = stage;
+            uint32_t ph_w = phase;
+            for (int g = 0; g < group; ++g) {
+              if (!ptx::mbar_wait(&full_bar[s_w], ph_w, abort_flag)) {
+                raise_abort(p, abort_flag, kStatusMmaTimeout);
+                ok = false;
+                break;
+              }
+              if (++s_w == STAGES) { s_w = 0; ph_w ^= 1u; }
             }
+            if (!ok) break;
             ptx::tc_fence_after_sync();
-            const uint32_t a_addr = ptx::smem_u32(smem + stage * Cfg::STAGE_BYTES);
-            const uint32_t b_addr = a_addr + Cfg::A_BYTES;
+            for (int g = 0; g < group; ++g) {
+              const uint32_t a_addr = ptx::smem_u32(smem + stage * Cfg::STAGE_BYTES);
+              const uint32_t b_addr = a_addr + Cfg::A_BYTES;
 #pragma unroll
-            for (int ks = 0; ks < Cfg::KSUB && !(p.debug_flags & 1); ++ks) {
-              const uint64_t adesc = ptx::umma_desc_sw128(a_addr + ks * 32, 16, 1024);
-              const uint64_t bdesc =
-                  ptx::umma_desc_sw128(b_addr + ks * Cfg::UMMA_K * 128, Cfg::BLK_BYTES, Cfg::B_SBO, Cfg::B_LAYOUT_TYPE);
-              const uint32_t acc = (kk > 0 || ks > 0 || pr.accumulate) ? 1u : 0u;
-              if (ESIZE == 2) ptx::umma_f16(tmem_d, adesc, bdesc, idesc, acc);
-              else ptx::umma_tf32(tmem_d, adesc, bdesc, idesc, acc);
+              for (int ks = 0; ks < Cfg::KSUB && !(p.debug_flags & 1); ++ks) {
+                const uint64_t adesc = ptx::umma_desc_sw128(a_addr + ks * 32, 16, 1024);
+                const uint64_t bdesc =
+                    ptx::umma_desc_sw128(b_addr + ks * Cfg::UMMA_K * 128, Cfg::BLK_BYTES, Cfg::B_SBO, Cfg::B_LAYOUT_TYPE);
+                const uint32_t acc = (kk + g > 0 || ks > 0 || pr.accumulate) ? 1u : 0u;
+                if (ESIZE == 2) ptx::umma_f16(tmem_d, adesc, bdesc, idesc, acc);
+                else ptx::umma_tf32(tmem_d, adesc, bdesc, idesc, acc);
+              }
+              ptx::umma_commit(&empty_bar[stage]);
+              if (++stage == STAGES) { stage = 0; phase ^= 1u; }
             }
-            ptx::umma_commit(&empty_bar[stage]);
-            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
           }
           if (ok && pr.commit) ptx::umma_commit(&slot_full[slot]);
         }
@@ -437,25 +472,28 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_kernel(const 
       const uint32_t sx = p.prog.alternate_slots ? (iter & 1u) : 0u;
       for (int es = 0; ok && es < p.prog.nepilogues; ++es) {
         const sb200_epilogue_t& ep = p.prog.epilogue[es];
-        for (int s = 0; s < SLOTS; ++s) {
-          if ((ep.wait_full_mask >> s) & 1u) {
-            const uint32_t slot = s ^ sx;
-            bool got = ptx::mbar_wait(&slot_full[slot], (full_bits >> slot) & 1u, abort_flag);
-            got = __all_sync(0xffffffffu, got);
-            if (!got) {
-              if (lane == 0) raise_abort(p, abort_flag, kStatusEpilogueTimeout);
-              ok = false;
-              break;
+        auto wait_slots = [&]() -> bool {
+          for (int s = 0; s < SLOTS; ++s) {
+            if ((ep.wait_full_mask >> s) & 1u) {
+              const uint32_t slot = s ^ sx;
+              bool got = ptx::mbar_wait(&slot_full[slot], (full_bits >> slot) & 1u, abort_flag);
+              got = __all_sync(0xffffffffu, got);
+              if (!got) {
+                if (lane == 0) raise_abort(p, abort_flag, kStatusEpilogueTimeout);
+                return false;
+              }
+              full_bits ^= (1u << slot);
             }
-            full_bits ^= (1u << slot);
           }
-        }
-        if (!ok) break;
-        ptx::tc_fence_after_sync();
+          ptx::tc_fence_after_sync();
+          return true;
+        };
         const long long tile_off = static_cast<long long>(tile.id) * (128 * BN);
-        if (!(p.debug_flags & 32))  // bit 5: measurement aid, skip the epilogue body
-          epilogue_body<ESIZE, BN, Cfg::NSRC_MAX>(p.out, p.ldo, p.out_rows, p.out_cols, p.ws, ep, sx, tmem_base, quarter, lane, tile_off,
-                                   tile.i * 128, tile.j * BN, staging + (warp - 2) * kStagingWarpBytes);
+        ok = epilogue_body<ESIZE, BN, Cfg::NSRC_MAX>(p.out, p.ldo, p.out_rows, p.out_cols, p.ws, ep, sx, tmem_base, quarter,
+                                                     lane, tile_off, tile.i * 128, tile.j * BN,
+                                                     staging + (warp - 2) * kStagingWarpBytes,
+                                                     (p.debug_flags & 32) != 0, wait_slots);
+        if (!ok) break;
         ptx::tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) {
@@ -467,7 +505,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_kernel(const 
   } else {
     // ------------------------------------------------------------------ presum warps
     if (Cfg::MODE == kPresumFeed) {
-      const int ptid = threadIdx.x - 6 * 32;
+      const int ptid = threadIdx.x - Cfg::FIRST_PRESUM_WARP * 32;
       constexpr int PT = Cfg::PRESUM_WARPS * 32;
       int stage = 0;
       uint32_t phase = 0;
@@ -501,7 +539,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_kernel(const 
         }
       }
     } else if (Cfg::MODE == kPresumJob) {
-      const int ptid = threadIdx.x - 6 * 32;
+      const int ptid = threadIdx.x - Cfg::FIRST_PRESUM_WARP * 32;
       constexpr int PT = Cfg::PRESUM_WARPS * 32;
       presum_job<ESIZE>(p, blockIdx.x * PT + ptid, gridDim.x * PT);
     }

@@ -46,7 +46,9 @@ struct PairConfig {
   static constexpr int SLOTS = 2;
   static constexpr int TMEM_COLS = 512;
   static constexpr int PRESUM_WARPS = (MODE == kPresumNone) ? 0 : 4;
-  static constexpr int THREADS = (7 + PRESUM_WARPS) * 32;  // warps 0-5 as in sw_kernel.cuh, warp 6 = B producer
+  // warps 0-5 as in sw_kernel.cuh; warps 6 and 7 = more TMA producers (see the producer section); presum warps follow
+  static constexpr int FIRST_PRESUM_WARP = 8;
+  static constexpr int THREADS = (FIRST_PRESUM_WARP + PRESUM_WARPS) * 32;
   static constexpr int BAR_BYTES = 1024;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + kStagingBytes + 1024;
   static constexpr uint32_t FMT = (ESIZE == 2) ? 0u : 2u;
@@ -105,14 +107,17 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_holder;
 
-  if (warp == 0 || warp == 6) {
+  if (warp == 0 || (warp >= 6 && warp < Cfg::FIRST_PRESUM_WARP)) {
     // ------------------------------------------------------------------ TMA producers (both CTAs)
-    // Two single-thread producers share the work so that neither's instruction stream limits the load rate:
-    // warp 0 loads the A tiles and (leader only) arms the full barrier with the pair's byte total,
-    // warp 6 loads the B tiles.  Both wait on the same stage-empty barrier.
+    // Measured on B200: the tiled loads of ONE warp complete one after the other, about 240 ns apiece whatever the
+    // box holds (4 to 32 KiB), while loads of different warps overlap.  A k-step lasts about 370 ns, so a single
+    // producer issuing two or three loads per k-step cannot keep up.  Three single-thread producers (warps 0, 6, 7)
+    // take the k-steps in turn; each issues the A load and the B load of its k-step (B is one 3-D load when the B
+    // maps are blocked) and, in the leader CTA, arms the full barrier with the pair's bytes.
     if (lane == 0) {
-      const bool is_a = (warp == 0);
-      if (is_a)
+      const uint32_t my_turn = (warp == 0) ? 0u : static_cast<uint32_t>(warp - 5);
+      uint32_t turn = 0;
+      if (warp == 0)
         for (int v = 0; v < SB200_NUM_VIEWS; ++v) ptx::prefetch_tmap(&p.tmap[v]);
       int stage = 0;
       uint32_t phase = 0;
@@ -132,8 +137,15 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
           const CUtensorMap* mb = &p.tmap[pr.b.view[0]];
           const bool no_load_all = (p.debug_flags & 2) != 0;
           for (int kk = 0; kk < p.num_k; ++kk) {
+            const bool mine = (turn == my_turn);
+            if (++turn == 3u) turn = 0;
+            if (!mine) {
+              if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+              continue;
+            }
             const long long tw = SB200_CLOCK();
-            if (!ptx::mbar_wait_cluster(&empty_bar[stage], phase ^ 1u, abort_flag)) {
+            // the stage-empty barrier is signalled by tcgen05.commit only: no cluster-scope acquire needed
+            if (!ptx::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) {
               raise_abort(p, abort_flag, kStatusProducerTimeout);
               ok = false;
               break;
@@ -144,23 +156,26 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
             uint8_t* sb = sa + Cfg::A_BYTES;
             // measurement aids: bit 1 = never load; bit 3 = load only while the ring fills for the first time
             const bool no_load = no_load_all || ((p.debug_flags & 8) != 0 && (w != pair || ps > 0 || kk >= STAGES));
-            if (is_a) {
-              if (rank == 0) {
-                if (tx && !no_load) ptx::mbar_arrive_expect_tx(&full_bar[stage], tx);
-                else ptx::mbar_arrive(&full_bar[stage]);
-              }
-              if (a_tma && !no_load) ptx::tma_load_2d_pair(sa, ma, &full_bar[stage], kk * BK, row0);
-            } else if (b_tma && !no_load) {
+            if (rank == 0) {
+              if (tx && !no_load) ptx::mbar_arrive_expect_tx(&full_bar[stage], tx);
+              else ptx::mbar_arrive(&full_bar[stage]);
+            }
+            if (a_tma && !no_load) ptx::tma_load_2d_pair(sa, ma, &full_bar[stage], kk * BK, row0);
+            if (b_tma && !no_load) {
+              if (p.b_blocked) {
+                ptx::tma_load_3d_pair(sb, mb, &full_bar[stage], 0, kk * BK, col0 / BK);
+              } else {
 #pragma unroll
-              for (int nb = 0; nb < Cfg::NBLK; ++nb)
-                ptx::tma_load_2d_pair(sb + nb * Cfg::BLK_BYTES, mb, &full_bar[stage], col0 + nb * BK, kk * BK);
+                for (int nb = 0; nb < Cfg::NBLK; ++nb)
+                  ptx::tma_load_2d_pair(sb + nb * Cfg::BLK_BYTES, mb, &full_bar[stage], col0 + nb * BK, kk * BK);
+              }
             }
             pw_issue += SB200_CLOCK() - tw2;
             if (++stage == STAGES) { stage = 0; phase ^= 1u; }
           }
         }
       }
-      if (p.prof && is_a) {
+      if (p.prof && warp == 0) {
         p.prof[blockIdx.x * 8 + 7] = pw_issue;
         p.prof[blockIdx.x * 8 + 3] = pw_empty;
         p.prof[blockIdx.x * 8 + 4] = SB200_CLOCK() - pt0;
@@ -200,16 +215,20 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
           const uint64_t adesc0 = ptx::umma_desc_sw128(ptx::smem_u32(smem), 16, 1024);
           const uint64_t bdesc0 =
               ptx::umma_desc_sw128(ptx::smem_u32(smem) + Cfg::A_BYTES, Cfg::BLK_BYTES, Cfg::B_SBO, Cfg::B_LAYOUT_TYPE);
-          // k-steps are taken two at a time: both full-barrier waits first, then 4 MMAs + stage release for each.
-          // (Measured on B200: with one wait per 4 MMAs the tensor pipe idles ~48 cycles per k-step; with the
-          // waits of two k-steps issued back to back ahead of their 8 MMAs it does not.)
-          for (int kk = 0; kk < p.num_k; kk += 2) {
-            const int group = (kk + 1 < p.num_k) ? 2 : 1;
+          // k-steps are taken kWaitGroup at a time: all their full-barrier waits first, then 4 MMAs + stage release
+          // for each.  (Measured on B200, 8192^3 f16: groups of 1 / 2 / 3 / 4 / 6 k-steps give 1175 / 1227 / 1256 /
+          // 1237 / 1168 TFLOPS: batching the waits keeps the MMA queue fed, too large a group adds ring latency.)
+          for (int kk = 0; kk < p.num_k; kk += kWaitGroup) {
+            const int group = min(kWaitGroup, p.num_k - kk);
             int s_w = stage;
             uint32_t ph_w = phase;
             const long long tw = SB200_CLOCK();
             for (int g = 0; g < group; ++g) {
-              if (!ptx::mbar_wait_cluster(&full_bar[s_w], ph_w, abort_flag)) {
+              // in FEED mode the peer's presum warps arrive on this barrier after writing their own shared memory
+              // through the generic proxy: that hand-over needs the cluster-scope acquire; TMA-only stages do not
+              const bool got_full = (Cfg::MODE == kPresumFeed) ? ptx::mbar_wait_cluster(&full_bar[s_w], ph_w, abort_flag)
+                                                               : ptx::mbar_wait(&full_bar[s_w], ph_w, abort_flag);
+              if (!got_full) {
                 raise_abort(p, abort_flag, kStatusMmaTimeout);
                 ok = false;
                 break;
@@ -261,27 +280,30 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
       const uint32_t sx = p.prog.alternate_slots ? (iter & 1u) : 0u;
       for (int es = 0; ok && es < p.prog.nepilogues; ++es) {
         const sb200_epilogue_t& ep = p.prog.epilogue[es];
-        for (int s0 = 0; s0 < SLOTS; ++s0) {
-          if ((ep.wait_full_mask >> s0) & 1u) {
-            const uint32_t s = s0 ^ sx;
-            const long long tw = SB200_CLOCK();
-            bool got = ptx::mbar_wait_cluster(&slot_full[s], (full_bits >> s) & 1u, abort_flag);
-            ew_full += SB200_CLOCK() - tw;
-            got = __all_sync(0xffffffffu, got);
-            if (!got) {
-              if (lane == 0) raise_abort(p, abort_flag, kStatusEpilogueTimeout);
-              ok = false;
-              break;
+        auto wait_slots = [&]() -> bool {
+          for (int s0 = 0; s0 < SLOTS; ++s0) {
+            if ((ep.wait_full_mask >> s0) & 1u) {
+              const uint32_t s = s0 ^ sx;
+              const long long tw = SB200_CLOCK();
+              bool got = ptx::mbar_wait_cluster(&slot_full[s], (full_bits >> s) & 1u, abort_flag);
+              ew_full += SB200_CLOCK() - tw;
+              got = __all_sync(0xffffffffu, got);
+              if (!got) {
+                if (lane == 0) raise_abort(p, abort_flag, kStatusEpilogueTimeout);
+                return false;
+              }
+              full_bits ^= (1u << s);
             }
-            full_bits ^= (1u << s);
           }
-        }
-        if (!ok) break;
-        ptx::tc_fence_after_sync();
+          ptx::tc_fence_after_sync();
+          return true;
+        };
         const long long tile_off = (static_cast<long long>(tile.id) * 2 + rank) * (128 * BN);
-        if (!(p.debug_flags & 32))  // bit 5: measurement aid, skip the epilogue body
-          epilogue_body<ESIZE, BN, Cfg::NSRC_MAX>(p.out, p.ldo, p.out_rows, p.out_cols, p.ws, ep, sx, tmem_base, quarter, lane, tile_off,
-                                   tile.i * Cfg::PAIR_M + static_cast<int>(rank) * Cfg::BM, tile.j * BN, staging + (warp - 2) * kStagingWarpBytes);
+        ok = epilogue_body<ESIZE, BN, Cfg::NSRC_MAX>(p.out, p.ldo, p.out_rows, p.out_cols, p.ws, ep, sx, tmem_base, quarter,
+                                                     lane, tile_off, tile.i * Cfg::PAIR_M + static_cast<int>(rank) * Cfg::BM,
+                                                     tile.j * BN, staging + (warp - 2) * kStagingWarpBytes,
+                                                     (p.debug_flags & 32) != 0, wait_slots);
+        if (!ok) break;
         ptx::tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) {
@@ -292,10 +314,10 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
     }
     (void)ew_full;
     (void)et0;
-  } else if (warp >= 7) {
+  } else if (warp >= Cfg::FIRST_PRESUM_WARP) {
     // ------------------------------------------------------------------ presum warps (both CTAs)
     if (Cfg::MODE == kPresumFeed) {
-      const int ptid = threadIdx.x - 7 * 32;
+      const int ptid = threadIdx.x - Cfg::FIRST_PRESUM_WARP * 32;
       constexpr int PT = Cfg::PRESUM_WARPS * 32;
       int stage = 0;
       uint32_t phase = 0;
@@ -330,7 +352,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
         }
       }
     } else if (Cfg::MODE == kPresumJob) {
-      const int ptid = threadIdx.x - 7 * 32;
+      const int ptid = threadIdx.x - Cfg::FIRST_PRESUM_WARP * 32;
       constexpr int PT = Cfg::PRESUM_WARPS * 32;
       presum_job<ESIZE>(p, blockIdx.x * PT + ptid, gridDim.x * PT);
     }

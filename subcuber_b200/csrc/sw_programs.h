@@ -59,7 +59,7 @@ inline void add_product(sb200_program_t& pg, sb200_operand_t a, sb200_operand_t 
   if (a.nterms > 1 || b.nterms > 1) pg.needs_feed = 1;
 }
 
-// slots/signs: up to 3 (slot, sign) pairs; srcs: up to 2 workspace ids; masks are bit sets of slot ids.
+// slots/signs: up to 3 (slot, sign) pairs; srcs: up to 3 workspace ids; masks are bit sets of slot ids.
 inline void add_epilogue(sb200_program_t& pg, int nslots, const int* slots, const int* signs, int nsrc, const int* srcs,
                          int wait_mask, int release_mask, int dst_kind, int dst) {
   sb200_epilogue_t& e = pg.epilogue[pg.nepilogues];
@@ -150,26 +150,112 @@ inline sb200_program_t level1_second() {
 }
 
 // Launch 2 of 2, variant with short taps: whenever the next product must wait for an epilogue step, that step is
-// only a copy of a slot into an fp32 hand-off tile (no global reads); the sums that need hand-off tiles from
-// global memory (C1, C3) run afterwards while the MMA pipeline is already on the next product.
-//   hand-offs: M4, U = M2, V = M2 + M3  (M0 comes from launch 1)
+// only a copy of a slot into an fp32 hand-off tile plus at most one hand-off read (requested before the wait, see
+// epilogue.cuh); the sums that need more hand-off tiles (C1, C3) run while the MMA pipeline is already on the next
+// product.  No step reads more than two hand-off tiles, which leaves one source free for the level above.
+//   hand-offs: M4, U = M0 + M2, V = M0 + (M2 + M3)   (M0 comes from launch 1)
 inline sb200_program_t level1_second_taps() {
   sb200_program_t pg;
   memset(&pg, 0, sizeof(pg));
   const int sP[] = {P}, sQ[] = {Q}, pos1[] = {1};
-  const int srcC1[] = {WS_M0, WS_U, WS_M4}, srcC3[] = {WS_M0, WS_V, WS_M4}, srcM0[] = {WS_M0};
+  const int srcC1[] = {WS_U, WS_M4}, srcC3[] = {WS_V, WS_M4}, srcM0[] = {WS_M0};
   add_product(pg, term1(PS1), term1(PB10), Q, 0, 0, 1, 1);             // Q  = M4
   add_product(pg, term1(PS2), term1(PS3), P, 0, 0, 1, 1);              // P  = M2
-  add_epilogue(pg, 1, sQ, pos1, 0, nullptr, mQ, mQ, 1, WS_M4);         // ws[M4] = Q        (overlaps M2)
-  add_epilogue(pg, 1, sP, pos1, 0, nullptr, mP, mP, 1, WS_U);          // ws[U]  = P        (overlaps M5)
+  add_epilogue(pg, 1, sQ, pos1, 0, nullptr, mQ, mQ, 1, WS_M4);         // ws[M4] = Q             (overlaps M2)
+  add_epilogue(pg, 1, sP, pos1, 1, srcM0, mP, mP, 1, WS_U);            // ws[U]  = M0 + P        (tap before M3)
   add_product(pg, term1(PA1S2), term1(B3), Q, 0, 0, 1, 1);             // Q  = M5
   add_product(pg, term1(PA02), term1(PB31), P, 1, 0, 1, 1);            // P += M3
-  add_epilogue(pg, 1, sQ, pos1, 3, srcC1, mQ, mQ, 0, 1);               // C1 = M0 + U + M4 + Q   (overlaps M3)
-  add_epilogue(pg, 1, sP, pos1, 0, nullptr, mP, mP, 1, WS_V);          // ws[V]  = P        (short tap before M6)
+  add_epilogue(pg, 1, sQ, pos1, 2, srcC1, mQ, mQ, 0, 1);               // C1 = U + M4 + Q        (overlaps M3)
+  add_epilogue(pg, 1, sP, pos1, 1, srcM0, mP, mP, 1, WS_V);            // ws[V]  = M0 + P        (tap before M6)
   add_product(pg, term1(A3), term1(PS3B2), P, 1, 1, 1, 1);             // P -= M6
-  add_epilogue(pg, 0, nullptr, nullptr, 3, srcC3, 0, 0, 0, 3);         // C3 = M0 + V + M4      (overlaps M6)
+  add_epilogue(pg, 0, nullptr, nullptr, 2, srcC3, 0, 0, 0, 3);         // C3 = V + M4            (overlaps M6)
   add_epilogue(pg, 1, sP, pos1, 1, srcM0, mP, mP, 0, 2);               // C2 = M0 + P
   return pg;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Level 2: the outer recursion step applies the same seven-product scheme to half-size blocks, and each outer
+// product is a level-1 GEMM (two launches) of this library.  The outer postsums are not separate passes: they ride
+// on the epilogue steps of the level-1 launches.  `OuterLink` says how one level-1 GEMM is tied into the outer
+// chain; `link_outer` rewrites a level-1 program accordingly (hand-off indices: tile_program.h).
+struct OuterLink {
+  int dst_fp32;  // 1: the four output quadrants stay in fp32 hand-off buffers ws[4 + q] instead of going to out[q]
+  int src;       // 1: ws[8 + q] is added to output quadrant q
+  int extra;     // 1: also ws[16 + q] = ws[4 + q] + ws[12 + q];  2: also out[q] = ws[4 + q] + ws[12 + q]
+  int negate;    // 1: every product enters with a minus sign (the outer product is subtracted)
+};
+
+// `launch` is 1 or 2 (first / second launch of the interleaved-presum plan).  All extra steps run in launch 2:
+// the one for quadrant 0 (whose sum launch 1 wrote) first, while the epilogue warps wait for the first product.
+inline sb200_program_t link_outer(const sb200_program_t& base, const OuterLink& l, int launch) {
+  sb200_program_t pg = base;
+  pg.nepilogues = 0;
+  memset(pg.epilogue, 0, sizeof(pg.epilogue));
+  memset(pg.epilogue_after, 0, sizeof(pg.epilogue_after));
+  if (l.negate)
+    for (int i = 0; i < pg.nproducts; ++i) pg.product[i].negate ^= 1;
+  auto push = [&](const sb200_epilogue_t& e, int after) {
+    pg.epilogue[pg.nepilogues] = e;
+    pg.epilogue_after[pg.nepilogues] = (uint8_t)after;
+    pg.nepilogues++;
+  };
+  auto extra = [&](int q, int after) {
+    sb200_epilogue_t e;
+    memset(&e, 0, sizeof(e));
+    e.nsrc = 2;
+    e.src[0] = (uint8_t)(SB200_WS_OUTER_DST + q);
+    e.src[1] = (uint8_t)(SB200_WS_OUTER_SRC2 + q);
+    e.dst_kind = (uint8_t)(l.extra == 1 ? 1 : 0);
+    e.dst = (uint8_t)(l.extra == 1 ? SB200_WS_EXTRA_DST + q : q);
+    push(e, after);
+  };
+  if (launch == 2 && l.extra) extra(0, 0);
+  for (int i = 0; i < base.nepilogues; ++i) {
+    sb200_epilogue_t e = base.epilogue[i];
+    if (e.dst_kind != 0) {
+      push(e, base.epilogue_after[i]);
+      continue;
+    }
+    const int q = e.dst;
+    if (l.src) e.src[e.nsrc++] = (uint8_t)(SB200_WS_OUTER_SRC + q);
+    if (l.dst_fp32) {
+      e.dst_kind = 1;
+      e.dst = (uint8_t)(SB200_WS_OUTER_DST + q);
+    }
+    push(e, base.epilogue_after[i]);
+    if (launch == 2 && l.extra) extra(q, base.epilogue_after[i]);
+  }
+  return pg;
+}
+
+// The seven level-1 GEMMs of a level-2 run, in execution order.  Operand codes: 0..3 = raw outer quadrant,
+// 4..7 = outer presum (A side: S1, S2, A02, A1S2; B side: B10, B31, S3, S3B2).  Outer chain buffers X0, X1, X2
+// (fp32, tile-contiguous, one half-size matrix each):
+//   M0:           X0 = M0
+//   M1:  C0 = X0 + M1
+//   M2:           X1 = X0 + M2              (U)
+//   M4:           X2 = M4,  X0 = X2 + X1    (U + M4)
+//   M5:  C1 = X0 + M5
+//   M3:           X0 = X1 + M3,  C3 = X0 + X2
+//   M6:  C2 = X0 - M6
+struct Level2Child {
+  const char* name;
+  int a, b;          // operand codes
+  OuterLink link;
+  int dst, src, src2, extra_dst;  // X buffer ids (-1: none)
+  int out_quadrant;               // output quadrant of C written in the output type (-1: none)
+};
+inline const Level2Child* level2_children() {
+  static const Level2Child kChildren[7] = {
+      {"m0", 0, 0, {1, 0, 0, 0}, 0, -1, -1, -1, -1},
+      {"m1", 1, 2, {0, 1, 0, 0}, -1, 0, -1, -1, 0},
+      {"m2", 5, 6, {1, 1, 0, 0}, 1, 0, -1, -1, -1},
+      {"m4", 4, 4, {1, 0, 1, 0}, 2, -1, 1, 0, -1},
+      {"m5", 7, 3, {0, 1, 0, 0}, -1, 0, -1, -1, 1},
+      {"m3", 6, 5, {1, 1, 2, 0}, 0, 1, 2, -1, 3},
+      {"m6", 3, 7, {0, 1, 0, 1}, -1, 0, -1, -1, 2},
+  };
+  return kChildren;
 }
 
 }  // namespace programs

@@ -20,17 +20,35 @@
 
 #define SB200_MAX_TERMS 4
 #define SB200_MAX_PRODUCTS 8
-#define SB200_MAX_EPILOGUES 8
+#define SB200_MAX_EPILOGUES 12
 #define SB200_MAX_SLOT_TERMS 3
 #define SB200_MAX_SRC_TERMS 3
 #define SB200_NUM_VIEWS 16
-#define SB200_NUM_WS 4
+#define SB200_NUM_WS 20
 
 // Operand view table (index into KernelParams::tmap / ::view):
 //   0..3   A quadrants A0,A1,A2,A3 (level 0: view 0 is the whole A)
 //   4..7   materialised A presums S1,S2,A02,A1S2
 //   8..11  B quadrants B0,B1,B2,B3 (level 0: view 8 is the whole B)
 //   12..15 materialised B presums B10,B31,S3,S3B2
+// fp32 hand-off buffer table (index into KernelParams::ws).  Every buffer is tile-contiguous and private to the
+// CTA that owns the tile.  0..3 belong to the level-1 program itself.  The others connect a level-1 launch to the
+// level above it (level 2: the launch computes one quadrant-product of the outer recursion step, and its four
+// output quadrants q = 0..3 continue the outer postsum chain):
+//   4 + q    outer destination: the launch's output quadrant q kept in fp32 for later launches
+//   8 + q    outer source added to output quadrant q
+//   12 + q   second outer source, used only by the extra step below
+//   16 + q   fp32 destination of the extra step
+// An "extra step" is an epilogue step without slots that follows the step writing output quadrant q: it adds
+// ws[4 + q] (just written by the same threads) and ws[12 + q] and writes either ws[16 + q] or output quadrant q.
+enum {
+  SB200_WS_INNER = 0,
+  SB200_WS_OUTER_DST = 4,
+  SB200_WS_OUTER_SRC = 8,
+  SB200_WS_OUTER_SRC2 = 12,
+  SB200_WS_EXTRA_DST = 16,
+};
+
 enum {
   SB200_VIEW_A0 = 0,
   SB200_VIEW_PA0 = 4,

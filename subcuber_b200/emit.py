@@ -151,19 +151,178 @@ def level1_second_program(ms) -> tp.Program:
 
 
 def level1_second_taps_program(ms) -> tp.Program:
-    """Launch 2 with short taps: a product never waits for an epilogue step that reads global memory.  Hand-offs:
-    m4, u = m2, v = m2 + m3 (and m0 from launch 1); c1 and c3 are summed from hand-offs off the critical path."""
+    """Launch 2 with short taps: a product only ever waits for a step that copies a slot to a hand-off tile (adding at
+    most one hand-off tile, requested before the wait).  Hand-offs: m4, u = m0 + m2, v = m0 + (m2 + m3), and m0 from
+    launch 1; c1 and c3 are summed off the critical path.  No step reads more than two hand-off tiles."""
     b = ProgramBuilder(_products_by_name(ms), fly=False)
     b.product("m4", Q).product("m2", P)
     b.epilogue([Q], [], wait=[Q], release=[Q], dst_kind=1, dst=WS_M4)
-    b.epilogue([P], [], wait=[P], release=[P], dst_kind=1, dst=WS_U)
+    b.epilogue([P], [WS_M0], wait=[P], release=[P], dst_kind=1, dst=WS_U)            # u = m0 + m2
     b.product("m5", Q).product("m3", P, accumulate=1)
-    b.epilogue([Q], [WS_M0, WS_U, WS_M4], wait=[Q], release=[Q], dst_kind=0, dst=1)  # c1 = m0 + m2 + m4 + m5
-    b.epilogue([P], [], wait=[P], release=[P], dst_kind=1, dst=WS_V)
+    b.epilogue([Q], [WS_U, WS_M4], wait=[Q], release=[Q], dst_kind=0, dst=1)         # c1 = u + m4 + m5
+    b.epilogue([P], [WS_M0], wait=[P], release=[P], dst_kind=1, dst=WS_V)            # v = m0 + m2 + m3
     b.product("m6", P, accumulate=1, negate=1)
-    b.epilogue([], [WS_M0, WS_V, WS_M4], wait=[], release=[], dst_kind=0, dst=3)     # c3 = m0 + m2 + m3 + m4
+    b.epilogue([], [WS_V, WS_M4], wait=[], release=[], dst_kind=0, dst=3)            # c3 = v + m4
     b.epilogue([P], [WS_M0], wait=[P], release=[P], dst_kind=0, dst=2)               # c2 = m0 + m2 + m3 - m6
     return b.pg
+
+
+# ------------------------------------------------------------------------------------------------------ level 2
+# One outer recursion step: the same algorithm over half-size blocks, every outer product a level-1 group (two
+# launches).  The outer postsums ride on the groups' epilogue steps through three fp32 chain buffers X0, X1, X2:
+#   m0: X0 = m0 | m1: c0 = X0 + m1 | m2: X1 = X0 + m2 | m4: X2 = m4, X0 = X2 + X1 | m5: c1 = X0 + m5
+#   m3: X0 = X1 + m3, c3 = X0 + X2 | m6: c2 = X0 - m6
+# Fields: link = (dst_fp32, src, extra, negate) as in csrc/sw_programs.h `OuterLink`; dst/src/src2/extra_dst = X ids.
+LEVEL2_CHAIN = [
+    # name, link,          dst, src, src2, extra_dst, out quadrant
+    ("m0", (1, 0, 0, 0), 0, -1, -1, -1, -1),
+    ("m1", (0, 1, 0, 0), -1, 0, -1, -1, 0),
+    ("m2", (1, 1, 0, 0), 1, 0, -1, -1, -1),
+    ("m4", (1, 0, 1, 0), 2, -1, 1, 0, -1),
+    ("m5", (0, 1, 0, 0), -1, 0, -1, -1, 1),
+    ("m3", (1, 1, 2, 0), 0, 1, 2, -1, 3),
+    ("m6", (0, 1, 0, 1), -1, 0, -1, -1, 2),
+]
+
+
+def operand_code(expr: Matrix) -> int:
+    """0..3 = raw quadrant, 4..7 = presum (the order of the presum workspace), for an operand of a DSL product."""
+    if not isinstance(expr, BinOp):
+        return QUADRANT_VIEW[expr.name] % 8
+    return 4 + PRESUM_VIEW[expr.name] % 4
+
+
+def level2_children(ms) -> List[dict]:
+    """The seven level-1 groups of a level-2 run in execution order, operands taken from the DSL products."""
+    by_name = _products_by_name(ms)
+    out = []
+    for name, link, dst, src, src2, extra_dst, quadrant in LEVEL2_CHAIN:
+        node = by_name[name]
+        out.append({"name": name, "a": operand_code(node.op1), "b": operand_code(node.op2), "link": link, "dst": dst,
+                    "src": src, "src2": src2, "extra_dst": extra_dst, "out_quadrant": quadrant})
+    return out
+
+
+def link_outer(base: tp.Program, link: Tuple[int, int, int, int], launch: int) -> tp.Program:
+    """Tie a level-1 program into the outer chain (same rewriting as csrc/sw_programs.h `link_outer`)."""
+    dst_fp32, src, extra, negate = link
+    pg = tp.Program.from_buffer_copy(tp.to_bytes(base))
+    C.memset(C.byref(pg.epilogue), 0, C.sizeof(pg.epilogue))
+    C.memset(C.byref(pg.epilogue_after), 0, C.sizeof(pg.epilogue_after))
+    pg.nepilogues = 0
+    if negate:
+        for i in range(pg.nproducts):
+            pg.product[i].negate ^= 1
+
+    def push(e: tp.Epilogue, after: int):
+        C.memmove(C.byref(pg.epilogue[pg.nepilogues]), C.byref(e), C.sizeof(tp.Epilogue))
+        pg.epilogue_after[pg.nepilogues] = after
+        pg.nepilogues += 1
+
+    def push_extra(q: int, after: int):
+        e = tp.Epilogue()
+        e.nsrc = 2
+        e.src[0], e.src[1] = tp.WS_OUTER_DST + q, tp.WS_OUTER_SRC2 + q
+        e.dst_kind = 1 if extra == 1 else 0
+        e.dst = tp.WS_EXTRA_DST + q if extra == 1 else q
+        push(e, after)
+
+    if launch == 2 and extra:
+        push_extra(0, 0)
+    for i in range(base.nepilogues):
+        e = tp.Epilogue.from_buffer_copy(bytes(memoryview(base.epilogue[i])))
+        after = base.epilogue_after[i]
+        if e.dst_kind != 0:
+            push(e, after)
+            continue
+        q = e.dst
+        if src:
+            e.src[e.nsrc] = tp.WS_OUTER_SRC + q
+            e.nsrc += 1
+        if dst_fp32:
+            e.dst_kind, e.dst = 1, tp.WS_OUTER_DST + q
+        push(e, after)
+        if launch == 2 and extra:
+            push_extra(q, after)
+    return pg
+
+
+def run_program_numeric(pg: tp.Program, views: Dict[int, np.ndarray], ws: Dict[int, np.ndarray],
+                        out: Dict[int, np.ndarray]) -> None:
+    """Execute a tile program on whole blocks with numpy (one 'tile' = one block): products in order, every epilogue
+    step as soon as the product it follows has been issued.  Protocol questions are `check_program`'s business."""
+    slots: Dict[int, np.ndarray] = {}
+
+    def operand(op):
+        return sum(int(op.coef[t]) * views[op.view[t]] for t in range(op.nterms))
+
+    e = 0
+    for i in range(pg.nproducts):
+        pr = pg.product[i]
+        val = operand(pr.a) @ operand(pr.b) * (-1 if pr.negate else 1)
+        slots[pr.slot] = slots[pr.slot] + val if pr.accumulate else val
+        while e < pg.nepilogues and pg.epilogue_after[e] <= i:
+            ep = pg.epilogue[e]
+            acc = 0
+            for t in range(ep.nsrc):
+                acc = acc + ws[ep.src[t]]
+            for t in range(ep.nslots):
+                acc = acc + int(ep.slot_sign[t]) * slots[ep.slot[t]]
+            if ep.dst_kind == 1:
+                ws[ep.dst] = acc
+            else:
+                out[ep.dst] = acc
+            e += 1
+    assert e == pg.nepilogues
+
+
+def _quadrants(x: np.ndarray) -> List[np.ndarray]:
+    r, c = x.shape[0] // 2, x.shape[1] // 2
+    return [x[:r, :c], x[:r, c:], x[r:, :c], x[r:, c:]]
+
+
+def _presums(quads: List[np.ndarray], side: str) -> List[np.ndarray]:
+    names = ["S1", "S2", "A02", "A1S2"] if side == "a" else ["B10", "B31", "S3", "S3B2"]
+    return [sum(cf * quads[i] for i, cf in enumerate(tp.VIEW_COEF[nm])) for nm in names]
+
+
+def simulate_level1(first: tp.Program, second: tp.Program, a: np.ndarray, b: np.ndarray, ws: Dict[int, np.ndarray],
+                    out: Dict[int, np.ndarray]) -> None:
+    qa, qb = _quadrants(a), _quadrants(b)
+    views = {i: v for i, v in enumerate(qa + _presums(qa, "a") + qb + _presums(qb, "b"))}
+    run_program_numeric(first, views, ws, out)
+    run_program_numeric(second, views, ws, out)
+
+
+def simulate_level2(programs: Dict[str, tp.Program], children: List[dict], a: np.ndarray, b: np.ndarray) -> np.ndarray:
+    """The whole level-2 launch plan on integer matrices: returns the product it computes."""
+    qa, qb = _quadrants(a), _quadrants(b)
+    oa, ob = qa + _presums(qa, "a"), qb + _presums(qb, "b")
+    x: Dict[int, Dict[int, np.ndarray]] = {0: {}, 1: {}, 2: {}}   # chain buffer -> inner quadrant -> block
+    mh, nh = a.shape[0] // 2, b.shape[1] // 2
+    c = np.zeros((a.shape[0], b.shape[1]), dtype=a.dtype)
+    for ch in children:
+        ws: Dict[int, np.ndarray] = {}
+        for q in range(4):
+            if ch["src"] >= 0:
+                ws[tp.WS_OUTER_SRC + q] = x[ch["src"]][q]
+            if ch["src2"] >= 0:
+                ws[tp.WS_OUTER_SRC2 + q] = x[ch["src2"]][q]
+        out: Dict[int, np.ndarray] = {}
+        simulate_level1(programs[f"level2_{ch['name']}_launch1"], programs[f"level2_{ch['name']}_launch2"],
+                        oa[ch["a"]], ob[ch["b"]], ws, out)
+        for q in range(4):
+            if ch["dst"] >= 0:
+                x[ch["dst"]][q] = ws[tp.WS_OUTER_DST + q]
+            if ch["extra_dst"] >= 0:
+                x[ch["extra_dst"]][q] = ws[tp.WS_EXTRA_DST + q]
+        if ch["out_quadrant"] >= 0:
+            oq = ch["out_quadrant"]
+            r0, c0 = (oq >> 1) * mh, (oq & 1) * nh
+            for q in range(4):
+                rr, cc = r0 + (q >> 1) * (mh // 2), c0 + (q & 1) * (nh // 2)
+                c[rr:rr + mh // 2, cc:cc + nh // 2] = out[q]
+    return c
 
 
 def all_programs() -> Dict[str, tp.Program]:
@@ -178,6 +337,9 @@ def all_programs() -> Dict[str, tp.Program]:
         "level1_first": level1_first_program(ms),
         "level1_second": level1_second_program(ms),
         "level1_second_taps": level1_second_taps_program(ms),
+        **{f"level2_{ch['name']}_launch{launch}":
+           link_outer(level1_first_program(ms) if launch == 1 else level1_second_taps_program(ms), ch["link"], launch)
+           for ch in level2_children(ms) for launch in (1, 2)},
     }
 
 
@@ -198,6 +360,17 @@ def verify_programs(programs: Dict[str, tp.Program]) -> None:
         r2 = tp.check_program(programs[name], level=1, ws_in=r1["ws"], expect=[1, 2, 3])
         for q in (1, 2, 3):
             assert np.array_equal(r2["outputs"][q], want[q]), (name, q)
+    # level 2: the protocol of every rewritten program, then the whole 14-launch plan on integer matrices
+    _, ms = strassen_winograd(4, 4, 4)
+    children = level2_children(ms)
+    outer = {i: np.zeros((4, 4), dtype=np.int64) for i in range(tp.WS_OUTER_DST, tp.NUM_WS)}
+    for ch in children:
+        r1 = tp.check_program(programs[f"level2_{ch['name']}_launch1"], level=1, ws_in=outer, algebra=False)
+        tp.check_program(programs[f"level2_{ch['name']}_launch2"], level=1, ws_in={**outer, **r1["ws"]}, algebra=False)
+    rng = np.random.default_rng(7)
+    a = rng.integers(-3, 4, size=(8, 12)).astype(np.int64)
+    b = rng.integers(-3, 4, size=(12, 16)).astype(np.int64)
+    assert np.array_equal(simulate_level2(programs, children, a, b), a @ b)
 
 
 # --------------------------------------------------------------------------------------------- schedule -> plan
@@ -223,6 +396,15 @@ def plan_for_schedule(schedule: list, level: int, mnk: Tuple[int, int, int], dty
                              {"program": "level1_second_taps", "products": ["m4", "m2", "m5", "m3", "m6"],
                               "presum": "read from the workspace by TMA"}]}
     plan["mnk"] = [m, n, k]
+    if level == 2:
+        from .algos.strassen_winograd_level1 import strassen_winograd
+
+        _, ms = strassen_winograd(4, 4, 4)
+        plan["kernel"] = f"blackwell_{dtype}_sw_level2_2sm"
+        plan["groups"] = [{"product": ch["name"], "a": ch["a"], "b": ch["b"],
+                           "launches": [f"level2_{ch['name']}_launch1", f"level2_{ch['name']}_launch2"],
+                           "outer_presum_job": {0: "A side", 1: "B side"}.get(i)}
+                          for i, ch in enumerate(level2_children(ms))]
     if level > 1:
         plan["level"] = level
         plan["children"] = {}
@@ -264,7 +446,8 @@ def program_to_c(name: str, pg: tp.Program) -> str:
 def artefacts(schedule: list, fusion: Optional[dict], plan: dict) -> Dict[str, str]:
     programs = all_programs()
     verify_programs(programs)
-    used = sorted({launch["program"] for launch in plan.get("launches", [])})
+    used = sorted({launch["program"] for launch in plan.get("launches", [])} |
+                  {name for group in plan.get("groups", []) for name in group["launches"]})
     files = {"schedule.json": json.dumps({"schedule": schedule, "fusion": fusion, "plan": plan}, indent=1, default=list)}
     files["tile_programs.json"] = json.dumps({name: program_to_dict(programs[name]) for name in used}, indent=1)
     files["sw_tile_programs.inc"] = "".join(program_to_c(name, programs[name]) for name in used)

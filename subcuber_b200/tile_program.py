@@ -20,9 +20,11 @@ import numpy as np
 
 MAX_TERMS = 4
 MAX_PRODUCTS = 8
-MAX_EPILOGUES = 8
+MAX_EPILOGUES = 12
 MAX_SLOT_TERMS = 3
 MAX_SRC_TERMS = 3
+NUM_WS = 20
+WS_OUTER_DST, WS_OUTER_SRC, WS_OUTER_SRC2, WS_EXTRA_DST = 4, 8, 12, 16
 
 VIEW_NAMES = ["A0", "A1", "A2", "A3", "S1", "S2", "A02", "A1S2", "B0", "B1", "B2", "B3", "B10", "B31", "S3", "S3B2"]
 # coefficient vectors of every view over (A0..A3) or (B0..B3):
@@ -99,10 +101,12 @@ def _operand_vector(op: Operand) -> np.ndarray:
 
 
 def check_program(pg: Program, level: int, nslots: int = 2, ws_in: Optional[Dict[int, np.ndarray]] = None,
-                  expect: Optional[Sequence[int]] = None, tiles: int = 3) -> Dict[str, object]:
+                  expect: Optional[Sequence[int]] = None, tiles: int = 3, algebra: bool = True) -> Dict[str, object]:
     """Validate `pg`.  Returns {"outputs": {quadrant: 4x4 matrix}, "ws": {...}, "bubbles": n}.
 
     ws_in: symbolic contents of workspace buffers written by an earlier launch.
+    algebra: False checks the hand-over protocol only (programs tied into an outer recursion step do not produce
+             the plain level-1 outputs).
     expect: output quadrants this program must write (default: all four at level 1, quadrant 0 at level 0).
     """
     np_, ne = pg.nproducts, pg.nepilogues
@@ -193,6 +197,9 @@ def check_program(pg: Program, level: int, nslots: int = 2, ws_in: Optional[Dict
         raise ProgramError(f"deadlock: mma at {mma_pos}, epilogue at {epi_pos}")
     if any(f != 1 for f in free[:nslots]) or any(f != 0 for f in full[:nslots]):
         raise ProgramError("credits do not return to their initial state after a tile")
+
+    if not algebra:
+        return {"outputs": outputs, "ws": ws, "bubbles": bubbles // max(1, tiles)}
 
     # ---- algebra ---------------------------------------------------------------------------------
     want = {}

@@ -18,6 +18,8 @@ L1_F16 = ["blackwell_f16_sw_interleaved_presum", "blackwell_f16_sw_fused_presum"
           "blackwell_f16_sw_interleaved_presum_2sm", "blackwell_f16_sw_fused_presum_2sm"]
 L1_F32 = ["blackwell_f32_sw_interleaved_presum", "blackwell_f32_sw_fused_presum",
           "blackwell_f32_sw_interleaved_presum_2sm", "blackwell_f32_sw_fused_presum_2sm"]
+L2_F16 = ["blackwell_f16_sw_level2", "blackwell_f16_sw_level2_2sm"]
+L2_F32 = ["blackwell_f32_sw_level2", "blackwell_f32_sw_level2_2sm"]
 L0_F16 = ["blackwell_f16_cubic_128x256", "blackwell_f16_cubic_128x128", "blackwell_f16_cubic_2sm_256x256"]
 L0_F32 = ["blackwell_f32_cubic_128x256", "blackwell_f32_cubic_128x128", "blackwell_f32_cubic_2sm_256x256"]
 
@@ -27,7 +29,7 @@ def _dt(kernel):
 
 
 def _level(kernel):
-    return 0 if "cubic" in kernel else 1
+    return 0 if "cubic" in kernel else (2 if "level2" in kernel else 1)
 
 
 def _run(kernel, a_np, b_np, device):
@@ -66,6 +68,61 @@ def test_bit_exact_on_harness_values(kernel, shape, oracle, cuda_device):
     truth = a.astype(np.float64) @ b.astype(np.float64)
     if dt == "f32":
         assert np.array_equal(got.astype(np.float64), truth)
+
+
+@pytest.mark.parametrize("kernel", L2_F16 + L2_F32)
+@pytest.mark.parametrize("shape", [(512, 1024, 256), (544, 1056, 288), (4, 32, 32), (260, 96, 160), (1024, 1024, 512),
+                                   (2048, 1536, 512)])
+def test_level2_bit_exact_on_harness_values(kernel, shape, oracle, cuda_device):
+    """49 products as seven chained level-1 groups.  On the harness' value set every presum of both recursion steps
+    (at most 16 terms of magnitude <= 4 in steps of 0.25) and every partial sum is exact, so the result equals the
+    oracle's level-2 recursion bit for bit, whatever the order of the additions."""
+    from subcuber_b200 import inputs
+
+    m, n, k = shape
+    dt = _dt(kernel)
+    a, b = inputs.operands(dt, "harness", m, n, k, seed=m + n + k)
+    got = _run(kernel, a, b, cuda_device)
+    want = oracle.sw_gemm(dt, 2, a, b)
+    assert not np.isnan(got).any()
+    assert np.array_equal(got, want), f"{np.count_nonzero(got != want)} elements differ from the oracle"
+    if dt == "f32":
+        assert np.array_equal(got.astype(np.float64), a.astype(np.float64) @ b.astype(np.float64))
+
+
+@pytest.mark.parametrize("kernel", L2_F16)
+@pytest.mark.parametrize("shape", [(1024, 1024, 1024), (1536, 1280, 2304)])
+def test_level2_uniform_inputs_f16(kernel, shape, oracle, cuda_device):
+    """Error gate at level 2: no worse than 1.5x the level-1 routine applied recursively with interim results rounded
+    to the output type at every hop, which is what the reference's level-2 operator does
+    (include/cutlass/gemm/device/strassen_gemm.h:1807-1914); this path keeps the interim sums in fp32."""
+    from subcuber_b200 import inputs
+
+    m, n, k = shape
+    a, b = inputs.operands("f16", "uniform1", m, n, k, seed=9)
+    got = _run(kernel, a, b, cuda_device)
+    truth = a.astype(np.float64) @ b.astype(np.float64)
+    ref = oracle.sw_gemm("f16", 2, a, b, interim_round=True)
+    ref32 = oracle.sw_gemm("f16", 2, a, b)
+    err, ref_err, ref32_err = _rel_fro(got, truth), _rel_fro(ref, truth), _rel_fro(ref32, truth)
+    assert err <= 1.5 * ref_err, f"rel. Frobenius error {err:.3e} vs reference routine {ref_err:.3e}"
+    assert err <= 1.5 * ref32_err, f"rel. Frobenius error {err:.3e} vs fp32-interim recursion {ref32_err:.3e}"
+    diff = np.abs(got.astype(np.float64) - ref32.astype(np.float64))
+    assert ((diff <= 7.0) | (diff <= 1e-2 * np.abs(ref32.astype(np.float64)))).all()
+
+
+@pytest.mark.parametrize("kernel", L2_F32)
+def test_level2_uniform_inputs_tf32(kernel, oracle, cuda_device):
+    from subcuber_b200 import inputs
+
+    m, n, k = 1024, 768, 1280
+    a, b = inputs.operands("f32", "normal", m, n, k, seed=8)
+    got = _run(kernel, a, b, cuda_device)
+    truth = a.astype(np.float64) @ b.astype(np.float64)
+    model = oracle.sw_gemm("tf32", 2, a, b)
+    err, model_err = _rel_fro(got, truth), _rel_fro(model, truth)
+    assert err <= 4.0 * model_err + 1e-6, f"{err:.3e} vs TF32 model {model_err:.3e}"
+    assert err < 6e-3
 
 
 @pytest.mark.parametrize("kernel", L1_F16 + L1_F32)
@@ -291,7 +348,7 @@ def test_timed_call_reports_every_launch(lib, cuda_device):
     d = torch.empty((1024, 1024), dtype=torch.float16, device=cuda_device)
     name = "blackwell_f16_sw_interleaved_presum"
     ws = runner.Workspace(name, 1024, 1024, 1024, cuda_device)
-    ms = (C.c_float * 3)()
+    ms = (C.c_float * 16)()
     nl = C.c_int(0)
     rc = lib.sb200_gemm_timed(name.encode(), a.data_ptr(), b.data_ptr(), d.data_ptr(), 1024, 1024, 1024, ws.ptr,
                               ws.nbytes, None, ms, C.byref(nl))
