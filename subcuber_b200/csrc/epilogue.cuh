@@ -27,31 +27,112 @@ constexpr int kStagingBytes = 4 * kStagingWarpBytes;
 
 struct KernelParams;
 
-// `wait_slots()` blocks until the slots in ep.wait_full_mask are ready and returns false when the wait was given up.
+// ---------------------------------------------------------------------------------------------------------------
+// K-split tiles (WorkUnit in sw_kernel.cuh): what an epilogue step does in each half.
+//   * a step that leaves the tile (output quadrant, or a buffer of the level above: index >= SB200_WS_OUTER_DST)
+//     - first half: sums its slots and level-1 hand-offs only and writes the partial sum to the split buffer
+//       (`redirect`), then raises the flag of its warp;
+//     - second half: waits for that flag and adds the partial sum (`add_partial`) to everything the step lists;
+//   * an extra step of the level above (no slots, reads ws[4 + q]) runs in the second half only (`skip`);
+//   * steps between level-1 hand-off tiles run in both halves on private tiles.
+struct SplitStep {
+  bool skip, redirect, add_partial;
+  int q;  // output quadrant the step belongs to
+};
+__device__ __forceinline__ SplitStep split_step(const sb200_epilogue_t& ep, int part, int nparts) {
+  SplitStep s;
+  s.skip = s.redirect = s.add_partial = false;
+  s.q = 0;
+  if (nparts == 1) return s;
+  const bool leaves = ep.dst_kind == 0 || ep.dst >= SB200_WS_OUTER_DST;
+  const bool extra = ep.nslots == 0 && ep.nsrc > 0 && ep.src[0] >= SB200_WS_OUTER_DST;
+  s.q = (ep.dst_kind == 0 ? ep.dst : ep.dst - SB200_WS_OUTER_DST) & 3;
+  if (part == 0) {
+    s.skip = extra;
+    s.redirect = leaves && !extra;
+  } else {
+    s.add_partial = leaves && !extra;
+  }
+  return s;
+}
+
+// Every lane has written its part of the partial tile: make the writes visible device-wide, then publish.
+__device__ __forceinline__ void raise_flag(int* flag, int epoch, int lane) {
+  __threadfence();
+  __syncwarp();
+  if (lane == 0) asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(flag), "r"(epoch) : "memory");
+}
+// Bounded wait (2 s, or until another thread of the CTA gives up) for the flag of the matching warp of the other half.
+__device__ __forceinline__ bool wait_flag(const int* flag, int epoch, volatile int* abort_flag) {
+  const uint64_t t0 = ptx::globaltimer_ns();
+  uint32_t polls = 0;
+  while (true) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    const bool all_ready = __all_sync(0xffffffffu, v == epoch);
+    if (all_ready) return true;
+    if ((++polls & 63u) == 0) {
+      const bool give_up = *abort_flag != 0 || ptx::globaltimer_ns() - t0 > 2000000000ull;
+      if (__any_sync(0xffffffffu, give_up)) return false;
+    }
+    __nanosleep(100);
+  }
+}
+
+// `wait_slots()` blocks until the slots in ep.wait_full_mask are ready (and, for the second half of a split tile,
+// until the first half's partial sum is published) and returns false when the wait was given up.
+//   tile_off / outer_off: float offsets of this unit's tile in the level-1 hand-off buffers (ws index < 4) and in the
+//                         buffers of the level above (index >= 4)
+//   redirect: non-null = first half of a split tile: write the fp32 partial sum there, skip the outer sources
+//   late_src: non-null = second half: one more fp32 source, readable only after wait_slots()
 template <int ESIZE, int BN, int NSRC_MAX, typename WaitFn>
 __device__ __forceinline__ bool epilogue_body(void* const* out, long long ldo, int out_rows, int out_cols,
                                               float* const* ws, const sb200_epilogue_t& ep, uint32_t sx,
                                               uint32_t tmem_base, int quarter, int lane, long long tile_off,
-                                              int grow_tile, int gcol_tile, uint32_t staging_warp, bool skip_body,
+                                              long long outer_off, int grow_tile, int gcol_tile, uint32_t staging_warp,
+                                              float* redirect, const float* late_src, bool skip_body,
                                               WaitFn wait_slots) {
   if (skip_body) return wait_slots();  // measurement aid
   constexpr int NCHUNK = BN / 32;
   const int row = quarter * 32 + lane;
-  const int nsrc = ep.nsrc;
+  // sources: the step's list (outer sources, which come last, are left to the second half of a split tile), then the
+  // late source
+  int nsrc = ep.nsrc;
+  if (redirect)
+    while (nsrc > 0 && ep.src[nsrc - 1] >= SB200_WS_OUTER_DST) --nsrc;
+  const int nearly = nsrc;  // sources that may be requested before the wait
+  if (late_src) ++nsrc;
   const float4* srcp[NSRC_MAX];
 #pragma unroll
-  for (int t = 0; t < NSRC_MAX; ++t)
-    srcp[t] = (t < nsrc) ? reinterpret_cast<const float4*>(ws[ep.src[t]] + tile_off) + row : nullptr;
+  for (int t = 0; t < NSRC_MAX; ++t) {
+    srcp[t] = nullptr;
+    if (t < nearly) {
+      const int id = ep.src[t];
+      srcp[t] = reinterpret_cast<const float4*>(ws[id] + (id < SB200_WS_OUTER_DST ? tile_off : outer_off)) + row;
+    } else if (t == nearly && late_src) {
+      srcp[t] = reinterpret_cast<const float4*>(late_src) + row;
+    }
+  }
   float4 nxt[NSRC_MAX][8];
 #pragma unroll
   for (int t = 0; t < NSRC_MAX; ++t)
-    if (t < nsrc) {
+    if (t < nearly) {
 #pragma unroll
       for (int q = 0; q < 8; ++q) nxt[t][q] = srcp[t][q * 128];
     }
-  float4* dstp = (ep.dst_kind == 1) ? reinterpret_cast<float4*>(ws[ep.dst] + tile_off) + row : nullptr;
-  char* outp = (ep.dst_kind == 1) ? nullptr : static_cast<char*>(out[ep.dst]);
+  const bool to_fp32 = redirect != nullptr || ep.dst_kind == 1;
+  float4* dstp = nullptr;
+  if (redirect) dstp = reinterpret_cast<float4*>(redirect) + row;
+  else if (ep.dst_kind == 1)
+    dstp = reinterpret_cast<float4*>(ws[ep.dst] + (ep.dst < SB200_WS_OUTER_DST ? tile_off : outer_off)) + row;
+  char* outp = to_fp32 ? nullptr : static_cast<char*>(out[ep.dst]);
   if (!wait_slots()) return false;
+#pragma unroll
+  for (int t = 0; t < NSRC_MAX; ++t)
+    if (t >= nearly && t < nsrc) {
+#pragma unroll
+      for (int q = 0; q < 8; ++q) nxt[t][q] = srcp[t][q * 128];
+    }
 
 #pragma unroll 1
   for (int c = 0; c < NCHUNK; ++c) {
@@ -92,7 +173,7 @@ __device__ __forceinline__ bool epilogue_body(void* const* out, long long ldo, i
         }
       }
     }
-    if (ep.dst_kind == 1) {
+    if (to_fp32) {
 #pragma unroll
       for (int q = 0; q < 8; ++q)
         dstp[(c * 8 + q) * 128] = make_float4(acc[4 * q], acc[4 * q + 1], acc[4 * q + 2], acc[4 * q + 3]);

@@ -74,9 +74,23 @@ struct Layout {
   // level 2 only: outer presums [4][m/2][k/2], [4][k/2][n/2] and three outer chain buffers (fp32, tile-contiguous,
   // four inner quadrants each)
   size_t off_opa, off_opb, off_x[3], quadrant_floats;
+  // K-split of the last wave (WorkUnit in sw_kernel.cuh)
+  int workers;       // CTAs (1-CTA kernels) or CTA pairs launched
+  int split_tiles;   // tiles of the last wave computed as two K-halves (0: none)
+  size_t off_split_buf, off_split_flags, split_flag_bytes;
 };
 
 int level_of(Variant v) { return v == kCubic ? 0 : (v == kInterleavedLevel2 ? 2 : 1); }
+
+int sm_count();
+
+// Tiles of the last wave to split: all of them when the wave is at most half full (then it lasts half as long),
+// none otherwise.  The fused-presum kernels are never split.
+int tiles_to_split(int tiles, int workers, int num_k, Variant v) {
+  if (v == kFusedPresum || workers <= 0 || num_k < 8 || getenv("SB200_NO_SPLIT")) return 0;
+  const int rem = tiles % workers;
+  return (rem > 0 && 2 * rem <= workers) ? rem : 0;
+}
 
 Layout make_layout(const GemmArgs& a) {
   Layout L;
@@ -106,13 +120,28 @@ Layout make_layout(const GemmArgs& a) {
     L.off_pb = off;
     off = align_up(off + size_t(4) * L.kq * L.nq * L.esize, 256);
   }
+  int cap = a.sm_limit > 0 ? a.sm_limit : sm_count();
+  if (const char* lim = getenv("SB200_SM_LIMIT"))  // test aid: run on fewer SMs (exercises multi-wave paths on small shapes)
+    if (atoi(lim) > 0 && atoi(lim) < cap) cap = atoi(lim);
+  if (a.pair) cap /= 2;  // one pair per two SMs
+  if (cap < 1) cap = 1;
+  L.workers = L.tiles_m * L.tiles_n < cap ? L.tiles_m * L.tiles_n : cap;
+  L.split_tiles = tiles_to_split(L.tiles_m * L.tiles_n, L.workers, L.num_k, a.variant);
   const int nws = a.variant == kCubic ? 0 : (a.variant == kFusedPresum ? 2 : 4);
-  const size_t tile_bytes = size_t(128) * L.bn * sizeof(float);
-  const size_t quadrant_bytes = size_t(L.tiles_m) * L.tiles_n * (a.pair ? 2 : 1) * tile_bytes;
+  const size_t tile_bytes = size_t(128) * L.bn * sizeof(float) * (a.pair ? 2 : 1);  // per tile of the grid
+  const size_t quadrant_bytes = size_t(L.tiles_m) * L.tiles_n * tile_bytes;
   L.quadrant_floats = quadrant_bytes / sizeof(float);
   for (int i = 0; i < nws; ++i) {
     L.off_ws[i] = off;
-    off = align_up(off + quadrant_bytes, 256);
+    // the second half of every split tile keeps its level-1 hand-off tiles in extra slots behind the grid's
+    off = align_up(off + quadrant_bytes + size_t(L.split_tiles) * tile_bytes, 256);
+  }
+  if (L.split_tiles) {
+    L.off_split_buf = off;
+    off = align_up(off + size_t(L.split_tiles) * 4 * tile_bytes, 256);
+    L.off_split_flags = off;
+    L.split_flag_bytes = size_t(L.split_tiles) * 4 * 8 * sizeof(int);
+    off = align_up(off + L.split_flag_bytes, 256);
   }
   if (L.level == 2)
     for (int i = 0; i < 3; ++i) {
@@ -274,6 +303,10 @@ struct LaunchSpec {
   PresumSideJob more_jobs[2];  // presum jobs of the level above, run by launch 1's presum warps
   int n_more_jobs;
   int* status;
+  int split_from;            // first split tile (= number of tiles when nothing is split)
+  float* split_buf;
+  int* split_flags;
+  int* split_epoch;          // counter shared by the launches of one run
 };
 
 template <typename MarkFn>
@@ -331,6 +364,9 @@ int launch_group(const LaunchSpec& s, cudaStream_t stream, MarkFn mark) {
   p.tiles_m = s.tiles_m;
   p.tiles_n = s.tiles_n;
   p.num_k = s.num_k;
+  p.split_from = s.split_from;
+  p.split_buf = s.split_buf;
+  p.split_flags = s.split_flags;
   p.band = 8;
   if (const char* bd = getenv("SB200_BAND")) p.band = atoi(bd) > 0 ? atoi(bd) : 8;
   if (const char* dbg = getenv("SB200_DEBUG_FLAGS")) p.debug_flags = atoi(dbg);
@@ -370,6 +406,7 @@ int launch_group(const LaunchSpec& s, cudaStream_t stream, MarkFn mark) {
   switch (s.variant) {
     case kCubic:
       p.prog = programs::level0();
+      p.split_epoch = ++*s.split_epoch;
       rc = launch_any(es, bn_sel, kPresumNone, p, s.grid, stream);
       break;
     case kFusedPresum:
@@ -381,10 +418,12 @@ int launch_group(const LaunchSpec& s, cudaStream_t stream, MarkFn mark) {
       const sb200_program_t second =
           getenv("SB200_L1_PLAIN") && !s.linked ? programs::level1_second() : programs::level1_second_taps();
       p.prog = s.linked ? programs::link_outer(first, s.link, 1) : first;
+      p.split_epoch = ++*s.split_epoch;
       rc = launch_any(es, bn_sel, kPresumJob, p, s.grid, stream);
       if (rc) return rc;
       if ((rc = mark())) return rc;
       p.prog = s.linked ? programs::link_outer(second, s.link, 2) : second;
+      p.split_epoch = ++*s.split_epoch;
       p.njobs = 0;
       rc = launch_any(es, bn_sel, kPresumNone, p, s.grid, stream);
       break;
@@ -422,10 +461,16 @@ int run(const GemmArgs& a, void* workspace, size_t workspace_size, cudaStream_t 
   s.es = es;
   s.bn = L.bn;
   s.pair = a.pair;
-  s.grid = L.tiles_m * L.tiles_n;
-  int cap = a.sm_limit > 0 ? a.sm_limit : sm_count();
-  if (a.pair) cap /= 2;  // one pair per two SMs
-  if (s.grid > cap) s.grid = cap;
+  s.grid = L.workers;
+  int epoch = 0;
+  s.split_epoch = &epoch;
+  s.split_from = L.tiles_m * L.tiles_n - L.split_tiles;
+  if (L.split_tiles) {
+    s.split_buf = reinterpret_cast<float*>(wsb + L.off_split_buf);
+    s.split_flags = reinterpret_cast<int*>(wsb + L.off_split_flags);
+    ce = cudaMemsetAsync(s.split_flags, 0, L.split_flag_bytes, stream);
+    if (ce != cudaSuccess) return static_cast<int>(ce);
+  }
   s.mq = L.mq; s.nq = L.nq; s.kq = L.kq;
   s.tiles_m = L.tiles_m; s.tiles_n = L.tiles_n; s.num_k = L.num_k;
   s.presum_a = wsb + L.off_pa;

@@ -40,6 +40,7 @@ enum StatusCode {
   kStatusMmaTimeout = 102,
   kStatusEpilogueTimeout = 103,
   kStatusPresumTimeout = 104,
+  kStatusSplitTimeout = 105,
 };
 
 struct View {
@@ -72,6 +73,12 @@ struct KernelParams {
   int num_k;                // k-steps per product
   int band;                 // raster band height in tiles
   int b_blocked;            // 1: the B tensor maps are 3-D [128-byte column block][row][block]: one load per B tile
+  // K-split of the last, partial wave of tiles (see WorkUnit): tiles >= split_from are computed as two K-halves by
+  // two CTAs (pairs); the first half hands its partial sums over through split_buf and raises split_flags.
+  int split_from;           // first split tile; = tiles_m * tiles_n when nothing is split
+  int split_epoch;          // value a raised flag holds in this launch (flags are zeroed once per run)
+  float* split_buf;         // [split tile][quadrant 4][CTA of the tile][128 x BN] fp32, hand-off tile order
+  int* split_flags;         // [split tile][quadrant 4][CTA of the tile 2][epilogue warp 4]
   int* status;              // device status word, 0 = ok
   int debug_flags;          // measurement aids: bit 0 = issue no MMA, bit 1 = issue no TMA load (results are garbage)
   int prefetch_dist;        // > 0: the producer asks L2 for the operand tiles this many k-steps ahead
@@ -90,9 +97,10 @@ struct KernelConfig {
   static constexpr int BK = 128 / ESIZE;          // elements per 128-byte swizzle row
   static constexpr int STAGES = STAGES_;
   static constexpr int MODE = MODE_;
-  // fp32 hand-off tiles an epilogue step may sum: only the kernels without presum warps (which have the register
-  // budget for it) run programs with more than one
-  static constexpr int NSRC_MAX = MODE_ == 0 ? SB200_MAX_SRC_TERMS : 1;
+  // fp32 sources an epilogue step may sum (hand-off tiles of the program, + one of the level above, + the partial
+  // sum of a split tile).  The kernels with presum warps have a smaller register budget and run programs that
+  // need fewer: JOB = first launch of the interleaved plan (1 + 1), FEED = one fused launch, never linked or split.
+  static constexpr int NSRC_MAX = MODE_ == 0 ? SB200_MAX_SRC_TERMS + 1 : (MODE_ == 2 ? 2 : 1);
   static constexpr int UMMA_K = 32 / ESIZE;
   static constexpr int KSUB = BK / UMMA_K;        // MMAs per stage (4)
   static constexpr int A_BYTES = BM * 128;
@@ -132,6 +140,40 @@ __device__ __forceinline__ TileCoord tile_of(int w, int tiles_m, int tiles_n, in
   t.j = r / rows_in_band;
   t.id = t.i * tiles_n + t.j;
   return t;
+}
+
+// Work unit of the persistent loop.  Tiles are dealt to the CTAs (pairs) round-robin, wave after wave.  When the
+// last wave is less than half full, each of its tiles is split into two K-halves that run at the same time on two
+// CTAs (pairs): the wave then lasts half as long.  Every postsum is linear in the products, so both halves run the
+// whole tile program on their K range with private hand-off tiles; at each step that leaves the tile (an output
+// quadrant or a buffer of the level above) the first half publishes its partial sum and the second half adds it.
+struct WorkUnit {
+  int tile;       // linear tile index (argument of tile_of)
+  int part;       // which K-half (0 when the tile is not split)
+  int nparts;     // 1 or 2
+  int k0, k1;     // k-step range [k0, k1)
+  int ws_slot;    // tile slot of this unit in the level-1 hand-off buffers (the second half uses an extra slot)
+  int split_idx;  // index of the tile among the split tiles
+};
+__device__ __forceinline__ int total_units(const KernelParams& p) {
+  return p.split_from + 2 * (p.tiles_m * p.tiles_n - p.split_from);
+}
+__device__ __forceinline__ WorkUnit unit_of(const KernelParams& p, int u) {
+  WorkUnit w;
+  if (u < p.split_from) {
+    w.tile = u; w.part = 0; w.nparts = 1; w.k0 = 0; w.k1 = p.num_k; w.ws_slot = u; w.split_idx = 0;
+  } else {
+    const int v = u - p.split_from;
+    const int h = p.num_k >> 1;
+    w.split_idx = v >> 1;
+    w.tile = p.split_from + w.split_idx;
+    w.part = v & 1;
+    w.nparts = 2;
+    w.k0 = w.part ? h : 0;
+    w.k1 = w.part ? p.num_k : h;
+    w.ws_slot = w.part ? p.tiles_m * p.tiles_n + w.split_idx : w.tile;
+  }
+  return w;
 }
 
 __device__ __forceinline__ void raise_abort(const KernelParams& p, volatile int* abort_flag, int code) {
@@ -320,7 +362,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_kernel(const 
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int total_tiles = p.tiles_m * p.tiles_n;
+  const int total_tiles = total_units(p);  // work units: tiles, or K-halves of the tiles of a split last wave
   const int nproducts = p.prog.nproducts;
 
   if (threadIdx.x == 0) {
@@ -355,7 +397,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_kernel(const 
       uint32_t phase = 0;
       bool ok = true;
       for (int w = blockIdx.x; ok && w < total_tiles; w += gridDim.x) {
-        const TileCoord tile = tile_of(w, p.tiles_m, p.tiles_n, p.band);
+        const WorkUnit wu = unit_of(p, w);
+        const TileCoord tile = tile_of(wu.tile, p.tiles_m, p.tiles_n, p.band);
         for (int ps = 0; ok && ps < nproducts; ++ps) {
           const sb200_product_t& pr = p.prog.product[ps];
           const bool a_tma = pr.a.nterms == 1;
@@ -363,7 +406,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_kernel(const 
           const uint32_t tx = (a_tma ? Cfg::A_BYTES : 0) + (b_tma ? Cfg::B_BYTES : 0);
           const CUtensorMap* ma = &p.tmap[pr.a.view[0]];
           const CUtensorMap* mb = &p.tmap[pr.b.view[0]];
-          for (int kk = 0; kk < p.num_k; ++kk) {
+          for (int kk = wu.k0; kk < wu.k1; ++kk) {
             const bool mine = (turn == my_turn);
             if (++turn == 3u) turn = 0;
             if (!mine) {
@@ -408,6 +451,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_kernel(const 
       uint32_t iter = 0;
       bool ok = true;
       for (int w = blockIdx.x; ok && w < total_tiles; w += gridDim.x, ++iter) {
+        const WorkUnit wu = unit_of(p, w);
+        const int nk = wu.k1 - wu.k0;
         const uint32_t sx = p.prog.alternate_slots ? (iter & 1u) : 0u;
         for (int ps = 0; ok && ps < nproducts; ++ps) {
           const sb200_product_t& pr = p.prog.product[ps];
@@ -427,8 +472,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_kernel(const 
           // that costs more ring latency than it saves (measured: groups of 3 give 1007 instead of 1293 TFLOPS at
           // 8192^3 f16), so the group is one k-step here
           constexpr int kGroup = 1;
-          for (int kk = 0; kk < p.num_k; kk += kGroup) {
-            const int group = min(kGroup, p.num_k - kk);
+          for (int kk = 0; kk < nk; kk += kGroup) {
+            const int group = min(kGroup, nk - kk);
             int s_w = stage;
             uint32_t ph_w = phase;
             for (int g = 0; g < group; ++g) {
@@ -468,10 +513,16 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_kernel(const 
     uint32_t iter = 0;
     bool ok = true;
     for (int w = blockIdx.x; ok && w < total_tiles; w += gridDim.x, ++iter) {
-      const TileCoord tile = tile_of(w, p.tiles_m, p.tiles_n, p.band);
+      const WorkUnit wu = unit_of(p, w);
+      const TileCoord tile = tile_of(wu.tile, p.tiles_m, p.tiles_n, p.band);
       const uint32_t sx = p.prog.alternate_slots ? (iter & 1u) : 0u;
       for (int es = 0; ok && es < p.prog.nepilogues; ++es) {
         const sb200_epilogue_t& ep = p.prog.epilogue[es];
+        const SplitStep sp = split_step(ep, wu.part, wu.nparts);
+        if (sp.skip) continue;
+        const long long split_tile = static_cast<long long>(wu.split_idx) * 4 + sp.q;
+        int* flag = p.split_flags + split_tile * 8 + quarter;
+        float* split_tile_buf = p.split_buf + split_tile * (128 * BN);
         auto wait_slots = [&]() -> bool {
           for (int s = 0; s < SLOTS; ++s) {
             if ((ep.wait_full_mask >> s) & 1u) {
@@ -485,15 +536,23 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_kernel(const 
               full_bits ^= (1u << slot);
             }
           }
+          if (sp.add_partial && !wait_flag(flag, p.split_epoch, abort_flag)) {
+            if (lane == 0) raise_abort(p, abort_flag, kStatusSplitTimeout);
+            return false;
+          }
           ptx::tc_fence_after_sync();
           return true;
         };
-        const long long tile_off = static_cast<long long>(tile.id) * (128 * BN);
+        const long long tile_off = static_cast<long long>(wu.ws_slot) * (128 * BN);
+        const long long outer_off = static_cast<long long>(wu.tile) * (128 * BN);
         ok = epilogue_body<ESIZE, BN, Cfg::NSRC_MAX>(p.out, p.ldo, p.out_rows, p.out_cols, p.ws, ep, sx, tmem_base, quarter,
-                                                     lane, tile_off, tile.i * 128, tile.j * BN,
+                                                     lane, tile_off, outer_off, tile.i * 128, tile.j * BN,
                                                      staging + (warp - 2) * kStagingWarpBytes,
+                                                     sp.redirect ? split_tile_buf : nullptr,
+                                                     sp.add_partial ? split_tile_buf : nullptr,
                                                      (p.debug_flags & 32) != 0, wait_slots);
         if (!ok) break;
+        if (sp.redirect) raise_flag(flag, p.split_epoch, lane);
         ptx::tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) {
@@ -511,12 +570,13 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_kernel(const 
       uint32_t phase = 0;
       bool ok = true;
       for (int w = blockIdx.x; ok && w < total_tiles; w += gridDim.x) {
-        const TileCoord tile = tile_of(w, p.tiles_m, p.tiles_n, p.band);
+        const WorkUnit wu = unit_of(p, w);
+        const TileCoord tile = tile_of(wu.tile, p.tiles_m, p.tiles_n, p.band);
         for (int ps = 0; ok && ps < nproducts; ++ps) {
           const sb200_product_t& pr = p.prog.product[ps];
           const bool a_mt = pr.a.nterms > 1;
           const bool b_mt = pr.b.nterms > 1;
-          for (int kk = 0; kk < p.num_k; ++kk) {
+          for (int kk = wu.k0; kk < wu.k1; ++kk) {
             bool got = ptx::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag);
             got = __all_sync(0xffffffffu, got);
             if (!got) {

@@ -33,9 +33,10 @@ struct PairConfig {
   static constexpr int BK = 128 / ESIZE;
   static constexpr int STAGES = STAGES_;
   static constexpr int MODE = MODE_;
-  // fp32 hand-off tiles an epilogue step may sum: only the kernels without presum warps (which have the register
-  // budget for it) run programs with more than one
-  static constexpr int NSRC_MAX = MODE_ == 0 ? SB200_MAX_SRC_TERMS : 1;
+  // fp32 sources an epilogue step may sum (hand-off tiles of the program, + one of the level above, + the partial
+  // sum of a split tile).  The kernels with presum warps have a smaller register budget and run programs that
+  // need fewer: JOB = first launch of the interleaved plan (1 + 1), FEED = one fused launch, never linked or split.
+  static constexpr int NSRC_MAX = MODE_ == 0 ? SB200_MAX_SRC_TERMS + 1 : (MODE_ == 2 ? 2 : 1);
   static constexpr int UMMA_K = 32 / ESIZE;
   static constexpr int KSUB = BK / UMMA_K;
   static constexpr int A_BYTES = BM * 128;
@@ -81,7 +82,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
   const uint32_t rank = ptx::cluster_ctarank();   // 0 = leader
   const int pair = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
-  const int total_tiles = p.tiles_m * p.tiles_n;  // pair tiles
+  const int total_tiles = total_units(p);  // work units: pair tiles, or K-halves of the tiles of a split last wave
   const int nproducts = p.prog.nproducts;
 
   if (threadIdx.x == 0) {
@@ -125,7 +126,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
       const long long pt0 = SB200_CLOCK();
       long long pw_empty = 0, pw_issue = 0;
       for (int w = pair; ok && w < total_tiles; w += num_pairs) {
-        const TileCoord tile = tile_of(w, p.tiles_m, p.tiles_n, p.band);
+        const WorkUnit wu = unit_of(p, w);
+        const TileCoord tile = tile_of(wu.tile, p.tiles_m, p.tiles_n, p.band);
         const int row0 = tile.i * Cfg::PAIR_M + static_cast<int>(rank) * Cfg::BM;
         const int col0 = tile.j * BN + static_cast<int>(rank) * Cfg::BN_CTA;
         for (int ps = 0; ok && ps < nproducts; ++ps) {
@@ -136,7 +138,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
           const CUtensorMap* ma = &p.tmap[pr.a.view[0]];
           const CUtensorMap* mb = &p.tmap[pr.b.view[0]];
           const bool no_load_all = (p.debug_flags & 2) != 0;
-          for (int kk = 0; kk < p.num_k; ++kk) {
+          for (int kk = wu.k0; kk < wu.k1; ++kk) {
             const bool mine = (turn == my_turn);
             if (++turn == 3u) turn = 0;
             if (!mine) {
@@ -155,7 +157,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
             uint8_t* sa = smem + stage * Cfg::STAGE_BYTES;
             uint8_t* sb = sa + Cfg::A_BYTES;
             // measurement aids: bit 1 = never load; bit 3 = load only while the ring fills for the first time
-            const bool no_load = no_load_all || ((p.debug_flags & 8) != 0 && (w != pair || ps > 0 || kk >= STAGES));
+            const bool no_load = no_load_all || ((p.debug_flags & 8) != 0 && (w != pair || ps > 0 || kk >= wu.k0 + STAGES));
             if (rank == 0) {
               if (tx && !no_load) ptx::mbar_arrive_expect_tx(&full_bar[stage], tx);
               else ptx::mbar_arrive(&full_bar[stage]);
@@ -193,6 +195,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
       long long mw_full = 0, mw_free = 0, mw_issue = 0;
       const long long mw_commit = 0;
       for (int w = pair; ok && w < total_tiles; w += num_pairs, ++iter) {
+        const WorkUnit wu = unit_of(p, w);
+        const int nk = wu.k1 - wu.k0;
         const uint32_t sx = p.prog.alternate_slots ? (iter & 1u) : 0u;
         for (int ps = 0; ok && ps < nproducts; ++ps) {
           const sb200_product_t& pr = p.prog.product[ps];
@@ -218,8 +222,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
           // k-steps are taken kWaitGroup at a time: all their full-barrier waits first, then 4 MMAs + stage release
           // for each.  (Measured on B200, 8192^3 f16: groups of 1 / 2 / 3 / 4 / 6 k-steps give 1175 / 1227 / 1256 /
           // 1237 / 1168 TFLOPS: batching the waits keeps the MMA queue fed, too large a group adds ring latency.)
-          for (int kk = 0; kk < p.num_k; kk += kWaitGroup) {
-            const int group = min(kWaitGroup, p.num_k - kk);
+          for (int kk = 0; kk < nk; kk += kWaitGroup) {
+            const int group = min(kWaitGroup, nk - kk);
             int s_w = stage;
             uint32_t ph_w = phase;
             const long long tw = SB200_CLOCK();
@@ -276,10 +280,16 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
     const long long et0 = SB200_CLOCK();
     long long ew_full = 0;
     for (int w = pair; ok && w < total_tiles; w += num_pairs, ++iter) {
-      const TileCoord tile = tile_of(w, p.tiles_m, p.tiles_n, p.band);
+      const WorkUnit wu = unit_of(p, w);
+      const TileCoord tile = tile_of(wu.tile, p.tiles_m, p.tiles_n, p.band);
       const uint32_t sx = p.prog.alternate_slots ? (iter & 1u) : 0u;
       for (int es = 0; ok && es < p.prog.nepilogues; ++es) {
         const sb200_epilogue_t& ep = p.prog.epilogue[es];
+        const SplitStep sp = split_step(ep, wu.part, wu.nparts);
+        if (sp.skip) continue;
+        const long long split_tile = static_cast<long long>(wu.split_idx) * 4 + sp.q;
+        int* flag = p.split_flags + split_tile * 8 + rank * 4 + quarter;
+        float* split_tile_buf = p.split_buf + (split_tile * 2 + rank) * (128 * BN);
         auto wait_slots = [&]() -> bool {
           for (int s0 = 0; s0 < SLOTS; ++s0) {
             if ((ep.wait_full_mask >> s0) & 1u) {
@@ -295,15 +305,24 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
               full_bits ^= (1u << s);
             }
           }
+          if (sp.add_partial && !wait_flag(flag, p.split_epoch, abort_flag)) {
+            if (lane == 0) raise_abort(p, abort_flag, kStatusSplitTimeout);
+            return false;
+          }
           ptx::tc_fence_after_sync();
           return true;
         };
-        const long long tile_off = (static_cast<long long>(tile.id) * 2 + rank) * (128 * BN);
+        const long long tile_off = (static_cast<long long>(wu.ws_slot) * 2 + rank) * (128 * BN);
+        const long long outer_off = (static_cast<long long>(wu.tile) * 2 + rank) * (128 * BN);
         ok = epilogue_body<ESIZE, BN, Cfg::NSRC_MAX>(p.out, p.ldo, p.out_rows, p.out_cols, p.ws, ep, sx, tmem_base, quarter,
-                                                     lane, tile_off, tile.i * Cfg::PAIR_M + static_cast<int>(rank) * Cfg::BM,
-                                                     tile.j * BN, staging + (warp - 2) * kStagingWarpBytes,
+                                                     lane, tile_off, outer_off,
+                                                     tile.i * Cfg::PAIR_M + static_cast<int>(rank) * Cfg::BM, tile.j * BN,
+                                                     staging + (warp - 2) * kStagingWarpBytes,
+                                                     sp.redirect ? split_tile_buf : nullptr,
+                                                     sp.add_partial ? split_tile_buf : nullptr,
                                                      (p.debug_flags & 32) != 0, wait_slots);
         if (!ok) break;
+        if (sp.redirect) raise_flag(flag, p.split_epoch, lane);
         ptx::tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) {
@@ -323,14 +342,15 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
       uint32_t phase = 0;
       bool ok = true;
       for (int w = pair; ok && w < total_tiles; w += num_pairs) {
-        const TileCoord tile = tile_of(w, p.tiles_m, p.tiles_n, p.band);
+        const WorkUnit wu = unit_of(p, w);
+        const TileCoord tile = tile_of(wu.tile, p.tiles_m, p.tiles_n, p.band);
         const int row0 = tile.i * Cfg::PAIR_M + static_cast<int>(rank) * Cfg::BM;
         const int col0 = tile.j * BN + static_cast<int>(rank) * Cfg::BN_CTA;
         for (int ps = 0; ok && ps < nproducts; ++ps) {
           const sb200_product_t& pr = p.prog.product[ps];
           const bool a_mt = pr.a.nterms > 1;
           const bool b_mt = pr.b.nterms > 1;
-          for (int kk = 0; kk < p.num_k; ++kk) {
+          for (int kk = wu.k0; kk < wu.k1; ++kk) {
             bool got = ptx::mbar_wait_cluster(&empty_bar[stage], phase ^ 1u, abort_flag);
             got = __all_sync(0xffffffffu, got);
             if (!got) {

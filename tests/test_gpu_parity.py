@@ -90,6 +90,57 @@ def test_level2_bit_exact_on_harness_values(kernel, shape, oracle, cuda_device):
         assert np.array_equal(got.astype(np.float64), a.astype(np.float64) @ b.astype(np.float64))
 
 
+# ------------------------------------------------------------------------------- K-split of the last wave
+SPLIT_CASES = [
+    # kernel, SMs, shape: the tile count leaves a last wave at most half full, whose tiles are split in two K-halves
+    ("blackwell_f16_cubic_128x256", 8, (384, 768, 1024)),              # 3 x 3 = 9 tiles on 8 CTAs
+    ("blackwell_f16_cubic_2sm_256x256", 8, (512, 640, 1024)),          # 2 x 3 = 6 pair tiles on 4 pairs... 2 left
+    ("blackwell_f32_cubic_2sm_256x256", 8, (1280, 256, 512)),          # 5 tiles on 4 pairs
+    ("blackwell_f16_sw_interleaved_presum", 8, (768, 1536, 2048)),     # quadrant 3 x 3 tiles on 8 CTAs
+    ("blackwell_f16_sw_interleaved_presum_2sm", 8, (512, 2560, 1024)),  # quadrant 1 x 5 pair tiles on 4 pairs
+    ("blackwell_f32_sw_interleaved_presum_2sm", 12, (3584, 512, 1024)),  # quadrant 7 x 1 on 6 pairs
+    ("blackwell_f16_sw_level2_2sm", 8, (1024, 5120, 2048)),            # every group: 1 x 5 pair tiles on 4 pairs
+    ("blackwell_f32_sw_level2", 8, (1536, 3072, 1024)),                # every group: 3 x 3 tiles on 8 CTAs
+    ("blackwell_f16_sw_level2", 0, (5120, 15360, 2048)),               # all SMs: 10 x 15 = 150 tiles on 148 CTAs
+]
+
+
+@pytest.mark.parametrize("kernel,sms,shape", SPLIT_CASES)
+def test_split_last_wave_bit_exact_on_harness_values(kernel, sms, shape, oracle, cuda_device, monkeypatch):
+    from subcuber_b200 import inputs
+
+    m, n, k = shape
+    dt = _dt(kernel)
+    level = _level(kernel)
+    a, b = inputs.operands(dt, "harness", m, n, k, seed=4)
+    if sms:
+        monkeypatch.setenv("SB200_SM_LIMIT", str(sms))
+    got = _run(kernel, a, b, cuda_device)
+    monkeypatch.setenv("SB200_NO_SPLIT", "1")
+    unsplit = _run(kernel, a, b, cuda_device)
+    assert not np.isnan(got).any()
+    assert np.array_equal(got, unsplit)
+    if m * n * k <= 2 ** 34:
+        assert np.array_equal(got, oracle.sw_gemm(dt, level, a, b))
+    else:
+        rows = np.arange(0, m, 97, dtype=np.int32)
+        assert np.array_equal(got[rows], oracle.sw_gemm(dt, 0, a, b, rows=rows)[rows])
+
+
+@pytest.mark.parametrize("kernel", ["blackwell_f16_sw_interleaved_presum_2sm", "blackwell_f16_sw_level2_2sm"])
+def test_split_last_wave_uniform_inputs(kernel, oracle, cuda_device, monkeypatch):
+    """On inexact inputs the split changes only the order of fp32 additions: the result stays within the error gate."""
+    from subcuber_b200 import inputs
+
+    m, n, k = (512, 2560, 1024) if _level(kernel) == 1 else (1024, 5120, 2048)
+    a, b = inputs.operands("f16", "uniform1", m, n, k, seed=6)
+    monkeypatch.setenv("SB200_SM_LIMIT", "8")
+    got = _run(kernel, a, b, cuda_device)
+    truth = a.astype(np.float64) @ b.astype(np.float64)
+    ref = oracle.sw_gemm("f16", _level(kernel), a, b)
+    assert _rel_fro(got, truth) <= 1.5 * _rel_fro(ref, truth)
+
+
 @pytest.mark.parametrize("kernel", L2_F16)
 @pytest.mark.parametrize("shape", [(1024, 1024, 1024), (1536, 1280, 2304)])
 def test_level2_uniform_inputs_f16(kernel, shape, oracle, cuda_device):
