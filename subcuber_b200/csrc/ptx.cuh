@@ -47,6 +47,37 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// True in exactly one lane of a fully active warp (the same lane every time).  Roles that issue single-thread
+// instructions (tcgen05.mma / commit, TMA loads) keep their loops warp-uniform and branch on this only around the
+// issue itself: measured on B200, a loop that runs in one thread of a divergent branch feeds tcgen05.mma about 10 %
+// slower than the tensor pipe drains it, because every operand has to be moved over from per-thread registers.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t elected;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(elected));
+  return elected != 0;
+}
+
+// Non-blocking test of a phase (never suspends the thread): used to look at a barrier ahead of time.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // Bounded wait.  Gives up after `limit_ns` of wall time (checked every 256 polls) or as soon as another
 // thread of the CTA has raised `*abort_flag`.  Returns false when it gave up.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,

@@ -375,7 +375,7 @@ int launch_group(const LaunchSpec& s, cudaStream_t stream, MarkFn mark) {
     // measurement aid: per-CTA cycle counters of the CTA-pair kernels (library built with SB200_PROFILE), printed by
     // the next call
     static long long* prof_dev = nullptr;
-    static long long prof_host[8 * 256];
+    static long long prof_host[8 * 256 + 64 * 8];
     if (!prof_dev) {
       cudaMalloc(&prof_dev, sizeof(prof_host));
     } else {
@@ -388,6 +388,16 @@ int launch_group(const LaunchSpec& s, cudaStream_t stream, MarkFn mark) {
       fprintf(stderr, "[prof] leader mma thread: total %.0f = wait_full %.0f + wait_free %.0f + issue %.0f + rest | "
               "producer: wait_empty %.0f issue %.0f total %.0f\n",
               sum[0] / n, sum[1] / n, sum[2] / n, sum[5] / n, sum[3] / n, sum[7] / n, sum[4] / n);
+      if (getenv("SB200_PROF_TRACE")) {
+        // per k-step of one tile of CTA 0 (cycles relative to the first entry): producer saw the stage empty / issued
+        // its loads, an observer saw the stage full, the MMA thread started waiting / got the stage / had issued
+        const long long* t = prof_host + 2048;
+        long long base = t[0];
+        fprintf(stderr, "[trace] kk: prod_empty prod_issued full_seen | mma_wait_start mma_got mma_issued | load_latency\n");
+        for (int kk = 0; kk < 64; ++kk, t += 8)
+          fprintf(stderr, "[trace] %2d: %7lld %7lld %7lld | %7lld %7lld %7lld | %6lld\n", kk, t[0] - base, t[1] - base,
+                  t[2] - base, t[3] - base, t[4] - base, t[5] - base, t[2] - t[1]);
+      }
     }
     cudaMemset(prof_dev, 0, sizeof(prof_host));
     p.prof = prof_dev;

@@ -48,7 +48,11 @@ struct PairConfig {
   static constexpr int TMEM_COLS = 512;
   static constexpr int PRESUM_WARPS = (MODE == kPresumNone) ? 0 : 4;
   // warps 0-5 as in sw_kernel.cuh; warps 6 and 7 = more TMA producers (see the producer section); presum warps follow
+#ifdef SB200_PROFILE
+  static constexpr int FIRST_PRESUM_WARP = (MODE_ == kPresumNone) ? 9 : 8;  // warp 8 = full-barrier monitor (tracing)
+#else
   static constexpr int FIRST_PRESUM_WARP = 8;
+#endif
   static constexpr int THREADS = (FIRST_PRESUM_WARP + PRESUM_WARPS) * 32;
   static constexpr int BAR_BYTES = 1024;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + kStagingBytes + 1024;
@@ -108,17 +112,18 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_holder;
 
-  if (warp == 0 || (warp >= 6 && warp < Cfg::FIRST_PRESUM_WARP)) {
+  if (warp == 0 || warp == 6 || warp == 7) {
     // ------------------------------------------------------------------ TMA producers (both CTAs)
     // Measured on B200: the tiled loads of ONE warp complete one after the other, about 240 ns apiece whatever the
     // box holds (4 to 32 KiB), while loads of different warps overlap.  A k-step lasts about 370 ns, so a single
     // producer issuing two or three loads per k-step cannot keep up.  Three single-thread producers (warps 0, 6, 7)
     // take the k-steps in turn; each issues the A load and the B load of its k-step (B is one 3-D load when the B
     // maps are blocked) and, in the leader CTA, arms the full barrier with the pair's bytes.
-    if (lane == 0) {
+    // Each producer warp runs its loop warp-uniformly and one elected lane issues (see ptx::elect_one).
+    {
       const uint32_t my_turn = (warp == 0) ? 0u : static_cast<uint32_t>(warp - 5);
       uint32_t turn = 0;
-      if (warp == 0)
+      if (warp == 0 && lane == 0)
         for (int v = 0; v < SB200_NUM_VIEWS; ++v) ptx::prefetch_tmap(&p.tmap[v]);
       int stage = 0;
       uint32_t phase = 0;
@@ -147,37 +152,49 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
             }
             const long long tw = SB200_CLOCK();
             // the stage-empty barrier is signalled by tcgen05.commit only: no cluster-scope acquire needed
-            if (!ptx::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) {
-              raise_abort(p, abort_flag, kStatusProducerTimeout);
+            bool got = ptx::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag);
+            got = __all_sync(0xffffffffu, got);
+            if (!got) {
+              if (lane == 0) raise_abort(p, abort_flag, kStatusProducerTimeout);
               ok = false;
               break;
             }
             const long long tw2 = SB200_CLOCK();
             pw_empty += tw2 - tw;
+#ifdef SB200_PROFILE
+            const bool traced = p.prof && lane == 0 && blockIdx.x == 0 && w == pair + 3 * num_pairs && ps == 0 && kk < 64;
+            if (traced) p.prof[2048 + kk * 8 + 0] = tw2;
+#endif
             uint8_t* sa = smem + stage * Cfg::STAGE_BYTES;
             uint8_t* sb = sa + Cfg::A_BYTES;
             // measurement aids: bit 1 = never load; bit 3 = load only while the ring fills for the first time
             const bool no_load = no_load_all || ((p.debug_flags & 8) != 0 && (w != pair || ps > 0 || kk >= wu.k0 + STAGES));
-            if (rank == 0) {
-              if (tx && !no_load) ptx::mbar_arrive_expect_tx(&full_bar[stage], tx);
-              else ptx::mbar_arrive(&full_bar[stage]);
-            }
-            if (a_tma && !no_load) ptx::tma_load_2d_pair(sa, ma, &full_bar[stage], kk * BK, row0);
-            if (b_tma && !no_load) {
-              if (p.b_blocked) {
-                ptx::tma_load_3d_pair(sb, mb, &full_bar[stage], 0, kk * BK, col0 / BK);
-              } else {
+            if (ptx::elect_one()) {
+              if (rank == 0) {
+                if (tx && !no_load) ptx::mbar_arrive_expect_tx(&full_bar[stage], tx);
+                else ptx::mbar_arrive(&full_bar[stage]);
+              }
+              if (a_tma && !no_load) ptx::tma_load_2d_pair(sa, ma, &full_bar[stage], kk * BK, row0);
+              if (b_tma && !no_load) {
+                if (p.b_blocked) {
+                  ptx::tma_load_3d_pair(sb, mb, &full_bar[stage], 0, kk * BK, col0 / BK);
+                } else {
 #pragma unroll
-                for (int nb = 0; nb < Cfg::NBLK; ++nb)
-                  ptx::tma_load_2d_pair(sb + nb * Cfg::BLK_BYTES, mb, &full_bar[stage], col0 + nb * BK, kk * BK);
+                  for (int nb = 0; nb < Cfg::NBLK; ++nb)
+                    ptx::tma_load_2d_pair(sb + nb * Cfg::BLK_BYTES, mb, &full_bar[stage], col0 + nb * BK, kk * BK);
+                }
               }
             }
+            __syncwarp();
             pw_issue += SB200_CLOCK() - tw2;
+#ifdef SB200_PROFILE
+            if (traced) p.prof[2048 + kk * 8 + 1] = SB200_CLOCK();
+#endif
             if (++stage == STAGES) { stage = 0; phase ^= 1u; }
           }
         }
       }
-      if (p.prof && warp == 0) {
+      if (p.prof && warp == 0 && lane == 0) {
         p.prof[blockIdx.x * 8 + 7] = pw_issue;
         p.prof[blockIdx.x * 8 + 3] = pw_empty;
         p.prof[blockIdx.x * 8 + 4] = SB200_CLOCK() - pt0;
@@ -185,7 +202,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (leader CTA only)
-    if (lane == 0 && rank == 0) {
+    // The whole warp runs the loop (see ptx::elect_one); one elected lane issues the MMAs and the commits.
+    if (rank == 0) {
       int stage = 0;
       uint32_t phase = 0;
       uint32_t free_bits = 0;
@@ -193,7 +211,6 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
       bool ok = true;
       const long long mt0 = SB200_CLOCK();
       long long mw_full = 0, mw_free = 0, mw_issue = 0;
-      const long long mw_commit = 0;
       for (int w = pair; ok && w < total_tiles; w += num_pairs, ++iter) {
         const WorkUnit wu = unit_of(p, w);
         const int nk = wu.k1 - wu.k0;
@@ -203,8 +220,10 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
           const uint32_t slot = pr.slot ^ sx;
           if (pr.wait_free) {
             const long long tw = SB200_CLOCK();
-            if (!ptx::mbar_wait_cluster(&slot_free[slot], ((free_bits >> slot) & 1u) ^ 1u, abort_flag)) {
-              raise_abort(p, abort_flag, kStatusMmaTimeout);
+            bool got = ptx::mbar_wait_cluster(&slot_free[slot], ((free_bits >> slot) & 1u) ^ 1u, abort_flag);
+            got = __all_sync(0xffffffffu, got);
+            if (!got) {
+              if (lane == 0) raise_abort(p, abort_flag, kStatusMmaTimeout);
               ok = false;
               break;
             }
@@ -219,58 +238,70 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
           const uint64_t adesc0 = ptx::umma_desc_sw128(ptx::smem_u32(smem), 16, 1024);
           const uint64_t bdesc0 =
               ptx::umma_desc_sw128(ptx::smem_u32(smem) + Cfg::A_BYTES, Cfg::BLK_BYTES, Cfg::B_SBO, Cfg::B_LAYOUT_TYPE);
-          // k-steps are taken kWaitGroup at a time: all their full-barrier waits first, then 4 MMAs + stage release
-          // for each.  (Measured on B200, 8192^3 f16: groups of 1 / 2 / 3 / 4 / 6 k-steps give 1175 / 1227 / 1256 /
-          // 1237 / 1168 TFLOPS: batching the waits keeps the MMA queue fed, too large a group adds ring latency.)
-          for (int kk = 0; kk < nk; kk += kWaitGroup) {
-            const int group = min(kWaitGroup, nk - kk);
-            int s_w = stage;
-            uint32_t ph_w = phase;
+          for (int kk = 0; ok && kk < nk; ++kk) {
             const long long tw = SB200_CLOCK();
-            for (int g = 0; g < group; ++g) {
-              // in FEED mode the peer's presum warps arrive on this barrier after writing their own shared memory
-              // through the generic proxy: that hand-over needs the cluster-scope acquire; TMA-only stages do not
-              const bool got_full = (Cfg::MODE == kPresumFeed) ? ptx::mbar_wait_cluster(&full_bar[s_w], ph_w, abort_flag)
-                                                               : ptx::mbar_wait(&full_bar[s_w], ph_w, abort_flag);
-              if (!got_full) {
-                raise_abort(p, abort_flag, kStatusMmaTimeout);
-                ok = false;
-                break;
-              }
-              if (++s_w == STAGES) { s_w = 0; ph_w ^= 1u; }
+            // in FEED mode the peer's presum warps arrive on this barrier after writing their own shared memory
+            // through the generic proxy: that hand-over needs the cluster-scope acquire; TMA-only stages do not
+            bool got = (Cfg::MODE == kPresumFeed) ? ptx::mbar_wait_cluster(&full_bar[stage], phase, abort_flag)
+                                                  : ptx::mbar_wait(&full_bar[stage], phase, abort_flag);
+            got = __all_sync(0xffffffffu, got);
+            if (!got) {
+              if (lane == 0) raise_abort(p, abort_flag, kStatusMmaTimeout);
+              ok = false;
+              break;
             }
-            if (!ok) break;
-            mw_full += SB200_CLOCK() - tw;
             const long long ti0 = SB200_CLOCK();
-            for (int g = 0; g < group; ++g) {
-              const uint64_t adesc_s = adesc0 + static_cast<uint64_t>((stage * Cfg::STAGE_BYTES) >> 4);
-              const uint64_t bdesc_s = bdesc0 + static_cast<uint64_t>((stage * Cfg::STAGE_BYTES) >> 4);
+            mw_full += ti0 - tw;
+            const uint64_t adesc_s = adesc0 + static_cast<uint64_t>((stage * Cfg::STAGE_BYTES) >> 4);
+            const uint64_t bdesc_s = bdesc0 + static_cast<uint64_t>((stage * Cfg::STAGE_BYTES) >> 4);
+            if (ptx::elect_one()) {
               if (!skip_mma) {
 #pragma unroll
                 for (int ks = 0; ks < Cfg::KSUB; ++ks) {
                   const uint64_t adesc = adesc_s + static_cast<uint64_t>((ks * 32) >> 4);
                   const uint64_t bdesc = bdesc_s + static_cast<uint64_t>((ks * Cfg::UMMA_K * 128) >> 4);
-                  const uint32_t acc = (kk + g > 0 || ks > 0 || pr.accumulate) ? 1u : 0u;
+                  const uint32_t acc = (kk > 0 || ks > 0 || pr.accumulate) ? 1u : 0u;
                   if (ESIZE == 2) ptx::umma_f16_pair(tmem_d, adesc, bdesc, idesc, acc);
                   else ptx::umma_tf32_pair(tmem_d, adesc, bdesc, idesc, acc);
                 }
               }
               ptx::umma_commit_pair(&empty_bar[stage], 3);
-              if (++stage == STAGES) { stage = 0; phase ^= 1u; }
             }
+            __syncwarp();
+            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
             mw_issue += SB200_CLOCK() - ti0;
           }
-          if (ok && pr.commit) ptx::umma_commit_pair(&slot_full[slot], 3);
+          if (ok && pr.commit) {
+            if (ptx::elect_one()) ptx::umma_commit_pair(&slot_full[slot], 3);
+            __syncwarp();
+          }
         }
       }
-      if (p.prof) {
+      if (p.prof && lane == 0) {
         p.prof[blockIdx.x * 8 + 0] = SB200_CLOCK() - mt0;
         p.prof[blockIdx.x * 8 + 1] = mw_full;
         p.prof[blockIdx.x * 8 + 2] = mw_free;
         p.prof[blockIdx.x * 8 + 5] = mw_issue;
-        p.prof[blockIdx.x * 8 + 6] = mw_commit;
       }
     }
+#ifdef SB200_PROFILE
+  } else if (warp == 8 && Cfg::MODE == kPresumNone) {
+    // tracing only: an observer that waits on the full barriers in ring order and notes when each completed
+    if (lane == 0 && rank == 0 && p.prof) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int w = pair; ok && w < total_tiles; w += num_pairs) {
+        const WorkUnit wu = unit_of(p, w);
+        for (int ps = 0; ok && ps < nproducts; ++ps)
+          for (int kk = 0; kk < wu.k1 - wu.k0; ++kk) {
+            if (!ptx::mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+            if (blockIdx.x == 0 && w == pair + 3 * num_pairs && ps == 0 && kk < 64) p.prof[2048 + kk * 8 + 2] = clock64();
+            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          }
+      }
+    }
+#endif
   } else if (warp < 6) {
     // ------------------------------------------------------------------ epilogue warps (both CTAs, own TMEM half)
     const int quarter = warp & 3;
