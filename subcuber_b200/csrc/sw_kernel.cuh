@@ -123,9 +123,6 @@ struct KernelConfig {
   static constexpr uint32_t B_SBO = B_SWZ32 ? 512u : 1024u;
 };
 
-// k-steps whose full-barrier waits the MMA issuer of the CTA-pair kernels batches (at most the number of stages)
-constexpr int kWaitGroup = 3;
-
 struct TileCoord {
   int i, j, id;
 };
@@ -388,10 +385,11 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_kernel(const 
 
   if (warp == 0 || (warp >= 6 && warp < Cfg::FIRST_PRESUM_WARP)) {
     // ------------------------------------------------------------------ TMA producers (take the k-steps in turn)
-    if (lane == 0) {
+    // Each producer warp runs its loop warp-uniformly and one elected lane issues (see ptx::elect_one).
+    {
       const uint32_t my_turn = (warp == 0) ? 0u : static_cast<uint32_t>(warp - 5);
       uint32_t turn = 0;
-      if (warp == 0)
+      if (warp == 0 && lane == 0)
         for (int v = 0; v < SB200_NUM_VIEWS; ++v) ptx::prefetch_tmap(&p.tmap[v]);
       int stage = 0;
       uint32_t phase = 0;
@@ -406,6 +404,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_kernel(const 
           const uint32_t tx = (a_tma ? Cfg::A_BYTES : 0) + (b_tma ? Cfg::B_BYTES : 0);
           const CUtensorMap* ma = &p.tmap[pr.a.view[0]];
           const CUtensorMap* mb = &p.tmap[pr.b.view[0]];
+          const bool no_load = (p.debug_flags & 2) != 0;  // measurement aid
           for (int kk = wu.k0; kk < wu.k1; ++kk) {
             const bool mine = (turn == my_turn);
             if (++turn == 3u) turn = 0;
@@ -413,30 +412,30 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_kernel(const 
               if (++stage == STAGES) { stage = 0; phase ^= 1u; }
               continue;
             }
-            if (!ptx::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) {
-              raise_abort(p, abort_flag, kStatusProducerTimeout);
+            bool got = ptx::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag);
+            got = __all_sync(0xffffffffu, got);
+            if (!got) {
+              if (lane == 0) raise_abort(p, abort_flag, kStatusProducerTimeout);
               ok = false;
               break;
             }
             uint8_t* sa = smem + stage * Cfg::STAGE_BYTES;
             uint8_t* sb = sa + Cfg::A_BYTES;
-            const bool no_load = (p.debug_flags & 2) != 0;
-            if (tx && !no_load) ptx::mbar_arrive_expect_tx(&full_bar[stage], tx);
-            else ptx::mbar_arrive(&full_bar[stage]);
-            if (no_load) {
-              if (++stage == STAGES) { stage = 0; phase ^= 1u; }
-              continue;
-            }
-            if (a_tma) ptx::tma_load_2d(sa, ma, &full_bar[stage], kk * BK, tile.i * Cfg::BM);
-            if (b_tma) {
-              if (p.b_blocked) {
-                ptx::tma_load_3d(sb, mb, &full_bar[stage], 0, kk * BK, tile.j * Cfg::NBLK);
-              } else {
+            if (ptx::elect_one()) {
+              if (tx && !no_load) ptx::mbar_arrive_expect_tx(&full_bar[stage], tx);
+              else ptx::mbar_arrive(&full_bar[stage]);
+              if (a_tma && !no_load) ptx::tma_load_2d(sa, ma, &full_bar[stage], kk * BK, tile.i * Cfg::BM);
+              if (b_tma && !no_load) {
+                if (p.b_blocked) {
+                  ptx::tma_load_3d(sb, mb, &full_bar[stage], 0, kk * BK, tile.j * Cfg::NBLK);
+                } else {
 #pragma unroll
-                for (int nb = 0; nb < Cfg::NBLK; ++nb)
-                  ptx::tma_load_2d(sb + nb * Cfg::BLK_BYTES, mb, &full_bar[stage], tile.j * BN + nb * BK, kk * BK);
+                  for (int nb = 0; nb < Cfg::NBLK; ++nb)
+                    ptx::tma_load_2d(sb + nb * Cfg::BLK_BYTES, mb, &full_bar[stage], tile.j * BN + nb * BK, kk * BK);
+                }
               }
             }
+            __syncwarp();
             if (++stage == STAGES) { stage = 0; phase ^= 1u; }
           }
         }
@@ -444,7 +443,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_kernel(const 
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // The whole warp runs the loop (see ptx::elect_one); one elected lane issues the MMAs and the commits.
+    {
       int stage = 0;
       uint32_t phase = 0;
       uint32_t free_bits = 0;
@@ -458,8 +458,10 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_kernel(const 
           const sb200_product_t& pr = p.prog.product[ps];
           const uint32_t slot = pr.slot ^ sx;
           if (pr.wait_free) {
-            if (!ptx::mbar_wait(&slot_free[slot], ((free_bits >> slot) & 1u) ^ 1u, abort_flag)) {
-              raise_abort(p, abort_flag, kStatusMmaTimeout);
+            bool got = ptx::mbar_wait(&slot_free[slot], ((free_bits >> slot) & 1u) ^ 1u, abort_flag);
+            got = __all_sync(0xffffffffu, got);
+            if (!got) {
+              if (lane == 0) raise_abort(p, abort_flag, kStatusMmaTimeout);
               ok = false;
               break;
             }
@@ -468,41 +470,42 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_kernel(const 
           }
           const uint32_t idesc = ptx::umma_idesc(Cfg::FMT, Cfg::BM, BN, pr.negate != 0);
           const uint32_t tmem_d = tmem_base + slot * BN;
-          // k-steps could be taken several at a time as in the CTA-pair kernels, but with only four 48 KiB stages
-          // that costs more ring latency than it saves (measured: groups of 3 give 1007 instead of 1293 TFLOPS at
-          // 8192^3 f16), so the group is one k-step here
-          constexpr int kGroup = 1;
-          for (int kk = 0; kk < nk; kk += kGroup) {
-            const int group = min(kGroup, nk - kk);
-            int s_w = stage;
-            uint32_t ph_w = phase;
-            for (int g = 0; g < group; ++g) {
-              if (!ptx::mbar_wait(&full_bar[s_w], ph_w, abort_flag)) {
-                raise_abort(p, abort_flag, kStatusMmaTimeout);
-                ok = false;
-                break;
-              }
-              if (++s_w == STAGES) { s_w = 0; ph_w ^= 1u; }
+          const bool skip_mma = (p.debug_flags & 1) != 0;  // measurement aid
+          // descriptors differ between stages and k-substeps only in the start-address field (low word, 16-byte units)
+          const uint64_t adesc0 = ptx::umma_desc_sw128(ptx::smem_u32(smem), 16, 1024);
+          const uint64_t bdesc0 =
+              ptx::umma_desc_sw128(ptx::smem_u32(smem) + Cfg::A_BYTES, Cfg::BLK_BYTES, Cfg::B_SBO, Cfg::B_LAYOUT_TYPE);
+          for (int kk = 0; ok && kk < nk; ++kk) {
+            bool got = ptx::mbar_wait(&full_bar[stage], phase, abort_flag);
+            got = __all_sync(0xffffffffu, got);
+            if (!got) {
+              if (lane == 0) raise_abort(p, abort_flag, kStatusMmaTimeout);
+              ok = false;
+              break;
             }
-            if (!ok) break;
             ptx::tc_fence_after_sync();
-            for (int g = 0; g < group; ++g) {
-              const uint32_t a_addr = ptx::smem_u32(smem + stage * Cfg::STAGE_BYTES);
-              const uint32_t b_addr = a_addr + Cfg::A_BYTES;
+            const uint64_t adesc_s = adesc0 + static_cast<uint64_t>((stage * Cfg::STAGE_BYTES) >> 4);
+            const uint64_t bdesc_s = bdesc0 + static_cast<uint64_t>((stage * Cfg::STAGE_BYTES) >> 4);
+            if (ptx::elect_one()) {
+              if (!skip_mma) {
 #pragma unroll
-              for (int ks = 0; ks < Cfg::KSUB && !(p.debug_flags & 1); ++ks) {
-                const uint64_t adesc = ptx::umma_desc_sw128(a_addr + ks * 32, 16, 1024);
-                const uint64_t bdesc =
-                    ptx::umma_desc_sw128(b_addr + ks * Cfg::UMMA_K * 128, Cfg::BLK_BYTES, Cfg::B_SBO, Cfg::B_LAYOUT_TYPE);
-                const uint32_t acc = (kk + g > 0 || ks > 0 || pr.accumulate) ? 1u : 0u;
-                if (ESIZE == 2) ptx::umma_f16(tmem_d, adesc, bdesc, idesc, acc);
-                else ptx::umma_tf32(tmem_d, adesc, bdesc, idesc, acc);
+                for (int ks = 0; ks < Cfg::KSUB; ++ks) {
+                  const uint64_t adesc = adesc_s + static_cast<uint64_t>((ks * 32) >> 4);
+                  const uint64_t bdesc = bdesc_s + static_cast<uint64_t>((ks * Cfg::UMMA_K * 128) >> 4);
+                  const uint32_t acc = (kk > 0 || ks > 0 || pr.accumulate) ? 1u : 0u;
+                  if (ESIZE == 2) ptx::umma_f16(tmem_d, adesc, bdesc, idesc, acc);
+                  else ptx::umma_tf32(tmem_d, adesc, bdesc, idesc, acc);
+                }
               }
               ptx::umma_commit(&empty_bar[stage]);
-              if (++stage == STAGES) { stage = 0; phase ^= 1u; }
             }
+            __syncwarp();
+            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
           }
-          if (ok && pr.commit) ptx::umma_commit(&slot_full[slot]);
+          if (ok && pr.commit) {
+            if (ptx::elect_one()) ptx::umma_commit(&slot_full[slot]);
+            __syncwarp();
+          }
         }
       }
     }
