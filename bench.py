@@ -182,7 +182,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--size", type=int, default=8192, help="M = N = K of the per-GPU problem")
-    ap.add_argument("--kernel", default="blackwell_f16_sw_interleaved_presum")
+    ap.add_argument("--kernel", default="blackwell_f16_sw_interleaved_presum_2sm")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -284,17 +284,18 @@ def main():
     per_launch = [x / args.steps for x in per_launch]
     lib.sb200_events_destroy(evl)
     dom = max(range(launches), key=lambda i: per_launch[i])
-    # algorithmic flops of a level-1 GEMM are 2MNK; each of its 7 products carries 1/7 of them
-    products = {1: [7], 2: [2, 5]}.get(launches, [7]) if "_sw_" in kernel else [1]
-    share = (products[dom] / sum(products)) if "_sw_" in kernel else 1.0
+    # algorithmic flops of a GEMM are 2MNK at every level; each of its 7 (49) products carries 1/7 (1/49) of them
+    level = {r.name: r.strassen_level for r in runner.kernels()}[kernel]
+    products = {0: [1], 1: {1: [7], 2: [2, 5]}.get(launches, [7]), 2: [2, 5] * 7}[level]
+    share = products[dom] / sum(products)
     peaks = _peaks()
     timed_s = elapsed_ms * 1e-3
     peak = peaks["burst"] if timed_s < 2.0 else peaks["sustained"]
     achieved = 2.0 * m * n * k * share / (per_launch[dom] * 1e-3) / 1e12
     traffic = NCU_TRAFFIC_BYTES.get((kernel, m, n, k))
     roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                "traffic": traffic, "kernel": f"launch {dom + 1} of {launches} ({products[dom] if '_sw_' in kernel else 1}"
-                f" of {sum(products) if '_sw_' in kernel else 1} products)", "launch_ms": per_launch,
+                "traffic": traffic, "kernel": f"launch {dom + 1} of {launches} ({products[dom]} of {sum(products)} products)",
+                "launch_ms": per_launch,
                 "peak_source": f"{peaks['source']} cuBLAS bf16 {'burst' if timed_s < 2.0 else 'sustained'}"}
 
     # end to end: pinned host buffers, copies inside the timed region, through the C ABI call
@@ -346,9 +347,9 @@ def main():
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": dtn, "data": "synthetic",
-            "config": {"workload": f"{dtn} Strassen-Winograd level 1, M=N=K={args.size} per GPU, uniform[-1,1) from seed 1"
-                       if "_sw_" in kernel else f"{dtn} GEMM level 0, M=N=K={args.size}",
-                       "kernel": kernel, "m": m * world, "n": n, "k": k, "level": 1 if "_sw_" in kernel else 0,
+            "config": {"workload": f"{dtn} Strassen-Winograd level {level}, M=N=K={args.size} per GPU, uniform[-1,1) from "
+                       "seed 1" if level else f"{dtn} GEMM level 0, M=N=K={args.size}",
+                       "kernel": kernel, "m": m * world, "n": n, "k": k, "level": level,
                        "l2": f"inputs larger than L2: {(m * k + k * n + m * n) * es / 2**20:.0f} MiB touched per step",
                        "parallelism": f"row slabs x{world}" + (", B all-gathered per step over NCCL" if world > 1 else "")},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches * args.steps, "roofline": roofline,

@@ -180,7 +180,8 @@ int sb200_gemm_events(const char* kernel, const void* a, const void* b, void* d,
                       size_t workspace_bytes, sb200_stream_t stream, sb200_event_list* list, int first_index);
 
 /* The tile program tables the kernels interpret (csrc/tile_program.h), for inspection and tests.
- * which: "level0" | "level1_full_fly" | "level1_full_ws" | "level1_first" | "level1_second" | "level1_second_taps" |
+ * which: "level0" | "level1_full_fly" | "level1_full_ws" | "level1_first" | "level1_first_early" | "level1_second" |
+ * "level1_second_taps" |
  * "level2_<child>_launch<1|2>" with child in m0, m1, m2, m4, m5, m3, m6. */
 int sb200_tile_program(const char* which, void* out, size_t out_bytes);
 size_t sb200_tile_program_bytes(void);

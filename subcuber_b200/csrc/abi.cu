@@ -449,6 +449,7 @@ extern "C" int sb200_tile_program(const char* which, void* out, size_t out_bytes
   else if (strcmp(which, "level1_full_fly") == 0) pg = sb200::programs::level1_full(true);
   else if (strcmp(which, "level1_full_ws") == 0) pg = sb200::programs::level1_full(false);
   else if (strcmp(which, "level1_first") == 0) pg = sb200::programs::level1_first();
+  else if (strcmp(which, "level1_first_early") == 0) pg = sb200::programs::level1_first_early();
   else if (strcmp(which, "level1_second") == 0) pg = sb200::programs::level1_second();
   else if (strcmp(which, "level1_second_taps") == 0) pg = sb200::programs::level1_second_taps();
   else if (strncmp(which, "level2_", 7) == 0) {

@@ -424,7 +424,7 @@ int launch_group(const LaunchSpec& s, cudaStream_t stream, MarkFn mark) {
       rc = launch_any(es, bn_sel, kPresumFeed, p, s.grid, stream);
       break;
     case kInterleavedPresum: {
-      const sb200_program_t first = programs::level1_first();
+      const sb200_program_t first = s.linked ? programs::level1_first() : programs::level1_first_early();
       const sb200_program_t second =
           getenv("SB200_L1_PLAIN") && !s.linked ? programs::level1_second() : programs::level1_second_taps();
       p.prog = s.linked ? programs::link_outer(first, s.link, 1) : first;

@@ -286,6 +286,7 @@ __device__ __forceinline__ void build_operand_tile(uint32_t smem_tile, uint32_t 
 template <int ESIZE>
 __device__ __forceinline__ void presum_side_job(const PresumSideJob& j, int gtid, int gthreads) {
   constexpr int EPV = 16 / ESIZE;
+  constexpr int U = 4;  // vector positions per thread per iteration: 16 loads in flight hide the memory latency
   const int vec_per_row = j.cols / EPV;
   const long long total = static_cast<long long>(j.rows) * vec_per_row;
   const long long q = static_cast<long long>(j.rows) * j.cols * ESIZE;  // bytes per result matrix
@@ -294,40 +295,53 @@ __device__ __forceinline__ void presum_side_job(const PresumSideJob& j, int gtid
   const char* s2 = static_cast<const char*>(j.src[2]);
   const char* s3 = static_cast<const char*>(j.src[3]);
   char* out = static_cast<char*>(j.dst);
-  for (long long v = gtid; v < total; v += gthreads) {
-    const int r = static_cast<int>(v / vec_per_row);
-    const int c = static_cast<int>(v - static_cast<long long>(r) * vec_per_row) * EPV;
-    const long long in = (r * j.ld + c) * ESIZE;
-    const uint4 x0 = ptx::ldg_nc_v4(s0 + in);
-    const uint4 x1 = ptx::ldg_nc_v4(s1 + in);
-    const uint4 x2 = ptx::ldg_nc_v4(s2 + in);
-    const uint4 x3 = ptx::ldg_nc_v4(s3 + in);
-    const long long o = (static_cast<long long>(r) * j.cols + c) * ESIZE;
-    if (j.side == 0) {
-      // A side: S1 = A2 + A3, S2 = S1 - A0, A02 = A0 - A2, A1S2 = A1 - S2
-      VecAcc<ESIZE> s;
-      s.set(x2, 1); s.add(x3, 1);                                   // S1
-      *reinterpret_cast<uint4*>(out + 0 * q + o) = s.pack();
-      s.add(x0, -1);                                                // S2 = S1 - A0 (unrounded S1)
-      *reinterpret_cast<uint4*>(out + 1 * q + o) = s.pack();
-      VecAcc<ESIZE> t;
-      t.set(x0, 1); t.add(x2, -1);                                  // A02
-      *reinterpret_cast<uint4*>(out + 2 * q + o) = t.pack();
-      VecAcc<ESIZE> u;                                              // A1S2 = A1 - S2 with the unrounded S2
-      u.set(x2, -1); u.add(x3, -1); u.add(x0, 1); u.add(x1, 1);
-      *reinterpret_cast<uint4*>(out + 3 * q + o) = u.pack();
-    } else {
-      // B side: B10 = B1 - B0, B31 = B3 - B1, S3 = B31 + B0, S3B2 = S3 - B2
-      VecAcc<ESIZE> s;
-      s.set(x1, 1); s.add(x0, -1);                                  // B10
-      *reinterpret_cast<uint4*>(out + 0 * q + o) = s.pack();
-      VecAcc<ESIZE> t;
-      t.set(x3, 1); t.add(x1, -1);                                  // B31
-      *reinterpret_cast<uint4*>(out + 1 * q + o) = t.pack();
-      t.add(x0, 1);                                                 // S3 = B31 + B0 (unrounded B31)
-      *reinterpret_cast<uint4*>(out + 2 * q + o) = t.pack();
-      t.add(x2, -1);                                                // S3B2 = S3 - B2 (unrounded S3)
-      *reinterpret_cast<uint4*>(out + 3 * q + o) = t.pack();
+  for (long long v0 = gtid; v0 < total; v0 += static_cast<long long>(gthreads) * U) {
+    uint4 x0[U], x1[U], x2[U], x3[U];
+    long long o[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long v = v0 + static_cast<long long>(u) * gthreads;
+      o[u] = -1;
+      if (v < total) {
+        const int r = static_cast<int>(v / vec_per_row);
+        const int c = static_cast<int>(v - static_cast<long long>(r) * vec_per_row) * EPV;
+        const long long in = (r * j.ld + c) * ESIZE;
+        x0[u] = ptx::ldg_nc_v4(s0 + in);
+        x1[u] = ptx::ldg_nc_v4(s1 + in);
+        x2[u] = ptx::ldg_nc_v4(s2 + in);
+        x3[u] = ptx::ldg_nc_v4(s3 + in);
+        o[u] = (static_cast<long long>(r) * j.cols + c) * ESIZE;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (o[u] < 0) continue;
+      if (j.side == 0) {
+        // A side: S1 = A2 + A3, S2 = S1 - A0, A02 = A0 - A2, A1S2 = A1 - S2
+        VecAcc<ESIZE> s;
+        s.set(x2[u], 1); s.add(x3[u], 1);                             // S1
+        *reinterpret_cast<uint4*>(out + 0 * q + o[u]) = s.pack();
+        s.add(x0[u], -1);                                             // S2 = S1 - A0 (unrounded S1)
+        *reinterpret_cast<uint4*>(out + 1 * q + o[u]) = s.pack();
+        VecAcc<ESIZE> t;
+        t.set(x0[u], 1); t.add(x2[u], -1);                            // A02
+        *reinterpret_cast<uint4*>(out + 2 * q + o[u]) = t.pack();
+        VecAcc<ESIZE> w;                                              // A1S2 = A1 - S2 with the unrounded S2
+        w.set(x2[u], -1); w.add(x3[u], -1); w.add(x0[u], 1); w.add(x1[u], 1);
+        *reinterpret_cast<uint4*>(out + 3 * q + o[u]) = w.pack();
+      } else {
+        // B side: B10 = B1 - B0, B31 = B3 - B1, S3 = B31 + B0, S3B2 = S3 - B2
+        VecAcc<ESIZE> s;
+        s.set(x1[u], 1); s.add(x0[u], -1);                            // B10
+        *reinterpret_cast<uint4*>(out + 0 * q + o[u]) = s.pack();
+        VecAcc<ESIZE> t;
+        t.set(x3[u], 1); t.add(x1[u], -1);                            // B31
+        *reinterpret_cast<uint4*>(out + 1 * q + o[u]) = t.pack();
+        t.add(x0[u], 1);                                              // S3 = B31 + B0 (unrounded B31)
+        *reinterpret_cast<uint4*>(out + 2 * q + o[u]) = t.pack();
+        t.add(x2[u], -1);                                             // S3B2 = S3 - B2 (unrounded S3)
+        *reinterpret_cast<uint4*>(out + 3 * q + o[u]) = t.pack();
+      }
     }
   }
 }

@@ -270,6 +270,13 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
             __syncwarp();
             if (++stage == STAGES) { stage = 0; phase ^= 1u; }
             mw_issue += SB200_CLOCK() - ti0;
+#ifdef SB200_PROFILE
+            if (p.prof && lane == 0 && blockIdx.x == 0 && iter == 3 && ps == 0 && kk < 64) {
+              p.prof[2048 + kk * 8 + 3] = tw;
+              p.prof[2048 + kk * 8 + 4] = ti0;
+              p.prof[2048 + kk * 8 + 5] = SB200_CLOCK();
+            }
+#endif
           }
           if (ok && pr.commit) {
             if (ptx::elect_one()) ptx::umma_commit_pair(&slot_full[slot], 3);

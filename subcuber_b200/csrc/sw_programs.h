@@ -131,6 +131,21 @@ inline sb200_program_t level1_first() {
   return pg;
 }
 
+// Launch 1 of 2 with an early release: the copy of M0 to the hand-off tile frees slot P at once and C0 is summed
+// from that tile (read back by the threads that wrote it) and slot Q.  The next tile's first product then never
+// waits for an epilogue step.  Used when the launch is not tied into a level above (one fp32 source fewer there).
+inline sb200_program_t level1_first_early() {
+  sb200_program_t pg;
+  memset(&pg, 0, sizeof(pg));
+  const int sP[] = {P}, sQ[] = {Q}, pos1[] = {1};
+  const int srcM0[] = {WS_M0};
+  add_product(pg, term1(A0), term1(B0), P, 0, 0, 1, 1);                // P = M0
+  add_product(pg, term1(A1), term1(B2), Q, 0, 0, 1, 1);                // Q = M1
+  add_epilogue(pg, 1, sP, pos1, 0, nullptr, mP, mP, 1, WS_M0);         // ws[M0] = P   (overlaps M1), P free
+  add_epilogue(pg, 1, sQ, pos1, 1, srcM0, mQ, mQ, 0, 0);               // C0 = M0 + Q
+  return pg;
+}
+
 // Launch 2 of 2: the five products that read presums from the workspace through TMA.
 inline sb200_program_t level1_second() {
   sb200_program_t pg;

@@ -136,6 +136,16 @@ def level1_first_program(ms) -> tp.Program:
     return b.pg
 
 
+def level1_first_early_program(ms) -> tp.Program:
+    """Launch 1 with an early release of slot P: c0 is summed from the m0 hand-off tile and slot Q, so the next tile's
+    first product never waits for an epilogue step (used when the launch is not tied into a level above)."""
+    b = ProgramBuilder(_products_by_name(ms), fly=False)
+    b.product("m0", P).product("m1", Q)
+    b.epilogue([P], [], wait=[P], release=[P], dst_kind=1, dst=WS_M0)
+    b.epilogue([Q], [WS_M0], wait=[Q], release=[Q], dst_kind=0, dst=0)               # c0 = m0 + m1
+    return b.pg
+
+
 def level1_second_program(ms) -> tp.Program:
     """Launch 2 of the interleaved-presum plan: the five products that read materialised presums."""
     b = ProgramBuilder(_products_by_name(ms), fly=False)
@@ -335,6 +345,7 @@ def all_programs() -> Dict[str, tp.Program]:
         "level1_full_fly": level1_full_program(ms, fly=True),
         "level1_full_ws": level1_full_program(ms, fly=False),
         "level1_first": level1_first_program(ms),
+        "level1_first_early": level1_first_early_program(ms),
         "level1_second": level1_second_program(ms),
         "level1_second_taps": level1_second_taps_program(ms),
         **{f"level2_{ch['name']}_launch{launch}":
@@ -354,8 +365,9 @@ def verify_programs(programs: Dict[str, tp.Program]) -> None:
         got = tp.check_program(programs[name], level=1)["outputs"]
         for q in range(4):
             assert np.array_equal(got[q], want[q]), (name, q)
-    r1 = tp.check_program(programs["level1_first"], level=1, expect=[0])
-    assert np.array_equal(r1["outputs"][0], want[0])
+    for name in ("level1_first_early", "level1_first"):
+        r1 = tp.check_program(programs[name], level=1, expect=[0])
+        assert np.array_equal(r1["outputs"][0], want[0]), name
     for name in ("level1_second", "level1_second_taps"):
         r2 = tp.check_program(programs[name], level=1, ws_in=r1["ws"], expect=[1, 2, 3])
         for q in (1, 2, 3):
@@ -391,7 +403,7 @@ def plan_for_schedule(schedule: list, level: int, mnk: Tuple[int, int, int], dty
                               "presum": "formed in shared memory by the presum warps"}]}
     else:
         plan = {"level": 1, "kernel": f"blackwell_{dtype}_sw_interleaved_presum_2sm",
-                "launches": [{"program": "level1_first", "products": ["m0", "m1"],
+                "launches": [{"program": "level1_first_early", "products": ["m0", "m1"],
                               "presum": "materialised by the presum warps of this launch"},
                              {"program": "level1_second_taps", "products": ["m4", "m2", "m5", "m3", "m6"],
                               "presum": "read from the workspace by TMA"}]}

@@ -117,7 +117,7 @@ def test_b200_target_and_build(tmp_path):
     assert "Generated Optimal Schedule:" in text and "Generated Fusion Schedule:" in text
     plan = json.load(open(tmp_path / "schedule.json"))["plan"]
     assert plan["kernel"] == "blackwell_f16_sw_interleaved_presum_2sm"
-    assert [l["program"] for l in plan["launches"]] == ["level1_first", "level1_second_taps"]
+    assert [l["program"] for l in plan["launches"]] == ["level1_first_early", "level1_second_taps"]
     programs = json.load(open(tmp_path / "tile_programs.json"))
     assert [p["a"] for p in programs["level1_second_taps"]["products"]][0] == [[1, "S1"]]
     assert "sb200_program_level1_second_taps" in open(tmp_path / "sw_tile_programs.inc").read()
