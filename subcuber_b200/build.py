@@ -64,8 +64,10 @@ def build(force: bool = False, verbose: bool = False) -> str:
         for src in sources:
             obj = os.path.join(CSRC, src.rsplit(".", 1)[0] + ".o")
             cmd = [nvcc, *NVCC_FLAGS, "-c", os.path.join(CSRC, src), "-o", obj]
-            if os.environ.get("SB200_PROFILE"):  # tuning aid: compile the in-kernel cycle counters in
-                cmd.insert(1, "-DSB200_PROFILE")
+            # tuning aid: compile in-kernel cycle counters in (SB200_PROFILE=1, or KSTEP / EPILOGUE / TRACE for more)
+            prof = os.environ.get("SB200_PROFILE")
+            if prof:
+                cmd.insert(1, "-DSB200_PROFILE" + ("" if prof == "1" else "_" + prof.upper()))
             if verbose:
                 cmd.insert(1, "-Xptxas")
                 cmd.insert(2, "-v")

@@ -83,15 +83,16 @@ __device__ __forceinline__ bool wait_flag(const int* flag, int epoch, volatile i
 // until the first half's partial sum is published) and returns false when the wait was given up.
 //   tile_off / outer_off: float offsets of this unit's tile in the level-1 hand-off buffers (ws index < 4) and in the
 //                         buffers of the level above (index >= 4)
+//   NSRC_MAX / NSLOT_MAX: most fp32 sources / TMEM slots a step of the programs this kernel runs can list
 //   redirect: non-null = first half of a split tile: write the fp32 partial sum there, skip the outer sources
 //   late_src: non-null = second half: one more fp32 source, readable only after wait_slots()
-template <int ESIZE, int BN, int NSRC_MAX, typename WaitFn>
+template <int ESIZE, int BN, int NSRC_MAX, int NSLOT_MAX, typename WaitFn>
 __device__ __forceinline__ bool epilogue_body(void* const* out, long long ldo, int out_rows, int out_cols,
                                               float* const* ws, const sb200_epilogue_t& ep, uint32_t sx,
                                               uint32_t tmem_base, int quarter, int lane, long long tile_off,
                                               long long outer_off, int grow_tile, int gcol_tile, uint32_t staging_warp,
                                               float* redirect, const float* late_src, bool skip_body,
-                                              WaitFn wait_slots) {
+                                              WaitFn wait_slots, long long* prof = nullptr) {
   if (skip_body) return wait_slots();  // measurement aid
   constexpr int NCHUNK = BN / 32;
   const int row = quarter * 32 + lane;
@@ -134,6 +135,16 @@ __device__ __forceinline__ bool epilogue_body(void* const* out, long long ldo, i
       for (int q = 0; q < 8; ++q) nxt[t][q] = srcp[t][q * 128];
     }
 
+  uint32_t rn[32];
+  const uint32_t tmem_slot0 = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + (ep.slot[0] ^ sx) * BN;
+  if (ep.nslots > 0) ptx::tmem_ld_32x32(tmem_slot0, rn);
+#ifdef SB200_PROFILE_EPILOGUE
+#define SB200_SEG(i) { const long long tn = clock64(); seg[i] += tn - tseg; tseg = tn; }
+  long long seg[5] = {0, 0, 0, 0, 0};
+  long long tseg = clock64();
+#else
+#define SB200_SEG(i)
+#endif
 #pragma unroll 1
   for (int c = 0; c < NCHUNK; ++c) {
     float acc[32];
@@ -158,8 +169,28 @@ __device__ __forceinline__ bool epilogue_body(void* const* out, long long ldo, i
           for (int q = 0; q < 8; ++q) nxt[t][q] = srcp[t][((c + 1) * 8 + q) * 128];
         }
     }
+    SB200_SEG(0)
+    // slot 0 of the step: its chunk was requested one iteration ago (or before the loop); take it, then request the
+    // next chunk at once so that the TMEM read overlaps the conversion and the stores below
+    if (ep.nslots > 0) {
+#ifdef SB200_PROFILE_EPILOGUE
+      const long long tl0 = clock64();
+#endif
+      ptx::tmem_ld_wait();
+#ifdef SB200_PROFILE_EPILOGUE
+      seg[4] += clock64() - tl0;
+#endif
+      if (ep.slot_sign[0] > 0) {
 #pragma unroll
-    for (int t = 0; t < SB200_MAX_SLOT_TERMS; ++t) {
+        for (int q = 0; q < 32; ++q) acc[q] += __uint_as_float(rn[q]);
+      } else {
+#pragma unroll
+        for (int q = 0; q < 32; ++q) acc[q] -= __uint_as_float(rn[q]);
+      }
+      if (c + 1 < NCHUNK) ptx::tmem_ld_32x32(tmem_slot0 + (c + 1) * 32, rn);
+    }
+#pragma unroll
+    for (int t = 1; t < NSLOT_MAX; ++t) {
       if (t < ep.nslots) {
         uint32_t r[32];
         ptx::tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + (ep.slot[t] ^ sx) * BN + c * 32, r);
@@ -173,6 +204,7 @@ __device__ __forceinline__ bool epilogue_body(void* const* out, long long ldo, i
         }
       }
     }
+    SB200_SEG(1)
     if (to_fp32) {
 #pragma unroll
       for (int q = 0; q < 8; ++q)
@@ -188,6 +220,7 @@ __device__ __forceinline__ bool epilogue_body(void* const* out, long long ldo, i
         for (int q = 0; q < 4; ++q) h[q] = __floats2half2_rn(acc[g * 8 + 2 * q], acc[g * 8 + 2 * q + 1]);
         ptx::sts_v4(wr + g * 16, o);
       }
+      SB200_SEG(2)
       if (c & 1) {
         __syncwarp();
         const int col = gcol_tile + (c - 1) * 32 + (lane & 7) * 8;
@@ -225,7 +258,15 @@ __device__ __forceinline__ bool epilogue_body(void* const* out, long long ldo, i
       }
       __syncwarp();
     }
+    SB200_SEG(3)
   }
+#ifdef SB200_PROFILE_EPILOGUE
+  if (prof && lane == 0) {
+    prof[0] += seg[4];
+    prof[1] += NCHUNK * ep.nslots;
+    for (int i = 0; i < 4; ++i) prof[2 + i] += seg[i];
+  }
+#endif
   return true;
 }
 

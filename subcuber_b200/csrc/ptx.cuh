@@ -288,6 +288,16 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity
     }
   }
 }
+// Warp-level wait: every lane polls and every lane returns the same result.  (Measured on B200: letting one lane poll
+// while the others wait at a warp barrier, or backing off between polls, changes neither the time nor the sustained
+// clock of the GEMM kernels.)  CLUSTER selects the cluster-scope acquire, for barriers that CTAs of the pair arrive
+// on after generic-proxy writes.
+template <bool CLUSTER>
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  const bool ok = CLUSTER ? mbar_wait_cluster(bar, parity, abort_flag) : mbar_wait(bar, parity, abort_flag);
+  return __all_sync(0xffffffffu, ok);
+}
+
 __device__ __forceinline__ void fence_proxy_async_all() {
   asm volatile("fence.proxy.async;" ::: "memory");
 }

@@ -388,6 +388,16 @@ int launch_group(const LaunchSpec& s, cudaStream_t stream, MarkFn mark) {
       fprintf(stderr, "[prof] leader mma thread: total %.0f = wait_full %.0f + wait_free %.0f + issue %.0f + rest | "
               "producer: wait_empty %.0f issue %.0f total %.0f\n",
               sum[0] / n, sum[1] / n, sum[2] / n, sum[5] / n, sum[3] / n, sum[7] / n, sum[4] / n);
+      if (prof_host[1191])
+        fprintf(stderr, "[prof] tcgen05.ld 32x32 + wait: %.0f cycles per load (%lld loads)\n",
+                double(prof_host[1190]) / double(prof_host[1191]), prof_host[1191]);
+      fprintf(stderr, "[prof] epilogue segments (cycles, whole launch, warp 2 of CTA 0): sources %lld, tmem+add %lld, "
+              "convert/stage or fp32 store %lld, output store %lld\n", prof_host[1192], prof_host[1193], prof_host[1194],
+              prof_host[1195]);
+      for (int es = 0; es < 16; ++es)
+        if (prof_host[1200 + es * 2 + 1])
+          fprintf(stderr, "[prof] epilogue step %d: %.0f cycles per call (%lld calls)\n", es,
+                  double(prof_host[1200 + es * 2]) / double(prof_host[1200 + es * 2 + 1]), prof_host[1200 + es * 2 + 1]);
       if (getenv("SB200_PROF_TRACE")) {
         // per k-step of one tile of CTA 0 (cycles relative to the first entry): producer saw the stage empty / issued
         // its loads, an observer saw the stage full, the MMA thread started waiting / got the stage / had issued

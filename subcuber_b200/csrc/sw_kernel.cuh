@@ -101,6 +101,8 @@ struct KernelConfig {
   // sum of a split tile).  The kernels with presum warps have a smaller register budget and run programs that
   // need fewer: JOB = first launch of the interleaved plan (1 + 1), FEED = one fused launch, never linked or split.
   static constexpr int NSRC_MAX = MODE_ == 0 ? SB200_MAX_SRC_TERMS + 1 : (MODE_ == 2 ? 2 : 1);
+  // TMEM slots a step may sum: the programs of the kernels without presum warps read one slot per step
+  static constexpr int NSLOT_MAX = MODE_ == 0 ? 1 : 2;
   static constexpr int UMMA_K = 32 / ESIZE;
   static constexpr int KSUB = BK / UMMA_K;        // MMAs per stage (4)
   static constexpr int A_BYTES = BM * 128;
@@ -562,7 +564,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_kernel(const 
         };
         const long long tile_off = static_cast<long long>(wu.ws_slot) * (128 * BN);
         const long long outer_off = static_cast<long long>(wu.tile) * (128 * BN);
-        ok = epilogue_body<ESIZE, BN, Cfg::NSRC_MAX>(p.out, p.ldo, p.out_rows, p.out_cols, p.ws, ep, sx, tmem_base, quarter,
+        ok = epilogue_body<ESIZE, BN, Cfg::NSRC_MAX, Cfg::NSLOT_MAX>(p.out, p.ldo, p.out_rows, p.out_cols, p.ws, ep, sx, tmem_base, quarter,
                                                      lane, tile_off, outer_off, tile.i * 128, tile.j * BN,
                                                      staging + (warp - 2) * kStagingWarpBytes,
                                                      sp.redirect ? split_tile_buf : nullptr,

@@ -14,8 +14,22 @@
 #pragma once
 #include "sw_kernel.cuh"
 
-// Cycle counters for tuning are compiled in only with -DSB200_PROFILE; otherwise they cost nothing.
+// Cycle counters for tuning are compiled in only on request; otherwise they cost nothing.
+//   -DSB200_PROFILE           per-launch totals and the MMA issuer's waits for a free TMEM slot (two clock reads per product)
+//   -DSB200_PROFILE_KSTEP     + clock reads around every k-step (MMA issuer, producer)
+//   -DSB200_PROFILE_EPILOGUE  + epilogue step and segment timers
+//   -DSB200_PROFILE_TRACE     + a per-k-step timeline of one tile (adds an observer warp)
+#if defined(SB200_PROFILE_KSTEP) || defined(SB200_PROFILE_EPILOGUE) || defined(SB200_PROFILE_TRACE)
+#ifndef SB200_PROFILE
+#define SB200_PROFILE
+#endif
+#endif
 #ifdef SB200_PROFILE
+#define SB200_CLOCK_LIGHT() clock64()
+#else
+#define SB200_CLOCK_LIGHT() 0ll
+#endif
+#if defined(SB200_PROFILE_KSTEP) || defined(SB200_PROFILE_TRACE)
 #define SB200_CLOCK() clock64()
 #else
 #define SB200_CLOCK() 0ll
@@ -37,6 +51,8 @@ struct PairConfig {
   // sum of a split tile).  The kernels with presum warps have a smaller register budget and run programs that
   // need fewer: JOB = first launch of the interleaved plan (1 + 1), FEED = one fused launch, never linked or split.
   static constexpr int NSRC_MAX = MODE_ == 0 ? SB200_MAX_SRC_TERMS + 1 : (MODE_ == 2 ? 2 : 1);
+  // TMEM slots a step may sum: the programs of the kernels without presum warps read one slot per step
+  static constexpr int NSLOT_MAX = MODE_ == 0 ? 1 : 2;
   static constexpr int UMMA_K = 32 / ESIZE;
   static constexpr int KSUB = BK / UMMA_K;
   static constexpr int A_BYTES = BM * 128;
@@ -48,7 +64,7 @@ struct PairConfig {
   static constexpr int TMEM_COLS = 512;
   static constexpr int PRESUM_WARPS = (MODE == kPresumNone) ? 0 : 4;
   // warps 0-5 as in sw_kernel.cuh; warps 6 and 7 = more TMA producers (see the producer section); presum warps follow
-#ifdef SB200_PROFILE
+#ifdef SB200_PROFILE_TRACE
   static constexpr int FIRST_PRESUM_WARP = (MODE_ == kPresumNone) ? 9 : 8;  // warp 8 = full-barrier monitor (tracing)
 #else
   static constexpr int FIRST_PRESUM_WARP = 8;
@@ -152,8 +168,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
             }
             const long long tw = SB200_CLOCK();
             // the stage-empty barrier is signalled by tcgen05.commit only: no cluster-scope acquire needed
-            bool got = ptx::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag);
-            got = __all_sync(0xffffffffu, got);
+            const bool got = ptx::mbar_wait_warp<false>(&empty_bar[stage], phase ^ 1u, abort_flag);
             if (!got) {
               if (lane == 0) raise_abort(p, abort_flag, kStatusProducerTimeout);
               ok = false;
@@ -161,7 +176,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
             }
             const long long tw2 = SB200_CLOCK();
             pw_empty += tw2 - tw;
-#ifdef SB200_PROFILE
+#ifdef SB200_PROFILE_TRACE
             const bool traced = p.prof && lane == 0 && blockIdx.x == 0 && w == pair + 3 * num_pairs && ps == 0 && kk < 64;
             if (traced) p.prof[2048 + kk * 8 + 0] = tw2;
 #endif
@@ -187,7 +202,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
             }
             __syncwarp();
             pw_issue += SB200_CLOCK() - tw2;
-#ifdef SB200_PROFILE
+#ifdef SB200_PROFILE_TRACE
             if (traced) p.prof[2048 + kk * 8 + 1] = SB200_CLOCK();
 #endif
             if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -209,7 +224,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
       uint32_t free_bits = 0;
       uint32_t iter = 0;
       bool ok = true;
-      const long long mt0 = SB200_CLOCK();
+      const long long mt0 = SB200_CLOCK_LIGHT();
       long long mw_full = 0, mw_free = 0, mw_issue = 0;
       for (int w = pair; ok && w < total_tiles; w += num_pairs, ++iter) {
         const WorkUnit wu = unit_of(p, w);
@@ -219,15 +234,14 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
           const sb200_product_t& pr = p.prog.product[ps];
           const uint32_t slot = pr.slot ^ sx;
           if (pr.wait_free) {
-            const long long tw = SB200_CLOCK();
-            bool got = ptx::mbar_wait_cluster(&slot_free[slot], ((free_bits >> slot) & 1u) ^ 1u, abort_flag);
-            got = __all_sync(0xffffffffu, got);
+            const long long tw = SB200_CLOCK_LIGHT();
+            const bool got = ptx::mbar_wait_warp<true>(&slot_free[slot], ((free_bits >> slot) & 1u) ^ 1u, abort_flag);
             if (!got) {
               if (lane == 0) raise_abort(p, abort_flag, kStatusMmaTimeout);
               ok = false;
               break;
             }
-            mw_free += SB200_CLOCK() - tw;
+            mw_free += SB200_CLOCK_LIGHT() - tw;
             free_bits ^= (1u << slot);
             ptx::tc_fence_after_sync();
           }
@@ -242,9 +256,9 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
             const long long tw = SB200_CLOCK();
             // in FEED mode the peer's presum warps arrive on this barrier after writing their own shared memory
             // through the generic proxy: that hand-over needs the cluster-scope acquire; TMA-only stages do not
-            bool got = (Cfg::MODE == kPresumFeed) ? ptx::mbar_wait_cluster(&full_bar[stage], phase, abort_flag)
-                                                  : ptx::mbar_wait(&full_bar[stage], phase, abort_flag);
-            got = __all_sync(0xffffffffu, got);
+            const bool got = (Cfg::MODE == kPresumFeed)
+                                 ? ptx::mbar_wait_warp<true>(&full_bar[stage], phase, abort_flag)
+                                 : ptx::mbar_wait_warp<false>(&full_bar[stage], phase, abort_flag);
             if (!got) {
               if (lane == 0) raise_abort(p, abort_flag, kStatusMmaTimeout);
               ok = false;
@@ -270,7 +284,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
             __syncwarp();
             if (++stage == STAGES) { stage = 0; phase ^= 1u; }
             mw_issue += SB200_CLOCK() - ti0;
-#ifdef SB200_PROFILE
+#ifdef SB200_PROFILE_TRACE
             if (p.prof && lane == 0 && blockIdx.x == 0 && iter == 3 && ps == 0 && kk < 64) {
               p.prof[2048 + kk * 8 + 3] = tw;
               p.prof[2048 + kk * 8 + 4] = ti0;
@@ -285,13 +299,13 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
         }
       }
       if (p.prof && lane == 0) {
-        p.prof[blockIdx.x * 8 + 0] = SB200_CLOCK() - mt0;
+        p.prof[blockIdx.x * 8 + 0] = SB200_CLOCK_LIGHT() - mt0;
         p.prof[blockIdx.x * 8 + 1] = mw_full;
         p.prof[blockIdx.x * 8 + 2] = mw_free;
         p.prof[blockIdx.x * 8 + 5] = mw_issue;
       }
     }
-#ifdef SB200_PROFILE
+#ifdef SB200_PROFILE_TRACE
   } else if (warp == 8 && Cfg::MODE == kPresumNone) {
     // tracing only: an observer that waits on the full barriers in ring order and notes when each completed
     if (lane == 0 && rank == 0 && p.prof) {
@@ -333,9 +347,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
             if ((ep.wait_full_mask >> s0) & 1u) {
               const uint32_t s = s0 ^ sx;
               const long long tw = SB200_CLOCK();
-              bool got = ptx::mbar_wait_cluster(&slot_full[s], (full_bits >> s) & 1u, abort_flag);
+              const bool got = ptx::mbar_wait_warp<true>(&slot_full[s], (full_bits >> s) & 1u, abort_flag);
               ew_full += SB200_CLOCK() - tw;
-              got = __all_sync(0xffffffffu, got);
               if (!got) {
                 if (lane == 0) raise_abort(p, abort_flag, kStatusEpilogueTimeout);
                 return false;
@@ -352,14 +365,26 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
         };
         const long long tile_off = (static_cast<long long>(wu.ws_slot) * 2 + rank) * (128 * BN);
         const long long outer_off = (static_cast<long long>(wu.tile) * 2 + rank) * (128 * BN);
-        ok = epilogue_body<ESIZE, BN, Cfg::NSRC_MAX>(p.out, p.ldo, p.out_rows, p.out_cols, p.ws, ep, sx, tmem_base, quarter,
+#ifdef SB200_PROFILE_EPILOGUE
+        const long long te0 = SB200_CLOCK();
+        const long long ew0 = ew_full;
+#endif
+        ok = epilogue_body<ESIZE, BN, Cfg::NSRC_MAX, Cfg::NSLOT_MAX>(p.out, p.ldo, p.out_rows, p.out_cols, p.ws, ep, sx, tmem_base, quarter,
                                                      lane, tile_off, outer_off,
                                                      tile.i * Cfg::PAIR_M + static_cast<int>(rank) * Cfg::BM, tile.j * BN,
                                                      staging + (warp - 2) * kStagingWarpBytes,
                                                      sp.redirect ? split_tile_buf : nullptr,
                                                      sp.add_partial ? split_tile_buf : nullptr,
-                                                     (p.debug_flags & 32) != 0, wait_slots);
+                                                     (p.debug_flags & 32) != 0, wait_slots,
+                                                     (p.prof && blockIdx.x == 0 && warp == 2) ? p.prof + 1190 : nullptr);
         if (!ok) break;
+#ifdef SB200_PROFILE_EPILOGUE
+        if (p.prof && blockIdx.x == 0 && warp == 2 && lane == 0 && es < 16) {
+          // per epilogue step: cycles in the body without the slot wait, and the count
+          p.prof[1200 + es * 2] += (SB200_CLOCK() - te0) - (ew_full - ew0);
+          p.prof[1200 + es * 2 + 1] += 1;
+        }
+#endif
         if (sp.redirect) raise_flag(flag, p.split_epoch, lane);
         ptx::tc_fence_before_sync();
         __syncwarp();

@@ -164,27 +164,33 @@ inline sb200_program_t level1_second() {
   return pg;
 }
 
-// Launch 2 of 2, variant with short taps: whenever the next product must wait for an epilogue step, that step is
-// only a copy of a slot into an fp32 hand-off tile plus at most one hand-off read (requested before the wait, see
-// epilogue.cuh); the sums that need more hand-off tiles (C1, C3) run while the MMA pipeline is already on the next
-// product.  No step reads more than two hand-off tiles, which leaves one source free for the level above.
+// Launch 2 of 2, the plan in use: no product ever waits for an epilogue step that has not had a whole product's
+// time to finish.
+//   * a slot that keeps accumulating (P: M2, then + M3) is tapped into an fp32 hand-off tile while the OTHER slot's
+//     product runs (the tap adds M0, requested before the wait, see epilogue.cuh);
+//   * the last product (M6) goes to slot Q instead of being subtracted into P, so the tap of P after M3 overlaps it,
+//     and C2 = V - Q is formed from the hand-off tile;
+//   * the slot roles swap from tile to tile (alternate_slots), so the next tile's first product takes the slot that
+//     was released a whole product earlier.
+// No step reads more than two hand-off tiles, which leaves one source free for the level above.
 //   hand-offs: M4, U = M0 + M2, V = M0 + (M2 + M3)   (M0 comes from launch 1)
 inline sb200_program_t level1_second_taps() {
   sb200_program_t pg;
   memset(&pg, 0, sizeof(pg));
-  const int sP[] = {P}, sQ[] = {Q}, pos1[] = {1};
-  const int srcC1[] = {WS_U, WS_M4}, srcC3[] = {WS_V, WS_M4}, srcM0[] = {WS_M0};
+  pg.alternate_slots = 1;
+  const int sP[] = {P}, sQ[] = {Q}, pos1[] = {1}, neg1[] = {-1};
+  const int srcC1[] = {WS_U, WS_M4}, srcC3[] = {WS_V, WS_M4}, srcM0[] = {WS_M0}, srcV[] = {WS_V};
   add_product(pg, term1(PS1), term1(PB10), Q, 0, 0, 1, 1);             // Q  = M4
   add_product(pg, term1(PS2), term1(PS3), P, 0, 0, 1, 1);              // P  = M2
-  add_epilogue(pg, 1, sQ, pos1, 0, nullptr, mQ, mQ, 1, WS_M4);         // ws[M4] = Q             (overlaps M2)
-  add_epilogue(pg, 1, sP, pos1, 1, srcM0, mP, mP, 1, WS_U);            // ws[U]  = M0 + P        (tap before M3)
+  add_epilogue(pg, 1, sQ, pos1, 0, nullptr, mQ, mQ, 1, WS_M4);         // ws[M4] = Q             (during M2)
+  add_epilogue(pg, 1, sP, pos1, 1, srcM0, mP, mP, 1, WS_U);            // ws[U]  = M0 + P        (during M5)
   add_product(pg, term1(PA1S2), term1(B3), Q, 0, 0, 1, 1);             // Q  = M5
   add_product(pg, term1(PA02), term1(PB31), P, 1, 0, 1, 1);            // P += M3
-  add_epilogue(pg, 1, sQ, pos1, 2, srcC1, mQ, mQ, 0, 1);               // C1 = U + M4 + Q        (overlaps M3)
-  add_epilogue(pg, 1, sP, pos1, 1, srcM0, mP, mP, 1, WS_V);            // ws[V]  = M0 + P        (tap before M6)
-  add_product(pg, term1(A3), term1(PS3B2), P, 1, 1, 1, 1);             // P -= M6
-  add_epilogue(pg, 0, nullptr, nullptr, 2, srcC3, 0, 0, 0, 3);         // C3 = V + M4            (overlaps M6)
-  add_epilogue(pg, 1, sP, pos1, 1, srcM0, mP, mP, 0, 2);               // C2 = M0 + P
+  add_epilogue(pg, 1, sQ, pos1, 2, srcC1, mQ, mQ, 0, 1);               // C1 = U + M4 + Q        (during M3)
+  add_epilogue(pg, 1, sP, pos1, 1, srcM0, mP, mP, 1, WS_V);            // ws[V]  = M0 + P        (during M6)
+  add_product(pg, term1(A3), term1(PS3B2), Q, 0, 0, 1, 1);             // Q  = M6
+  add_epilogue(pg, 0, nullptr, nullptr, 2, srcC3, 0, 0, 0, 3);         // C3 = V + M4
+  add_epilogue(pg, 1, sQ, neg1, 1, srcV, mQ, mQ, 0, 2);                // C2 = V - Q             (during the next M4)
   return pg;
 }
 

@@ -161,19 +161,21 @@ def level1_second_program(ms) -> tp.Program:
 
 
 def level1_second_taps_program(ms) -> tp.Program:
-    """Launch 2 with short taps: a product only ever waits for a step that copies a slot to a hand-off tile (adding at
-    most one hand-off tile, requested before the wait).  Hand-offs: m4, u = m0 + m2, v = m0 + (m2 + m3), and m0 from
-    launch 1; c1 and c3 are summed off the critical path.  No step reads more than two hand-off tiles."""
+    """Launch 2, the plan in use: no product waits for an epilogue step that has not had a whole product's time.
+    A slot that keeps accumulating is tapped into a hand-off tile while the other slot's product runs; m6 goes to
+    slot Q (c2 = v - Q) so that the tap after m3 overlaps it; slot roles swap from tile to tile.  Hand-offs: m4,
+    u = m0 + m2, v = m0 + (m2 + m3), and m0 from launch 1.  No step reads more than two hand-off tiles."""
     b = ProgramBuilder(_products_by_name(ms), fly=False)
+    b.pg.alternate_slots = 1
     b.product("m4", Q).product("m2", P)
     b.epilogue([Q], [], wait=[Q], release=[Q], dst_kind=1, dst=WS_M4)
     b.epilogue([P], [WS_M0], wait=[P], release=[P], dst_kind=1, dst=WS_U)            # u = m0 + m2
     b.product("m5", Q).product("m3", P, accumulate=1)
     b.epilogue([Q], [WS_U, WS_M4], wait=[Q], release=[Q], dst_kind=0, dst=1)         # c1 = u + m4 + m5
     b.epilogue([P], [WS_M0], wait=[P], release=[P], dst_kind=1, dst=WS_V)            # v = m0 + m2 + m3
-    b.product("m6", P, accumulate=1, negate=1)
+    b.product("m6", Q)
     b.epilogue([], [WS_V, WS_M4], wait=[], release=[], dst_kind=0, dst=3)            # c3 = v + m4
-    b.epilogue([P], [WS_M0], wait=[P], release=[P], dst_kind=0, dst=2)               # c2 = m0 + m2 + m3 - m6
+    b.epilogue([Q], [WS_V], wait=[Q], release=[Q], dst_kind=0, dst=2, signs=[-1])    # c2 = v - m6
     return b.pg
 
 
