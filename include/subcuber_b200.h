@@ -86,6 +86,12 @@ SB200_DECLARE_RUN(run_blackwell_f16_sw_level2);
 SB200_DECLARE_RUN(run_blackwell_f32_sw_level2);
 SB200_DECLARE_RUN(run_blackwell_f16_sw_level2_2sm);
 SB200_DECLARE_RUN(run_blackwell_f32_sw_level2_2sm);
+/* fp64 on the double-precision tensor-core instruction (mma.sync.m16n8k16.f64): plain GEMM, level 1 (2 standalone
+ * presum launches + 7 product launches whose epilogue adds the postsums) and level 2 (2 + 7 x 9 launches).  Stand where the reference has its f64 DMMA kernels
+ * (src/cuda/kernels/ampere_f64_*.cu via kernel_runner.cpp:99-180). */
+SB200_DECLARE_RUN(run_blackwell_f64_cubic_dmma);
+SB200_DECLARE_RUN(run_blackwell_f64_sw_level1);
+SB200_DECLARE_RUN(run_blackwell_f64_sw_level2);
 /* cuBLAS baselines behind the same ABI (reference: src/cuda/cublas_runner.cpp:151-175); the tf32 row is
  * an addition: the reference's f32 row is CUBLAS_COMPUTE_32F_PEDANTIC (cublas_runner.cpp:14). */
 SB200_DECLARE_RUN(run_cublas_f16);
@@ -166,7 +172,7 @@ int sb200_gemm_workspace_layout(const char* kernel, int m, int n, int k, sb200_w
 
 /* Like sb200_gemm, but synchronises and reports the device time of each kernel launch of the call
  * (CUDA events on `stream`); launch_ms must have room for SB200_MAX_LAUNCHES floats. */
-#define SB200_MAX_LAUNCHES 16
+#define SB200_MAX_LAUNCHES 80
 int sb200_gemm_timed(const char* kernel, const void* a, const void* b, void* d, int m, int n, int k, void* workspace,
                      size_t workspace_bytes, sb200_stream_t stream, float* launch_ms, int* num_launches);
 

@@ -44,6 +44,9 @@ const KernelDesc kDescs[] = {
     {"blackwell_f32_sw_level2", "f32", 2, sb200::kF32, sb200::kInterleavedLevel2, 256, 0},
     {"blackwell_f16_sw_level2_2sm", "f16", 2, sb200::kF16, sb200::kInterleavedLevel2, 256, 1},
     {"blackwell_f32_sw_level2_2sm", "f32", 2, sb200::kF32, sb200::kInterleavedLevel2, 256, 1},
+    {"blackwell_f64_cubic_dmma", "f64", 0, sb200::kF64, sb200::kCubic, 0, 0},
+    {"blackwell_f64_sw_level1", "f64", 1, sb200::kF64, sb200::kFusedPresum, 0, 0},
+    {"blackwell_f64_sw_level2", "f64", 2, sb200::kF64, sb200::kInterleavedLevel2, 0, 0},
 };
 constexpr int kNumDescs = sizeof(kDescs) / sizeof(kDescs[0]);
 
@@ -278,6 +281,9 @@ SB200_DEFINE_RUN(blackwell_f16_sw_level2)
 SB200_DEFINE_RUN(blackwell_f32_sw_level2)
 SB200_DEFINE_RUN(blackwell_f16_sw_level2_2sm)
 SB200_DEFINE_RUN(blackwell_f32_sw_level2_2sm)
+SB200_DEFINE_RUN(blackwell_f64_cubic_dmma)
+SB200_DEFINE_RUN(blackwell_f64_sw_level1)
+SB200_DEFINE_RUN(blackwell_f64_sw_level2)
 
 #define SB200_DEFINE_BLAS(fn, impl, type)                                                                      \
   extern "C" int fn(KernelRunnerBuffers buffers, int m, int n, int k, int warmup_iterations, int iterations,   \
@@ -318,6 +324,9 @@ static const sb200_kernel_entry kRegistry[] = {
     {"blackwell_f32_sw_level2", "blackwell", "f32", 2, run_blackwell_f32_sw_level2},
     {"blackwell_f16_sw_level2_2sm", "blackwell", "f16", 2, run_blackwell_f16_sw_level2_2sm},
     {"blackwell_f32_sw_level2_2sm", "blackwell", "f32", 2, run_blackwell_f32_sw_level2_2sm},
+    {"blackwell_f64_cubic_dmma", "blackwell", "f64", 0, run_blackwell_f64_cubic_dmma},
+    {"blackwell_f64_sw_level1", "blackwell", "f64", 1, run_blackwell_f64_sw_level1},
+    {"blackwell_f64_sw_level2", "blackwell", "f64", 2, run_blackwell_f64_sw_level2},
 };
 
 extern "C" int sb200_num_kernels(void) { return static_cast<int>(sizeof(kRegistry) / sizeof(kRegistry[0])); }

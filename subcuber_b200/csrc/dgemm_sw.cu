@@ -1,0 +1,376 @@
+// fp64 path: Strassen-Winograd levels 0, 1 and 2 on the double-precision tensor-core instruction (DMMA,
+// mma.sync.m16n8k16.f64).  tcgen05 has no fp64 kind, so this path is a classic shared-memory tiled kernel.
+//
+// It covers, for fp64, what the reference covers with its f64 kernels (DMMA mainloop
+// include/cutlass/gemm/threadblock/strassen_mma_multistage.h, standalone presum kernel
+// strassen_presum_global_kernel.h:18-202 = the reference's "kernel presum" mode, postsum epilogue
+// epilogue/threadblock/strassen_epilogue.h):
+//   * the eight presums of a recursion step are materialised by one standalone elementwise kernel per operand
+//     (at fp64 rates the extra traffic is under one percent of the product time);
+//   * one product kernel computes P = X * Y for a 128 x 128 tile through a four-stage cp.async ring;
+//   * its epilogue adds +-P straight into every output block the product belongs to (or stores it, for the first
+//     writer of a block): the postsum needs no interim matrices and no separate pass;
+//   * level 1 = 2 presum + 7 product launches; level 2 = 2 outer presum launches + 7 x (2 + 7).
+// All sums are fp64, so the only difference to the reference routine is the order of the additions.
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <string.h>
+
+#include <vector>
+
+#include "sw_host.h"
+
+namespace sb200 {
+namespace f64 {
+
+constexpr int BM = 128, BN = 128, BK = 16;
+constexpr int PA = BK + 4;    // row pitch of the A tile in doubles: fragment loads of a half-warp hit 16 distinct banks
+constexpr int PB = BN + 4;    // row pitch of the B tile
+constexpr int THREADS = 256;  // 8 warps: 4 (rows) x 2 (columns), 32 x 64 outputs each
+constexpr int STAGES = 4;
+constexpr int STAGE_DOUBLES = BM * PA + BK * PB;
+constexpr int MAX_DST = 16;
+
+struct Dst {
+  double* ptr;
+  double sign;     // +1 or -1
+  int accumulate;  // 0: store sign * P; 1: add it to what is there
+};
+struct ProductParams {
+  const double* a;     // m x k, row-major
+  const double* b;     // k x n, row-major
+  long long lda, ldb;  // leading dimensions in elements
+  Dst dst[MAX_DST];
+  int ndst;
+  long long ldd;
+  int m, n, k;         // extent of the product
+};
+
+// D (16 x 8) += A (16 x 16, row) * B (16 x 8, col).  Per lane, with g = lane / 4 and t = lane % 4:
+//   a[i]: row g + 8 * (i & 1), column t + 4 * (i >> 1);   b[i]: row t + 4 * i, column g;
+//   c[i]: row g + 8 * (i >> 1), column 2 * t + (i & 1)
+__device__ __forceinline__ void dmma(double (&c)[4], const double (&a)[8], const double (&b)[4]) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f64.f64.f64.f64 {%0, %1, %2, %3}, {%4, %5, %6, %7, %8, %9, %10, %11}, "
+      "{%12, %13, %14, %15}, {%0, %1, %2, %3};"
+      : "+d"(c[0]), "+d"(c[1]), "+d"(c[2]), "+d"(c[3])
+      : "d"(a[0]), "d"(a[1]), "d"(a[2]), "d"(a[3]), "d"(a[4]), "d"(a[5]), "d"(a[6]), "d"(a[7]), "d"(b[0]), "d"(b[1]),
+        "d"(b[2]), "d"(b[3]));
+}
+
+// 16-byte asynchronous copy global -> shared; bytes beyond `src_bytes` (0 or 16) are filled with zeros.
+__device__ __forceinline__ void cp_async16(double* smem_dst, const double* gsrc, int src_bytes) {
+  const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(gsrc), "r"(src_bytes) : "memory");
+}
+
+// One 128 x 16 slice of A and one 16 x 128 slice of B into a stage of the ring (out-of-range parts become zero).
+__device__ __forceinline__ void load_stage(const ProductParams& p, int row0, int col0, int k0, double* stage) {
+  const int t = threadIdx.x;
+  double* sa = stage;
+  double* sb = stage + BM * PA;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {  // A: 128 rows x 8 pairs per row
+    const int v = t + i * THREADS;
+    const int r = v >> 3, c = (v & 7) * 2;
+    const int gr = row0 + r, gc = k0 + c;
+    const bool ok = gr < p.m && gc < p.k;
+    cp_async16(sa + r * PA + c, ok ? p.a + static_cast<long long>(gr) * p.lda + gc : p.a, ok ? 16 : 0);
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {  // B: 16 rows x 64 pairs per row
+    const int v = t + i * THREADS;
+    const int r = v >> 6, c = (v & 63) * 2;
+    const int gr = k0 + r, gc = col0 + c;
+    const bool ok = gr < p.k && gc < p.n;
+    cp_async16(sb + r * PB + c, ok ? p.b + static_cast<long long>(gr) * p.ldb + gc : p.b, ok ? 16 : 0);
+  }
+}
+
+__global__ void __launch_bounds__(THREADS, 1) dmma_product_kernel(const __grid_constant__ ProductParams p) {
+  extern __shared__ __align__(16) double smem_f64[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int wm = (warp >> 1) * 32, wn = (warp & 1) * 64;
+  const int row0 = blockIdx.y * BM, col0 = blockIdx.x * BN;
+  double acc[2][8][4];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[i][j][e] = 0.0;
+
+  const int nk = (p.k + BK - 1) / BK;
+  // prologue: STAGES - 1 slices in flight (empty groups keep the group count uniform)
+  for (int s = 0; s < STAGES - 1; ++s) {
+    if (s < nk) load_stage(p, row0, col0, s * BK, smem_f64 + s * STAGE_DOUBLES);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
+  for (int kt = 0; kt < nk; ++kt) {
+    asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2) : "memory");  // slice kt has landed
+    __syncthreads();  // ... for every thread, and everyone is done with the stage refilled below
+    const int nxt = kt + STAGES - 1;
+    if (nxt < nk) load_stage(p, row0, col0, nxt * BK, smem_f64 + (nxt % STAGES) * STAGE_DOUBLES);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    const double* a_s = smem_f64 + (kt % STAGES) * STAGE_DOUBLES;
+    const double* b_s = a_s + BM * PA;
+    double af[2][8];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int e = 0; e < 8; ++e)
+        af[i][e] = a_s[(wm + i * 16 + (lane >> 2) + 8 * (e & 1)) * PA + (lane & 3) + 4 * (e >> 1)];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      double bf[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) bf[e] = b_s[((lane & 3) + 4 * e) * PB + wn + j * 8 + (lane >> 2)];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) dmma(acc[i][j], af[i], bf);
+    }
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+
+  // postsum epilogue: +-P into every block this product belongs to
+  for (int d = 0; d < p.ndst; ++d) {
+    double* out = p.dst[d].ptr;
+    const double sign = p.dst[d].sign;
+    const bool accumulate = p.dst[d].accumulate != 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {  // i = 16-row block * 2 + upper / lower 8 rows
+      const int r = row0 + wm + (i >> 1) * 16 + (i & 1) * 8 + (lane >> 2);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int c = col0 + wn + j * 8 + (lane & 3) * 2;
+        if (r < p.m && c < p.n) {
+          double2* q = reinterpret_cast<double2*>(out + static_cast<long long>(r) * p.ldd + c);
+          double2 v = make_double2(sign * acc[i >> 1][j][(i & 1) * 2], sign * acc[i >> 1][j][(i & 1) * 2 + 1]);
+          if (accumulate) {
+            const double2 old = *q;
+            v.x += old.x;
+            v.y += old.y;
+          }
+          *q = v;
+        }
+      }
+    }
+  }
+}
+
+// Standalone presum kernel (the reference's KernelPresumGlobalCompute): the four combinations of one operand's
+// quadrants.  side 0: S1 = X2 + X3, S2 = S1 - X0, A02 = X0 - X2, A1S2 = X1 - S2;  side 1: B10 = X1 - X0,
+// B31 = X3 - X1, S3 = B31 + X0, S3B2 = S3 - X2.
+__global__ void presum_kernel(const double* x0, const double* x1, const double* x2, const double* x3, long long ld,
+                              double* out, int rows, int cols, int side) {
+  const long long q = static_cast<long long>(rows) * cols;
+  const long long total = q / 2;
+  for (long long v = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; v < total;
+       v += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int r = static_cast<int>((v * 2) / cols), c = static_cast<int>((v * 2) % cols);
+    const long long in = static_cast<long long>(r) * ld + c;
+    const double2 a0 = *reinterpret_cast<const double2*>(x0 + in), a1 = *reinterpret_cast<const double2*>(x1 + in);
+    const double2 a2 = *reinterpret_cast<const double2*>(x2 + in), a3 = *reinterpret_cast<const double2*>(x3 + in);
+    double2 o[4];
+    if (side == 0) {
+      o[0] = make_double2(a2.x + a3.x, a2.y + a3.y);
+      o[1] = make_double2(o[0].x - a0.x, o[0].y - a0.y);
+      o[2] = make_double2(a0.x - a2.x, a0.y - a2.y);
+      o[3] = make_double2(a1.x - o[1].x, a1.y - o[1].y);
+    } else {
+      o[0] = make_double2(a1.x - a0.x, a1.y - a0.y);
+      o[1] = make_double2(a3.x - a1.x, a3.y - a1.y);
+      o[2] = make_double2(o[1].x + a0.x, o[1].y + a0.y);
+      o[3] = make_double2(o[2].x - a2.x, o[2].y - a2.y);
+    }
+    const long long off = static_cast<long long>(r) * cols + c;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) *reinterpret_cast<double2*>(out + i * q + off) = o[i];
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ host side
+namespace {
+
+// One product of the scheme (src/algos/strassen_winograd_level1.py:16-42 in the reference project): operand codes
+// (0..3 = raw quadrant, 4..7 = presum S1,S2,A02,A1S2 / B10,B31,S3,S3B2) and the output quadrants it enters with signs.
+struct QTerm { int q; int coef; };
+struct Scheme {
+  int a, b;
+  int ndst; QTerm dst[4];
+};
+const Scheme kScheme[7] = {
+    {0, 0, 4, {{0, 1}, {1, 1}, {2, 1}, {3, 1}}},  // M0 = A0 B0      -> C0, C1, C2, C3
+    {1, 2, 1, {{0, 1}}},                          // M1 = A1 B2      -> C0
+    {5, 6, 3, {{1, 1}, {2, 1}, {3, 1}}},          // M2 = S2 S3      -> C1, C2, C3
+    {6, 5, 2, {{2, 1}, {3, 1}}},                  // M3 = A02 B31    -> C2, C3
+    {4, 4, 2, {{1, 1}, {3, 1}}},                  // M4 = S1 B10     -> C1, C3
+    {7, 3, 1, {{1, 1}}},                          // M5 = A1S2 B3    -> C1
+    {3, 7, 1, {{2, -1}}},                         // M6 = A3 S3B2    -> C2 (subtracted)
+};
+
+struct Mat {
+  const double* ptr;
+  long long ld;
+};
+struct OutBlock {
+  double* ptr;
+  double sign;
+};
+
+constexpr int kSmemBytes = STAGES * STAGE_DOUBLES * static_cast<int>(sizeof(double));
+
+int launch_product(const ProductParams& p, cudaStream_t stream) {
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(dmma_product_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr_done = true;
+  }
+  dim3 grid((p.n + BN - 1) / BN, (p.m + BM - 1) / BM, 1);
+  dmma_product_kernel<<<grid, THREADS, kSmemBytes, stream>>>(p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// The eight presums of (A, B) with quadrant extents (m, k), (k, n) into pa[4][m][k], pb[4][k][n].
+int launch_presums(const Mat& A, const Mat& B, int m, int n, int k, double* pa, double* pb, cudaStream_t stream) {
+  const double* aq[4];
+  const double* bq[4];
+  for (int q = 0; q < 4; ++q) {
+    aq[q] = A.ptr + (q >> 1) * static_cast<long long>(m) * A.ld + (q & 1) * k;
+    bq[q] = B.ptr + (q >> 1) * static_cast<long long>(k) * B.ld + (q & 1) * n;
+  }
+  presum_kernel<<<1184, 256, 0, stream>>>(aq[0], aq[1], aq[2], aq[3], A.ld, pa, m, k, 0);
+  presum_kernel<<<1184, 256, 0, stream>>>(bq[0], bq[1], bq[2], bq[3], B.ld, pb, k, n, 1);
+  return static_cast<int>(cudaGetLastError());
+}
+
+Mat operand(const Mat& X, int rows, int cols, const double* presums, int code) {
+  if (code < 4) return Mat{X.ptr + (code >> 1) * static_cast<long long>(rows) * X.ld + (code & 1) * cols, X.ld};
+  return Mat{presums + static_cast<size_t>(code - 4) * rows * cols, cols};
+}
+
+// One level-1 step over (A, B) of extent (2m x 2k), (2k x 2n): presums, then seven products of extent (m, n, k).
+// Every product goes to the blocks `outs[q]` lists for its output quadrants; `written` remembers which output blocks
+// already hold a value (the first writer stores, later ones accumulate).
+int level1(const Mat& A, const Mat& B, int m, int n, int k, double* pa, double* pb,
+           const std::vector<OutBlock> (&outs)[4], long long ldd, std::vector<const double*>& written,
+           cudaStream_t stream) {
+  int rc = launch_presums(A, B, m, n, k, pa, pb, stream);
+  if (rc) return rc;
+  for (int i = 0; i < 7; ++i) {
+    const Scheme& s = kScheme[i];
+    ProductParams p;
+    memset(&p, 0, sizeof(p));
+    const Mat a = operand(A, m, k, pa, s.a), b = operand(B, k, n, pb, s.b);
+    p.a = a.ptr; p.lda = a.ld;
+    p.b = b.ptr; p.ldb = b.ld;
+    p.ldd = ldd;
+    p.m = m; p.n = n; p.k = k;
+    for (int d = 0; d < s.ndst; ++d)
+      for (const OutBlock& ob : outs[s.dst[d].q]) {
+        if (p.ndst == MAX_DST) return kErrInternal;
+        Dst& dst = p.dst[p.ndst++];
+        dst.ptr = ob.ptr;
+        dst.sign = ob.sign * s.dst[d].coef;
+        dst.accumulate = 0;
+        for (const double* w : written)
+          if (w == ob.ptr) dst.accumulate = 1;
+        if (!dst.accumulate) written.push_back(ob.ptr);
+      }
+    if ((rc = launch_product(p, stream))) return rc;
+  }
+  return kOk;
+}
+
+int level_of(const GemmArgs& a) { return a.variant == kCubic ? 0 : (a.variant == kInterleavedLevel2 ? 2 : 1); }
+
+}  // namespace
+
+int can_implement(const GemmArgs& a) {
+  if (a.m <= 0 || a.n <= 0 || a.k <= 0 || !a.a || !a.b || !a.d) return kErrInvalidProblem;
+  const int div = 1 << level_of(a);
+  if ((a.m % div) || (a.n % div) || (a.k % div)) return kErrInvalidProblem;
+  // every block row starts on a 16-byte boundary (16-byte copies, double2 stores)
+  if ((a.k / div) % 2 || (a.n / div) % 2) return kErrMisalignedOperand;
+  if ((reinterpret_cast<uintptr_t>(a.a) | reinterpret_cast<uintptr_t>(a.b) | reinterpret_cast<uintptr_t>(a.d)) & 15)
+    return kErrMisalignedOperand;
+  return kOk;
+}
+
+size_t workspace_bytes(const GemmArgs& a) {
+  size_t doubles = 0;
+  for (int l = 1, d = 2; l <= level_of(a); ++l, d *= 2)  // presums of every recursion step
+    doubles += 4 * (size_t(a.m / d) * (a.k / d) + size_t(a.k / d) * (a.n / d));
+  return 256 + sizeof(double) * doubles;  // 256: status word (kept zero: this path has no device-side waits)
+}
+
+int launches_per_run(const GemmArgs& a) {
+  const int level = level_of(a);
+  return level == 0 ? 1 : (level == 1 ? 9 : 2 + 7 * 9);
+}
+
+int run(const GemmArgs& a, void* workspace, size_t workspace_size, cudaStream_t stream) {
+  int rc = f64::can_implement(a);
+  if (rc) return rc;
+  if (!workspace || workspace_size < f64::workspace_bytes(a) || (reinterpret_cast<uintptr_t>(workspace) & 255))
+    return kErrWorkspaceNull;
+  cudaError_t ce = cudaMemsetAsync(workspace, 0, 256, stream);
+  if (ce != cudaSuccess) return static_cast<int>(ce);
+  if (a.events && (rc = static_cast<int>(cudaEventRecord(a.events[0], stream)))) return rc;
+  const double* A = static_cast<const double*>(a.a);
+  const double* B = static_cast<const double*>(a.b);
+  double* D = static_cast<double*>(a.d);
+  double* wsd = reinterpret_cast<double*>(static_cast<char*>(workspace) + 256);
+  const int level = level_of(a);
+  if (level == 0) {
+    ProductParams p;
+    memset(&p, 0, sizeof(p));
+    p.a = A; p.lda = a.k;
+    p.b = B; p.ldb = a.n;
+    p.ldd = a.n;
+    p.ndst = 1;
+    p.dst[0].ptr = D; p.dst[0].sign = 1.0;
+    p.m = a.m; p.n = a.n; p.k = a.k;
+    rc = launch_product(p, stream);
+  } else if (level == 1) {
+    const int m = a.m / 2, n = a.n / 2, k = a.k / 2;
+    std::vector<OutBlock> outs[4];
+    for (int q = 0; q < 4; ++q) outs[q].push_back({D + (q >> 1) * static_cast<long long>(m) * a.n + (q & 1) * n, 1.0});
+    std::vector<const double*> written;
+    rc = level1(Mat{A, a.k}, Mat{B, a.n}, m, n, k, wsd, wsd + 4 * size_t(m) * k, outs, a.n, written, stream);
+  } else {
+    // level 2: the outer step's products are level-1 steps over quarter-size blocks that add into the quarter blocks
+    // of the outer outputs (the reference wires seven child operators, strassen_gemm.h:1300-2008)
+    const int mh = a.m / 2, nh = a.n / 2, kh = a.k / 2;
+    const int m = mh / 2, n = nh / 2, k = kh / 2;
+    double* opa = wsd;
+    double* opb = opa + 4 * size_t(mh) * kh;
+    double* ipa = opb + 4 * size_t(kh) * nh;
+    double* ipb = ipa + 4 * size_t(m) * k;
+    const Mat Aw{A, a.k}, Bw{B, a.n};
+    rc = launch_presums(Aw, Bw, mh, nh, kh, opa, opb, stream);
+    std::vector<const double*> written;
+    for (int i = 0; i < 7 && !rc; ++i) {
+      const Mat Ao = operand(Aw, mh, kh, opa, kScheme[i].a), Bo = operand(Bw, kh, nh, opb, kScheme[i].b);
+      std::vector<OutBlock> outs[4];
+      for (int d = 0; d < kScheme[i].ndst; ++d) {
+        const int oq = kScheme[i].dst[d].q;
+        double* base = D + (oq >> 1) * static_cast<long long>(mh) * a.n + (oq & 1) * nh;
+        for (int q = 0; q < 4; ++q)
+          outs[q].push_back({base + (q >> 1) * static_cast<long long>(m) * a.n + (q & 1) * n,
+                             static_cast<double>(kScheme[i].dst[d].coef)});
+      }
+      rc = level1(Ao, Bo, m, n, k, ipa, ipb, outs, a.n, written, stream);
+    }
+  }
+  if (rc) return rc;
+  if (a.events) {
+    // one pair of events around the whole run: the launches of this path are not timed one by one
+    for (int i = 1; i <= f64::launches_per_run(a); ++i)
+      if ((rc = static_cast<int>(cudaEventRecord(a.events[i], stream)))) return rc;
+  }
+  return kOk;
+}
+
+}  // namespace f64
+}  // namespace sb200

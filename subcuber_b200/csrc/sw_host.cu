@@ -243,6 +243,7 @@ int launch_any_pair(int esize, int mode, const KernelParams& p, int pairs, cudaS
 }  // namespace
 
 int can_implement(const GemmArgs& a) {
+  if (a.dtype == kF64) return f64::can_implement(a);
   if (a.m <= 0 || a.n <= 0 || a.k <= 0 || !a.a || !a.b || !a.d) return kErrInvalidProblem;
   if (a.dtype != kF16 && a.dtype != kF32) return kErrNotSupported;
   if (a.bn != 0 && a.bn != 128 && a.bn != 256) return kErrNotSupported;
@@ -258,12 +259,18 @@ int can_implement(const GemmArgs& a) {
   return kOk;
 }
 
-size_t workspace_bytes(const GemmArgs& a) { return make_layout(a).total; }
+size_t workspace_bytes(const GemmArgs& a) {
+  return a.dtype == kF64 ? f64::workspace_bytes(a) : make_layout(a).total;
+}
 
 WorkspaceLayout workspace_layout(const GemmArgs& a) {
-  const Layout L = make_layout(a);
   WorkspaceLayout w;
   memset(&w, 0, sizeof(w));
+  if (a.dtype == kF64) {
+    w.total = f64::workspace_bytes(a);
+    return w;
+  }
+  const Layout L = make_layout(a);
   w.status = L.off_status;
   w.presum_a = L.off_pa;
   w.presum_b = L.off_pb;
@@ -275,6 +282,7 @@ WorkspaceLayout workspace_layout(const GemmArgs& a) {
 }
 
 int launches_per_run(const GemmArgs& a) {
+  if (a.dtype == kF64) return f64::launches_per_run(a);
   return a.variant == kInterleavedLevel2 ? 14 : (a.variant == kInterleavedPresum ? 2 : 1);
 }
 
@@ -458,6 +466,7 @@ int launch_group(const LaunchSpec& s, cudaStream_t stream, MarkFn mark) {
 }  // namespace
 
 int run(const GemmArgs& a, void* workspace, size_t workspace_size, cudaStream_t stream) {
+  if (a.dtype == kF64) return f64::run(a, workspace, workspace_size, stream);
   int rc = can_implement(a);
   if (rc) return rc;
   const Layout L = make_layout(a);

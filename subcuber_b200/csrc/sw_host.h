@@ -61,4 +61,14 @@ int read_status(void* workspace, cudaStream_t stream);
 // Launches of this library's kernels made by the last `run` with these args (for launch accounting).
 int launches_per_run(const GemmArgs& args);
 
+// fp64 path (dgemm_sw.cu): DMMA kernels, same four calls; `run` and friends above dispatch here for kF64.
+//   kCubic = one launch, kFusedPresum = level 1 (2 presum + 7 product launches),
+//   kInterleavedLevel2 = level 2 (2 outer presum launches + 7 x (2 + 7))
+namespace f64 {
+int can_implement(const GemmArgs& args);
+size_t workspace_bytes(const GemmArgs& args);
+int run(const GemmArgs& args, void* workspace, size_t workspace_size, cudaStream_t stream);
+int launches_per_run(const GemmArgs& args);
+}  // namespace f64
+
 }  // namespace sb200

@@ -25,7 +25,7 @@ L0_F32 = ["blackwell_f32_cubic_128x256", "blackwell_f32_cubic_128x128", "blackwe
 
 
 def _dt(kernel):
-    return "f16" if "_f16_" in kernel else "f32"
+    return "f16" if "_f16_" in kernel else ("f64" if "_f64_" in kernel else "f32")
 
 
 def _level(kernel):
@@ -88,6 +88,56 @@ def test_level2_bit_exact_on_harness_values(kernel, shape, oracle, cuda_device):
     assert np.array_equal(got, want), f"{np.count_nonzero(got != want)} elements differ from the oracle"
     if dt == "f32":
         assert np.array_equal(got.astype(np.float64), a.astype(np.float64) @ b.astype(np.float64))
+
+
+# ------------------------------------------------------------------------------------------ fp64 (DMMA)
+F64 = ["blackwell_f64_cubic_dmma", "blackwell_f64_sw_level1", "blackwell_f64_sw_level2"]
+
+
+@pytest.mark.parametrize("kernel", F64)
+@pytest.mark.parametrize("shape", [(256, 512, 128), (384, 768, 320), (264, 520, 136), (4, 16, 16), (132, 48, 80),
+                                   (1024, 1024, 512)])
+def test_f64_bit_exact_on_harness_values(kernel, shape, oracle, cuda_device):
+    from subcuber_b200 import inputs
+
+    m, n, k = shape
+    level = {"cubic": 0, "level1": 1, "level2": 2}[kernel.rsplit("_", 1)[-1].replace("dmma", "cubic")]
+    a, b = inputs.operands("f64", "harness", m, n, k, seed=m + n + k)
+    got = _run(kernel, a, b, cuda_device)
+    assert not np.isnan(got).any()
+    assert np.array_equal(got, a @ b)                      # every sum is exact on this value set
+    assert np.array_equal(got, oracle.sw_gemm("f64", level, a, b))
+
+
+@pytest.mark.parametrize("kernel", F64)
+@pytest.mark.parametrize("dist", ["uniform1", "normal"])
+def test_f64_uniform_inputs(kernel, dist, oracle, cuda_device):
+    """fp64 throughout: the result differs from the reference routine only by the order of fp64 additions, and its
+    error against a higher-precision product stays within 1.5x the routine's."""
+    from subcuber_b200 import inputs
+
+    m, n, k = 768, 1280, 1024
+    level = {"cubic": 0, "level1": 1, "level2": 2}[kernel.rsplit("_", 1)[-1].replace("dmma", "cubic")]
+    a, b = inputs.operands("f64", dist, m, n, k, seed=12)
+    got = _run(kernel, a, b, cuda_device)
+    truth = (a.astype(np.longdouble) @ b.astype(np.longdouble)).astype(np.float64)
+    ref = oracle.sw_gemm("f64", level, a, b)
+    err, ref_err = _rel_fro(got, truth), _rel_fro(ref, truth)
+    assert err <= 1.5 * ref_err + 1e-17, f"{err:.3e} vs reference routine {ref_err:.3e}"
+    assert np.allclose(got, ref, rtol=1e-11, atol=1e-11)
+
+
+def test_f64_agrees_with_cublas(cuda_device):
+    import torch
+
+    from subcuber_b200 import inputs, runner
+
+    a = inputs.fill_device("f64", "uniform1", (1024, 768), 3, 0, cuda_device)
+    b = inputs.fill_device("f64", "uniform1", (768, 1536), 3, 1, cuda_device)
+    d = runner.gemm("blackwell_f64_sw_level2", a, b)
+    ref, _ = runner.run_kernel("cublas_f64", a, b, warmup=0, iterations=1)
+    torch.cuda.synchronize()
+    assert torch.allclose(d, ref, rtol=1e-11, atol=1e-11)
 
 
 # ------------------------------------------------------------------------------- K-split of the last wave
