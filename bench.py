@@ -205,8 +205,15 @@ def main():
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     if world > 1:
+        from subcuber_b200 import multi_gpu
+
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        # the all-gather of B overlaps the GEMM of the step before: NCCL runs on a bounded number of SMs that the GEMM
+        # grid leaves free (the persistent GEMM kernels would otherwise hold every SM until they end)
+        os.environ.setdefault("NCCL_MAX_CTAS", str(multi_gpu.PipelinedGather.NCCL_CTAS))
         dist.init_process_group("nccl", device_id=device)
+        sms = torch.cuda.get_device_properties(device).multi_processor_count
+        os.environ["SB200_SM_LIMIT"] = str(sms - multi_gpu.PipelinedGather.reserved_sms())
 
     lib = _lib.load()
     kernel = args.kernel
@@ -216,14 +223,14 @@ def main():
     m = n = k = args.size
     # operands: this rank's A slab (subsequence 2*rank so slabs differ) and its row shard of B
     a = inputs.fill_device(dtn, "uniform1", (m, k), seed=1, subsequence=2 * rank, device=device)
+    gather = None
     if world > 1:
-        from subcuber_b200 import multi_gpu
-
         b_full_ref = inputs.fill_device(dtn, "uniform1", (k, n), seed=1, subsequence=1, device=device)
         shard = multi_gpu.row_shard(k, world, rank)
         b_shard = b_full_ref[shard[0]:shard[1]].contiguous()
-        b = torch.empty((k, n), dtype=tdt, device=device)
         del b_full_ref
+        gather = multi_gpu.PipelinedGather(b_shard, k, world)
+        b = gather.bufs[0]
     else:
         b = inputs.fill_device(dtn, "uniform1", (k, n), seed=1, subsequence=1, device=device)
     d = torch.empty((m, n), dtype=tdt, device=device)
@@ -234,16 +241,17 @@ def main():
     evl = lib.sb200_events_create((launches + 1) * args.steps)
 
     def step(i):
-        if world > 1:
-            multi_gpu.all_gather_rows(b, b_shard, world)
+        bi = gather.next() if gather else b  # replicated B of this step; the next step's all-gather is now in flight
         if i >= args.warmup:
-            rc = lib.sb200_gemm_events(kernel.encode(), a.data_ptr(), b.data_ptr(), d.data_ptr(), m, n, k, ws.ptr,
+            rc = lib.sb200_gemm_events(kernel.encode(), a.data_ptr(), bi.data_ptr(), d.data_ptr(), m, n, k, ws.ptr,
                                        ws.nbytes, stream.cuda_stream, evl, (launches + 1) * (i - args.warmup))
         else:
-            rc = lib.sb200_gemm(kernel.encode(), a.data_ptr(), b.data_ptr(), d.data_ptr(), m, n, k, ws.ptr, ws.nbytes,
+            rc = lib.sb200_gemm(kernel.encode(), a.data_ptr(), bi.data_ptr(), d.data_ptr(), m, n, k, ws.ptr, ws.nbytes,
                                 stream.cuda_stream)
         if rc != 0:
             raise runner.KernelError(kernel, rc)
+        if gather:
+            gather.done(bi)
 
     def barrier():
         if world > 1:
@@ -351,7 +359,7 @@ def main():
                        "seed 1" if level else f"{dtn} GEMM level 0, M=N=K={args.size}",
                        "kernel": kernel, "m": m * world, "n": n, "k": k, "level": level,
                        "l2": f"inputs larger than L2: {(m * k + k * n + m * n) * es / 2**20:.0f} MiB touched per step",
-                       "parallelism": f"row slabs x{world}" + (", B all-gathered per step over NCCL" if world > 1 else "")},
+                       "parallelism": f"row slabs x{world}" + (", B all-gathered every step over NCCL, overlapped with the GEMM of the step before" if world > 1 else "")},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches * args.steps, "roofline": roofline,
             "cpu_baseline": cpu_baseline,
         }

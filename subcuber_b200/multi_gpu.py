@@ -92,6 +92,63 @@ def all_gather_rows(full: torch.Tensor, shard: torch.Tensor, world: int, group=N
             p.copy_(buf[: p.shape[0]])
 
 
+class PipelinedGather:
+    """Double-buffered replication of B that overlaps the exchange with compute.
+
+    Step i multiplies with buffer i % 2 while the all-gather that fills buffer (i + 1) % 2 runs on its own stream;
+    events order the two streams (a buffer is refilled only after the GEMM that read it, and read only after its
+    gather).  NCCL's kernels need SMs of their own while the persistent GEMM kernels hold theirs, so the caller
+    leaves `reserved_sms()` SMs out of the GEMM grid.  Without CUDA (gloo tests) the gathers run synchronously.
+    """
+
+    NCCL_CTAS = 8  # upper bound given to NCCL (NCCL_MAX_CTAS) before the process group is created
+
+    def __init__(self, shard: torch.Tensor, rows: int, world: int, group=None):
+        self.shard, self.world, self.group = shard, world, group
+        self.bufs = [torch.empty((rows, shard.shape[1]), dtype=shard.dtype, device=shard.device) for _ in range(2)]
+        self.cuda = shard.is_cuda
+        if self.cuda:
+            self.comm = torch.cuda.Stream(device=shard.device)
+            self.filled = [torch.cuda.Event() for _ in range(2)]
+            self.consumed = [torch.cuda.Event() for _ in range(2)]
+            for ev in self.consumed:
+                ev.record(torch.cuda.current_stream(shard.device))
+        self.issued = 0  # gathers started so far
+        self.taken = 0   # buffers handed to compute so far
+
+    @classmethod
+    def reserved_sms(cls) -> int:
+        """SMs to keep out of the GEMM grid: one TPC (two SMs) per NCCL CTA, since a CTA pair needs a whole TPC."""
+        return 2 * cls.NCCL_CTAS
+
+    def _start(self) -> None:
+        i = self.issued % 2
+        if self.cuda:
+            self.comm.wait_event(self.consumed[i])
+            with torch.cuda.stream(self.comm):
+                all_gather_rows(self.bufs[i], self.shard, self.world, self.group)
+                self.filled[i].record(self.comm)
+        else:
+            all_gather_rows(self.bufs[i], self.shard, self.world, self.group)
+        self.issued += 1
+
+    def next(self) -> torch.Tensor:
+        """The replicated B for this step (valid on the current stream); the gather for the next step is started."""
+        while self.issued < self.taken + 2:
+            self._start()
+        i = self.taken % 2
+        if self.cuda:
+            torch.cuda.current_stream(self.shard.device).wait_event(self.filled[i])
+        self.taken += 1
+        return self.bufs[i]
+
+    def done(self, buf: torch.Tensor) -> None:
+        """Call after the GEMM that reads `buf` has been enqueued: its buffer may be refilled once that GEMM is over."""
+        if self.cuda:
+            i = 0 if buf is self.bufs[0] else 1
+            self.consumed[i].record(torch.cuda.current_stream(self.shard.device))
+
+
 def slab_gemm(a_slab: torch.Tensor, b_shard: torch.Tensor, k: int, world: int, rank: int,
               local_gemm: Callable[[torch.Tensor, torch.Tensor], torch.Tensor],
               b_full: Optional[torch.Tensor] = None, group=None) -> torch.Tensor:

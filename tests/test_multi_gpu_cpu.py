@@ -86,3 +86,45 @@ def test_slab_gemm_two_gloo_ranks(k, ragged):
         assert p.exitcode == 0
     results = dict(out.get(timeout=10) for _ in range(world))
     assert results == {0: True, 1: True}
+
+
+def _pipeline_worker(rank, world, port, out):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        k, n = 8, 6
+        g = torch.Generator().manual_seed(3)
+        b_all = torch.randint(-3, 4, (k, n), generator=g).float()
+        b0, b1 = multi_gpu.row_shard(k, world, rank)
+        shard = b_all[b0:b1].contiguous()
+        pipe = multi_gpu.PipelinedGather(shard, k, world)
+        seen = []
+        for step in range(5):
+            buf = pipe.next()
+            seen.append((buf.data_ptr(), bool(torch.equal(buf, b_all))))
+            shard += 1          # the next gathers must pick up the new values ...
+            b_all = b_all + 1   # ... which every rank changes the same way
+            pipe.done(buf)
+        out.put((rank, seen))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_pipelined_gather_alternates_buffers_on_two_ranks():
+    """Two gloo ranks: every step sees a fully replicated B, in alternating buffers.  (On CPU the gathers run
+    synchronously, two steps ahead, so a step sees the shard values of two steps earlier.)"""
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_pipeline_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = dict(out.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank in (0, 1):
+        ptrs = [ptr for ptr, _ in results[rank]]
+        assert ptrs[0] != ptrs[1] and ptrs[0::2] == [ptrs[0]] * 3 and ptrs[1::2] == [ptrs[1]] * 2
+    assert multi_gpu.PipelinedGather.reserved_sms() == 2 * multi_gpu.PipelinedGather.NCCL_CTAS
