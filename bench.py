@@ -167,8 +167,10 @@ def reference_arm(args):
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": 1e3 * tot_t / max(1, len(times)), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-        "config": {"workload": f"f16 Strassen-Winograd level 1 M=N=K={size} (CPU row sample)", "m": size, "n": size,
-                   "k": size, "level": 1},
+        # the same workload as the CUDA arm; every step covers a bounded sample of its rows (see cpu_baseline.sample)
+        "config": {"workload": f"f16 Strassen-Winograd level 1, M=N=K={size} per GPU, uniform[-1,1) from seed 1",
+                   "kernel": "reference oracle kernels compiled for the host", "m": size, "n": size, "k": size,
+                   "level": 1},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
