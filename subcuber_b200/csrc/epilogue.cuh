@@ -81,8 +81,11 @@ __device__ __forceinline__ bool wait_flag(const int* flag, int epoch, volatile i
 
 // `wait_slots()` blocks until the slots in ep.wait_full_mask are ready (and, for the second half of a split tile,
 // until the first half's partial sum is published) and returns false when the wait was given up.
-//   tile_off / outer_off: float offsets of this unit's tile in the level-1 hand-off buffers (ws index < 4) and in the
-//                         buffers of the level above (index >= 4)
+//   tile_off / cta_off / outer_off: float offsets into the hand-off buffers.  Buffer 0 (M0) crosses from launch 1 to
+//                         launch 2 and is indexed by the unit's tile slot; buffers 1..3 live only within one tile
+//                         program, so they are indexed by the CTA: the same 128 x BN tile is rewritten for every
+//                         tile the CTA computes and stays in L2 instead of streaming through HBM; buffers of the
+//                         level above (index >= 4) are indexed by the tile
 //   NSRC_MAX / NSLOT_MAX: most fp32 sources / TMEM slots a step of the programs this kernel runs can list
 //   redirect: non-null = first half of a split tile: write the fp32 partial sum there, skip the outer sources
 //   late_src: non-null = second half: one more fp32 source, readable only after wait_slots()
@@ -90,7 +93,7 @@ template <int ESIZE, int BN, int NSRC_MAX, int NSLOT_MAX, typename WaitFn>
 __device__ __forceinline__ bool epilogue_body(void* const* out, long long ldo, int out_rows, int out_cols,
                                               float* const* ws, const sb200_epilogue_t& ep, uint32_t sx,
                                               uint32_t tmem_base, int quarter, int lane, long long tile_off,
-                                              long long outer_off, int grow_tile, int gcol_tile, uint32_t staging_warp,
+                                              long long cta_off, long long outer_off, int grow_tile, int gcol_tile, uint32_t staging_warp,
                                               float* redirect, const float* late_src, bool skip_body,
                                               WaitFn wait_slots, long long* prof = nullptr) {
   if (skip_body) return wait_slots();  // measurement aid
@@ -109,7 +112,7 @@ __device__ __forceinline__ bool epilogue_body(void* const* out, long long ldo, i
     srcp[t] = nullptr;
     if (t < nearly) {
       const int id = ep.src[t];
-      srcp[t] = reinterpret_cast<const float4*>(ws[id] + (id < SB200_WS_OUTER_DST ? tile_off : outer_off)) + row;
+      srcp[t] = reinterpret_cast<const float4*>(ws[id] + (id == 0 ? tile_off : (id < SB200_WS_OUTER_DST ? cta_off : outer_off))) + row;
     } else if (t == nearly && late_src) {
       srcp[t] = reinterpret_cast<const float4*>(late_src) + row;
     }
@@ -125,7 +128,8 @@ __device__ __forceinline__ bool epilogue_body(void* const* out, long long ldo, i
   float4* dstp = nullptr;
   if (redirect) dstp = reinterpret_cast<float4*>(redirect) + row;
   else if (ep.dst_kind == 1)
-    dstp = reinterpret_cast<float4*>(ws[ep.dst] + (ep.dst < SB200_WS_OUTER_DST ? tile_off : outer_off)) + row;
+    dstp = reinterpret_cast<float4*>(ws[ep.dst] +
+                                     (ep.dst == 0 ? tile_off : (ep.dst < SB200_WS_OUTER_DST ? cta_off : outer_off))) + row;
   char* outp = to_fp32 ? nullptr : static_cast<char*>(out[ep.dst]);
   if (!wait_slots()) return false;
 #pragma unroll
@@ -230,7 +234,7 @@ __device__ __forceinline__ bool epilogue_body(void* const* out, long long ldo, i
           const int grow = grow_tile + quarter * 32 + r_in;
           const uint4 v = ptx::lds_v4(staging_warp + r_in * kStagingRowBytes + (lane & 7) * 16);
           if (grow < out_rows && col < out_cols)
-            *reinterpret_cast<uint4*>(outp + (static_cast<long long>(grow) * ldo + col) * 2) = v;
+            ptx::stg_cs_v4(outp + (static_cast<long long>(grow) * ldo + col) * 2, v);
         }
         __syncwarp();
       }
@@ -254,7 +258,7 @@ __device__ __forceinline__ bool epilogue_body(void* const* out, long long ldo, i
         const int grow = grow_tile + quarter * 32 + r_in;
         const uint4 v = ptx::lds_v4(staging_warp + r_in * kStagingRowBytes + (lane & 7) * 16);
         if (grow < out_rows && col < out_cols)
-          *reinterpret_cast<uint4*>(outp + (static_cast<long long>(grow) * ldo + col) * 4) = v;
+          ptx::stg_cs_v4(outp + (static_cast<long long>(grow) * ldo + col) * 4, v);
       }
       __syncwarp();
     }

@@ -224,6 +224,11 @@ __device__ __forceinline__ uint4 ldg_nc_v4(const void* p) {
                : "l"(p));
   return v;
 }
+// Streaming 16-byte global store (evict-first): for output tiles, which nothing in the same GEMM reads again, so that
+// they do not push operand and hand-off tiles out of L2.
+__device__ __forceinline__ void stg_cs_v4(void* p, uint4 v) {
+  asm volatile("st.global.cs.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
 __device__ __forceinline__ void sts_v4(uint32_t smem_addr, uint4 v) {
   asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(smem_addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
                : "memory");

@@ -565,7 +565,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_kernel(const 
         const long long tile_off = static_cast<long long>(wu.ws_slot) * (128 * BN);
         const long long outer_off = static_cast<long long>(wu.tile) * (128 * BN);
         ok = epilogue_body<ESIZE, BN, Cfg::NSRC_MAX, Cfg::NSLOT_MAX>(p.out, p.ldo, p.out_rows, p.out_cols, p.ws, ep, sx, tmem_base, quarter,
-                                                     lane, tile_off, outer_off, tile.i * 128, tile.j * BN,
+                                                     lane, tile_off, static_cast<long long>(blockIdx.x) * (128 * BN), outer_off,
+                                                     tile.i * 128, tile.j * BN,
                                                      staging + (warp - 2) * kStagingWarpBytes,
                                                      sp.redirect ? split_tile_buf : nullptr,
                                                      sp.add_partial ? split_tile_buf : nullptr,

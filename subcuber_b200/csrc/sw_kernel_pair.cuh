@@ -370,7 +370,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
         const long long ew0 = ew_full;
 #endif
         ok = epilogue_body<ESIZE, BN, Cfg::NSRC_MAX, Cfg::NSLOT_MAX>(p.out, p.ldo, p.out_rows, p.out_cols, p.ws, ep, sx, tmem_base, quarter,
-                                                     lane, tile_off, outer_off,
+                                                     lane, tile_off, static_cast<long long>(blockIdx.x) * (128 * BN), outer_off,
                                                      tile.i * Cfg::PAIR_M + static_cast<int>(rank) * Cfg::BM, tile.j * BN,
                                                      staging + (warp - 2) * kStagingWarpBytes,
                                                      sp.redirect ? split_tile_buf : nullptr,
@@ -434,7 +434,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
           }
         }
       }
-    } else if (Cfg::MODE == kPresumJob) {
+    } else if (Cfg::MODE == kPresumJob && !(p.debug_flags & 16)) {  // bit 4: measurement aid, skip the presum job
       const int ptid = threadIdx.x - Cfg::FIRST_PRESUM_WARP * 32;
       constexpr int PT = Cfg::PRESUM_WARPS * 32;
       presum_job<ESIZE>(p, blockIdx.x * PT + ptid, gridDim.x * PT);

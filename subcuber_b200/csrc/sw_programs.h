@@ -80,7 +80,8 @@ inline void add_epilogue(sb200_program_t& pg, int nslots, const int* slots, cons
 }
 
 enum { P = 0, Q = 1, mP = 1, mQ = 2 };
-enum { WS_M0 = 0, WS_M4 = 1, WS_U = 2, WS_V = 3 };
+// U is dead once C1 is formed, before V is written: they share a buffer (a smaller L2-resident hand-off set)
+enum { WS_M0 = 0, WS_M4 = 1, WS_U = 2, WS_V = 2 };
 
 // Level 0: one product per tile, the two (or four) slots used alternately so that the epilogue of tile t
 // overlaps the mainloop of tile t+1.

@@ -22,7 +22,7 @@ from .dsl import BinOp, Matrix, expand_terms
 QUADRANT_VIEW = {"a0": 0, "a1": 1, "a2": 2, "a3": 3, "b0": 8, "b1": 9, "b2": 10, "b3": 11}
 PRESUM_VIEW = {"s1": 4, "s2": 5, "a02": 6, "a1s2": 7, "b10": 12, "b31": 13, "s3": 14, "s3b2": 15}
 P, Q = 0, 1
-WS_M0, WS_M4, WS_U, WS_V = 0, 1, 2, 3
+WS_M0, WS_M4, WS_U, WS_V = 0, 1, 2, 2  # u is dead once c1 is formed, before v is written: one buffer
 
 
 # ------------------------------------------------------------------------------------------- algebra from the DSL
