@@ -127,6 +127,16 @@ size_t sb200_gemm_workspace_bytes(const char* kernel, int m, int n, int k);
  * 256-byte aligned device memory of at least sb200_gemm_workspace_bytes().  Allocates nothing. */
 int sb200_gemm(const char* kernel, const void* a, const void* b, void* d, int m, int n, int k, void* workspace,
                size_t workspace_bytes, sb200_stream_t stream);
+/* General form D = alpha * (A * B) + beta * C (the argument set of the reference's operators,
+ * include/cutlass/gemm/device/strassen_gemm.h:365-451; the reference's runner fixes alpha = 1, beta = 0).  C is m x n
+ * row-major in the output type, may be the same buffer as D, and is read only when beta != 0.  The scaling is applied
+ * in fp32 (fp64 for the f64 kernels) to the finished sum, once, before the rounding to the output type. */
+int sb200_gemm_ex(const char* kernel, double alpha, const void* a, const void* b, double beta, const void* c, void* d,
+                  int m, int n, int k, void* workspace, size_t workspace_bytes, sb200_stream_t stream);
+/* Column-major A (m x k), B (k x n), D (m x n), each packed: runs the row-major kernels on the swapped problem
+ * (the reference's swap trick, strassen_gemm.h:3925-4170).  Workspace size: sb200_gemm_workspace_bytes(kernel, n, m, k). */
+int sb200_gemm_colmajor(const char* kernel, const void* a, const void* b, void* d, int m, int n, int k, void* workspace,
+                        size_t workspace_bytes, sb200_stream_t stream);
 /* Synchronise `stream` and return the device status word of the last sb200_gemm on `workspace`
  * (0 = every bounded wait was satisfied). */
 int sb200_gemm_status(void* workspace, sb200_stream_t stream);

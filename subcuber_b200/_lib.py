@@ -61,6 +61,9 @@ def load(build_if_missing: bool = True) -> C.CDLL:
     lib.sb200_gemm_workspace_bytes.argtypes = [C.c_char_p, C.c_int, C.c_int, C.c_int]
     lib.sb200_gemm.argtypes = [C.c_char_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p,
                                C.c_size_t, C.c_void_p]
+    lib.sb200_gemm_ex.argtypes = [C.c_char_p, C.c_double, C.c_void_p, C.c_void_p, C.c_double, C.c_void_p, C.c_void_p,
+                                  C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_size_t, C.c_void_p]
+    lib.sb200_gemm_colmajor.argtypes = lib.sb200_gemm.argtypes
     lib.sb200_gemm_status.argtypes = [C.c_void_p, C.c_void_p]
     lib.sb200_gemm_launches.argtypes = [C.c_char_p]
     lib.sb200_gemm_host.argtypes = [C.c_char_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int]

@@ -358,6 +358,30 @@ extern "C" int sb200_gemm(const char* kernel, const void* a, const void* b, void
   return sb200::run(g, workspace, workspace_bytes, reinterpret_cast<cudaStream_t>(stream));
 }
 
+extern "C" int sb200_gemm_ex(const char* kernel, double alpha, const void* a, const void* b, double beta, const void* c,
+                             void* d_out, int m, int n, int k, void* workspace, size_t workspace_bytes,
+                             sb200_stream_t stream) {
+  const KernelDesc* d = find_desc(kernel);
+  if (!d) return SB200_ERR_NO_KERNEL;
+  GemmArgs g = make_args(*d, a, b, d_out, m, n, k);
+  g.scaled = 1;
+  g.alpha = alpha;
+  g.beta = beta;
+  g.c = c;
+  return sb200::run(g, workspace, workspace_bytes, reinterpret_cast<cudaStream_t>(stream));
+}
+
+// Column-major operands: the same memory read row-major holds the transposes, and (A B)^T = B^T A^T, so the
+// row-major kernels run with the operands swapped (the reference's swap trick,
+// include/cutlass/gemm/device/strassen_gemm.h:3925-4170).
+extern "C" int sb200_gemm_colmajor(const char* kernel, const void* a, const void* b, void* d_out, int m, int n, int k,
+                                   void* workspace, size_t workspace_bytes, sb200_stream_t stream) {
+  const KernelDesc* d = find_desc(kernel);
+  if (!d) return SB200_ERR_NO_KERNEL;
+  GemmArgs g = make_args(*d, b, a, d_out, n, m, k);
+  return sb200::run(g, workspace, workspace_bytes, reinterpret_cast<cudaStream_t>(stream));
+}
+
 extern "C" int sb200_gemm_status(void* workspace, sb200_stream_t stream) {
   if (!workspace) return SB200_ERR_WORKSPACE_NULL;
   return sb200::read_status(workspace, reinterpret_cast<cudaStream_t>(stream));

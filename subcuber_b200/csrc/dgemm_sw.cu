@@ -33,8 +33,10 @@ constexpr int MAX_DST = 16;
 
 struct Dst {
   double* ptr;
-  double sign;     // +1 or -1
-  int accumulate;  // 0: store sign * P; 1: add it to what is there
+  double sign;        // +-alpha
+  int accumulate;     // 0: store sign * P (+ beta * C); 1: add sign * P to what is there
+  const double* cin;  // first writer only: block of C to add with `beta`, or null
+  double beta;
 };
 struct ProductParams {
   const double* a;     // m x k, row-major
@@ -149,6 +151,10 @@ __global__ void __launch_bounds__(THREADS, 1) dmma_product_kernel(const __grid_c
             const double2 old = *q;
             v.x += old.x;
             v.y += old.y;
+          } else if (p.dst[d].cin) {
+            const double2 cv = *reinterpret_cast<const double2*>(p.dst[d].cin + static_cast<long long>(r) * p.ldd + c);
+            v.x += p.dst[d].beta * cv.x;
+            v.y += p.dst[d].beta * cv.y;
           }
           *q = v;
         }
@@ -214,7 +220,9 @@ struct Mat {
 };
 struct OutBlock {
   double* ptr;
-  double sign;
+  double sign;        // includes alpha
+  const double* cin;  // matching block of C when beta != 0, else null
+  double beta;
 };
 
 constexpr int kSmemBytes = STAGES * STAGE_DOUBLES * static_cast<int>(sizeof(double));
@@ -275,7 +283,11 @@ int level1(const Mat& A, const Mat& B, int m, int n, int k, double* pa, double* 
         dst.accumulate = 0;
         for (const double* w : written)
           if (w == ob.ptr) dst.accumulate = 1;
-        if (!dst.accumulate) written.push_back(ob.ptr);
+        if (!dst.accumulate) {
+          written.push_back(ob.ptr);
+          dst.cin = ob.cin;
+          dst.beta = ob.beta;
+        }
       }
     if ((rc = launch_product(p, stream))) return rc;
   }
@@ -322,6 +334,9 @@ int run(const GemmArgs& a, void* workspace, size_t workspace_size, cudaStream_t 
   double* D = static_cast<double*>(a.d);
   double* wsd = reinterpret_cast<double*>(static_cast<char*>(workspace) + 256);
   const int level = level_of(a);
+  const double alpha = a.scaled ? a.alpha : 1.0, beta = a.scaled ? a.beta : 0.0;
+  const double* C = (a.scaled && a.beta != 0.0) ? static_cast<const double*>(a.c) : nullptr;
+  if (a.scaled && a.beta != 0.0 && !a.c) return kErrInvalidProblem;
   if (level == 0) {
     ProductParams p;
     memset(&p, 0, sizeof(p));
@@ -329,13 +344,16 @@ int run(const GemmArgs& a, void* workspace, size_t workspace_size, cudaStream_t 
     p.b = B; p.ldb = a.n;
     p.ldd = a.n;
     p.ndst = 1;
-    p.dst[0].ptr = D; p.dst[0].sign = 1.0;
+    p.dst[0].ptr = D; p.dst[0].sign = alpha; p.dst[0].cin = C; p.dst[0].beta = beta;
     p.m = a.m; p.n = a.n; p.k = a.k;
     rc = launch_product(p, stream);
   } else if (level == 1) {
     const int m = a.m / 2, n = a.n / 2, k = a.k / 2;
     std::vector<OutBlock> outs[4];
-    for (int q = 0; q < 4; ++q) outs[q].push_back({D + (q >> 1) * static_cast<long long>(m) * a.n + (q & 1) * n, 1.0});
+    for (int q = 0; q < 4; ++q) {
+      const long long off = (q >> 1) * static_cast<long long>(m) * a.n + (q & 1) * n;
+      outs[q].push_back({D + off, alpha, C ? C + off : nullptr, beta});
+    }
     std::vector<const double*> written;
     rc = level1(Mat{A, a.k}, Mat{B, a.n}, m, n, k, wsd, wsd + 4 * size_t(m) * k, outs, a.n, written, stream);
   } else {
@@ -355,10 +373,11 @@ int run(const GemmArgs& a, void* workspace, size_t workspace_size, cudaStream_t 
       std::vector<OutBlock> outs[4];
       for (int d = 0; d < kScheme[i].ndst; ++d) {
         const int oq = kScheme[i].dst[d].q;
-        double* base = D + (oq >> 1) * static_cast<long long>(mh) * a.n + (oq & 1) * nh;
-        for (int q = 0; q < 4; ++q)
-          outs[q].push_back({base + (q >> 1) * static_cast<long long>(m) * a.n + (q & 1) * n,
-                             static_cast<double>(kScheme[i].dst[d].coef)});
+        const long long base = (oq >> 1) * static_cast<long long>(mh) * a.n + (oq & 1) * nh;
+        for (int q = 0; q < 4; ++q) {
+          const long long off = base + (q >> 1) * static_cast<long long>(m) * a.n + (q & 1) * n;
+          outs[q].push_back({D + off, alpha * kScheme[i].dst[d].coef, C ? C + off : nullptr, beta});
+        }
       }
       rc = level1(Ao, Bo, m, n, k, ipa, ipb, outs, a.n, written, stream);
     }

@@ -87,15 +87,19 @@ __device__ __forceinline__ bool wait_flag(const int* flag, int epoch, volatile i
 //                         tile the CTA computes and stays in L2 instead of streaming through HBM; buffers of the
 //                         level above (index >= 4) are indexed by the tile
 //   NSRC_MAX / NSLOT_MAX: most fp32 sources / TMEM slots a step of the programs this kernel runs can list
+//   SCALED: outputs are alpha * sum + beta * C (separate kernel instantiations, so that the plain D = A * B kernels
+//           do not carry the registers of this path)
 //   redirect: non-null = first half of a split tile: write the fp32 partial sum there, skip the outer sources
 //   late_src: non-null = second half: one more fp32 source, readable only after wait_slots()
-template <int ESIZE, int BN, int NSRC_MAX, int NSLOT_MAX, typename WaitFn>
+template <int ESIZE, int BN, int NSRC_MAX, int NSLOT_MAX, bool SCALED, typename WaitFn>
 __device__ __forceinline__ bool epilogue_body(void* const* out, long long ldo, int out_rows, int out_cols,
                                               float* const* ws, const sb200_epilogue_t& ep, uint32_t sx,
                                               uint32_t tmem_base, int quarter, int lane, long long tile_off,
                                               long long cta_off, long long outer_off, int grow_tile, int gcol_tile, uint32_t staging_warp,
                                               float* redirect, const float* late_src, bool skip_body,
-                                              WaitFn wait_slots, long long* prof = nullptr) {
+                                              WaitFn wait_slots, float alpha = 1.f, float beta = 0.f,
+                                              const void* const* cin = nullptr, long long ldc = 0,
+                                              long long* prof = nullptr) {
   if (skip_body) return wait_slots();  // measurement aid
   constexpr int NCHUNK = BN / 32;
   const int row = quarter * 32 + lane;
@@ -209,6 +213,38 @@ __device__ __forceinline__ bool epilogue_body(void* const* out, long long ldo, i
       }
     }
     SB200_SEG(1)
+    if (SCALED && !to_fp32) {
+      // general form D = alpha * sum + beta * C: this thread's row, 32 columns, read 16 bytes at a time
+      const char* cp = (beta != 0.f && cin) ? static_cast<const char*>(cin[ep.dst]) : nullptr;
+      const int grow = grow_tile + row;
+      const int gcol = gcol_tile + c * 32;
+#pragma unroll
+      for (int v = 0; v < 32 * ESIZE / 16; ++v) {
+        constexpr int EPV = 16 / ESIZE;
+        float cv[EPV];
+#pragma unroll
+        for (int e = 0; e < EPV; ++e) cv[e] = 0.f;
+        if (cp && grow < out_rows && gcol + v * EPV < out_cols) {
+          const uint4 raw = *reinterpret_cast<const uint4*>(cp + (static_cast<long long>(grow) * ldc + gcol + v * EPV) * ESIZE);
+          if (ESIZE == 2) {
+            const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 f = __half22float2(h[e]);
+              cv[(2 * e) % EPV] = f.x;
+              cv[(2 * e + 1) % EPV] = f.y;
+            }
+          } else {
+            cv[0] = __uint_as_float(raw.x);
+            cv[1] = __uint_as_float(raw.y);
+            cv[2 % EPV] = __uint_as_float(raw.z);
+            cv[3 % EPV] = __uint_as_float(raw.w);
+          }
+        }
+#pragma unroll
+        for (int e = 0; e < EPV; ++e) acc[v * EPV + e] = alpha * acc[v * EPV + e] + beta * cv[e];
+      }
+    }
     if (to_fp32) {
 #pragma unroll
       for (int q = 0; q < 8; ++q)

@@ -165,9 +165,20 @@ int launch(const KernelParams& p, int grid, cudaStream_t stream) {
   return static_cast<int>(cudaGetLastError());
 }
 
+// The scaled form (alpha, beta, C) has kernel instantiations of its own, for the modes whose programs write outputs
+// in the plans that support it (not the fused-presum variant).
+inline bool is_scaled(const KernelParams& p) { return p.alpha != 1.f || p.beta != 0.f; }
+
 template <int ESIZE, int BN>
 int launch_mode(int mode, const KernelParams& p, int grid, cudaStream_t stream) {
   constexpr int STAGES = (BN == 256) ? 4 : 6;
+  if (is_scaled(p)) {
+    switch (mode) {
+      case kPresumNone: return launch<KernelConfig<ESIZE, BN, STAGES, kPresumNone, true>>(p, grid, stream);
+      case kPresumJob: return launch<KernelConfig<ESIZE, BN, STAGES, kPresumJob, true>>(p, grid, stream);
+    }
+    return kErrNotSupported;
+  }
   switch (mode) {
     case kPresumNone: return launch<KernelConfig<ESIZE, BN, STAGES, kPresumNone>>(p, grid, stream);
     case kPresumFeed: return launch<KernelConfig<ESIZE, BN, STAGES, kPresumFeed>>(p, grid, stream);
@@ -216,6 +227,13 @@ int launch_pair(const KernelParams& p, int pairs, cudaStream_t stream) {
 template <int ESIZE>
 int launch_pair_mode(int mode, const KernelParams& p, int pairs, cudaStream_t stream) {
   constexpr int STAGES = 6;
+  if (is_scaled(p)) {
+    switch (mode) {
+      case kPresumNone: return launch_pair<PairConfig<ESIZE, STAGES, kPresumNone, true>>(p, pairs, stream);
+      case kPresumJob: return launch_pair<PairConfig<ESIZE, STAGES, kPresumJob, true>>(p, pairs, stream);
+    }
+    return kErrNotSupported;
+  }
   switch (mode) {
     case kPresumNone: return launch_pair<PairConfig<ESIZE, STAGES, kPresumNone>>(p, pairs, stream);
     case kPresumFeed: return launch_pair<PairConfig<ESIZE, STAGES, kPresumFeed>>(p, pairs, stream);
@@ -246,6 +264,7 @@ int can_implement(const GemmArgs& a) {
   if (a.dtype == kF64) return f64::can_implement(a);
   if (a.m <= 0 || a.n <= 0 || a.k <= 0 || !a.a || !a.b || !a.d) return kErrInvalidProblem;
   if (a.dtype != kF16 && a.dtype != kF32) return kErrNotSupported;
+  if (a.scaled && a.beta != 0.0 && (!a.c || (reinterpret_cast<uintptr_t>(a.c) & 15))) return kErrInvalidProblem;
   if (a.bn != 0 && a.bn != 128 && a.bn != 256) return kErrNotSupported;
   if (a.pair && a.bn == 128) return kErrNotSupported;
   const int es = esize_of(a.dtype);
@@ -298,6 +317,8 @@ struct LaunchSpec {
   int tiles_m, tiles_n, num_k;
   char* out;                 // output matrix in the output type (2mq x 2nq, or mq x nq at level 0), or null
   long long ldo;
+  const char* cin;           // C input laid out like `out` (same leading dimension), or null
+  float alpha, beta;
   char* presum_a;            // [4][mq][kq], interleaved only
   char* presum_b;            // [4][kq][nq]
   float* ws_inner[4];
@@ -330,11 +351,13 @@ int launch_group(const LaunchSpec& s, cudaStream_t stream, MarkFn mark) {
     for (int v = 0; v < 8; ++v) p.view[v] = s.a;
     for (int v = 8; v < 16; ++v) p.view[v] = s.b;
     p.out[0] = s.out;
+    p.cin[0] = s.cin;
   } else {
     for (int q = 0; q < 4; ++q) {
       p.view[SB200_VIEW_A0 + q] = View{A + ((q >> 1) * s.mq * s.a.ld + (q & 1) * s.kq) * es, s.a.ld, s.mq, s.kq};
       p.view[SB200_VIEW_B0 + q] = View{B + ((q >> 1) * s.kq * s.b.ld + (q & 1) * s.nq) * es, s.b.ld, s.kq, s.nq};
       p.out[q] = s.out ? s.out + ((q >> 1) * s.mq * s.ldo + (q & 1) * s.nq) * es : nullptr;
+      p.cin[q] = (s.out && s.cin) ? s.cin + ((q >> 1) * s.mq * s.ldo + (q & 1) * s.nq) * es : nullptr;
       if (s.variant == kInterleavedPresum) {
         p.view[SB200_VIEW_PA0 + q] =
             View{s.presum_a + size_t(q) * s.mq * s.kq * es, static_cast<long long>(s.kq), s.mq, s.kq};
@@ -359,6 +382,9 @@ int launch_group(const LaunchSpec& s, cudaStream_t stream, MarkFn mark) {
     if (rc) return rc;
   }
   p.ldo = s.ldo;
+  p.ldc = s.ldo;
+  p.alpha = s.alpha;
+  p.beta = s.beta;
   p.out_rows = s.mq;
   p.out_cols = s.nq;
   for (int i = 0; i < 4; ++i) p.ws[SB200_WS_INNER + i] = s.ws_inner[i];
@@ -507,6 +533,9 @@ int run(const GemmArgs& a, void* workspace, size_t workspace_size, cudaStream_t 
   for (int i = 0; i < 4; ++i) s.ws_inner[i] = reinterpret_cast<float*>(wsb + L.off_ws[i]);
   s.quadrant_floats = L.quadrant_floats;
   s.status = status;
+  s.alpha = a.scaled ? static_cast<float>(a.alpha) : 1.f;
+  s.beta = a.scaled ? static_cast<float>(a.beta) : 0.f;
+  const char* Cin = (a.scaled && a.beta != 0.0) ? static_cast<const char*>(a.c) : nullptr;
 
   if ((rc = mark())) return rc;
   if (L.level < 2) {
@@ -514,6 +543,7 @@ int run(const GemmArgs& a, void* workspace, size_t workspace_size, cudaStream_t 
     s.a = View{a.a, static_cast<long long>(a.k), a.m, a.k};
     s.b = View{a.b, static_cast<long long>(a.n), a.k, a.n};
     s.out = static_cast<char*>(a.d);
+    s.cin = Cin;
     s.ldo = a.n;
     return launch_group(s, stream, mark);
   }
@@ -546,7 +576,9 @@ int run(const GemmArgs& a, void* workspace, size_t workspace_size, cudaStream_t 
     s.a = operand_a(ch.a);
     s.b = operand_b(ch.b);
     s.link = ch.link;
-    s.out = ch.out_quadrant >= 0 ? D + ((ch.out_quadrant >> 1) * mh * ldd + (ch.out_quadrant & 1) * nh) * es : nullptr;
+    const long long out_off = ch.out_quadrant >= 0 ? ((ch.out_quadrant >> 1) * mh * ldd + (ch.out_quadrant & 1) * nh) * es : 0;
+    s.out = ch.out_quadrant >= 0 ? D + out_off : nullptr;
+    s.cin = (ch.out_quadrant >= 0 && Cin) ? Cin + out_off : nullptr;
     s.ldo = ldd;
     s.outer_dst = ch.dst >= 0 ? X[ch.dst] : nullptr;
     s.outer_src = ch.src >= 0 ? X[ch.src] : nullptr;

@@ -40,6 +40,12 @@ struct GemmArgs {
   int pair;       // 1: CTA-pair kernels (256 x 256 tiles on two SMs, cta_group::2); requires bn == 256
   int sm_limit;   // CTAs to launch at most (0: one per SM of the current device)
   cudaEvent_t* events;  // optional: launches_per_run()+1 events, recorded before the first and after each launch
+  // D = alpha * (A * B) + beta * C when `scaled` is set (else alpha = 1, beta = 0 and `c` is never read), the general
+  // form of the reference's operators (include/cutlass/gemm/device/strassen_gemm.h:365-451).  C is m x n row-major,
+  // ldc = n, in the output type, and may be the same buffer as D; it is read only when beta != 0.
+  int scaled;
+  double alpha, beta;
+  const void* c;
 };
 
 // Byte offsets of the parts of the workspace (tests read the presum buffers through this).

@@ -68,6 +68,10 @@ struct KernelParams {
   long long ldo;      // leading dimension of the output in elements
   int out_rows;       // rows of one output quadrant
   int out_cols;       // columns of one output quadrant
+  // output scaling: every value written to an output quadrant is alpha * sum + beta * C (cin[q] is null when beta = 0)
+  float alpha, beta;
+  const void* cin[4];
+  long long ldc;
   float* ws[SB200_NUM_WS];  // fp32 hand-off buffers, tile-contiguous: [tile id][BN/32][128][32]
   int tiles_m, tiles_n;     // tile grid over one output quadrant
   int num_k;                // k-steps per product
@@ -89,8 +93,9 @@ struct KernelParams {
   sb200_program_t prog;
 };
 
-template <int ESIZE_, int BN_, int STAGES_, int MODE_>
+template <int ESIZE_, int BN_, int STAGES_, int MODE_, bool SCALED_ = false>
 struct KernelConfig {
+  static constexpr bool SCALED = SCALED_;  // D = alpha * sum + beta * C instead of D = sum
   static constexpr int ESIZE = ESIZE_;            // operand element size: 2 (f16) or 4 (f32 storage, tf32 math)
   static constexpr int BM = 128;
   static constexpr int BN = BN_;
@@ -564,13 +569,13 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_kernel(const 
         };
         const long long tile_off = static_cast<long long>(wu.ws_slot) * (128 * BN);
         const long long outer_off = static_cast<long long>(wu.tile) * (128 * BN);
-        ok = epilogue_body<ESIZE, BN, Cfg::NSRC_MAX, Cfg::NSLOT_MAX>(p.out, p.ldo, p.out_rows, p.out_cols, p.ws, ep, sx, tmem_base, quarter,
+        ok = epilogue_body<ESIZE, BN, Cfg::NSRC_MAX, Cfg::NSLOT_MAX, Cfg::SCALED>(p.out, p.ldo, p.out_rows, p.out_cols, p.ws, ep, sx, tmem_base, quarter,
                                                      lane, tile_off, static_cast<long long>(blockIdx.x) * (128 * BN), outer_off,
                                                      tile.i * 128, tile.j * BN,
                                                      staging + (warp - 2) * kStagingWarpBytes,
                                                      sp.redirect ? split_tile_buf : nullptr,
                                                      sp.add_partial ? split_tile_buf : nullptr,
-                                                     (p.debug_flags & 32) != 0, wait_slots);
+                                                     (p.debug_flags & 32) != 0, wait_slots, p.alpha, p.beta, p.cin, p.ldc);
         if (!ok) break;
         if (sp.redirect) raise_flag(flag, p.split_epoch, lane);
         ptx::tc_fence_before_sync();

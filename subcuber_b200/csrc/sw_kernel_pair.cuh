@@ -37,8 +37,9 @@
 
 namespace sb200 {
 
-template <int ESIZE_, int STAGES_, int MODE_>
+template <int ESIZE_, int STAGES_, int MODE_, bool SCALED_ = false>
 struct PairConfig {
+  static constexpr bool SCALED = SCALED_;  // D = alpha * sum + beta * C instead of D = sum
   static constexpr int ESIZE = ESIZE_;
   static constexpr int BM = 128;                  // rows per CTA
   static constexpr int PAIR_M = 256;              // rows per pair tile
@@ -369,13 +370,13 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
         const long long te0 = SB200_CLOCK();
         const long long ew0 = ew_full;
 #endif
-        ok = epilogue_body<ESIZE, BN, Cfg::NSRC_MAX, Cfg::NSLOT_MAX>(p.out, p.ldo, p.out_rows, p.out_cols, p.ws, ep, sx, tmem_base, quarter,
+        ok = epilogue_body<ESIZE, BN, Cfg::NSRC_MAX, Cfg::NSLOT_MAX, Cfg::SCALED>(p.out, p.ldo, p.out_rows, p.out_cols, p.ws, ep, sx, tmem_base, quarter,
                                                      lane, tile_off, static_cast<long long>(blockIdx.x) * (128 * BN), outer_off,
                                                      tile.i * Cfg::PAIR_M + static_cast<int>(rank) * Cfg::BM, tile.j * BN,
                                                      staging + (warp - 2) * kStagingWarpBytes,
                                                      sp.redirect ? split_tile_buf : nullptr,
                                                      sp.add_partial ? split_tile_buf : nullptr,
-                                                     (p.debug_flags & 32) != 0, wait_slots,
+                                                     (p.debug_flags & 32) != 0, wait_slots, p.alpha, p.beta, p.cin, p.ldc,
                                                      (p.prof && blockIdx.x == 0 && warp == 2) ? p.prof + 1190 : nullptr);
         if (!ok) break;
 #ifdef SB200_PROFILE_EPILOGUE

@@ -143,8 +143,10 @@ class Workspace:
 
 
 def gemm(kernel: str, a: torch.Tensor, b: torch.Tensor, d: Optional[torch.Tensor] = None,
-         workspace: Optional[Workspace] = None, check: bool = True) -> torch.Tensor:
-    """D = A @ B with the named kernel, asynchronous on the current stream (synchronises only if `check`)."""
+         workspace: Optional[Workspace] = None, check: bool = True, alpha: float = 1.0, beta: float = 0.0,
+         c: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """D = A @ B, or D = alpha * (A @ B) + beta * C when alpha / beta / c are given, with the named kernel;
+    asynchronous on the current stream (synchronises only if `check`).  C may be D itself."""
     lib = _lib.load()
     _check_inputs(a, b)
     m, k = a.shape
@@ -154,15 +156,44 @@ def gemm(kernel: str, a: torch.Tensor, b: torch.Tensor, d: Optional[torch.Tensor
     if workspace is None or workspace.key != (kernel, m, n, k):
         workspace = Workspace(kernel, m, n, k, a.device)
     s = torch.cuda.current_stream(a.device).cuda_stream
+    scaled = alpha != 1.0 or beta != 0.0
+    if scaled and beta != 0.0:
+        if c is None or not c.is_cuda or not c.is_contiguous() or c.shape != d.shape or c.dtype != d.dtype:
+            raise ValueError("beta != 0 needs a contiguous CUDA tensor C with the shape and dtype of D")
     with torch.cuda.device(a.device):
-        rc = lib.sb200_gemm(kernel.encode(), a.data_ptr(), b.data_ptr(), d.data_ptr(), m, n, k, workspace.ptr,
-                            workspace.nbytes, s)
+        if scaled:
+            rc = lib.sb200_gemm_ex(kernel.encode(), alpha, a.data_ptr(), b.data_ptr(), beta,
+                                   c.data_ptr() if c is not None else None, d.data_ptr(), m, n, k, workspace.ptr,
+                                   workspace.nbytes, s)
+        else:
+            rc = lib.sb200_gemm(kernel.encode(), a.data_ptr(), b.data_ptr(), d.data_ptr(), m, n, k, workspace.ptr,
+                                workspace.nbytes, s)
         if rc != 0:
             raise KernelError(kernel, rc)
         if check:
             rc = lib.sb200_gemm_status(workspace.ptr, s)
             if rc != 0:
                 raise KernelError(kernel, rc)
+    return d
+
+
+def gemm_colmajor(kernel: str, a_cm: torch.Tensor, b_cm: torch.Tensor, m: int, n: int, k: int) -> torch.Tensor:
+    """Column-major problem: `a_cm` holds A (m x k) column-major, i.e. it is the contiguous (k x m) tensor A^T; `b_cm`
+    likewise is the contiguous (n x k) tensor B^T.  Returns the contiguous (n x m) tensor D^T = column-major D."""
+    lib = _lib.load()
+    if tuple(a_cm.shape) != (k, m) or tuple(b_cm.shape) != (n, k):
+        raise ValueError("column-major operands are passed as their contiguous transposes")
+    _check_inputs(b_cm, a_cm)
+    d = torch.empty((n, m), dtype=a_cm.dtype, device=a_cm.device)
+    workspace = Workspace(kernel, n, m, k, a_cm.device)
+    s = torch.cuda.current_stream(a_cm.device).cuda_stream
+    with torch.cuda.device(a_cm.device):
+        rc = lib.sb200_gemm_colmajor(kernel.encode(), a_cm.data_ptr(), b_cm.data_ptr(), d.data_ptr(), m, n, k,
+                                     workspace.ptr, workspace.nbytes, s)
+        if rc == 0:
+            rc = lib.sb200_gemm_status(workspace.ptr, s)
+    if rc != 0:
+        raise KernelError(kernel, rc)
     return d
 
 

@@ -90,6 +90,68 @@ def test_level2_bit_exact_on_harness_values(kernel, shape, oracle, cuda_device):
         assert np.array_equal(got.astype(np.float64), a.astype(np.float64) @ b.astype(np.float64))
 
 
+# ------------------------------------------------------------------------- alpha / beta / C, column-major
+SCALED_KERNELS = ["blackwell_f16_cubic_2sm_256x256", "blackwell_f16_sw_interleaved_presum_2sm",
+                  "blackwell_f16_sw_interleaved_presum", "blackwell_f32_sw_interleaved_presum_2sm",
+                  "blackwell_f16_sw_level2_2sm", "blackwell_f32_sw_level2", "blackwell_f64_cubic_dmma",
+                  "blackwell_f64_sw_level1", "blackwell_f64_sw_level2"]
+
+
+@pytest.mark.parametrize("kernel", SCALED_KERNELS)
+@pytest.mark.parametrize("alpha,beta", [(2.0, -0.5), (-1.0, 0.0), (0.5, 1.0)])
+def test_alpha_beta_bit_exact_on_harness_values(kernel, alpha, beta, oracle, cuda_device):
+    """D = alpha * A B + beta * C, the reference operators' general form (strassen_gemm.h:365-451): on the harness'
+    value set and with power-of-two scales every sum stays exact, so the result equals the oracle's bit for bit."""
+    import torch
+
+    from subcuber_b200 import inputs, runner
+
+    m, n, k = (520, 1040, 272) if _level(kernel) == 2 else (264, 520, 136)
+    dt = _dt(kernel)
+    a_np, b_np = inputs.operands(dt, "harness", m, n, k, seed=17)
+    c_np = inputs.operands(dt, "harness", m, n, n, seed=18)[0]   # an m x n matrix of the same value set
+    a, b, c = (torch.from_numpy(x).to(cuda_device) for x in (a_np, b_np, c_np))
+    d = runner.gemm(kernel, a, b, alpha=alpha, beta=beta, c=c)
+    torch.cuda.synchronize()
+    want = oracle.sw_gemm(dt, _level(kernel), a_np, b_np, alpha=alpha, beta=beta, Cin=c_np)
+    assert np.array_equal(d.cpu().numpy(), want)
+    if beta != 0.0:  # in place: C and D the same buffer
+        d2 = runner.gemm(kernel, a, b, d=c, alpha=alpha, beta=beta, c=c)
+        torch.cuda.synchronize()
+        assert np.array_equal(d2.cpu().numpy(), want)
+
+
+def test_scaled_form_is_refused_where_it_is_not_built(cuda_device):
+    import torch
+
+    from subcuber_b200 import inputs, runner
+
+    a_np, b_np = inputs.operands("f16", "harness", 256, 256, 128, seed=1)
+    a, b = torch.from_numpy(a_np).to(cuda_device), torch.from_numpy(b_np).to(cuda_device)
+    with pytest.raises(runner.KernelError):
+        runner.gemm("blackwell_f16_sw_fused_presum", a, b, alpha=2.0)   # fused-presum plan: D = A B only
+    with pytest.raises(ValueError):
+        runner.gemm("blackwell_f16_cubic_2sm_256x256", a, b, beta=1.0)  # beta without C
+
+
+@pytest.mark.parametrize("kernel", ["blackwell_f16_sw_interleaved_presum_2sm", "blackwell_f64_sw_level1",
+                                    "blackwell_f32_cubic_2sm_256x256"])
+def test_column_major_operands(kernel, cuda_device):
+    import torch
+
+    from subcuber_b200 import inputs, runner
+
+    m, n, k = 384, 272, 528
+    dt = _dt(kernel)
+    a_np, b_np = inputs.operands(dt, "harness", m, n, k, seed=23)
+    a_cm = torch.from_numpy(np.ascontiguousarray(a_np.T)).to(cuda_device)   # column-major A = contiguous A^T
+    b_cm = torch.from_numpy(np.ascontiguousarray(b_np.T)).to(cuda_device)
+    d_cm = runner.gemm_colmajor(kernel, a_cm, b_cm, m, n, k)
+    torch.cuda.synchronize()
+    want = a_np.astype(np.float64) @ b_np.astype(np.float64)
+    assert np.array_equal(d_cm.cpu().numpy().T.astype(np.float64), want.astype(a_np.dtype).astype(np.float64))
+
+
 # ------------------------------------------------------------------------------------------ fp64 (DMMA)
 F64 = ["blackwell_f64_cubic_dmma", "blackwell_f64_sw_level1", "blackwell_f64_sw_level2"]
 
