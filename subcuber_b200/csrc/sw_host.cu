@@ -404,7 +404,6 @@ int launch_group(const LaunchSpec& s, cudaStream_t stream, MarkFn mark) {
   p.band = 8;
   if (const char* bd = getenv("SB200_BAND")) p.band = atoi(bd) > 0 ? atoi(bd) : 8;
   if (const char* dbg = getenv("SB200_DEBUG_FLAGS")) p.debug_flags = atoi(dbg);
-  if (const char* pf = getenv("SB200_PREFETCH")) p.prefetch_dist = atoi(pf);
   if (getenv("SB200_PROF")) {
     // measurement aid: per-CTA cycle counters of the CTA-pair kernels (library built with SB200_PROFILE), printed by
     // the next call

@@ -84,8 +84,9 @@ struct KernelParams {
   float* split_buf;         // [split tile][quadrant 4][CTA of the tile][128 x BN] fp32, hand-off tile order
   int* split_flags;         // [split tile][quadrant 4][CTA of the tile 2][epilogue warp 4]
   int* status;              // device status word, 0 = ok
-  int debug_flags;          // measurement aids: bit 0 = issue no MMA, bit 1 = issue no TMA load (results are garbage)
-  int prefetch_dist;        // > 0: the producer asks L2 for the operand tiles this many k-steps ahead
+  int debug_flags;          // measurement aids (results are garbage): bit 0 = issue no MMA, bit 1 = issue no TMA load,
+                            // bit 3 = load only while the ring fills for the first time (pairs), bit 4 = skip the
+                            // presum job (pairs), bit 5 = skip the epilogue bodies
   long long* prof;          // measurement aid (CTA-pair kernels): 8 cycle counters per CTA, or null
   // presum jobs (mode JOB), run by the presum warps of the whole grid one after the other
   int njobs;
