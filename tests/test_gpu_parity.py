@@ -106,7 +106,7 @@ def test_alpha_beta_bit_exact_on_harness_values(kernel, alpha, beta, oracle, cud
 
     from subcuber_b200 import inputs, runner
 
-    m, n, k = (520, 1040, 272) if _level(kernel) == 2 else (264, 520, 136)
+    m, n, k = (528, 1056, 288) if _level(kernel) == 2 else (272, 528, 144)
     dt = _dt(kernel)
     a_np, b_np = inputs.operands(dt, "harness", m, n, k, seed=17)
     c_np = inputs.operands(dt, "harness", m, n, n, seed=18)[0]   # an m x n matrix of the same value set
