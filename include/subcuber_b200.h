@@ -92,6 +92,13 @@ SB200_DECLARE_RUN(run_blackwell_f32_sw_level2_2sm);
 SB200_DECLARE_RUN(run_blackwell_f64_cubic_dmma);
 SB200_DECLARE_RUN(run_blackwell_f64_sw_level1);
 SB200_DECLARE_RUN(run_blackwell_f64_sw_level2);
+/* Level (0, 1 or 2) and kernel family chosen by problem size, crossover points measured on B200: the role of the
+ * reference front end's size-based choice (src/compile.py:200-212).  Accepted wherever a kernel name is. */
+SB200_DECLARE_RUN(run_blackwell_f16_sw_auto);
+SB200_DECLARE_RUN(run_blackwell_f32_sw_auto);
+SB200_DECLARE_RUN(run_blackwell_f64_sw_auto);
+/* Name of the kernel "blackwell_<dtype>_sw_auto" resolves to for this problem (dtype: "f16" | "f32" | "f64"). */
+const char* sb200_auto_kernel(const char* dtype, int m, int n, int k);
 /* cuBLAS baselines behind the same ABI (reference: src/cuda/cublas_runner.cpp:151-175); the tf32 row is
  * an addition: the reference's f32 row is CUBLAS_COMPUTE_32F_PEDANTIC (cublas_runner.cpp:14). */
 SB200_DECLARE_RUN(run_cublas_f16);

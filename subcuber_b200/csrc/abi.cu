@@ -57,6 +57,42 @@ const KernelDesc* find_desc(const char* name) {
   return nullptr;
 }
 
+// Size-based choice of level and kernel family ("blackwell_<dtype>_sw_auto"): the role of the reference front end's
+// cost model (src/compile.py:200-212, should_use_k2 / level by size), with crossover points measured on B200.
+// The recursion pays off once a product is large enough for its presum and postsum traffic to be small against it:
+//   f16 : level 1 from 12288, level 2 from 24576 (smallest of m, n, k); below that the plain pair kernel is fastest
+//   tf32: level 1 from 12288, level 2 from 16384
+//   f64 : level 1 from 6144, level 2 from 16384
+const char* auto_kernel(sb200::DType dt, int m, int n, int k) {
+  int s = m < n ? m : n;
+  if (k < s) s = k;
+  const bool l2_ok = (m % 4 == 0) && (n % 4 == 0) && (k % 4 == 0);
+  const bool l1_ok = (m % 2 == 0) && (n % 2 == 0) && (k % 2 == 0);
+  switch (dt) {
+    case sb200::kF16:
+      if (s >= 24576 && l2_ok) return "blackwell_f16_sw_level2_2sm";
+      if (s >= 12288 && l1_ok) return "blackwell_f16_sw_interleaved_presum_2sm";
+      return "blackwell_f16_cubic_2sm_256x256";
+    case sb200::kF32:
+      if (s >= 16384 && l2_ok) return "blackwell_f32_sw_level2_2sm";
+      if (s >= 12288 && l1_ok) return "blackwell_f32_sw_interleaved_presum_2sm";
+      return "blackwell_f32_cubic_2sm_256x256";
+    default:
+      if (s >= 16384 && l2_ok) return "blackwell_f64_sw_level2";
+      if (s >= 6144 && l1_ok) return "blackwell_f64_sw_level1";
+      return "blackwell_f64_cubic_dmma";
+  }
+}
+
+// Registry name -> descriptor for a given problem: "…_sw_auto" names resolve by size, all others by name.
+const KernelDesc* resolve_desc(const char* name, int m, int n, int k) {
+  if (!name) return nullptr;
+  if (strcmp(name, "blackwell_f16_sw_auto") == 0) return find_desc(auto_kernel(sb200::kF16, m, n, k));
+  if (strcmp(name, "blackwell_f32_sw_auto") == 0) return find_desc(auto_kernel(sb200::kF32, m, n, k));
+  if (strcmp(name, "blackwell_f64_sw_auto") == 0) return find_desc(auto_kernel(sb200::kF64, m, n, k));
+  return find_desc(name);
+}
+
 GemmArgs make_args(const KernelDesc& d, const void* a, const void* b, void* out, int m, int n, int k) {
   GemmArgs g;
   memset(&g, 0, sizeof(g));
@@ -79,7 +115,7 @@ GemmArgs make_args(const KernelDesc& d, const void* a, const void* b, void* out,
 // CUDA events, free.  Events are recorded on the stream the kernels run on.
 int run_registry_kernel(const char* name, KernelRunnerBuffers buf, int m, int n, int k, int warmup, int iterations,
                         sb200_stream_t* streams, int num_streams, int split_k, float* avg_ms) {
-  const KernelDesc* d = find_desc(name);
+  const KernelDesc* d = resolve_desc(name, m, n, k);
   if (!d) return SB200_ERR_NO_KERNEL;
   if (split_k != 1) return SB200_ERR_NOT_SUPPORTED;
   if (iterations <= 0 || warmup < 0 || !avg_ms) return SB200_ERR_INVALID_PROBLEM;
@@ -284,6 +320,9 @@ SB200_DEFINE_RUN(blackwell_f32_sw_level2_2sm)
 SB200_DEFINE_RUN(blackwell_f64_cubic_dmma)
 SB200_DEFINE_RUN(blackwell_f64_sw_level1)
 SB200_DEFINE_RUN(blackwell_f64_sw_level2)
+SB200_DEFINE_RUN(blackwell_f16_sw_auto)
+SB200_DEFINE_RUN(blackwell_f32_sw_auto)
+SB200_DEFINE_RUN(blackwell_f64_sw_auto)
 
 #define SB200_DEFINE_BLAS(fn, impl, type)                                                                      \
   extern "C" int fn(KernelRunnerBuffers buffers, int m, int n, int k, int warmup_iterations, int iterations,   \
@@ -327,6 +366,10 @@ static const sb200_kernel_entry kRegistry[] = {
     {"blackwell_f64_cubic_dmma", "blackwell", "f64", 0, run_blackwell_f64_cubic_dmma},
     {"blackwell_f64_sw_level1", "blackwell", "f64", 1, run_blackwell_f64_sw_level1},
     {"blackwell_f64_sw_level2", "blackwell", "f64", 2, run_blackwell_f64_sw_level2},
+    // level chosen by size; listed under level 1 so that "--strassen_level=1" runs show it next to the fixed plans
+    {"blackwell_f16_sw_auto", "blackwell", "f16", 1, run_blackwell_f16_sw_auto},
+    {"blackwell_f32_sw_auto", "blackwell", "f32", 1, run_blackwell_f32_sw_auto},
+    {"blackwell_f64_sw_auto", "blackwell", "f64", 1, run_blackwell_f64_sw_auto},
 };
 
 extern "C" int sb200_num_kernels(void) { return static_cast<int>(sizeof(kRegistry) / sizeof(kRegistry[0])); }
@@ -335,7 +378,7 @@ extern "C" const sb200_kernel_entry* sb200_kernel(int index) {
 }
 
 extern "C" int sb200_gemm_can_implement(const char* kernel, int m, int n, int k) {
-  const KernelDesc* d = find_desc(kernel);
+  const KernelDesc* d = resolve_desc(kernel, m, n, k);
   if (!d) return SB200_ERR_NO_KERNEL;
   // operand pointers are checked by sb200_gemm; use aligned placeholders here
   GemmArgs g = make_args(*d, reinterpret_cast<const void*>(256), reinterpret_cast<const void*>(256),
@@ -344,7 +387,7 @@ extern "C" int sb200_gemm_can_implement(const char* kernel, int m, int n, int k)
 }
 
 extern "C" size_t sb200_gemm_workspace_bytes(const char* kernel, int m, int n, int k) {
-  const KernelDesc* d = find_desc(kernel);
+  const KernelDesc* d = resolve_desc(kernel, m, n, k);
   if (!d || m <= 0 || n <= 0 || k <= 0) return 0;
   GemmArgs g = make_args(*d, nullptr, nullptr, nullptr, m, n, k);
   return sb200::workspace_bytes(g);
@@ -352,7 +395,7 @@ extern "C" size_t sb200_gemm_workspace_bytes(const char* kernel, int m, int n, i
 
 extern "C" int sb200_gemm(const char* kernel, const void* a, const void* b, void* d_out, int m, int n, int k,
                           void* workspace, size_t workspace_bytes, sb200_stream_t stream) {
-  const KernelDesc* d = find_desc(kernel);
+  const KernelDesc* d = resolve_desc(kernel, m, n, k);
   if (!d) return SB200_ERR_NO_KERNEL;
   GemmArgs g = make_args(*d, a, b, d_out, m, n, k);
   return sb200::run(g, workspace, workspace_bytes, reinterpret_cast<cudaStream_t>(stream));
@@ -361,7 +404,7 @@ extern "C" int sb200_gemm(const char* kernel, const void* a, const void* b, void
 extern "C" int sb200_gemm_ex(const char* kernel, double alpha, const void* a, const void* b, double beta, const void* c,
                              void* d_out, int m, int n, int k, void* workspace, size_t workspace_bytes,
                              sb200_stream_t stream) {
-  const KernelDesc* d = find_desc(kernel);
+  const KernelDesc* d = resolve_desc(kernel, m, n, k);
   if (!d) return SB200_ERR_NO_KERNEL;
   GemmArgs g = make_args(*d, a, b, d_out, m, n, k);
   g.scaled = 1;
@@ -376,10 +419,18 @@ extern "C" int sb200_gemm_ex(const char* kernel, double alpha, const void* a, co
 // include/cutlass/gemm/device/strassen_gemm.h:3925-4170).
 extern "C" int sb200_gemm_colmajor(const char* kernel, const void* a, const void* b, void* d_out, int m, int n, int k,
                                    void* workspace, size_t workspace_bytes, sb200_stream_t stream) {
-  const KernelDesc* d = find_desc(kernel);
+  const KernelDesc* d = resolve_desc(kernel, m, n, k);
   if (!d) return SB200_ERR_NO_KERNEL;
   GemmArgs g = make_args(*d, b, a, d_out, n, m, k);
   return sb200::run(g, workspace, workspace_bytes, reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" const char* sb200_auto_kernel(const char* dtype, int m, int n, int k) {
+  if (!dtype) return nullptr;
+  if (strcmp(dtype, "f16") == 0) return auto_kernel(sb200::kF16, m, n, k);
+  if (strcmp(dtype, "f32") == 0) return auto_kernel(sb200::kF32, m, n, k);
+  if (strcmp(dtype, "f64") == 0) return auto_kernel(sb200::kF64, m, n, k);
+  return nullptr;
 }
 
 extern "C" int sb200_gemm_status(void* workspace, sb200_stream_t stream) {
@@ -396,7 +447,7 @@ extern "C" int sb200_gemm_launches(const char* kernel) {
 
 extern "C" int sb200_gemm_host(const char* kernel, const void* a_host, const void* b_host, void* d_host, int m, int n,
                                int k) {
-  const KernelDesc* d = find_desc(kernel);
+  const KernelDesc* d = resolve_desc(kernel, m, n, k);
   if (!d) return SB200_ERR_NO_KERNEL;
   if (!a_host || !b_host || !d_host || m <= 0 || n <= 0 || k <= 0) return SB200_ERR_INVALID_PROBLEM;
   const size_t es = d->dt == sb200::kF16 ? 2 : 4;
@@ -430,7 +481,7 @@ extern "C" int sb200_gemm_host(const char* kernel, const void* a_host, const voi
 }
 
 extern "C" int sb200_gemm_workspace_layout(const char* kernel, int m, int n, int k, sb200_workspace_layout* out) {
-  const KernelDesc* d = find_desc(kernel);
+  const KernelDesc* d = resolve_desc(kernel, m, n, k);
   if (!d) return SB200_ERR_NO_KERNEL;
   if (!out || m <= 0 || n <= 0 || k <= 0) return SB200_ERR_INVALID_PROBLEM;
   GemmArgs g = make_args(*d, nullptr, nullptr, nullptr, m, n, k);
@@ -448,7 +499,7 @@ extern "C" int sb200_gemm_workspace_layout(const char* kernel, int m, int n, int
 extern "C" int sb200_gemm_timed(const char* kernel, const void* a, const void* b, void* d_out, int m, int n, int k,
                                 void* workspace, size_t workspace_bytes, sb200_stream_t stream, float* launch_ms,
                                 int* num_launches) {
-  const KernelDesc* d = find_desc(kernel);
+  const KernelDesc* d = resolve_desc(kernel, m, n, k);
   if (!d) return SB200_ERR_NO_KERNEL;
   if (!launch_ms || !num_launches) return SB200_ERR_INVALID_PROBLEM;
   GemmArgs g = make_args(*d, a, b, d_out, m, n, k);
@@ -544,7 +595,7 @@ extern "C" int sb200_events_elapsed_ms(sb200_event_list* l, int first, int secon
 extern "C" int sb200_gemm_events(const char* kernel, const void* a, const void* b, void* d_out, int m, int n, int k,
                                  void* workspace, size_t workspace_bytes, sb200_stream_t stream, sb200_event_list* l,
                                  int first_index) {
-  const KernelDesc* d = find_desc(kernel);
+  const KernelDesc* d = resolve_desc(kernel, m, n, k);
   if (!d) return SB200_ERR_NO_KERNEL;
   GemmArgs g = make_args(*d, a, b, d_out, m, n, k);
   if (!l || first_index < 0 || first_index + sb200::launches_per_run(g) + 1 > l->count) return SB200_ERR_INVALID_PROBLEM;

@@ -38,9 +38,32 @@ def test_registry_rows(lib):
     assert sorted("run_" + n for n in names) == sorted(runs)
     assert [r.name for r in runner.kernels(dtype="half", level=1)] == [
         "blackwell_f16_sw_fused_presum", "blackwell_f16_sw_interleaved_presum",
-        "blackwell_f16_sw_fused_presum_2sm", "blackwell_f16_sw_interleaved_presum_2sm"]
+        "blackwell_f16_sw_fused_presum_2sm", "blackwell_f16_sw_interleaved_presum_2sm", "blackwell_f16_sw_auto"]
     assert [r.name for r in runner.kernels(dtype="f32", level=0, regex="cubic")] == [
         "blackwell_f32_cubic_128x256", "blackwell_f32_cubic_128x128", "blackwell_f32_cubic_2sm_256x256"]
+
+
+def test_auto_kernel_choice(lib):
+    """Size-based choice of level and family: small problems run the plain pair kernel, large ones recurse; sizes the
+    recursion cannot split fall back to the level below."""
+    import ctypes as C
+
+    lib.sb200_auto_kernel.restype = C.c_char_p
+    lib.sb200_auto_kernel.argtypes = [C.c_char_p, C.c_int, C.c_int, C.c_int]
+    pick = lambda dt, m, n, k: lib.sb200_auto_kernel(dt.encode(), m, n, k).decode()
+    assert pick("f16", 8192, 8192, 8192) == "blackwell_f16_cubic_2sm_256x256"
+    assert pick("f16", 16384, 16384, 16384) == "blackwell_f16_sw_interleaved_presum_2sm"
+    assert pick("f16", 32768, 32768, 32768) == "blackwell_f16_sw_level2_2sm"
+    assert pick("f16", 32768, 32768, 4096) == "blackwell_f16_cubic_2sm_256x256"      # the smallest extent decides
+    assert pick("f16", 32770, 32768, 32768) == "blackwell_f16_sw_interleaved_presum_2sm"  # not divisible by 4
+    assert pick("f32", 16384, 8192, 32768) == "blackwell_f32_cubic_2sm_256x256"
+    assert pick("f32", 16384, 16384, 16384) == "blackwell_f32_sw_level2_2sm"
+    assert pick("f64", 8192, 8192, 8192) == "blackwell_f64_sw_level1"
+    assert pick("f64", 16384, 16384, 16384) == "blackwell_f64_sw_level2"
+    assert lib.sb200_auto_kernel(b"bf16", 1, 1, 1) is None
+    assert lib.sb200_gemm_can_implement(b"blackwell_f16_sw_auto", 512, 512, 512) == 0
+    assert lib.sb200_gemm_workspace_bytes(b"blackwell_f16_sw_auto", 512, 512, 512) == \
+        lib.sb200_gemm_workspace_bytes(b"blackwell_f16_cubic_2sm_256x256", 512, 512, 512)
 
 
 def test_alias_tables():

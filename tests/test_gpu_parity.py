@@ -152,6 +152,25 @@ def test_column_major_operands(kernel, cuda_device):
     assert np.array_equal(d_cm.cpu().numpy().T.astype(np.float64), want.astype(a_np.dtype).astype(np.float64))
 
 
+def test_auto_kernel_runs_the_kernel_it_names(lib, cuda_device):
+    import ctypes as C
+
+    import torch
+
+    from subcuber_b200 import inputs, runner
+
+    lib.sb200_auto_kernel.restype = C.c_char_p
+    lib.sb200_auto_kernel.argtypes = [C.c_char_p, C.c_int, C.c_int, C.c_int]
+    for dt, (m, n, k) in (("f16", (512, 768, 256)), ("f64", (256, 384, 128))):
+        a_np, b_np = inputs.operands(dt, "harness", m, n, k, seed=31)
+        a, b = torch.from_numpy(a_np).to(cuda_device), torch.from_numpy(b_np).to(cuda_device)
+        d = runner.gemm(f"blackwell_{dt}_sw_auto", a, b)
+        named = lib.sb200_auto_kernel(dt.encode(), m, n, k).decode()
+        ref = runner.gemm(named, a, b)
+        torch.cuda.synchronize()
+        assert torch.equal(d, ref)
+
+
 # ------------------------------------------------------------------------------------------ fp64 (DMMA)
 F64 = ["blackwell_f64_cubic_dmma", "blackwell_f64_sw_level1", "blackwell_f64_sw_level2"]
 
