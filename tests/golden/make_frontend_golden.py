@@ -1,6 +1,6 @@
 """Generate tests/golden/frontend_golden.json by running the reference project's Python front end.
 
-Needs the reference tree (default /root/reference); it is imported from where it lies, nothing is copied:
+Needs the reference tree; it is imported from where it lies, nothing is copied:
 
     python tests/golden/make_frontend_golden.py [/path/to/reference]
 
