@@ -24,7 +24,7 @@ NVCC_FLAGS = [
     "-Xcompiler", "-fPIC",
 ]
 
-LIB_SOURCES = ["sw_host.cu", "dgemm_sw.cu", "abi.cu", "fill.cu", "static_scratch.cu"]
+LIB_SOURCES = ["sw_host.cu", "any_size.cu", "dgemm_sw.cu", "abi.cu", "fill.cu", "static_scratch.cu"]
 RUNNER_SOURCES = ["kernel_runner.cpp"]
 
 

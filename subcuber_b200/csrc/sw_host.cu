@@ -99,9 +99,13 @@ Layout make_layout(const GemmArgs& a) {
   L.bn = a.bn == 128 ? 128 : 256;
   L.level = level_of(a.variant);
   const int div = 1 << L.level;
-  L.mq = a.m / div;
-  L.nq = a.n / div;
-  L.kq = a.k / div;
+  // Block extents: the matrices are cut at multiples of these; extents that do not divide leave the last block row /
+  // column short, and the kernels treat the missing part as zeros (TMA fills loads outside a view with zeros, the
+  // presum jobs and the output stores are bounded).  Column cuts keep every block row on a 16-byte boundary.
+  const int vec = 16 / L.esize;
+  L.mq = ceil_div(a.m, div);
+  L.nq = static_cast<int>(align_up(ceil_div(a.n, div), vec));
+  L.kq = static_cast<int>(align_up(ceil_div(a.k, div), vec));
   L.tiles_m = ceil_div(L.mq, a.pair ? 256 : 128);
   L.tiles_n = ceil_div(L.nq, L.bn);
   L.num_k = ceil_div(L.kq, 128 / L.esize);
@@ -260,8 +264,9 @@ int launch_any_pair(int esize, int mode, const KernelParams& p, int pairs, cudaS
 
 }  // namespace
 
+namespace tc {
+
 int can_implement(const GemmArgs& a) {
-  if (a.dtype == kF64) return f64::can_implement(a);
   if (a.m <= 0 || a.n <= 0 || a.k <= 0 || !a.a || !a.b || !a.d) return kErrInvalidProblem;
   if (a.dtype != kF16 && a.dtype != kF32) return kErrNotSupported;
   if (a.scaled && a.beta != 0.0 && (!a.c || (reinterpret_cast<uintptr_t>(a.c) & 15))) return kErrInvalidProblem;
@@ -270,25 +275,23 @@ int can_implement(const GemmArgs& a) {
   const int es = esize_of(a.dtype);
   const int vec = 16 / es;  // elements per 16 bytes
   const int div = 1 << level_of(a.variant);
-  if ((a.m % div) || (a.n % div) || (a.k % div)) return kErrInvalidProblem;
-  // every block row must start on a 16-byte boundary (TMA base/stride rule, vector loads and stores)
-  if ((a.k / div) % vec || (a.n / div) % vec) return kErrMisalignedOperand;
+  // every row must start on a 16-byte boundary (TMA base/stride rule, vector loads and stores)
+  if (a.k % vec || a.n % vec) return kErrMisalignedOperand;
+  // the last block row / column of every cut may be short but not empty
+  const int mq = ceil_div(a.m, div);
+  const int nq = static_cast<int>(align_up(ceil_div(a.n, div), vec));
+  const int kq = static_cast<int>(align_up(ceil_div(a.k, div), vec));
+  if (a.m - (div - 1) * mq < 1 || a.n - (div - 1) * nq < 1 || a.k - (div - 1) * kq < 1) return kErrInvalidProblem;
   if ((reinterpret_cast<uintptr_t>(a.a) | reinterpret_cast<uintptr_t>(a.b) | reinterpret_cast<uintptr_t>(a.d)) & 15)
     return kErrMisalignedOperand;
   return kOk;
 }
 
-size_t workspace_bytes(const GemmArgs& a) {
-  return a.dtype == kF64 ? f64::workspace_bytes(a) : make_layout(a).total;
-}
+size_t workspace_bytes(const GemmArgs& a) { return make_layout(a).total; }
 
 WorkspaceLayout workspace_layout(const GemmArgs& a) {
   WorkspaceLayout w;
   memset(&w, 0, sizeof(w));
-  if (a.dtype == kF64) {
-    w.total = f64::workspace_bytes(a);
-    return w;
-  }
   const Layout L = make_layout(a);
   w.status = L.off_status;
   w.presum_a = L.off_pa;
@@ -301,7 +304,6 @@ WorkspaceLayout workspace_layout(const GemmArgs& a) {
 }
 
 int launches_per_run(const GemmArgs& a) {
-  if (a.dtype == kF64) return f64::launches_per_run(a);
   return a.variant == kInterleavedLevel2 ? 14 : (a.variant == kInterleavedPresum ? 2 : 1);
 }
 
@@ -312,10 +314,11 @@ namespace {
 struct LaunchSpec {
   Variant variant;
   int es, bn, pair, grid;
-  View a, b;                 // whole operands of this group
+  View a, b;                 // whole operands of this group (extents up to twice the block extents)
   int mq, nq, kq;            // extents of one block (level 0: of the whole problem)
   int tiles_m, tiles_n, num_k;
-  char* out;                 // output matrix in the output type (2mq x 2nq, or mq x nq at level 0), or null
+  char* out;                 // output matrix in the output type (up to 2mq x 2nq, or mq x nq at level 0), or null
+  int out_rows, out_cols;    // its extents
   long long ldo;
   const char* cin;           // C input laid out like `out` (same leading dimension), or null
   float alpha, beta;
@@ -338,6 +341,16 @@ struct LaunchSpec {
   int* split_epoch;          // counter shared by the launches of one run
 };
 
+// Block (br, bc) of a matrix cut at multiples of (rows, cols): the last block row / column keeps what is left.
+View block_of(const View& w, int br, int bc, int rows, int cols, int es) {
+  View v;
+  v.ptr = static_cast<const char*>(w.ptr) + (static_cast<long long>(br) * rows * w.ld + static_cast<long long>(bc) * cols) * es;
+  v.ld = w.ld;
+  v.rows = w.rows - br * rows < rows ? w.rows - br * rows : rows;
+  v.cols = w.cols - bc * cols < cols ? w.cols - bc * cols : cols;
+  return v;
+}
+
 template <typename MarkFn>
 int launch_group(const LaunchSpec& s, cudaStream_t stream, MarkFn mark) {
   KernelParams p;
@@ -354,8 +367,8 @@ int launch_group(const LaunchSpec& s, cudaStream_t stream, MarkFn mark) {
     p.cin[0] = s.cin;
   } else {
     for (int q = 0; q < 4; ++q) {
-      p.view[SB200_VIEW_A0 + q] = View{A + ((q >> 1) * s.mq * s.a.ld + (q & 1) * s.kq) * es, s.a.ld, s.mq, s.kq};
-      p.view[SB200_VIEW_B0 + q] = View{B + ((q >> 1) * s.kq * s.b.ld + (q & 1) * s.nq) * es, s.b.ld, s.kq, s.nq};
+      p.view[SB200_VIEW_A0 + q] = block_of(s.a, q >> 1, q & 1, s.mq, s.kq, es);
+      p.view[SB200_VIEW_B0 + q] = block_of(s.b, q >> 1, q & 1, s.kq, s.nq, es);
       p.out[q] = s.out ? s.out + ((q >> 1) * s.mq * s.ldo + (q & 1) * s.nq) * es : nullptr;
       p.cin[q] = (s.out && s.cin) ? s.cin + ((q >> 1) * s.mq * s.ldo + (q & 1) * s.nq) * es : nullptr;
       if (s.variant == kInterleavedPresum) {
@@ -375,7 +388,9 @@ int launch_group(const LaunchSpec& s, cudaStream_t stream, MarkFn mark) {
   const CUtensorMapSwizzle b_swz = es == 4 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B;
   // column blocks of B one CTA loads per k-step: BN (1-CTA kernels) or BN / 2 (CTA pairs) columns of 128 bytes each
   const int b_nblk = (s.pair ? 128 : s.bn) * es / 128;
-  p.b_blocked = (p.view[SB200_VIEW_B0].cols % (128 / es) == 0) ? 1 : 0;
+  p.b_blocked = 1;  // needs whole 128-byte column blocks in every view
+  for (int v = 8; v < 16; ++v)
+    if (p.view[v].cols % (128 / es)) p.b_blocked = 0;
   for (int v = 8; v < 16; ++v) {
     rc = p.b_blocked ? make_tmap_b_blocked(&p.tmap[v], es, p.view[v], 128 / es, b_nblk, b_swz)
                      : make_tmap(&p.tmap[v], es, p.view[v], 128 / es, b_swz);
@@ -385,8 +400,10 @@ int launch_group(const LaunchSpec& s, cudaStream_t stream, MarkFn mark) {
   p.ldc = s.ldo;
   p.alpha = s.alpha;
   p.beta = s.beta;
-  p.out_rows = s.mq;
-  p.out_cols = s.nq;
+  p.out_rows = s.out_rows < s.mq ? s.out_rows : s.mq;
+  p.out_cols = s.out_cols < s.nq ? s.out_cols : s.nq;
+  p.out_rows2 = s.out_rows - s.mq;
+  p.out_cols2 = s.out_cols - s.nq;
   for (int i = 0; i < 4; ++i) p.ws[SB200_WS_INNER + i] = s.ws_inner[i];
   for (int q = 0; q < 4; ++q) {
     const size_t o = size_t(q) * s.quadrant_floats;
@@ -454,7 +471,9 @@ int launch_group(const LaunchSpec& s, cudaStream_t stream, MarkFn mark) {
       p.job[1].src[q] = p.view[SB200_VIEW_B0 + q].ptr;
     }
     p.job[0].ld = s.a.ld; p.job[0].dst = s.presum_a; p.job[0].rows = s.mq; p.job[0].cols = s.kq; p.job[0].side = 0;
+    p.job[0].rows2 = s.a.rows - s.mq; p.job[0].cols2 = s.a.cols - s.kq;
     p.job[1].ld = s.b.ld; p.job[1].dst = s.presum_b; p.job[1].rows = s.kq; p.job[1].cols = s.nq; p.job[1].side = 1;
+    p.job[1].rows2 = s.b.rows - s.kq; p.job[1].cols2 = s.b.cols - s.nq;
     for (int j = 0; j < s.n_more_jobs; ++j) p.job[p.njobs++] = s.more_jobs[j];
   }
   const int bn_sel = s.pair ? -1 : s.bn;  // -1 routes launch_any to the CTA-pair kernels (grid = pairs)
@@ -493,8 +512,7 @@ int launch_group(const LaunchSpec& s, cudaStream_t stream, MarkFn mark) {
 }  // namespace
 
 int run(const GemmArgs& a, void* workspace, size_t workspace_size, cudaStream_t stream) {
-  if (a.dtype == kF64) return f64::run(a, workspace, workspace_size, stream);
-  int rc = can_implement(a);
+  int rc = tc::can_implement(a);
   if (rc) return rc;
   const Layout L = make_layout(a);
   if (!workspace) return kErrWorkspaceNull;
@@ -544,6 +562,8 @@ int run(const GemmArgs& a, void* workspace, size_t workspace_size, cudaStream_t 
     s.a = View{a.a, static_cast<long long>(a.k), a.m, a.k};
     s.b = View{a.b, static_cast<long long>(a.n), a.k, a.n};
     s.out = static_cast<char*>(a.d);
+    s.out_rows = a.m;
+    s.out_cols = a.n;
     s.cin = Cin;
     s.ldo = a.n;
     return launch_group(s, stream, mark);
@@ -561,12 +581,13 @@ int run(const GemmArgs& a, void* workspace, size_t workspace_size, cudaStream_t 
   char* opb = wsb + L.off_opb;
   float* X[3];
   for (int i = 0; i < 3; ++i) X[i] = reinterpret_cast<float*>(wsb + L.off_x[i]);
+  const View whole_a{A, lda, a.m, a.k}, whole_b{B, ldb, a.k, a.n};
   auto operand_a = [&](int code) -> View {
-    if (code < 4) return View{A + ((code >> 1) * mh * lda + (code & 1) * kh) * es, lda, mh, kh};
+    if (code < 4) return block_of(whole_a, code >> 1, code & 1, mh, kh, es);
     return View{opa + size_t(code - 4) * mh * kh * es, static_cast<long long>(kh), mh, kh};
   };
   auto operand_b = [&](int code) -> View {
-    if (code < 4) return View{B + ((code >> 1) * kh * ldb + (code & 1) * nh) * es, ldb, kh, nh};
+    if (code < 4) return block_of(whole_b, code >> 1, code & 1, kh, nh, es);
     return View{opb + size_t(code - 4) * kh * nh * es, static_cast<long long>(nh), kh, nh};
   };
   const programs::Level2Child* children = programs::level2_children();
@@ -579,6 +600,8 @@ int run(const GemmArgs& a, void* workspace, size_t workspace_size, cudaStream_t 
     s.link = ch.link;
     const long long out_off = ch.out_quadrant >= 0 ? ((ch.out_quadrant >> 1) * mh * ldd + (ch.out_quadrant & 1) * nh) * es : 0;
     s.out = ch.out_quadrant >= 0 ? D + out_off : nullptr;
+    s.out_rows = (ch.out_quadrant >= 0 && (ch.out_quadrant >> 1)) ? a.m - mh : mh;
+    s.out_cols = (ch.out_quadrant >= 0 && (ch.out_quadrant & 1)) ? a.n - nh : nh;
     s.cin = (ch.out_quadrant >= 0 && Cin) ? Cin + out_off : nullptr;
     s.ldo = ldd;
     s.outer_dst = ch.dst >= 0 ? X[ch.dst] : nullptr;
@@ -597,6 +620,8 @@ int run(const GemmArgs& a, void* workspace, size_t workspace_size, cudaStream_t 
       j.dst = c == 0 ? opa : opb;
       j.rows = c == 0 ? mh : kh;
       j.cols = c == 0 ? kh : nh;
+      j.rows2 = c == 0 ? a.m - mh : a.k - kh;
+      j.cols2 = c == 0 ? a.k - kh : a.n - nh;
       j.side = c;
       s.n_more_jobs = 1;
     }
@@ -604,6 +629,8 @@ int run(const GemmArgs& a, void* workspace, size_t workspace_size, cudaStream_t 
   }
   return kOk;
 }
+
+}  // namespace tc
 
 int read_status(void* workspace, cudaStream_t stream) {
   int st = 0;

@@ -67,7 +67,22 @@ int read_status(void* workspace, cudaStream_t stream);
 // Launches of this library's kernels made by the last `run` with these args (for launch accounting).
 int launches_per_run(const GemmArgs& args);
 
-// fp64 path (dgemm_sw.cu): DMMA kernels, same four calls; `run` and friends above dispatch here for kF64.
+// The calls above accept every positive m, n, k.  Problems the kernels cannot take as they are (row pitches that are
+// not multiples of 16 bytes, fp64 extents that do not divide) run on
+// zero-padded copies of the operands held in the workspace (any_size.cu): the padded product equals the product, and
+// the result is copied back without another rounding.
+//
+// Tensor-core path for f16 and f32/tf32 (sw_host.cu): same calls on problems whose rows are 16-byte aligned; extents
+// that do not divide by the number of blocks leave the last block row / column short.
+namespace tc {
+int can_implement(const GemmArgs& args);
+size_t workspace_bytes(const GemmArgs& args);
+WorkspaceLayout workspace_layout(const GemmArgs& args);
+int run(const GemmArgs& args, void* workspace, size_t workspace_size, cudaStream_t stream);
+int launches_per_run(const GemmArgs& args);
+}  // namespace tc
+
+// fp64 path (dgemm_sw.cu): DMMA kernels, same four calls.
 //   kCubic = one launch, kFusedPresum = level 1 (2 presum + 7 product launches),
 //   kInterleavedLevel2 = level 2 (2 outer presum launches + 7 x (2 + 7))
 namespace f64 {

@@ -56,7 +56,9 @@ struct PresumSideJob {
   const void* src[4];  // quadrant base pointers, row-major with a common leading dimension
   long long ld;        // in elements
   void* dst;           // [4][rows][cols], packed
-  int rows, cols;      // extent of one quadrant
+  int rows, cols;      // extent of one quadrant (and of each result)
+  int rows2, cols2;    // rows present in quadrants 2, 3 and columns present in quadrants 1, 3 (<= rows, cols): an
+                       // operand whose extents are not twice the block extents reads as if padded with zeros
   int side;
 };
 constexpr int SB200_MAX_JOBS = 4;
@@ -68,6 +70,8 @@ struct KernelParams {
   long long ldo;      // leading dimension of the output in elements
   int out_rows;       // rows of one output quadrant
   int out_cols;       // columns of one output quadrant
+  int out_rows2;      // rows present in output quadrants 2, 3 and columns present in quadrants 1, 3 (<= out_rows,
+  int out_cols2;      //   out_cols): the rest of those blocks lies outside the output matrix and is not stored
   // output scaling: every value written to an output quadrant is alpha * sum + beta * C (cin[q] is null when beta = 0)
   float alpha, beta;
   const void* cin[4];
@@ -314,10 +318,12 @@ __device__ __forceinline__ void presum_side_job(const PresumSideJob& j, int gtid
         const int r = static_cast<int>(v / vec_per_row);
         const int c = static_cast<int>(v - static_cast<long long>(r) * vec_per_row) * EPV;
         const long long in = (r * j.ld + c) * ESIZE;
+        const bool has_r = r < j.rows2, has_c = c < j.cols2;
+        const uint4 zero = make_uint4(0, 0, 0, 0);
         x0[u] = ptx::ldg_nc_v4(s0 + in);
-        x1[u] = ptx::ldg_nc_v4(s1 + in);
-        x2[u] = ptx::ldg_nc_v4(s2 + in);
-        x3[u] = ptx::ldg_nc_v4(s3 + in);
+        x1[u] = has_c ? ptx::ldg_nc_v4(s1 + in) : zero;
+        x2[u] = has_r ? ptx::ldg_nc_v4(s2 + in) : zero;
+        x3[u] = (has_r && has_c) ? ptx::ldg_nc_v4(s3 + in) : zero;
         o[u] = (static_cast<long long>(r) * j.cols + c) * ESIZE;
       }
     }
@@ -570,7 +576,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_kernel(const 
         };
         const long long tile_off = static_cast<long long>(wu.ws_slot) * (128 * BN);
         const long long outer_off = static_cast<long long>(wu.tile) * (128 * BN);
-        ok = epilogue_body<ESIZE, BN, Cfg::NSRC_MAX, Cfg::NSLOT_MAX, Cfg::SCALED>(p.out, p.ldo, p.out_rows, p.out_cols, p.ws, ep, sx, tmem_base, quarter,
+        ok = epilogue_body<ESIZE, BN, Cfg::NSRC_MAX, Cfg::NSLOT_MAX, Cfg::SCALED>(p.out, p.ldo, (ep.dst & 2) ? p.out_rows2 : p.out_rows,
+                                                     (ep.dst & 1) ? p.out_cols2 : p.out_cols, p.ws, ep, sx, tmem_base, quarter,
                                                      lane, tile_off, static_cast<long long>(blockIdx.x) * (128 * BN), outer_off,
                                                      tile.i * 128, tile.j * BN,
                                                      staging + (warp - 2) * kStagingWarpBytes,

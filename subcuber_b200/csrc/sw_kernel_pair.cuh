@@ -370,7 +370,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
         const long long te0 = SB200_CLOCK();
         const long long ew0 = ew_full;
 #endif
-        ok = epilogue_body<ESIZE, BN, Cfg::NSRC_MAX, Cfg::NSLOT_MAX, Cfg::SCALED>(p.out, p.ldo, p.out_rows, p.out_cols, p.ws, ep, sx, tmem_base, quarter,
+        ok = epilogue_body<ESIZE, BN, Cfg::NSRC_MAX, Cfg::NSLOT_MAX, Cfg::SCALED>(p.out, p.ldo, (ep.dst & 2) ? p.out_rows2 : p.out_rows,
+                                                     (ep.dst & 1) ? p.out_cols2 : p.out_cols, p.ws, ep, sx, tmem_base, quarter,
                                                      lane, tile_off, static_cast<long long>(blockIdx.x) * (128 * BN), outer_off,
                                                      tile.i * Cfg::PAIR_M + static_cast<int>(rank) * Cfg::BM, tile.j * BN,
                                                      staging + (warp - 2) * kStagingWarpBytes,

@@ -44,8 +44,8 @@ def test_registry_rows(lib):
 
 
 def test_auto_kernel_choice(lib):
-    """Size-based choice of level and family: small problems run the plain pair kernel, large ones recurse; sizes the
-    recursion cannot split fall back to the level below."""
+    """Size-based choice of level and family: small problems run the plain pair kernel, large ones recurse, whatever
+    the extents divide by (the last block row / column may be short)."""
     import ctypes as C
 
     lib.sb200_auto_kernel.restype = C.c_char_p
@@ -55,7 +55,7 @@ def test_auto_kernel_choice(lib):
     assert pick("f16", 16384, 16384, 16384) == "blackwell_f16_sw_interleaved_presum_2sm"
     assert pick("f16", 32768, 32768, 32768) == "blackwell_f16_sw_level2_2sm"
     assert pick("f16", 32768, 32768, 4096) == "blackwell_f16_cubic_2sm_256x256"      # the smallest extent decides
-    assert pick("f16", 32770, 32768, 32768) == "blackwell_f16_sw_interleaved_presum_2sm"  # not divisible by 4
+    assert pick("f16", 32770, 32768, 32768) == "blackwell_f16_sw_level2_2sm"  # need not divide by 4
     assert pick("f32", 16384, 8192, 32768) == "blackwell_f32_cubic_2sm_256x256"
     assert pick("f32", 16384, 16384, 16384) == "blackwell_f32_sw_level2_2sm"
     assert pick("f64", 8192, 8192, 8192) == "blackwell_f64_sw_level1"
@@ -78,11 +78,16 @@ def test_alias_tables():
 @pytest.mark.parametrize("kernel,m,n,k,rc", [
     ("blackwell_f16_cubic_128x256", 128, 256, 64, 0),
     ("blackwell_f16_cubic_128x256", 100, 264, 72, 0),       # ragged sizes are fine (TMA zero fill, masked stores)
-    ("blackwell_f16_cubic_128x256", 128, 260, 64, 1),       # a row of B would not start on 16 bytes
+    ("blackwell_f16_cubic_128x256", 128, 260, 64, 0),       # rows off the 16-byte grid: runs on padded copies
     ("blackwell_f16_cubic_128x256", 0, 256, 64, 4),
     ("blackwell_f16_sw_interleaved_presum", 256, 512, 128, 0),
-    ("blackwell_f16_sw_interleaved_presum", 255, 512, 128, 4),  # odd size cannot be split in quadrants
-    ("blackwell_f16_sw_interleaved_presum", 256, 520, 128, 1),  # quadrant rows would be misaligned
+    ("blackwell_f16_sw_interleaved_presum", 255, 512, 128, 0),  # short last block row
+    ("blackwell_f16_sw_interleaved_presum", 256, 520, 128, 0),  # blocks are cut on the 16-byte grid: 264 + 256 columns
+    ("blackwell_f16_sw_interleaved_presum", 255, 517, 129, 0),  # padded copies, then short blocks
+    ("blackwell_f16_sw_interleaved_presum", 1, 512, 128, 4),    # a block row would be empty
+    ("blackwell_f16_sw_level2", 1000, 520, 136, 0),
+    ("blackwell_f16_sw_level2", 1000, 520, 24, 4),              # 24 columns cannot be cut in four 16-byte aligned blocks
+    ("blackwell_f64_sw_level1", 1001, 515, 129, 0),
     ("blackwell_f32_sw_fused_presum", 64, 72, 40, 0),
     ("no_such_kernel", 128, 128, 128, 8),
 ])

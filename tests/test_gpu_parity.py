@@ -121,6 +121,99 @@ def test_alpha_beta_bit_exact_on_harness_values(kernel, alpha, beta, oracle, cud
         assert np.array_equal(d2.cpu().numpy(), want)
 
 
+# ----------------------------------------------------------------- extents that do not divide into blocks
+def _padded_oracle(oracle, dt, level, a, b, alpha=1.0, beta=0.0, cin=None):
+    """The oracle on the zero-padded problem the kernels compute: rows are padded to 16 bytes (fp64: extents to a
+    multiple of the block count, 16-byte aligned block rows), then the matrices are cut at multiples of the block
+    extents (m: ceil(m / blocks); n, k: the same rounded up to 16 bytes) and the short last blocks read as zeros."""
+    m, k = a.shape
+    n = b.shape[1]
+    div = 1 << level
+    vec = 16 // a.dtype.itemsize
+    up = lambda x, g: -(-x // g) * g
+    if dt == "f64":
+        mp, np_, kp = up(m, div), up(n, div * vec), up(k, div * vec)
+    else:
+        mp, np_, kp = div * (-(-m // div)), div * up(-(-up(n, vec) // div), vec), div * up(-(-up(k, vec) // div), vec)
+    ap = np.zeros((mp, kp), dtype=a.dtype); ap[:m, :k] = a
+    bp = np.zeros((kp, np_), dtype=b.dtype); bp[:k, :n] = b
+    cp = None
+    if cin is not None:
+        cp = np.zeros((mp, np_), dtype=cin.dtype); cp[:m, :n] = cin
+    return oracle.sw_gemm(dt, level, ap, bp, alpha=alpha, beta=beta, Cin=cp)[:m, :n]
+
+
+RAGGED_KERNELS = ["blackwell_f16_sw_interleaved_presum", "blackwell_f16_sw_interleaved_presum_2sm",
+                  "blackwell_f16_sw_fused_presum_2sm", "blackwell_f32_sw_interleaved_presum_2sm",
+                  "blackwell_f32_sw_fused_presum", "blackwell_f16_sw_level2", "blackwell_f16_sw_level2_2sm",
+                  "blackwell_f32_sw_level2_2sm", "blackwell_f16_cubic_2sm_256x256", "blackwell_f64_cubic_dmma",
+                  "blackwell_f64_sw_level1", "blackwell_f64_sw_level2"]
+# rows on the 16-byte grid (short last blocks only), and rows off it (zero-padded copies, then short blocks)
+RAGGED_SHAPES = [(255, 520, 136), (1001, 776, 264), (131, 264, 200), (257, 517, 129), (1023, 1030, 515)]
+
+
+@pytest.mark.parametrize("kernel", RAGGED_KERNELS)
+@pytest.mark.parametrize("shape", RAGGED_SHAPES)
+def test_any_extents_bit_exact_on_harness_values(kernel, shape, oracle, cuda_device):
+    """Extents that do not divide into 2 (4) blocks per dimension, and rows that do not start on 16 bytes: the
+    kernels compute the zero-padded problem, whose product is the product.  Exact on the harness' value set."""
+    from subcuber_b200 import inputs
+
+    m, n, k = shape
+    dt = _dt(kernel)
+    a, b = inputs.operands(dt, "harness", m, n, k, seed=m + n + k)
+    got = _run(kernel, a, b, cuda_device)
+    assert not np.isnan(got).any()
+    want = _padded_oracle(oracle, dt, _level(kernel), a, b)
+    assert np.array_equal(got, want), f"{np.count_nonzero(got != want)} elements differ from the oracle"
+    assert np.array_equal(got, oracle.sw_gemm(dt, 0, a, b))  # and equals the plain product of the unpadded operands
+
+
+@pytest.mark.parametrize("kernel", ["blackwell_f16_sw_interleaved_presum_2sm", "blackwell_f16_sw_level2_2sm",
+                                    "blackwell_f32_sw_interleaved_presum", "blackwell_f64_sw_level1"])
+@pytest.mark.parametrize("shape", [(1001, 776, 264), (517, 1030, 259)])
+def test_any_extents_alpha_beta(kernel, shape, oracle, cuda_device):
+    import torch
+
+    from subcuber_b200 import inputs, runner
+
+    m, n, k = shape
+    dt = _dt(kernel)
+    a_np, b_np = inputs.operands(dt, "harness", m, n, k, seed=21)
+    c_np = np.ascontiguousarray(inputs.operands(dt, "harness", m, n + 8, n + 8, seed=22)[0][:, :n])
+    a, b, c = (torch.from_numpy(x).to(cuda_device) for x in (a_np, b_np, c_np))
+    d = runner.gemm(kernel, a, b, alpha=2.0, beta=-0.5, c=c)
+    torch.cuda.synchronize()
+    want = _padded_oracle(oracle, dt, _level(kernel), a_np, b_np, alpha=2.0, beta=-0.5, cin=c_np)
+    assert np.array_equal(d.cpu().numpy(), want)
+
+
+@pytest.mark.parametrize("kernel", ["blackwell_f16_sw_interleaved_presum_2sm", "blackwell_f16_sw_level2_2sm",
+                                    "blackwell_f16_sw_interleaved_presum"])
+@pytest.mark.parametrize("shape", [(1537, 1288, 1032), (1025, 2051, 1283)])
+def test_any_extents_uniform_inputs_f16(kernel, shape, oracle, cuda_device):
+    """Inexact inputs: the error gate against the reference routine on the padded problem."""
+    from subcuber_b200 import inputs
+
+    m, n, k = shape
+    a, b = inputs.operands("f16", "uniform1", m, n, k, seed=9)
+    got = _run(kernel, a, b, cuda_device)
+    truth = a.astype(np.float64) @ b.astype(np.float64)
+    ref = _padded_oracle(oracle, "f16", _level(kernel), a, b)
+    assert _rel_fro(got, truth) <= 1.5 * _rel_fro(ref, truth)
+
+
+def test_any_extents_split_last_wave(oracle, cuda_device, monkeypatch):
+    from subcuber_b200 import inputs
+
+    kernel = "blackwell_f16_sw_interleaved_presum_2sm"
+    m, n, k = 1001, 2568, 1160
+    a, b = inputs.operands("f16", "harness", m, n, k, seed=4)
+    monkeypatch.setenv("SB200_SM_LIMIT", "16")
+    got = _run(kernel, a, b, cuda_device)
+    assert np.array_equal(got, oracle.sw_gemm("f16", 0, a, b))
+
+
 def test_scaled_form_is_refused_where_it_is_not_built(cuda_device):
     import torch
 
@@ -462,7 +555,7 @@ def test_run_entry_point_error_codes(cuda_device):
 
     from subcuber_b200 import runner
 
-    a = torch.zeros((255, 128), dtype=torch.float16, device=cuda_device)
+    a = torch.zeros((1, 128), dtype=torch.float16, device=cuda_device)   # one row cannot be cut in two block rows
     b = torch.zeros((128, 256), dtype=torch.float16, device=cuda_device)
     with pytest.raises(runner.KernelError) as e:
         runner.run_kernel("blackwell_f16_sw_interleaved_presum", a, b)
@@ -471,10 +564,8 @@ def test_run_entry_point_error_codes(cuda_device):
     with pytest.raises(runner.KernelError) as e:
         runner.run_kernel("blackwell_f16_sw_interleaved_presum", a, b, split_k=2)
     assert e.value.code == 5
-    b = torch.zeros((128, 264), dtype=torch.float16, device=cuda_device)  # quadrant rows start at 8 mod 16 bytes
-    with pytest.raises(runner.KernelError) as e:
-        runner.run_kernel("blackwell_f16_sw_interleaved_presum", a, b)
-    assert e.value.code == 1
+    b = torch.zeros((128, 261), dtype=torch.float16, device=cuda_device)  # rows off the 16-byte grid run on copies
+    assert runner.run_kernel("blackwell_f16_sw_interleaved_presum", a, b)[1] > 0
 
 
 def test_workspace_checks(lib, cuda_device):

@@ -63,5 +63,5 @@ def test_static_scratch_rejects_what_does_not_fit(lib, cuda_device):
     torch.cuda.synchronize()
     assert float(d.min()) == 7.0 and float(d.max()) == 7.0  # nothing ran
     with torch.cuda.device(cuda_device):
-        rc = lib.sb200_gemm_f16_sw_static_scratch(a.data_ptr(), b.data_ptr(), d.data_ptr(), 1023, 1024, 1024, None, 1)
-    assert rc == 4  # the ordinary argument checks still apply
+        rc = lib.sb200_gemm_f16_sw_static_scratch(a.data_ptr(), b.data_ptr(), d.data_ptr(), 1, 1024, 1024, None, 1)
+    assert rc == 4  # the ordinary argument checks still apply (one row cannot be cut in two block rows)
