@@ -86,6 +86,13 @@ SB200_DECLARE_RUN(run_blackwell_f16_sw_level2);
 SB200_DECLARE_RUN(run_blackwell_f32_sw_level2);
 SB200_DECLARE_RUN(run_blackwell_f16_sw_level2_2sm);
 SB200_DECLARE_RUN(run_blackwell_f32_sw_level2_2sm);
+/* Level 1 of Strassen's original algorithm (7 products, 18 additions; no operand sums more than two blocks), one launch,
+ * operand sums formed in shared memory.  The reference names other Strassen-like algorithms as future work
+ * (README.md:179) and leaves StrassenType::Strassen stubbed (include/cutlass/gemm/kernel/strassen_gemm.h:1360-1398). */
+SB200_DECLARE_RUN(run_blackwell_f16_strassen_fused_presum);
+SB200_DECLARE_RUN(run_blackwell_f32_strassen_fused_presum);
+SB200_DECLARE_RUN(run_blackwell_f16_strassen_fused_presum_2sm);
+SB200_DECLARE_RUN(run_blackwell_f32_strassen_fused_presum_2sm);
 /* fp64 on the double-precision tensor-core instruction (mma.sync.m16n8k16.f64): plain GEMM, level 1 (2 standalone
  * presum launches + 7 product launches whose epilogue adds the postsums) and level 2 (2 + 7 x 9 launches).  Stand where the reference has its f64 DMMA kernels
  * (src/cuda/kernels/ampere_f64_*.cu via kernel_runner.cpp:99-180). */

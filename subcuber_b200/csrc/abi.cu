@@ -44,6 +44,10 @@ const KernelDesc kDescs[] = {
     {"blackwell_f32_sw_level2", "f32", 2, sb200::kF32, sb200::kInterleavedLevel2, 256, 0},
     {"blackwell_f16_sw_level2_2sm", "f16", 2, sb200::kF16, sb200::kInterleavedLevel2, 256, 1},
     {"blackwell_f32_sw_level2_2sm", "f32", 2, sb200::kF32, sb200::kInterleavedLevel2, 256, 1},
+    {"blackwell_f16_strassen_fused_presum", "f16", 1, sb200::kF16, sb200::kStrassenFused, 256, 0},
+    {"blackwell_f32_strassen_fused_presum", "f32", 1, sb200::kF32, sb200::kStrassenFused, 256, 0},
+    {"blackwell_f16_strassen_fused_presum_2sm", "f16", 1, sb200::kF16, sb200::kStrassenFused, 256, 1},
+    {"blackwell_f32_strassen_fused_presum_2sm", "f32", 1, sb200::kF32, sb200::kStrassenFused, 256, 1},
     {"blackwell_f64_cubic_dmma", "f64", 0, sb200::kF64, sb200::kCubic, 0, 0},
     {"blackwell_f64_sw_level1", "f64", 1, sb200::kF64, sb200::kFusedPresum, 0, 0},
     {"blackwell_f64_sw_level2", "f64", 2, sb200::kF64, sb200::kInterleavedLevel2, 0, 0},
@@ -315,6 +319,10 @@ SB200_DEFINE_RUN(blackwell_f16_sw_level2)
 SB200_DEFINE_RUN(blackwell_f32_sw_level2)
 SB200_DEFINE_RUN(blackwell_f16_sw_level2_2sm)
 SB200_DEFINE_RUN(blackwell_f32_sw_level2_2sm)
+SB200_DEFINE_RUN(blackwell_f16_strassen_fused_presum)
+SB200_DEFINE_RUN(blackwell_f32_strassen_fused_presum)
+SB200_DEFINE_RUN(blackwell_f16_strassen_fused_presum_2sm)
+SB200_DEFINE_RUN(blackwell_f32_strassen_fused_presum_2sm)
 SB200_DEFINE_RUN(blackwell_f64_cubic_dmma)
 SB200_DEFINE_RUN(blackwell_f64_sw_level1)
 SB200_DEFINE_RUN(blackwell_f64_sw_level2)
@@ -361,6 +369,10 @@ static const sb200_kernel_entry kRegistry[] = {
     {"blackwell_f32_sw_level2", "blackwell", "f32", 2, run_blackwell_f32_sw_level2},
     {"blackwell_f16_sw_level2_2sm", "blackwell", "f16", 2, run_blackwell_f16_sw_level2_2sm},
     {"blackwell_f32_sw_level2_2sm", "blackwell", "f32", 2, run_blackwell_f32_sw_level2_2sm},
+    {"blackwell_f16_strassen_fused_presum", "blackwell", "f16", 1, run_blackwell_f16_strassen_fused_presum},
+    {"blackwell_f32_strassen_fused_presum", "blackwell", "f32", 1, run_blackwell_f32_strassen_fused_presum},
+    {"blackwell_f16_strassen_fused_presum_2sm", "blackwell", "f16", 1, run_blackwell_f16_strassen_fused_presum_2sm},
+    {"blackwell_f32_strassen_fused_presum_2sm", "blackwell", "f32", 1, run_blackwell_f32_strassen_fused_presum_2sm},
     {"blackwell_f64_cubic_dmma", "blackwell", "f64", 0, run_blackwell_f64_cubic_dmma},
     {"blackwell_f64_sw_level1", "blackwell", "f64", 1, run_blackwell_f64_sw_level1},
     {"blackwell_f64_sw_level2", "blackwell", "f64", 2, run_blackwell_f64_sw_level2},
@@ -530,6 +542,7 @@ extern "C" int sb200_tile_program(const char* which, void* out, size_t out_bytes
   if (strcmp(which, "level0") == 0) pg = sb200::programs::level0();
   else if (strcmp(which, "level1_full_fly") == 0) pg = sb200::programs::level1_full(true);
   else if (strcmp(which, "level1_full_ws") == 0) pg = sb200::programs::level1_full(false);
+  else if (strcmp(which, "level1_strassen") == 0) pg = sb200::programs::level1_strassen();
   else if (strcmp(which, "level1_first") == 0) pg = sb200::programs::level1_first();
   else if (strcmp(which, "level1_first_early") == 0) pg = sb200::programs::level1_first_early();
   else if (strcmp(which, "level1_second") == 0) pg = sb200::programs::level1_second();

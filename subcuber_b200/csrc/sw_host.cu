@@ -87,7 +87,7 @@ int sm_count();
 // Tiles of the last wave to split: all of them when the wave is at most half full (then it lasts half as long),
 // none otherwise.  The fused-presum kernels are never split.
 int tiles_to_split(int tiles, int workers, int num_k, Variant v) {
-  if (v == kFusedPresum || workers <= 0 || num_k < 8 || getenv("SB200_NO_SPLIT")) return 0;
+  if (v == kFusedPresum || v == kStrassenFused || workers <= 0 || num_k < 8 || getenv("SB200_NO_SPLIT")) return 0;
   const int rem = tiles % workers;
   return (rem > 0 && 2 * rem <= workers) ? rem : 0;
 }
@@ -131,7 +131,7 @@ Layout make_layout(const GemmArgs& a) {
   if (cap < 1) cap = 1;
   L.workers = L.tiles_m * L.tiles_n < cap ? L.tiles_m * L.tiles_n : cap;
   L.split_tiles = tiles_to_split(L.tiles_m * L.tiles_n, L.workers, L.num_k, a.variant);
-  const int nws = a.variant == kCubic ? 0 : (a.variant == kFusedPresum ? 2 : 4);
+  const int nws = a.variant == kCubic ? 0 : (a.variant == kFusedPresum ? 2 : (a.variant == kStrassenFused ? 3 : 4));
   const size_t tile_bytes = size_t(128) * L.bn * sizeof(float) * (a.pair ? 2 : 1);  // per tile of the grid
   const size_t quadrant_bytes = size_t(L.tiles_m) * L.tiles_n * tile_bytes;
   L.quadrant_floats = quadrant_bytes / sizeof(float);
@@ -485,6 +485,10 @@ int launch_group(const LaunchSpec& s, cudaStream_t stream, MarkFn mark) {
       break;
     case kFusedPresum:
       p.prog = programs::level1_full(true);
+      rc = launch_any(es, bn_sel, kPresumFeed, p, s.grid, stream);
+      break;
+    case kStrassenFused:
+      p.prog = programs::level1_strassen();
       rc = launch_any(es, bn_sel, kPresumFeed, p, s.grid, stream);
       break;
     case kInterleavedPresum: {

@@ -15,6 +15,7 @@ enum Variant {
   kFusedPresum = 1,       // level 1, one launch, presums formed in shared memory by the presum warps
   kInterleavedPresum = 2, // level 1, two launches, presums materialised by the first launch's presum warps
   kInterleavedLevel2 = 3, // level 2, seven level-1 interleaved groups (14 launches) chained through fp32 buffers
+  kStrassenFused = 4,     // level 1 of Strassen's original algorithm, one launch, operand sums formed in shared memory
 };
 
 // Error codes returned across the C ABI.  Small values keep the meaning of the reference's

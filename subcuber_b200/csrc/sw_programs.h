@@ -119,6 +119,37 @@ inline sb200_program_t level1_full(bool fly) {
   return pg;
 }
 
+// Strassen's original algorithm (the second <2,2,2;7> algorithm of this library; the reference names other
+// Strassen-like algorithms as future work, README.md:179, and leaves StrassenType::Strassen stubbed,
+// include/cutlass/gemm/kernel/strassen_gemm.h:1360-1398):
+//   M1=(A0+A3)(B0+B3)  M2=(A2+A3)B0  M3=A0(B1-B3)  M4=A3(B2-B0)  M5=(A0+A1)B3  M6=(A2-A0)(B0+B1)  M7=(A1-A3)(B2+B3)
+//   C0=M1+M4-M5+M7     C1=M3+M5      C2=M2+M4      C3=M1-M2+M3+M6
+// All seven products of a tile in one CTA, operand sums formed on the fly (no operand has more than two terms).
+// Slot P accumulates M1+M7, then M3+M6; slot Q accumulates M4-M5, then holds M2; M1 and M4 are tapped into per-CTA
+// fp32 tiles before their slots go on accumulating.
+enum { WS_T1 = 1, WS_T4 = 2 };
+inline sb200_operand_t pair_of(int v0, int v1, int c1) { int v[] = {v0, v1}; int c[] = {1, c1}; return terms(2, v, c); }
+inline sb200_program_t level1_strassen() {
+  sb200_program_t pg;
+  memset(&pg, 0, sizeof(pg));
+  const int sP[] = {P}, sQ[] = {Q}, sPQ[] = {P, Q}, pos1[] = {1}, pos2[] = {1, 1}, posneg[] = {1, -1};
+  const int srcT1[] = {WS_T1}, srcT4[] = {WS_T4};
+  add_product(pg, pair_of(A0, A3, 1), pair_of(B0, B3, 1), P, 0, 0, 1, 1);    // P  = M1
+  add_epilogue(pg, 1, sP, pos1, 0, nullptr, mP, mP, 1, WS_T1);                // ws[T1] = M1
+  add_product(pg, term1(A3), pair_of(B2, B0, -1), Q, 0, 0, 1, 1);             // Q  = M4
+  add_epilogue(pg, 1, sQ, pos1, 0, nullptr, mQ, mQ, 1, WS_T4);                // ws[T4] = M4
+  add_product(pg, pair_of(A1, A3, -1), pair_of(B2, B3, 1), P, 1, 0, 1, 1);    // P += M7
+  add_product(pg, pair_of(A0, A1, 1), term1(B3), Q, 1, 1, 1, 1);              // Q -= M5
+  add_epilogue(pg, 2, sPQ, pos2, 0, nullptr, mP | mQ, mP, 0, 0);              // C0 = (M1+M7) + (M4-M5)
+  add_product(pg, term1(A0), pair_of(B1, B3, -1), P, 0, 0, 1, 1);             // P  = M3
+  add_epilogue(pg, 2, sPQ, posneg, 1, srcT4, mP, mP | mQ, 0, 1);              // C1 = M3 - (M4-M5) + M4
+  add_product(pg, pair_of(A2, A0, -1), pair_of(B0, B1, 1), P, 1, 0, 1, 1);    // P += M6
+  add_product(pg, pair_of(A2, A3, 1), term1(B0), Q, 0, 0, 1, 1);              // Q  = M2
+  add_epilogue(pg, 1, sQ, pos1, 1, srcT4, mQ, 0, 0, 2);                       // C2 = M2 + M4
+  add_epilogue(pg, 2, sPQ, posneg, 1, srcT1, mP, mP | mQ, 0, 3);              // C3 = (M3+M6) - M2 + M1
+  return pg;
+}
+
 // Level 1 with interleaved presum, launch 1 of 2: the two products that need no presum; M0 is also handed
 // to launch 2 through the fp32 workspace.  The presum warps of this launch materialise the eight presums.
 inline sb200_program_t level1_first() {

@@ -23,6 +23,7 @@ QUADRANT_VIEW = {"a0": 0, "a1": 1, "a2": 2, "a3": 3, "b0": 8, "b1": 9, "b2": 10,
 PRESUM_VIEW = {"s1": 4, "s2": 5, "a02": 6, "a1s2": 7, "b10": 12, "b31": 13, "s3": 14, "s3b2": 15}
 P, Q = 0, 1
 WS_M0, WS_M4, WS_U, WS_V = 0, 1, 2, 2  # u is dead once c1 is formed, before v is written: one buffer
+WS_T1, WS_T4 = 1, 2                     # Strassen's original algorithm: taps of m1 and m4 (per-CTA scratch tiles)
 
 
 # ------------------------------------------------------------------------------------------- algebra from the DSL
@@ -176,6 +177,26 @@ def level1_second_taps_program(ms) -> tp.Program:
     b.product("m6", Q)
     b.epilogue([], [WS_V, WS_M4], wait=[], release=[], dst_kind=0, dst=3)            # c3 = v + m4
     b.epilogue([Q], [WS_V], wait=[Q], release=[Q], dst_kind=0, dst=2, signs=[-1])    # c2 = v - m6
+    return b.pg
+
+
+def level1_strassen_program(ms) -> tp.Program:
+    """Strassen's original algorithm (algos/strassen_level1.py), all seven products of a tile in one CTA, operand sums
+    formed on the fly.  Slot P accumulates m1 + m7, then m3 + m6; slot Q accumulates m4 - m5, then holds m2; m1 and
+    m4 are tapped into fp32 tiles before their slots go on accumulating:
+        c0 = P + Q          c1 = m3 - (m4 - m5) + m4          c2 = m2 + m4          c3 = (m3 + m6) - m2 + m1"""
+    b = ProgramBuilder(_products_by_name(ms), fly=True)
+    b.product("m1", P)
+    b.epilogue([P], [], wait=[P], release=[P], dst_kind=1, dst=WS_T1)                # tap: m1
+    b.product("m4", Q)
+    b.epilogue([Q], [], wait=[Q], release=[Q], dst_kind=1, dst=WS_T4)                # tap: m4
+    b.product("m7", P, accumulate=1).product("m5", Q, accumulate=1, negate=1)
+    b.epilogue([P, Q], [], wait=[P, Q], release=[P], dst_kind=0, dst=0)              # c0 = (m1 + m7) + (m4 - m5)
+    b.product("m3", P)
+    b.epilogue([P, Q], [WS_T4], wait=[P], release=[P, Q], dst_kind=0, dst=1, signs=[1, -1])  # c1 = m3 + m5
+    b.product("m6", P, accumulate=1).product("m2", Q)
+    b.epilogue([Q], [WS_T4], wait=[Q], release=[], dst_kind=0, dst=2)                # c2 = m2 + m4
+    b.epilogue([P, Q], [WS_T1], wait=[P], release=[P, Q], dst_kind=0, dst=3, signs=[1, -1])  # c3
     return b.pg
 
 
@@ -341,9 +362,12 @@ def all_programs() -> Dict[str, tp.Program]:
     """The named tables, generated from the DSL (names as in `sb200_tile_program`)."""
     from .algos.strassen_winograd_level1 import strassen_winograd
 
+    from .algos.strassen_level1 import strassen
+
     _, ms = strassen_winograd(4, 4, 4)
     return {
         "level0": level0_program(),
+        "level1_strassen": level1_strassen_program(strassen(4, 4, 4)[1]),
         "level1_full_fly": level1_full_program(ms, fly=True),
         "level1_full_ws": level1_full_program(ms, fly=False),
         "level1_first": level1_first_program(ms),
@@ -367,6 +391,12 @@ def verify_programs(programs: Dict[str, tp.Program]) -> None:
         got = tp.check_program(programs[name], level=1)["outputs"]
         for q in range(4):
             assert np.array_equal(got[q], want[q]), (name, q)
+    # Strassen's original algorithm: its own postsum expressions must give the same four blocks
+    from .algos.strassen_level1 import strassen
+
+    got = tp.check_program(programs["level1_strassen"], level=1)["outputs"]
+    for q, part in enumerate(strassen(4, 4, 4)[0].parts):
+        assert np.array_equal(bilinear_form(part), want[q]) and np.array_equal(got[q], want[q]), ("level1_strassen", q)
     for name in ("level1_first_early", "level1_first"):
         r1 = tp.check_program(programs[name], level=1, expect=[0])
         assert np.array_equal(r1["outputs"][0], want[0]), name

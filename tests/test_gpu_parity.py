@@ -20,6 +20,9 @@ L1_F32 = ["blackwell_f32_sw_interleaved_presum", "blackwell_f32_sw_fused_presum"
           "blackwell_f32_sw_interleaved_presum_2sm", "blackwell_f32_sw_fused_presum_2sm"]
 L2_F16 = ["blackwell_f16_sw_level2", "blackwell_f16_sw_level2_2sm"]
 L2_F32 = ["blackwell_f32_sw_level2", "blackwell_f32_sw_level2_2sm"]
+# Strassen's original algorithm: the same products of blocks summed another way, checked against the same oracle
+STRASSEN_F16 = ["blackwell_f16_strassen_fused_presum", "blackwell_f16_strassen_fused_presum_2sm"]
+STRASSEN_F32 = ["blackwell_f32_strassen_fused_presum", "blackwell_f32_strassen_fused_presum_2sm"]
 L0_F16 = ["blackwell_f16_cubic_128x256", "blackwell_f16_cubic_128x128", "blackwell_f16_cubic_2sm_256x256"]
 L0_F32 = ["blackwell_f32_cubic_128x256", "blackwell_f32_cubic_128x128", "blackwell_f32_cubic_2sm_256x256"]
 
@@ -53,7 +56,7 @@ def _rel_fro(x, truth):
 SMALL_SHAPES = [(256, 512, 128), (384, 768, 320), (272, 528, 144), (2, 16, 16), (130, 48, 80), (1024, 1024, 1024)]
 
 
-@pytest.mark.parametrize("kernel", L0_F16 + L0_F32 + L1_F16 + L1_F32)
+@pytest.mark.parametrize("kernel", L0_F16 + L0_F32 + L1_F16 + L1_F32 + STRASSEN_F16 + STRASSEN_F32)
 @pytest.mark.parametrize("shape", SMALL_SHAPES)
 def test_bit_exact_on_harness_values(kernel, shape, oracle, cuda_device):
     from subcuber_b200 import inputs
@@ -147,7 +150,8 @@ RAGGED_KERNELS = ["blackwell_f16_sw_interleaved_presum", "blackwell_f16_sw_inter
                   "blackwell_f16_sw_fused_presum_2sm", "blackwell_f32_sw_interleaved_presum_2sm",
                   "blackwell_f32_sw_fused_presum", "blackwell_f16_sw_level2", "blackwell_f16_sw_level2_2sm",
                   "blackwell_f32_sw_level2_2sm", "blackwell_f16_cubic_2sm_256x256", "blackwell_f64_cubic_dmma",
-                  "blackwell_f64_sw_level1", "blackwell_f64_sw_level2"]
+                  "blackwell_f64_sw_level1", "blackwell_f64_sw_level2", "blackwell_f16_strassen_fused_presum_2sm",
+                  "blackwell_f32_strassen_fused_presum"]
 # rows on the 16-byte grid (short last blocks only), and rows off it (zero-padded copies, then short blocks)
 RAGGED_SHAPES = [(255, 520, 136), (1001, 776, 264), (131, 264, 200), (257, 517, 129), (1023, 1030, 515)]
 
@@ -459,7 +463,7 @@ def _harness_tol(dt, level):
     return 1e-4, 1e-4
 
 
-@pytest.mark.parametrize("kernel", L1_F16 + L0_F16)
+@pytest.mark.parametrize("kernel", L1_F16 + L0_F16 + STRASSEN_F16)
 @pytest.mark.parametrize("shape", [(512, 512, 512), (1024, 1024, 1024), (1536, 640, 1152)])
 def test_uniform_inputs_f16(kernel, shape, oracle, cuda_device):
     from subcuber_b200 import inputs
@@ -480,7 +484,7 @@ def test_uniform_inputs_f16(kernel, shape, oracle, cuda_device):
         assert np.allclose(got.astype(np.float64), truth, rtol=1e-2, atol=2e-2)
 
 
-@pytest.mark.parametrize("kernel", L1_F32 + L0_F32)
+@pytest.mark.parametrize("kernel", L1_F32 + L0_F32 + STRASSEN_F32)
 @pytest.mark.parametrize("dist", ["uniform1", "normal"])
 def test_uniform_inputs_tf32(kernel, dist, oracle, cuda_device):
     """fp32 storage with TF32 tensor-core math: the reference has no TF32 oracle; the CPU model rounds every
