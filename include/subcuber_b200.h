@@ -86,6 +86,17 @@ SB200_DECLARE_RUN(run_blackwell_f16_sw_level2);
 SB200_DECLARE_RUN(run_blackwell_f32_sw_level2);
 SB200_DECLARE_RUN(run_blackwell_f16_sw_level2_2sm);
 SB200_DECLARE_RUN(run_blackwell_f32_sw_level2_2sm);
+/* bfloat16 storage, fp32 accumulate: the f16 kernels with the other 16-bit format (same tiles, programs and plans; the
+ * reference has no bfloat16 kernels and lists the type as future work, README.md:179). */
+SB200_DECLARE_RUN(run_cublas_bf16);
+SB200_DECLARE_RUN(run_blackwell_bf16_cubic_128x256);
+SB200_DECLARE_RUN(run_blackwell_bf16_cubic_2sm_256x256);
+SB200_DECLARE_RUN(run_blackwell_bf16_sw_fused_presum_2sm);
+SB200_DECLARE_RUN(run_blackwell_bf16_sw_interleaved_presum);
+SB200_DECLARE_RUN(run_blackwell_bf16_sw_interleaved_presum_2sm);
+SB200_DECLARE_RUN(run_blackwell_bf16_sw_level2);
+SB200_DECLARE_RUN(run_blackwell_bf16_sw_level2_2sm);
+SB200_DECLARE_RUN(run_blackwell_bf16_sw_auto);
 /* Level 1 of Strassen's original algorithm (7 products, 18 additions; no operand sums more than two blocks), one launch,
  * operand sums formed in shared memory.  The reference names other Strassen-like algorithms as future work
  * (README.md:179) and leaves StrassenType::Strassen stubbed (include/cutlass/gemm/kernel/strassen_gemm.h:1360-1398). */
@@ -104,7 +115,7 @@ SB200_DECLARE_RUN(run_blackwell_f64_sw_level2);
 SB200_DECLARE_RUN(run_blackwell_f16_sw_auto);
 SB200_DECLARE_RUN(run_blackwell_f32_sw_auto);
 SB200_DECLARE_RUN(run_blackwell_f64_sw_auto);
-/* Name of the kernel "blackwell_<dtype>_sw_auto" resolves to for this problem (dtype: "f16" | "f32" | "f64"). */
+/* Name of the kernel "blackwell_<dtype>_sw_auto" resolves to for this problem (dtype: "f16" | "bf16" | "f32" | "f64"). */
 const char* sb200_auto_kernel(const char* dtype, int m, int n, int k);
 /* cuBLAS baselines behind the same ABI (reference: src/cuda/cublas_runner.cpp:151-175); the tf32 row is
  * an addition: the reference's f32 row is CUBLAS_COMPUTE_32F_PEDANTIC (cublas_runner.cpp:14). */
@@ -122,7 +133,7 @@ typedef SB200_DECLARE_RUN((*sb200_run_fn));
 typedef struct sb200_kernel_entry {
   const char* name;
   const char* arch;  /* "blackwell" */
-  const char* dtype; /* "f16" | "f32" | "f64" */
+  const char* dtype; /* "f16" | "bf16" | "f32" | "f64" */
   int strassen_level;
   sb200_run_fn run;
 } sb200_kernel_entry;
@@ -217,7 +228,7 @@ int sb200_tile_program(const char* which, void* out, size_t out_bytes);
 size_t sb200_tile_program_bytes(void);
 
 /* Seeded synthetic inputs, bit-identical on host and device for dist 0 and 2 (dist 1 uses libm / device
- * math and agrees to rounding).  dtype: 0 f16, 1 f32, 2 f64.  dist: 0 uniform[-1,1), 1 normal(0,1),
+ * math and agrees to rounding).  dtype: 0 f16, 1 f32, 2 f64, 3 bf16.  dist: 0 uniform[-1,1), 1 normal(0,1),
  * 2 the reference harness' value set (multiples of 0.25 in [-4,4] for f16, [-16,16] otherwise;
  * tests/base_test.cuh:248-262 in the reference).  Element i takes Philox4x32-10(key = seed,
  * counter = (i, subsequence)); by convention A uses subsequence 0 and B subsequence 1. */

@@ -11,11 +11,13 @@ import ctypes as C
 import os
 import subprocess
 
+import ml_dtypes  # numpy's bfloat16
 import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-DTYPE_CODE = {"f16": 0, "f32": 1, "f64": 2, "tf32": 3}
-NP_DTYPE = {"f16": np.float16, "f32": np.float32, "f64": np.float64, "tf32": np.float32}
+
+DTYPE_CODE = {"f16": 0, "f32": 1, "f64": 2, "tf32": 3, "bf16": 4}
+NP_DTYPE = {"f16": np.float16, "f32": np.float32, "f64": np.float64, "tf32": np.float32, "bf16": ml_dtypes.bfloat16}
 
 
 def build(ref: bool = True) -> None:

@@ -5,6 +5,7 @@
 #pragma once
 
 typedef _Float16 ref_half;
+typedef __bf16 ref_bf16;
 
 // rows [ref_row_begin, ref_row_end) of the thread grid are replayed (whole grid by default); a bounded row
 // range is what the benchmark's CPU-reference arm times, since every output element is an independent thread.
@@ -44,7 +45,8 @@ static void ref_run(int level, int M, int N, int K, double alpha, const void *A,
 }
 
 // dtype: 0 = <half,half,half,float,float> (the harness instantiation, tests/base_test.cuh:290),
-//        1 = all float, 2 = all double.
+//        1 = all float, 2 = all double, 4 = <bfloat16,bfloat16,bfloat16,float,float> (the same templates with the
+//        storage type exchanged; code 3 is the oracle's TF32 model, which the reference does not have).
 extern "C" int ref_sw_gemm(int dtype, int level, int M, int N, int K, double alpha, const void *A, int lda,
                            const void *B, int ldb, double beta, void *C, int ldc) {
   if (M <= 0 || N <= 0 || K <= 0 || !A || !B || !C) return 1;
@@ -52,6 +54,7 @@ extern "C" int ref_sw_gemm(int dtype, int level, int M, int N, int K, double alp
     case 0: ref_run<ref_half, ref_half, float>(level, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc); return 0;
     case 1: ref_run<float, float, float>(level, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc); return 0;
     case 2: ref_run<double, double, double>(level, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc); return 0;
+    case 4: ref_run<ref_bf16, ref_bf16, float>(level, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc); return 0;
   }
   return 1;
 }

@@ -39,6 +39,10 @@
  *            on the dropped 13 bits) before the multiply; accumulate in float.  The reference has no
  *            oracle of this kind; it models the tensor-core input conversion and is used for tolerance
  *            tests only, never for bit-exact claims.
+ *   4  bf16: A,B,C bfloat16 (round-to-nearest-even conversions); scalar and accumulator float.  The same
+ *            generic bodies as the f16 set with the storage type exchanged, pinned against the reference's
+ *            oracle templates instantiated for bfloat16 storage (the reference's harness itself has no
+ *            bfloat16 case).
  *
  * Row sampling: every routine takes (nrows, rows).  rows == NULL means all rows of the (quadrant) row
  * space.  For orc_gemm a listed row r produces C row r.  For orc_sw_gemm at level 1 a listed row r in
@@ -51,6 +55,7 @@
 #include <string.h>
 
 typedef _Float16 half_t;
+typedef __bf16 bf16_t;
 
 static inline float tf32_round(float x) {
   uint32_t u;
@@ -274,6 +279,7 @@ DEFINE_ORACLE(f16, half_t, half_t, float, IDENT)
 DEFINE_ORACLE(f32, float, float, float, IDENT)
 DEFINE_ORACLE(f64, double, double, double, IDENT)
 DEFINE_ORACLE(tf32, float, float, float, tf32_round)
+DEFINE_ORACLE(bf16, bf16_t, bf16_t, float, IDENT)
 
 /* ------------------------------------------------------------------------------------------- */
 /* C entry points (bound with ctypes by the tests).  Return 0 on success, 1 on bad arguments.   */
@@ -286,6 +292,7 @@ int orc_gemm(int dtype, int M, int N, int K, double alpha, const void *A, int ld
     case 1: gemm_rows_f32(M, N, K, (float)alpha, A, lda, B, ldb, (float)beta, Cin, C, ldc, nrows, rows); return 0;
     case 2: gemm_rows_f64(M, N, K, alpha, A, lda, B, ldb, beta, Cin, C, ldc, nrows, rows); return 0;
     case 3: gemm_rows_tf32(M, N, K, (float)alpha, A, lda, B, ldb, (float)beta, Cin, C, ldc, nrows, rows); return 0;
+    case 4: gemm_rows_bf16(M, N, K, (float)alpha, A, lda, B, ldb, (float)beta, Cin, C, ldc, nrows, rows); return 0;
   }
   return 1;
 }
@@ -304,6 +311,7 @@ int orc_sw_gemm(int dtype, int level, int M, int N, int K, double alpha, const v
       case 1: sw1_rows_f32(M, N, K, (float)alpha, A, lda, B, ldb, (float)beta, Cin, C, ldc, nrows, rows, NULL); return 0;
       case 2: sw1_rows_f64(M, N, K, alpha, A, lda, B, ldb, beta, Cin, C, ldc, nrows, rows, NULL); return 0;
       case 3: sw1_rows_tf32(M, N, K, (float)alpha, A, lda, B, ldb, (float)beta, Cin, C, ldc, nrows, rows, NULL); return 0;
+      case 4: sw1_rows_bf16(M, N, K, (float)alpha, A, lda, B, ldb, (float)beta, Cin, C, ldc, nrows, rows, NULL); return 0;
     }
     return 1;
   }
@@ -314,6 +322,7 @@ int orc_sw_gemm(int dtype, int level, int M, int N, int K, double alpha, const v
       case 1: return sw2_f32(M, N, K, (float)alpha, A, lda, B, ldb, (float)beta, Cin, C, ldc, interim_round);
       case 2: return sw2_f64(M, N, K, alpha, A, lda, B, ldb, beta, Cin, C, ldc, interim_round);
       case 3: return sw2_tf32(M, N, K, (float)alpha, A, lda, B, ldb, (float)beta, Cin, C, ldc, interim_round);
+      case 4: return sw2_bf16(M, N, K, (float)alpha, A, lda, B, ldb, (float)beta, Cin, C, ldc, interim_round);
     }
   }
   return 1;
@@ -328,6 +337,7 @@ int orc_sw_presums(int dtype, int M, int N, int K, const void *A, int lda, const
     case 1:
     case 3: presums_f32(M, N, K, A, lda, B, ldb, pa, pb); return 0;
     case 2: presums_f64(M, N, K, A, lda, B, ldb, pa, pb); return 0;
+    case 4: presums_bf16(M, N, K, A, lda, B, ldb, pa, pb); return 0;
   }
   return 1;
 }
@@ -345,11 +355,15 @@ int orc_truth_rows(int dtype, int M, int N, int K, const void *A, int lda, const
     for (int k = 0; k < K; ++k) {
       double a;
       if (dtype == 0) a = (double)((const half_t *)A)[(size_t)i * lda + k];
+      else if (dtype == 4) a = (double)(float)((const bf16_t *)A)[(size_t)i * lda + k];
       else if (dtype == 2) a = ((const double *)A)[(size_t)i * lda + k];
       else a = (double)((const float *)A)[(size_t)i * lda + k];
       if (dtype == 0) {
         const half_t *b = (const half_t *)B + (size_t)k * ldb;
         for (int j = 0; j < N; ++j) acc[j] += a * (double)b[j];
+      } else if (dtype == 4) {
+        const bf16_t *b = (const bf16_t *)B + (size_t)k * ldb;
+        for (int j = 0; j < N; ++j) acc[j] += a * (double)(float)b[j];
       } else if (dtype == 2) {
         const double *b = (const double *)B + (size_t)k * ldb;
         for (int j = 0; j < N; ++j) acc[j] += a * b[j];

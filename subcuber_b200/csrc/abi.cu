@@ -44,6 +44,13 @@ const KernelDesc kDescs[] = {
     {"blackwell_f32_sw_level2", "f32", 2, sb200::kF32, sb200::kInterleavedLevel2, 256, 0},
     {"blackwell_f16_sw_level2_2sm", "f16", 2, sb200::kF16, sb200::kInterleavedLevel2, 256, 1},
     {"blackwell_f32_sw_level2_2sm", "f32", 2, sb200::kF32, sb200::kInterleavedLevel2, 256, 1},
+    {"blackwell_bf16_cubic_128x256", "bf16", 0, sb200::kBF16, sb200::kCubic, 256, 0},
+    {"blackwell_bf16_cubic_2sm_256x256", "bf16", 0, sb200::kBF16, sb200::kCubic, 256, 1},
+    {"blackwell_bf16_sw_fused_presum_2sm", "bf16", 1, sb200::kBF16, sb200::kFusedPresum, 256, 1},
+    {"blackwell_bf16_sw_interleaved_presum", "bf16", 1, sb200::kBF16, sb200::kInterleavedPresum, 256, 0},
+    {"blackwell_bf16_sw_interleaved_presum_2sm", "bf16", 1, sb200::kBF16, sb200::kInterleavedPresum, 256, 1},
+    {"blackwell_bf16_sw_level2", "bf16", 2, sb200::kBF16, sb200::kInterleavedLevel2, 256, 0},
+    {"blackwell_bf16_sw_level2_2sm", "bf16", 2, sb200::kBF16, sb200::kInterleavedLevel2, 256, 1},
     {"blackwell_f16_strassen_fused_presum", "f16", 1, sb200::kF16, sb200::kStrassenFused, 256, 0},
     {"blackwell_f32_strassen_fused_presum", "f32", 1, sb200::kF32, sb200::kStrassenFused, 256, 0},
     {"blackwell_f16_strassen_fused_presum_2sm", "f16", 1, sb200::kF16, sb200::kStrassenFused, 256, 1},
@@ -65,6 +72,7 @@ const KernelDesc* find_desc(const char* name) {
 // cost model (src/compile.py:200-212, should_use_k2 / level by size), with crossover points measured on B200.
 // The recursion pays off once a product is large enough for its presum and postsum traffic to be small against it:
 //   f16 : level 1 from 12288, level 2 from 24576 (smallest of m, n, k); below that the plain pair kernel is fastest
+//   bf16: the same kernels with the other 16-bit format, the same crossover points
 //   tf32: level 1 from 12288, level 2 from 16384
 //   f64 : level 1 from 6144, level 2 from 16384
 const char* auto_kernel(sb200::DType dt, int m, int n, int k) {
@@ -75,6 +83,10 @@ const char* auto_kernel(sb200::DType dt, int m, int n, int k) {
       if (s >= 24576) return "blackwell_f16_sw_level2_2sm";
       if (s >= 12288) return "blackwell_f16_sw_interleaved_presum_2sm";
       return "blackwell_f16_cubic_2sm_256x256";
+    case sb200::kBF16:
+      if (s >= 24576) return "blackwell_bf16_sw_level2_2sm";
+      if (s >= 12288) return "blackwell_bf16_sw_interleaved_presum_2sm";
+      return "blackwell_bf16_cubic_2sm_256x256";
     case sb200::kF32:
       if (s >= 16384) return "blackwell_f32_sw_level2_2sm";
       if (s >= 12288) return "blackwell_f32_sw_interleaved_presum_2sm";
@@ -90,6 +102,7 @@ const char* auto_kernel(sb200::DType dt, int m, int n, int k) {
 const KernelDesc* resolve_desc(const char* name, int m, int n, int k) {
   if (!name) return nullptr;
   if (strcmp(name, "blackwell_f16_sw_auto") == 0) return find_desc(auto_kernel(sb200::kF16, m, n, k));
+  if (strcmp(name, "blackwell_bf16_sw_auto") == 0) return find_desc(auto_kernel(sb200::kBF16, m, n, k));
   if (strcmp(name, "blackwell_f32_sw_auto") == 0) return find_desc(auto_kernel(sb200::kF32, m, n, k));
   if (strcmp(name, "blackwell_f64_sw_auto") == 0) return find_desc(auto_kernel(sb200::kF64, m, n, k));
   return find_desc(name);
@@ -175,6 +188,7 @@ struct BlasType {
 };
 // f16 / f32 / f64 rows use the reference's settings (src/cuda/cublas_runner.cpp:9-35).
 const BlasType kBlasF16 = {CUDA_R_16F, CUBLAS_COMPUTE_32F_FAST_16F, CUBLAS_TENSOR_OP_MATH, CUBLAS_GEMM_DEFAULT_TENSOR_OP, false};
+const BlasType kBlasBF16 = {CUDA_R_16BF, CUBLAS_COMPUTE_32F, CUBLAS_TENSOR_OP_MATH, CUBLAS_GEMM_DEFAULT_TENSOR_OP, false};
 const BlasType kBlasF32 = {CUDA_R_32F, CUBLAS_COMPUTE_32F_PEDANTIC, CUBLAS_DEFAULT_MATH, CUBLAS_GEMM_DEFAULT, false};
 const BlasType kBlasF64 = {CUDA_R_64F, CUBLAS_COMPUTE_64F_PEDANTIC, CUBLAS_DEFAULT_MATH, CUBLAS_GEMM_DEFAULT, true};
 const BlasType kBlasTF32 = {CUDA_R_32F, CUBLAS_COMPUTE_32F_FAST_TF32, CUBLAS_TF32_TENSOR_OP_MATH, CUBLAS_GEMM_DEFAULT_TENSOR_OP, false};
@@ -319,6 +333,14 @@ SB200_DEFINE_RUN(blackwell_f16_sw_level2)
 SB200_DEFINE_RUN(blackwell_f32_sw_level2)
 SB200_DEFINE_RUN(blackwell_f16_sw_level2_2sm)
 SB200_DEFINE_RUN(blackwell_f32_sw_level2_2sm)
+SB200_DEFINE_RUN(blackwell_bf16_cubic_128x256)
+SB200_DEFINE_RUN(blackwell_bf16_cubic_2sm_256x256)
+SB200_DEFINE_RUN(blackwell_bf16_sw_fused_presum_2sm)
+SB200_DEFINE_RUN(blackwell_bf16_sw_interleaved_presum)
+SB200_DEFINE_RUN(blackwell_bf16_sw_interleaved_presum_2sm)
+SB200_DEFINE_RUN(blackwell_bf16_sw_level2)
+SB200_DEFINE_RUN(blackwell_bf16_sw_level2_2sm)
+SB200_DEFINE_RUN(blackwell_bf16_sw_auto)
 SB200_DEFINE_RUN(blackwell_f16_strassen_fused_presum)
 SB200_DEFINE_RUN(blackwell_f32_strassen_fused_presum)
 SB200_DEFINE_RUN(blackwell_f16_strassen_fused_presum_2sm)
@@ -336,6 +358,7 @@ SB200_DEFINE_RUN(blackwell_f64_sw_auto)
     return impl(type, buffers, m, n, k, warmup_iterations, iterations, streams, num_streams, avg_ms);          \
   }
 SB200_DEFINE_BLAS(run_cublas_f16, run_cublas, kBlasF16)
+SB200_DEFINE_BLAS(run_cublas_bf16, run_cublas, kBlasBF16)
 SB200_DEFINE_BLAS(run_cublas_f32, run_cublas, kBlasF32)
 SB200_DEFINE_BLAS(run_cublas_f64, run_cublas, kBlasF64)
 SB200_DEFINE_BLAS(run_cublas_tf32, run_cublas, kBlasTF32)
@@ -348,6 +371,7 @@ static const sb200_kernel_entry kRegistry[] = {
     {"cublas_f16", "blackwell", "f16", 0, run_cublas_f16},
     {"cublas_f64", "blackwell", "f64", 0, run_cublas_f64},
     {"cublas_tf32", "blackwell", "f32", 0, run_cublas_tf32},
+    {"cublas_bf16", "blackwell", "bf16", 0, run_cublas_bf16},
     {"cublaslt_f32", "blackwell", "f32", 0, run_cublaslt_f32},
     {"cublaslt_f16", "blackwell", "f16", 0, run_cublaslt_f16},
     {"cublaslt_f64", "blackwell", "f64", 0, run_cublaslt_f64},
@@ -369,6 +393,13 @@ static const sb200_kernel_entry kRegistry[] = {
     {"blackwell_f32_sw_level2", "blackwell", "f32", 2, run_blackwell_f32_sw_level2},
     {"blackwell_f16_sw_level2_2sm", "blackwell", "f16", 2, run_blackwell_f16_sw_level2_2sm},
     {"blackwell_f32_sw_level2_2sm", "blackwell", "f32", 2, run_blackwell_f32_sw_level2_2sm},
+    {"blackwell_bf16_cubic_128x256", "blackwell", "bf16", 0, run_blackwell_bf16_cubic_128x256},
+    {"blackwell_bf16_cubic_2sm_256x256", "blackwell", "bf16", 0, run_blackwell_bf16_cubic_2sm_256x256},
+    {"blackwell_bf16_sw_fused_presum_2sm", "blackwell", "bf16", 1, run_blackwell_bf16_sw_fused_presum_2sm},
+    {"blackwell_bf16_sw_interleaved_presum", "blackwell", "bf16", 1, run_blackwell_bf16_sw_interleaved_presum},
+    {"blackwell_bf16_sw_interleaved_presum_2sm", "blackwell", "bf16", 1, run_blackwell_bf16_sw_interleaved_presum_2sm},
+    {"blackwell_bf16_sw_level2", "blackwell", "bf16", 2, run_blackwell_bf16_sw_level2},
+    {"blackwell_bf16_sw_level2_2sm", "blackwell", "bf16", 2, run_blackwell_bf16_sw_level2_2sm},
     {"blackwell_f16_strassen_fused_presum", "blackwell", "f16", 1, run_blackwell_f16_strassen_fused_presum},
     {"blackwell_f32_strassen_fused_presum", "blackwell", "f32", 1, run_blackwell_f32_strassen_fused_presum},
     {"blackwell_f16_strassen_fused_presum_2sm", "blackwell", "f16", 1, run_blackwell_f16_strassen_fused_presum_2sm},
@@ -378,6 +409,7 @@ static const sb200_kernel_entry kRegistry[] = {
     {"blackwell_f64_sw_level2", "blackwell", "f64", 2, run_blackwell_f64_sw_level2},
     // level chosen by size; listed under level 1 so that "--strassen_level=1" runs show it next to the fixed plans
     {"blackwell_f16_sw_auto", "blackwell", "f16", 1, run_blackwell_f16_sw_auto},
+    {"blackwell_bf16_sw_auto", "blackwell", "bf16", 1, run_blackwell_bf16_sw_auto},
     {"blackwell_f32_sw_auto", "blackwell", "f32", 1, run_blackwell_f32_sw_auto},
     {"blackwell_f64_sw_auto", "blackwell", "f64", 1, run_blackwell_f64_sw_auto},
 };
@@ -438,6 +470,7 @@ extern "C" int sb200_gemm_colmajor(const char* kernel, const void* a, const void
 extern "C" const char* sb200_auto_kernel(const char* dtype, int m, int n, int k) {
   if (!dtype) return nullptr;
   if (strcmp(dtype, "f16") == 0) return auto_kernel(sb200::kF16, m, n, k);
+  if (strcmp(dtype, "bf16") == 0) return auto_kernel(sb200::kBF16, m, n, k);
   if (strcmp(dtype, "f32") == 0) return auto_kernel(sb200::kF32, m, n, k);
   if (strcmp(dtype, "f64") == 0) return auto_kernel(sb200::kF64, m, n, k);
   return nullptr;
@@ -460,7 +493,7 @@ extern "C" int sb200_gemm_host(const char* kernel, const void* a_host, const voi
   const KernelDesc* d = resolve_desc(kernel, m, n, k);
   if (!d) return SB200_ERR_NO_KERNEL;
   if (!a_host || !b_host || !d_host || m <= 0 || n <= 0 || k <= 0) return SB200_ERR_INVALID_PROBLEM;
-  const size_t es = d->dt == sb200::kF16 ? 2 : 4;
+  const size_t es = (d->dt == sb200::kF16 || d->dt == sb200::kBF16) ? 2 : (d->dt == sb200::kF64 ? 8 : 4);
   const size_t a_bytes = size_t(m) * k * es, b_bytes = size_t(k) * n * es, d_bytes = size_t(m) * n * es;
   void *da = nullptr, *db = nullptr, *dd = nullptr, *ws = nullptr;
   int rc = 0;

@@ -12,7 +12,7 @@ namespace sb200 {
 namespace {
 
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
-inline int esize_of(DType t) { return t == kF16 ? 2 : (t == kF32 ? 4 : 8); }
+inline int esize_of(DType t) { return (t == kF16 || t == kBF16) ? 2 : (t == kF32 ? 4 : 8); }
 inline int level_of(Variant v) { return v == kCubic ? 0 : (v == kInterleavedLevel2 ? 2 : 1); }
 
 struct PadPlan {
@@ -127,7 +127,7 @@ int pad_copy_es(int es, void* dst, int rows_d, int cols_d, const void* src, int 
 
 int can_implement(const GemmArgs& a) {
   if (a.m <= 0 || a.n <= 0 || a.k <= 0 || !a.a || !a.b || !a.d) return kErrInvalidProblem;
-  if (a.dtype != kF16 && a.dtype != kF32 && a.dtype != kF64) return kErrNotSupported;
+  if (a.dtype != kF16 && a.dtype != kF32 && a.dtype != kF64 && a.dtype != kBF16) return kErrNotSupported;
   if (a.scaled && a.beta != 0.0 && !a.c) return kErrInvalidProblem;
   const PadPlan p = plan(a);
   return p.needed ? inner_can_implement(padded_args(a, p, nullptr)) : inner_can_implement(a);

@@ -16,6 +16,8 @@
 //     area in shared memory (32 rows x 128 payload bytes, 144-byte pitch = conflict-free 16-byte accesses) and leave
 //     as full 128-byte row segments: each warp-wide store writes 4 rows x 128 contiguous bytes.
 #pragma once
+#include <cuda_bf16.h>
+
 #include "ptx.cuh"
 #include "tile_program.h"
 
@@ -99,7 +101,7 @@ __device__ __forceinline__ bool epilogue_body(void* const* out, long long ldo, i
                                               float* redirect, const float* late_src, bool skip_body,
                                               WaitFn wait_slots, float alpha = 1.f, float beta = 0.f,
                                               const void* const* cin = nullptr, long long ldc = 0,
-                                              long long* prof = nullptr) {
+                                              long long* prof = nullptr, bool bf16 = false) {
   if (skip_body) return wait_slots();  // measurement aid
   constexpr int NCHUNK = BN / 32;
   const int row = quarter * 32 + lane;
@@ -227,10 +229,11 @@ __device__ __forceinline__ bool epilogue_body(void* const* out, long long ldo, i
         if (cp && grow < out_rows && gcol + v * EPV < out_cols) {
           const uint4 raw = *reinterpret_cast<const uint4*>(cp + (static_cast<long long>(grow) * ldc + gcol + v * EPV) * ESIZE);
           if (ESIZE == 2) {
-            const __half2* h = reinterpret_cast<const __half2*>(&raw);
+            const uint32_t* h = reinterpret_cast<const uint32_t*>(&raw);
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-              const float2 f = __half22float2(h[e]);
+              const float2 f = bf16 ? make_float2(__uint_as_float(h[e] << 16), __uint_as_float(h[e] & 0xffff0000u))
+                                    : __half22float2(*reinterpret_cast<const __half2*>(&h[e]));
               cv[(2 * e) % EPV] = f.x;
               cv[(2 * e + 1) % EPV] = f.y;
             }
@@ -255,9 +258,15 @@ __device__ __forceinline__ bool epilogue_body(void* const* out, long long ldo, i
 #pragma unroll
       for (int g = 0; g < 4; ++g) {
         uint4 o;
-        __half2* h = reinterpret_cast<__half2*>(&o);
+        if (bf16) {
+          __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
-        for (int q = 0; q < 4; ++q) h[q] = __floats2half2_rn(acc[g * 8 + 2 * q], acc[g * 8 + 2 * q + 1]);
+          for (int q = 0; q < 4; ++q) h[q] = __floats2bfloat162_rn(acc[g * 8 + 2 * q], acc[g * 8 + 2 * q + 1]);
+        } else {
+          __half2* h = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) h[q] = __floats2half2_rn(acc[g * 8 + 2 * q], acc[g * 8 + 2 * q + 1]);
+        }
         ptx::sts_v4(wr + g * 16, o);
       }
       SB200_SEG(2)

@@ -8,6 +8,7 @@
 //   0 uniform1  U[-1, 1)          24-bit mantissa draw, exact in fp32
 //   1 normal    N(0, 1)           Box-Muller on two draws of the same counter (fp32 math)
 //   2 harness   the reference harness' value set: multiples of 0.25 in [-R, R], R = 4 (f16) or 16
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <math.h>
@@ -52,7 +53,7 @@ __host__ __device__ inline float draw(int dist, int dtype, uint64_t index, uint3
     float u2 = static_cast<float>(p.v[1] >> 8) * (1.0f / 16777216.0f);
     return sqrtf(-2.0f * logf(u1)) * cosf(6.28318530717958647692f * u2);
   }
-  const int range = (dtype == 0) ? 4 : 16;
+  const int range = (dtype == 0 || dtype == 3) ? 4 : 16;  // 16-bit types: +-4 (sums of 16 terms stay exact in bfloat16 too)
   const uint32_t steps = static_cast<uint32_t>(8 * range + 1);
   return -static_cast<float>(range) + 0.25f * static_cast<float>(p.v[0] % steps);
 }
@@ -61,6 +62,8 @@ template <typename T>
 __host__ __device__ inline T convert(float x);
 template <>
 __host__ __device__ inline __half convert<__half>(float x) { return __float2half_rn(x); }
+template <>
+__host__ __device__ inline __nv_bfloat16 convert<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
 template <>
 __host__ __device__ inline float convert<float>(float x) { return x; }
 template <>
@@ -82,12 +85,13 @@ void fill_host_t(T* out, uint64_t n, int dist, int dtype, uint32_t subseq, uint6
 
 extern "C" int sb200_fill_device(int dtype, int dist, unsigned long long seed, unsigned subsequence, void* ptr,
                                  unsigned long long count, sb200_stream_t stream) {
-  if (!ptr || dist < 0 || dist > 2 || dtype < 0 || dtype > 2) return SB200_ERR_INVALID_PROBLEM;
+  if (!ptr || dist < 0 || dist > 2 || dtype < 0 || dtype > 3) return SB200_ERR_INVALID_PROBLEM;
   if (count == 0) return 0;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const int threads = 256;
   const int blocks = static_cast<int>(count / threads + 1 < 148ull * 16 ? count / threads + 1 : 148ull * 16);
   if (dtype == 0) fill_kernel<__half><<<blocks, threads, 0, s>>>(static_cast<__half*>(ptr), count, dist, dtype, subsequence, seed);
+  else if (dtype == 3) fill_kernel<__nv_bfloat16><<<blocks, threads, 0, s>>>(static_cast<__nv_bfloat16*>(ptr), count, dist, dtype, subsequence, seed);
   else if (dtype == 1) fill_kernel<float><<<blocks, threads, 0, s>>>(static_cast<float*>(ptr), count, dist, dtype, subsequence, seed);
   else fill_kernel<double><<<blocks, threads, 0, s>>>(static_cast<double*>(ptr), count, dist, dtype, subsequence, seed);
   return static_cast<int>(cudaGetLastError());
@@ -95,8 +99,9 @@ extern "C" int sb200_fill_device(int dtype, int dist, unsigned long long seed, u
 
 extern "C" int sb200_fill_host(int dtype, int dist, unsigned long long seed, unsigned subsequence, void* ptr,
                                unsigned long long count) {
-  if (!ptr || dist < 0 || dist > 2 || dtype < 0 || dtype > 2) return SB200_ERR_INVALID_PROBLEM;
+  if (!ptr || dist < 0 || dist > 2 || dtype < 0 || dtype > 3) return SB200_ERR_INVALID_PROBLEM;
   if (dtype == 0) fill_host_t<__half>(static_cast<__half*>(ptr), count, dist, dtype, subsequence, seed);
+  else if (dtype == 3) fill_host_t<__nv_bfloat16>(static_cast<__nv_bfloat16*>(ptr), count, dist, dtype, subsequence, seed);
   else if (dtype == 1) fill_host_t<float>(static_cast<float*>(ptr), count, dist, dtype, subsequence, seed);
   else fill_host_t<double>(static_cast<double*>(ptr), count, dist, dtype, subsequence, seed);
   return 0;

@@ -52,6 +52,7 @@ std::string canonical_dtype(const std::string& raw) {
   if (d == "float" || d == "fp32" || d == "s") return "f32";
   if (d == "half" || d == "fp16" || d == "h") return "f16";
   if (d == "double" || d == "fp64" || d == "d") return "f64";
+  if (d == "bfloat16" || d == "bf") return "bf16";
   return d;
 }
 
@@ -93,7 +94,8 @@ void usage(const char* prog) {
   std::cerr << "Usage: " << prog
             << " --m=<M> --n=<N> --k=<K> --dtype=f32|f16|f64 --gpu_arch=blackwell --strassen_level=0|1|2|all "
                "--iterations=N --warmup=N --streams=N [--kernel_regex=REGEX] [--dist=harness|uniform1|normal] "
-               "[--seed=S] [--cooldown_s=X] [--json]\n";
+               "[--seed=S] [--cooldown_s=X] [--json]\n"
+               "       (--dtype also takes bf16)\n";
 }
 
 struct Options {
@@ -152,7 +154,7 @@ int main(int argc, char** argv) {
   }
   const bool known_arch = o.arch == "volta" || o.arch == "ampere" || o.arch == "hopper" || o.arch == "blackwell";
   if (!ok || o.m <= 0 || o.n <= 0 || o.k <= 0 || o.iterations <= 0 || o.warmup < 0 || o.streams <= 0 ||
-      o.streams > max_streams || (o.dtype != "f32" && o.dtype != "f16" && o.dtype != "f64") || !known_arch ||
+      o.streams > max_streams || (o.dtype != "f32" && o.dtype != "f16" && o.dtype != "f64" && o.dtype != "bf16") || !known_arch ||
       dist_code < 0 || (!o.all_levels && (o.level < 0 || o.level > 2))) {
     usage(argv[0]);
     return 1;
@@ -174,8 +176,8 @@ int main(int argc, char** argv) {
     return 1;
   }
 
-  const int dtype_code = o.dtype == "f16" ? 0 : (o.dtype == "f32" ? 1 : 2);
-  const size_t es = dtype_code == 0 ? 2 : (dtype_code == 1 ? 4 : 8);
+  const int dtype_code = o.dtype == "f16" ? 0 : (o.dtype == "f32" ? 1 : (o.dtype == "bf16" ? 3 : 2));
+  const size_t es = (dtype_code == 0 || dtype_code == 3) ? 2 : (dtype_code == 1 ? 4 : 8);
   void *da = nullptr, *db = nullptr, *dd = nullptr;
   auto fail = [&](cudaError_t e) {
     std::cerr << "CUDA error: " << cudaGetErrorString(e) << "\n";

@@ -64,7 +64,7 @@ int make_tmap_b_blocked(CUtensorMap* m, int esize, const View& v, int box_rows, 
 
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
-inline int esize_of(DType t) { return t == kF16 ? 2 : 4; }
+inline int esize_of(DType t) { return (t == kF16 || t == kBF16) ? 2 : 4; }
 
 struct Layout {
   int esize, bn, level;
@@ -268,7 +268,7 @@ namespace tc {
 
 int can_implement(const GemmArgs& a) {
   if (a.m <= 0 || a.n <= 0 || a.k <= 0 || !a.a || !a.b || !a.d) return kErrInvalidProblem;
-  if (a.dtype != kF16 && a.dtype != kF32) return kErrNotSupported;
+  if (a.dtype != kF16 && a.dtype != kF32 && a.dtype != kBF16) return kErrNotSupported;
   if (a.scaled && a.beta != 0.0 && (!a.c || (reinterpret_cast<uintptr_t>(a.c) & 15))) return kErrInvalidProblem;
   if (a.bn != 0 && a.bn != 128 && a.bn != 256) return kErrNotSupported;
   if (a.pair && a.bn == 128) return kErrNotSupported;
@@ -314,6 +314,7 @@ namespace {
 struct LaunchSpec {
   Variant variant;
   int es, bn, pair, grid;
+  int bf16;                  // 16-bit operands are bfloat16
   View a, b;                 // whole operands of this group (extents up to twice the block extents)
   int mq, nq, kq;            // extents of one block (level 0: of the whole problem)
   int tiles_m, tiles_n, num_k;
@@ -356,6 +357,7 @@ int launch_group(const LaunchSpec& s, cudaStream_t stream, MarkFn mark) {
   KernelParams p;
   memset(&p, 0, sizeof(p));
   p.status = s.status;
+  p.bf16 = s.bf16;
   const int es = s.es;
   const char* A = static_cast<const char*>(s.a.ptr);
   const char* B = static_cast<const char*>(s.b.ptr);
@@ -537,6 +539,7 @@ int run(const GemmArgs& a, void* workspace, size_t workspace_size, cudaStream_t 
   LaunchSpec s;
   memset(&s, 0, sizeof(s));
   s.es = es;
+  s.bf16 = a.dtype == kBF16 ? 1 : 0;
   s.bn = L.bn;
   s.pair = a.pair;
   s.grid = L.workers;

@@ -8,7 +8,9 @@
 
 namespace sb200 {
 
-enum DType { kF16 = 0, kF32 = 1, kF64 = 2 };  // kF32: fp32 storage, TF32 tensor-core math, fp32 accumulate
+// kF32: fp32 storage, TF32 tensor-core math, fp32 accumulate; kBF16: bfloat16 storage, fp32 accumulate (the f16 kernels
+// with the other 16-bit format: same tiles, same programs, one run-time flag)
+enum DType { kF16 = 0, kF32 = 1, kF64 = 2, kBF16 = 3 };
 
 enum Variant {
   kCubic = 0,             // level 0, plain GEMM

@@ -26,6 +26,8 @@
 // Shared-memory stage (48 KiB at BN = 256): A tile 128 rows x 128 B (K-major, 128B swizzle) followed by the
 // B tile as BN*ESIZE/128 blocks of [BK rows x 128 B] (N-major, 128B swizzle), exactly as TMA deposits them.
 #pragma once
+#include <cuda_bf16.h>
+
 #include "ptx.cuh"
 #include "tile_program.h"
 #include "epilogue.cuh"
@@ -68,6 +70,7 @@ struct KernelParams {
   View view[SB200_NUM_VIEWS];
   void* out[4];       // output quadrant base pointers (level 0: out[0] = D)
   long long ldo;      // leading dimension of the output in elements
+  int bf16;           // 16-bit kernels only: the operand and output type is bfloat16 (else IEEE half)
   int out_rows;       // rows of one output quadrant
   int out_cols;       // columns of one output quadrant
   int out_rows2;      // rows present in output quadrants 2, 3 and columns present in quadrants 1, 3 (<= out_rows,
@@ -200,29 +203,41 @@ struct VecAcc;
 template <>
 struct VecAcc<2> {
   float v[8];
+  bool bf;  // the 16-bit type is bfloat16 (else IEEE half)
+  __device__ __forceinline__ explicit VecAcc(bool is_bf16) : bf(is_bf16) {}
+  __device__ __forceinline__ float2 widen(uint32_t pair) const {
+    if (bf) return make_float2(__uint_as_float(pair << 16), __uint_as_float(pair & 0xffff0000u));
+    return __half22float2(*reinterpret_cast<const __half2*>(&pair));
+  }
   __device__ __forceinline__ void set(uint4 x, int c) {
-    const __half2* h = reinterpret_cast<const __half2*>(&x);
+    const uint32_t* h = reinterpret_cast<const uint32_t*>(&x);
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
-      float2 f = __half22float2(h[q]);
+      float2 f = widen(h[q]);
       v[2 * q] = c > 0 ? f.x : -f.x;
       v[2 * q + 1] = c > 0 ? f.y : -f.y;
     }
   }
   __device__ __forceinline__ void add(uint4 x, int c) {
-    const __half2* h = reinterpret_cast<const __half2*>(&x);
+    const uint32_t* h = reinterpret_cast<const uint32_t*>(&x);
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
-      float2 f = __half22float2(h[q]);
+      float2 f = widen(h[q]);
       v[2 * q] = c > 0 ? __fadd_rn(v[2 * q], f.x) : __fsub_rn(v[2 * q], f.x);
       v[2 * q + 1] = c > 0 ? __fadd_rn(v[2 * q + 1], f.y) : __fsub_rn(v[2 * q + 1], f.y);
     }
   }
   __device__ __forceinline__ uint4 pack() const {
     uint4 o;
-    __half2* h = reinterpret_cast<__half2*>(&o);
+    if (bf) {
+      __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
-    for (int q = 0; q < 4; ++q) h[q] = __floats2half2_rn(v[2 * q], v[2 * q + 1]);
+      for (int q = 0; q < 4; ++q) h[q] = __floats2bfloat162_rn(v[2 * q], v[2 * q + 1]);
+    } else {
+      __half2* h = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) h[q] = __floats2half2_rn(v[2 * q], v[2 * q + 1]);
+    }
     return o;
   }
 };
@@ -230,6 +245,7 @@ struct VecAcc<2> {
 template <>
 struct VecAcc<4> {
   float v[4];
+  __device__ __forceinline__ explicit VecAcc(bool) {}
   __device__ __forceinline__ void set(uint4 x, int c) {
     const float* f = reinterpret_cast<const float*>(&x);
 #pragma unroll
@@ -257,7 +273,7 @@ struct VecAcc<4> {
 //   SWZ32         false: 16-byte chunk index XOR (row & 7); true: 32-byte chunk index XOR (row & 3)
 template <int ESIZE, int ROWS, int VEC_PER_ROW, int NTHREADS, bool SWZ32>
 __device__ __forceinline__ void build_operand_tile(uint32_t smem_tile, uint32_t blk_bytes, const sb200_operand_t& op,
-                                                   const View* views, int row0, int col0, int tid) {
+                                                   const View* views, int row0, int col0, int tid, bool bf) {
   constexpr int EPV = 16 / ESIZE;  // elements per vector
   constexpr int TOTAL = ROWS * VEC_PER_ROW;
   const int nterms = op.nterms;
@@ -279,7 +295,7 @@ __device__ __forceinline__ void build_operand_tile(uint32_t smem_tile, uint32_t 
         }
       }
     }
-    VecAcc<ESIZE> acc;
+    VecAcc<ESIZE> acc(bf);
     acc.set(x[0], op.coef[0]);
 #pragma unroll
     for (int t = 1; t < SB200_MAX_TERMS; ++t)
@@ -296,7 +312,7 @@ __device__ __forceinline__ void build_operand_tile(uint32_t smem_tile, uint32_t 
 // loop; per position it reads the four raw quadrant vectors and writes the four combinations of that side.
 // Sums are formed from the raw values left to right in fp32 and rounded once (VecAcc).
 template <int ESIZE>
-__device__ __forceinline__ void presum_side_job(const PresumSideJob& j, int gtid, int gthreads) {
+__device__ __forceinline__ void presum_side_job(const PresumSideJob& j, int gtid, int gthreads, bool bf) {
   constexpr int EPV = 16 / ESIZE;
   constexpr int U = 4;  // vector positions per thread per iteration: 16 loads in flight hide the memory latency
   const int vec_per_row = j.cols / EPV;
@@ -332,23 +348,23 @@ __device__ __forceinline__ void presum_side_job(const PresumSideJob& j, int gtid
       if (o[u] < 0) continue;
       if (j.side == 0) {
         // A side: S1 = A2 + A3, S2 = S1 - A0, A02 = A0 - A2, A1S2 = A1 - S2
-        VecAcc<ESIZE> s;
+        VecAcc<ESIZE> s(bf);
         s.set(x2[u], 1); s.add(x3[u], 1);                             // S1
         *reinterpret_cast<uint4*>(out + 0 * q + o[u]) = s.pack();
         s.add(x0[u], -1);                                             // S2 = S1 - A0 (unrounded S1)
         *reinterpret_cast<uint4*>(out + 1 * q + o[u]) = s.pack();
-        VecAcc<ESIZE> t;
+        VecAcc<ESIZE> t(bf);
         t.set(x0[u], 1); t.add(x2[u], -1);                            // A02
         *reinterpret_cast<uint4*>(out + 2 * q + o[u]) = t.pack();
-        VecAcc<ESIZE> w;                                              // A1S2 = A1 - S2 with the unrounded S2
+        VecAcc<ESIZE> w(bf);                                              // A1S2 = A1 - S2 with the unrounded S2
         w.set(x2[u], -1); w.add(x3[u], -1); w.add(x0[u], 1); w.add(x1[u], 1);
         *reinterpret_cast<uint4*>(out + 3 * q + o[u]) = w.pack();
       } else {
         // B side: B10 = B1 - B0, B31 = B3 - B1, S3 = B31 + B0, S3B2 = S3 - B2
-        VecAcc<ESIZE> s;
+        VecAcc<ESIZE> s(bf);
         s.set(x1[u], 1); s.add(x0[u], -1);                            // B10
         *reinterpret_cast<uint4*>(out + 0 * q + o[u]) = s.pack();
-        VecAcc<ESIZE> t;
+        VecAcc<ESIZE> t(bf);
         t.set(x3[u], 1); t.add(x1[u], -1);                            // B31
         *reinterpret_cast<uint4*>(out + 1 * q + o[u]) = t.pack();
         t.add(x0[u], 1);                                              // S3 = B31 + B0 (unrounded B31)
@@ -362,7 +378,7 @@ __device__ __forceinline__ void presum_side_job(const PresumSideJob& j, int gtid
 
 template <int ESIZE>
 __device__ __forceinline__ void presum_job(const KernelParams& p, int gtid, int gthreads) {
-  for (int j = 0; j < p.njobs; ++j) presum_side_job<ESIZE>(p.job[j], gtid, gthreads);
+  for (int j = 0; j < p.njobs; ++j) presum_side_job<ESIZE>(p.job[j], gtid, gthreads, p.bf16 != 0);
 }
 
 // ---------------------------------------------------------------------------------------------------
@@ -496,7 +512,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_kernel(const 
             free_bits ^= (1u << slot);
             ptx::tc_fence_after_sync();
           }
-          const uint32_t idesc = ptx::umma_idesc(Cfg::FMT, Cfg::BM, BN, pr.negate != 0);
+          const uint32_t idesc = ptx::umma_idesc((ESIZE == 2 && p.bf16) ? 1u : Cfg::FMT, Cfg::BM, BN, pr.negate != 0);
           const uint32_t tmem_d = tmem_base + slot * BN;
           const bool skip_mma = (p.debug_flags & 1) != 0;  // measurement aid
           // descriptors differ between stages and k-substeps only in the start-address field (low word, 16-byte units)
@@ -583,7 +599,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_kernel(const 
                                                      staging + (warp - 2) * kStagingWarpBytes,
                                                      sp.redirect ? split_tile_buf : nullptr,
                                                      sp.add_partial ? split_tile_buf : nullptr,
-                                                     (p.debug_flags & 32) != 0, wait_slots, p.alpha, p.beta, p.cin, p.ldc);
+                                                     (p.debug_flags & 32) != 0, wait_slots, p.alpha, p.beta, p.cin, p.ldc, nullptr,
+                                                     ESIZE == 2 && p.bf16 != 0);
         if (!ok) break;
         if (sp.redirect) raise_flag(flag, p.split_epoch, lane);
         ptx::tc_fence_before_sync();
@@ -620,10 +637,10 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_kernel(const 
             const uint32_t sa = ptx::smem_u32(smem + stage * Cfg::STAGE_BYTES);
             const uint32_t sb = sa + Cfg::A_BYTES;
             if (a_mt)
-              build_operand_tile<ESIZE, Cfg::BM, 8, PT, false>(sa, 0u, pr.a, p.view, tile.i * Cfg::BM, kk * BK, ptid);
+              build_operand_tile<ESIZE, Cfg::BM, 8, PT, false>(sa, 0u, pr.a, p.view, tile.i * Cfg::BM, kk * BK, ptid, p.bf16 != 0);
             if (b_mt)
               build_operand_tile<ESIZE, BK, BN * ESIZE / 16, PT, Cfg::B_SWZ32>(sb, Cfg::BLK_BYTES, pr.b, p.view, kk * BK, tile.j * BN,
-                                                                  ptid);
+                                                                  ptid, p.bf16 != 0);
             if (a_mt || b_mt) ptx::fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(&full_bar[stage]);

@@ -246,7 +246,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
             free_bits ^= (1u << slot);
             ptx::tc_fence_after_sync();
           }
-          const uint32_t idesc = ptx::umma_idesc(Cfg::FMT, Cfg::PAIR_M, BN, pr.negate != 0);
+          const uint32_t idesc = ptx::umma_idesc((ESIZE == 2 && p.bf16) ? 1u : Cfg::FMT, Cfg::PAIR_M, BN, pr.negate != 0);
           const uint32_t tmem_d = tmem_base + slot * BN;
           const bool skip_mma = (p.debug_flags & 1) != 0;
           // descriptors differ between stages and k-substeps only in the start-address field (low word, 16-byte units)
@@ -378,7 +378,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
                                                      sp.redirect ? split_tile_buf : nullptr,
                                                      sp.add_partial ? split_tile_buf : nullptr,
                                                      (p.debug_flags & 32) != 0, wait_slots, p.alpha, p.beta, p.cin, p.ldc,
-                                                     (p.prof && blockIdx.x == 0 && warp == 2) ? p.prof + 1190 : nullptr);
+                                                     (p.prof && blockIdx.x == 0 && warp == 2) ? p.prof + 1190 : nullptr,
+                                                     ESIZE == 2 && p.bf16 != 0);
         if (!ok) break;
 #ifdef SB200_PROFILE_EPILOGUE
         if (p.prof && blockIdx.x == 0 && warp == 2 && lane == 0 && es < 16) {
@@ -425,10 +426,10 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
             }
             const uint32_t sa = ptx::smem_u32(smem + stage * Cfg::STAGE_BYTES);
             const uint32_t sb = sa + Cfg::A_BYTES;
-            if (a_mt) build_operand_tile<ESIZE, Cfg::BM, 8, PT, false>(sa, 0u, pr.a, p.view, row0, kk * BK, ptid);
+            if (a_mt) build_operand_tile<ESIZE, Cfg::BM, 8, PT, false>(sa, 0u, pr.a, p.view, row0, kk * BK, ptid, p.bf16 != 0);
             if (b_mt)
               build_operand_tile<ESIZE, BK, Cfg::BN_CTA * ESIZE / 16, PT, Cfg::B_SWZ32>(sb, Cfg::BLK_BYTES, pr.b, p.view,
-                                                                                        kk * BK, col0, ptid);
+                                                                                        kk * BK, col0, ptid, p.bf16 != 0);
             if (a_mt || b_mt) ptx::fence_proxy_async_all();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive_cluster(&full_bar[stage], 0);

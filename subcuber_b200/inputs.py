@@ -12,14 +12,23 @@ import numpy as np
 
 from . import _lib
 
-DTYPE_CODE = {"f16": 0, "f32": 1, "f64": 2}
+DTYPE_CODE = {"f16": 0, "f32": 1, "f64": 2, "bf16": 3}
 DIST_CODE = {"uniform1": 0, "normal": 1, "harness": 2}
 NP_DTYPE = {"f16": np.float16, "f32": np.float32, "f64": np.float64}
 
 
+def np_dtype(dtype: str):
+    """numpy element type of `dtype`; bfloat16 comes from the ml_dtypes package (imported only when asked for)."""
+    if dtype == "bf16":
+        import ml_dtypes
+
+        return ml_dtypes.bfloat16
+    return NP_DTYPE[dtype]
+
+
 def fill_host(dtype: str, dist: str, shape, seed: int = 1, subsequence: int = 0) -> np.ndarray:
     """Matrix of `shape` filled on the host."""
-    out = np.empty(shape, dtype=NP_DTYPE[dtype])
+    out = np.empty(shape, dtype=np_dtype(dtype))
     rc = _lib.load().sb200_fill_host(DTYPE_CODE[dtype], DIST_CODE[dist], seed, subsequence,
                                      out.ctypes.data_as(C.c_void_p), out.size)
     if rc != 0:
@@ -31,7 +40,7 @@ def fill_device(dtype: str, dist: str, shape, seed: int = 1, subsequence: int = 
     """torch CUDA tensor of `shape` filled on the device (same values as fill_host)."""
     import torch
 
-    tdt = {"f16": torch.float16, "f32": torch.float32, "f64": torch.float64}[dtype]
+    tdt = {"f16": torch.float16, "f32": torch.float32, "f64": torch.float64, "bf16": torch.bfloat16}[dtype]
     out = torch.empty(shape, dtype=tdt, device=device)
     with torch.cuda.device(out.device):
         s = torch.cuda.current_stream(out.device).cuda_stream

@@ -29,7 +29,7 @@ ERROR_NAMES = {
     104: "device: presum wait timed out",
 }
 
-TORCH_DTYPE = {"f16": torch.float16, "f32": torch.float32, "f64": torch.float64}
+TORCH_DTYPE = {"f16": torch.float16, "f32": torch.float32, "f64": torch.float64, "bf16": torch.bfloat16}
 
 
 class KernelError(RuntimeError):
@@ -61,6 +61,24 @@ def normalize_arch(arch: str) -> str:
     return arch
 
 
+def to_torch(x, device) -> torch.Tensor:
+    """Host array -> tensor on `device` (bfloat16 arrays of the ml_dtypes package go through their bit pattern)."""
+    import numpy as np
+
+    if x.dtype.name == "bfloat16":
+        return torch.from_numpy(np.ascontiguousarray(x).view(np.int16)).to(device).view(torch.bfloat16)
+    return torch.from_numpy(x).to(device)
+
+
+def to_numpy(t: torch.Tensor):
+    """Tensor -> host array (bfloat16 as the ml_dtypes type)."""
+    if t.dtype == torch.bfloat16:
+        import ml_dtypes
+
+        return t.contiguous().view(torch.int16).cpu().numpy().view(ml_dtypes.bfloat16)
+    return t.cpu().numpy()
+
+
 def normalize_dtype(dtype: str) -> str:
     """Reference aliases (src/cuda/kernel_runner.cpp:198-204)."""
     dtype = dtype.lower()
@@ -68,6 +86,8 @@ def normalize_dtype(dtype: str) -> str:
         return "f32"
     if dtype in ("half", "fp16", "h"):
         return "f16"
+    if dtype in ("bfloat16", "bf"):
+        return "bf16"
     if dtype in ("double", "fp64", "d"):
         return "f64"
     return dtype

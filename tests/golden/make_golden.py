@@ -33,7 +33,15 @@ CASES = [
     ("f64", 1, 64, 48, 32, "uniform1", 1.0, 0.0),
     ("f64", 1, 32, 96, 48, "normal", -1.0, 1.0),
     ("f64", 0, 16, 16, 16, "harness", 1.0, 0.0),
+    # the same kernel templates instantiated for bfloat16 storage (stored as their 16-bit patterns)
+    ("bf16", 1, 64, 48, 32, "uniform1", 1.0, 0.0),
+    ("bf16", 1, 48, 80, 24, "harness", 0.5, 2.0),
+    ("bf16", 0, 40, 24, 56, "uniform1", 1.0, 0.0),
 ]
+
+
+def _stored(x):
+    return x.view(np.uint16) if x.dtype.name == "bfloat16" else x
 
 
 def main():
@@ -50,11 +58,11 @@ def main():
         names.append(name)
         out[name + "_meta"] = np.array([ob.DTYPE_CODE[dt], level, m, n, k, inputs.DIST_CODE[dist]], dtype=np.int64)
         out[name + "_ab"] = np.array([alpha, beta], dtype=np.float64)
-        out[name + "_a"] = a
-        out[name + "_b"] = b
+        out[name + "_a"] = _stored(a)
+        out[name + "_b"] = _stored(b)
         if cin is not None:
-            out[name + "_c"] = cin
-        out[name + "_d"] = d
+            out[name + "_c"] = _stored(cin)
+        out[name + "_d"] = _stored(d)
     # presum dump kernel (strassen_reference_l1.cuh:119-183) for the types where it rounds like the GEMM kernel
     for dt in ("f32", "f64"):
         a, b = inputs.operands(dt, "uniform1", 32, 48, 24, seed=7)

@@ -61,7 +61,8 @@ def test_auto_kernel_choice(lib):
     assert pick("f32", 16384, 16384, 16384) == "blackwell_f32_sw_level2_2sm"
     assert pick("f64", 8192, 8192, 8192) == "blackwell_f64_sw_level1"
     assert pick("f64", 16384, 16384, 16384) == "blackwell_f64_sw_level2"
-    assert lib.sb200_auto_kernel(b"bf16", 1, 1, 1) is None
+    assert pick("bf16", 16384, 16384, 16384) == "blackwell_bf16_sw_interleaved_presum_2sm"
+    assert lib.sb200_auto_kernel(b"int8", 1, 1, 1) is None
     assert lib.sb200_gemm_can_implement(b"blackwell_f16_sw_auto", 512, 512, 512) == 0
     assert lib.sb200_gemm_workspace_bytes(b"blackwell_f16_sw_auto", 512, 512, 512) == \
         lib.sb200_gemm_workspace_bytes(b"blackwell_f16_cubic_2sm_256x256", 512, 512, 512)

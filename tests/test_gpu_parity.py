@@ -23,11 +23,17 @@ L2_F32 = ["blackwell_f32_sw_level2", "blackwell_f32_sw_level2_2sm"]
 # Strassen's original algorithm: the same products of blocks summed another way, checked against the same oracle
 STRASSEN_F16 = ["blackwell_f16_strassen_fused_presum", "blackwell_f16_strassen_fused_presum_2sm"]
 STRASSEN_F32 = ["blackwell_f32_strassen_fused_presum", "blackwell_f32_strassen_fused_presum_2sm"]
+# bfloat16 storage: the f16 kernels with the other 16-bit format
+BF16 = ["blackwell_bf16_cubic_128x256", "blackwell_bf16_cubic_2sm_256x256", "blackwell_bf16_sw_fused_presum_2sm",
+        "blackwell_bf16_sw_interleaved_presum", "blackwell_bf16_sw_interleaved_presum_2sm"]
+L2_BF16 = ["blackwell_bf16_sw_level2", "blackwell_bf16_sw_level2_2sm"]
 L0_F16 = ["blackwell_f16_cubic_128x256", "blackwell_f16_cubic_128x128", "blackwell_f16_cubic_2sm_256x256"]
 L0_F32 = ["blackwell_f32_cubic_128x256", "blackwell_f32_cubic_128x128", "blackwell_f32_cubic_2sm_256x256"]
 
 
 def _dt(kernel):
+    if "_bf16_" in kernel:
+        return "bf16"
     return "f16" if "_f16_" in kernel else ("f64" if "_f64_" in kernel else "f32")
 
 
@@ -40,12 +46,12 @@ def _run(kernel, a_np, b_np, device):
 
     from subcuber_b200 import runner
 
-    a = torch.from_numpy(a_np).to(device)
-    b = torch.from_numpy(b_np).to(device)
+    a = runner.to_torch(a_np, device)
+    b = runner.to_torch(b_np, device)
     d = torch.full((a.shape[0], b.shape[1]), float("nan"), dtype=a.dtype, device=device)
     runner.gemm(kernel, a, b, d)
     torch.cuda.synchronize()
-    return d.cpu().numpy()
+    return runner.to_numpy(d)
 
 
 def _rel_fro(x, truth):
@@ -56,7 +62,7 @@ def _rel_fro(x, truth):
 SMALL_SHAPES = [(256, 512, 128), (384, 768, 320), (272, 528, 144), (2, 16, 16), (130, 48, 80), (1024, 1024, 1024)]
 
 
-@pytest.mark.parametrize("kernel", L0_F16 + L0_F32 + L1_F16 + L1_F32 + STRASSEN_F16 + STRASSEN_F32)
+@pytest.mark.parametrize("kernel", L0_F16 + L0_F32 + L1_F16 + L1_F32 + STRASSEN_F16 + STRASSEN_F32 + BF16)
 @pytest.mark.parametrize("shape", SMALL_SHAPES)
 def test_bit_exact_on_harness_values(kernel, shape, oracle, cuda_device):
     from subcuber_b200 import inputs
@@ -66,14 +72,14 @@ def test_bit_exact_on_harness_values(kernel, shape, oracle, cuda_device):
     a, b = inputs.operands(dt, "harness", m, n, k, seed=m + n + k)
     got = _run(kernel, a, b, cuda_device)
     want = oracle.sw_gemm(dt, _level(kernel), a, b)
-    assert not np.isnan(got).any()
+    assert not np.isnan(got.astype(np.float32)).any()
     assert np.array_equal(got, want), f"{np.count_nonzero(got != want)} elements differ from the oracle"
     truth = a.astype(np.float64) @ b.astype(np.float64)
     if dt == "f32":
         assert np.array_equal(got.astype(np.float64), truth)
 
 
-@pytest.mark.parametrize("kernel", L2_F16 + L2_F32)
+@pytest.mark.parametrize("kernel", L2_F16 + L2_F32 + L2_BF16)
 @pytest.mark.parametrize("shape", [(512, 1024, 256), (544, 1056, 288), (4, 32, 32), (260, 96, 160), (1024, 1024, 512),
                                    (2048, 1536, 512)])
 def test_level2_bit_exact_on_harness_values(kernel, shape, oracle, cuda_device):
@@ -87,7 +93,7 @@ def test_level2_bit_exact_on_harness_values(kernel, shape, oracle, cuda_device):
     a, b = inputs.operands(dt, "harness", m, n, k, seed=m + n + k)
     got = _run(kernel, a, b, cuda_device)
     want = oracle.sw_gemm(dt, 2, a, b)
-    assert not np.isnan(got).any()
+    assert not np.isnan(got.astype(np.float32)).any()
     assert np.array_equal(got, want), f"{np.count_nonzero(got != want)} elements differ from the oracle"
     if dt == "f32":
         assert np.array_equal(got.astype(np.float64), a.astype(np.float64) @ b.astype(np.float64))
@@ -553,6 +559,54 @@ def test_level0_agrees_with_cublas(cuda_device):
     assert diff <= 0.07  # both round an fp32 sum of 1024 products to fp16 (values up to ~64: ulp 0.03)
 
 
+# ------------------------------------------------------------------------------------------- bfloat16
+@pytest.mark.parametrize("kernel", BF16 + L2_BF16)
+@pytest.mark.parametrize("shape", [(1024, 1024, 1024), (1536, 640, 1152), (1001, 776, 264)])
+def test_uniform_inputs_bf16(kernel, shape, oracle, cuda_device):
+    """Inexact inputs: error against the fp64 product no worse than 1.5x that of the reference routine with bfloat16
+    storage (its templates instantiated for the type; the zero-padded problem where extents do not divide)."""
+    from subcuber_b200 import inputs
+
+    m, n, k = shape
+    a, b = inputs.operands("bf16", "uniform1", m, n, k, seed=5)
+    got = _run(kernel, a, b, cuda_device)
+    truth = a.astype(np.float64) @ b.astype(np.float64)
+    ref = _padded_oracle(oracle, "bf16", _level(kernel), a, b)
+    err, ref_err = _rel_fro(got, truth), _rel_fro(ref, truth)
+    assert err <= 1.5 * ref_err, f"rel. Frobenius error {err:.3e} vs reference routine {ref_err:.3e}"
+    assert err < 2e-2  # bfloat16 keeps 8 significant bits; level-1 presums are rounded to it once
+
+
+@pytest.mark.parametrize("kernel", ["blackwell_bf16_sw_interleaved_presum_2sm", "blackwell_bf16_sw_level2_2sm"])
+def test_alpha_beta_bf16(kernel, oracle, cuda_device):
+    import torch
+
+    from subcuber_b200 import inputs, runner
+
+    m, n, k = (528, 1056, 288) if _level(kernel) == 2 else (272, 528, 144)
+    a_np, b_np = inputs.operands("bf16", "harness", m, n, k, seed=17)
+    c_np = inputs.operands("bf16", "harness", m, n, n, seed=18)[0]
+    a, b, c = (runner.to_torch(x, cuda_device) for x in (a_np, b_np, c_np))
+    d = runner.gemm(kernel, a, b, alpha=2.0, beta=-0.5, c=c)
+    torch.cuda.synchronize()
+    want = oracle.sw_gemm("bf16", _level(kernel), a_np, b_np, alpha=2.0, beta=-0.5, Cin=c_np)
+    assert np.array_equal(runner.to_numpy(d), want)
+
+
+def test_bf16_agrees_with_cublas(cuda_device):
+    import torch
+
+    from subcuber_b200 import inputs, runner
+
+    a = inputs.fill_device("bf16", "uniform1", (1024, 1024), seed=3, device=cuda_device)
+    b = inputs.fill_device("bf16", "uniform1", (1024, 1024), seed=3, subsequence=1, device=cuda_device)
+    d_ours = runner.gemm("blackwell_bf16_cubic_2sm_256x256", a, b)
+    d_blas, _ = runner.run_kernel("cublas_bf16", a, b)
+    torch.cuda.synchronize()
+    diff = (d_blas.double() - d_ours.double()).abs().max().item()
+    assert diff <= 0.26  # both round an fp32 sum of 1024 products to bfloat16 (values up to ~32: ulp 0.125)
+
+
 # --------------------------------------------------------------------------------------- ABI behaviour
 def test_run_entry_point_error_codes(cuda_device):
     import torch
@@ -602,15 +656,15 @@ def test_host_buffer_call_and_determinism(oracle, cuda_device):
     assert np.allclose(d2.astype(np.float64), d4.astype(np.float64), rtol=2e-3, atol=2e-2)
 
 
-@pytest.mark.parametrize("dt", ["f16", "f32", "f64"])
+@pytest.mark.parametrize("dt", ["f16", "f32", "f64", "bf16"])
 @pytest.mark.parametrize("dist", ["uniform1", "harness", "normal"])
 def test_device_fill_matches_host_fill(dt, dist, cuda_device):
-    from subcuber_b200 import inputs
+    from subcuber_b200 import inputs, runner
 
     h = inputs.fill_host(dt, dist, (257, 129), seed=6, subsequence=1)
-    d = inputs.fill_device(dt, dist, (257, 129), seed=6, subsequence=1, device=cuda_device).cpu().numpy()
+    d = runner.to_numpy(inputs.fill_device(dt, dist, (257, 129), seed=6, subsequence=1, device=cuda_device))
     if dist == "normal":
-        assert np.allclose(h.astype(np.float64), d.astype(np.float64), rtol=2e-3, atol=2e-3)
+        assert np.allclose(h.astype(np.float64), d.astype(np.float64), rtol=1e-2 if dt == "bf16" else 2e-3, atol=2e-3)
     else:
         assert np.array_equal(h, d)
 

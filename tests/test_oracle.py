@@ -7,7 +7,17 @@ import numpy as np
 import pytest
 
 GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "ref_oracle_vectors.npz")
-DT = {0: "f16", 1: "f32", 2: "f64"}
+DT = {0: "f16", 1: "f32", 2: "f64", 4: "bf16"}
+
+
+def _load(z, key, code):
+    """bfloat16 arrays are stored as their 16-bit patterns."""
+    x = z[key]
+    if code == 4:
+        import ml_dtypes
+
+        return x.view(ml_dtypes.bfloat16)
+    return x
 
 
 def _cases():
@@ -22,9 +32,10 @@ def test_golden_vectors_bit_exact(oracle):
     for nm in names:
         code, level, m, n, k, _ = (int(v) for v in z[nm + "_meta"])
         alpha, beta = (float(v) for v in z[nm + "_ab"])
-        cin = z[nm + "_c"] if (nm + "_c") in z.files else None
-        got = oracle.sw_gemm(DT[code], level, z[nm + "_a"], z[nm + "_b"], alpha=alpha, beta=beta, Cin=cin)
-        want = z[nm + "_d"]
+        cin = _load(z, nm + "_c", code) if (nm + "_c") in z.files else None
+        got = oracle.sw_gemm(DT[code], level, _load(z, nm + "_a", code), _load(z, nm + "_b", code), alpha=alpha,
+                             beta=beta, Cin=cin)
+        want = _load(z, nm + "_d", code)
         assert got.dtype == want.dtype and got.shape == (m, n)
         assert np.array_equal(got, want), f"{nm}: oracle differs from the reference kernels' output"
 
@@ -40,7 +51,7 @@ def test_golden_inputs_come_from_the_seeded_generator():
         if dist_name[dist] == "normal":
             assert np.allclose(a, z[nm + "_a"], rtol=1e-5, atol=1e-6)
         else:
-            assert np.array_equal(a, z[nm + "_a"]) and np.array_equal(b, z[nm + "_b"])
+            assert np.array_equal(a, _load(z, nm + "_a", code)) and np.array_equal(b, _load(z, nm + "_b", code))
 
 
 def test_golden_presums(oracle):
@@ -51,7 +62,7 @@ def test_golden_presums(oracle):
         assert np.array_equal(pb, z[f"presum_{dt}_pb"])
 
 
-@pytest.mark.parametrize("dt", ["f16", "f32", "f64"])
+@pytest.mark.parametrize("dt", ["f16", "f32", "f64", "bf16"])
 @pytest.mark.parametrize("shape", [(8, 8, 8), (64, 48, 32), (130, 66, 34), (33, 20, 16), (2, 2, 2)])
 def test_against_reference_host_build(oracle, dt, shape):
     if oracle.ref_oracle() is None:
@@ -86,7 +97,7 @@ def test_presum_rounding_convention_f16(oracle):
     assert np.array_equal(pb[3], (s3 - b2).astype(np.float16))
 
 
-@pytest.mark.parametrize("dt,tol", [("f16", 2e-2), ("f32", 2e-5), ("f64", 1e-13), ("tf32", 5e-3)])
+@pytest.mark.parametrize("dt,tol", [("f16", 2e-2), ("f32", 2e-5), ("f64", 1e-13), ("tf32", 5e-3), ("bf16", 2e-2)])
 @pytest.mark.parametrize("level", [0, 1, 2])
 def test_levels_agree_with_fp64_matmul(oracle, dt, tol, level):
     rng = np.random.default_rng(level)
