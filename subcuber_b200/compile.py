@@ -309,18 +309,23 @@ class StrassenCompiler:
 
 
 def build(level, m, n, k, datatype, output_dir, dry_run=False, hw="A100", print_all_recursive=False,
-          print_all_schedules=False):
+          print_all_schedules=False, algorithm="strassen_winograd"):
     """Generate the schedule and emit the artefacts for it.  Signature of the reference's `build`
-    (src/compile.py:563-653); returns the final schedule, or the list of all schedules when
-    `print_all_schedules` is set (which implies a dry run).
+    (src/compile.py:563-653) plus `algorithm` ("strassen_winograd", or "strassen" for Strassen's original algorithm,
+    level 1); returns the final schedule, or the list of all schedules when `print_all_schedules` is set (which
+    implies a dry run).
 
     Artefacts written to `output_dir` (or listed, with `dry_run`): `schedule.json` (schedule, fusion groups and
     the Blackwell launch plan) and, for level 1, `tile_programs.json` / `sw_tile_programs.inc`: the per-tile
     programs of each launch in the form the CUDA kernels interpret.
     """
     from . import emit
+    from .algos.strassen_level1 import strassen
     from .algos.strassen_winograd_level1 import strassen_winograd
 
+    if algorithm not in ("strassen_winograd", "strassen"):
+        raise ValueError(f"Unsupported algorithm '{algorithm}'. Supported: strassen_winograd, strassen")
+    alg_func = strassen_winograd if algorithm == "strassen_winograd" else strassen
     dtype = datatype.lower()
     if dtype not in ("fp32", "f32", "fp16", "f16"):
         raise ValueError(f"Unsupported datatype '{datatype}'. Supported: f32, f16")
@@ -332,7 +337,7 @@ def build(level, m, n, k, datatype, output_dir, dry_run=False, hw="A100", print_
         print(f"Total schedules at level {level}: {total}")
         found = []
         try:
-            for idx, schedule in enumerate(compiler.iter_all_schedules(strassen_winograd, level=level, mnk=(m, n, k)), 1):
+            for idx, schedule in enumerate(compiler.iter_all_schedules(alg_func, level=level, mnk=(m, n, k)), 1):
                 print(f"Schedule {idx}/{total}: {schedule}")
                 kernel = "K2" if "K2(" in str(schedule) else "K4"
                 print(f"Fusion Schedule {idx}/{total}: "
@@ -342,11 +347,11 @@ def build(level, m, n, k, datatype, output_dir, dry_run=False, hw="A100", print_
             pass
         return found
 
-    final_schedule = compiler.gen_sched(strassen_winograd, level=level, mnk=(m, n, k))
+    final_schedule = compiler.gen_sched(alg_func, level=level, mnk=(m, n, k))
     print(f"Generated Optimal Schedule:\n{final_schedule}")
     print(f"Generated Fusion Schedule:\n{compiler.last_fusion_schedule}")
 
-    plan = emit.plan_for_schedule(final_schedule, level, (m, n, k), "f16" if "16" in dtype else "f32")
+    plan = emit.plan_for_schedule(final_schedule, level, (m, n, k), "f16" if "16" in dtype else "f32", algorithm)
     files = emit.artefacts(final_schedule, compiler.last_fusion_schedule, plan)
     for name, text in files.items():
         path = os.path.join(output_dir, name)

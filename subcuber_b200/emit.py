@@ -418,8 +418,12 @@ def verify_programs(programs: Dict[str, tp.Program]) -> None:
 
 
 # --------------------------------------------------------------------------------------------- schedule -> plan
-def plan_for_schedule(schedule: list, level: int, mnk: Tuple[int, int, int], dtype: str) -> dict:
+def plan_for_schedule(schedule: list, level: int, mnk: Tuple[int, int, int], dtype: str,
+                      algorithm: str = "strassen_winograd") -> dict:
     """Map a schedule of the generator (K1/K2/K4 vocabulary) to launches of this library.
+
+    algorithm "strassen" (Strassen's original algorithm, algos/strassen_level1.py) has one plan: level 1, all seven
+    products of a tile in one launch with the operand sums formed in shared memory.
 
       ['K2(..)']                       -> one launch: all seven products per tile, presums formed in shared memory
       ['K1(m0)', 'K4(m1)', ... 'K4(m6)'] -> two launches: {m0, m1} + presum materialisation, then {m4, m2, m5, m3, m6}
@@ -428,6 +432,15 @@ def plan_for_schedule(schedule: list, level: int, mnk: Tuple[int, int, int], dty
     m, n, k = mnk
     if level <= 0:
         return {"level": 0, "kernel": f"blackwell_{dtype}_cubic_2sm_256x256", "launches": [{"program": "level0"}]}
+    if algorithm == "strassen":
+        if level != 1:
+            raise ValueError("Strassen's original algorithm is planned for level 1 only")
+        return {"level": 1, "algorithm": "strassen", "kernel": f"blackwell_{dtype}_strassen_fused_presum_2sm",
+                "mnk": [m, n, k],
+                "launches": [{"program": "level1_strassen", "products": ["m1", "m4", "m7", "m5", "m3", "m6", "m2"],
+                              "presum": "formed in shared memory by the presum warps"}]}
+    if algorithm != "strassen_winograd":
+        raise ValueError(f"unknown algorithm '{algorithm}'")
     labels = [s if isinstance(s, str) else next(iter(s)) for s in schedule]
     if len(labels) == 1 and labels[0].startswith("K2("):
         plan = {"level": 1, "kernel": f"blackwell_{dtype}_sw_fused_presum",

@@ -148,3 +148,40 @@ def test_bilinear_forms_from_the_dsl():
         t = emit.bilinear_form(part)
         assert sorted(zip(*np.nonzero(t))) == want[q] and t.sum() == 2
     assert emit.quadrant_vector(ms[5].op1).tolist() == [1, 1, -1, -1]   # a1s2 = a1 - (a2 + a3 - a0)
+
+
+def test_strassen_original_algorithm_through_the_dsl(tmp_path, capsys):
+    """A second <2,2,2;7> algorithm stated in the DSL: the same block product, a generated tile program that the
+    checker accepts, and a build() plan that names the kernels that run it."""
+    import json
+
+    from subcuber_b200.algos.strassen_level1 import strassen
+
+    c, ms = strassen(4, 4, 4)
+    assert [m.name for m in ms] == ["m1", "m2", "m3", "m4", "m5", "m6", "m7"]
+    want = {0: [(0, 0), (1, 2)], 1: [(0, 1), (1, 3)], 2: [(2, 0), (3, 2)], 3: [(2, 1), (3, 3)]}
+    for q, part in enumerate(c.parts):
+        t = emit.bilinear_form(part)
+        assert sorted(zip(*np.nonzero(t))) == want[q] and t.sum() == 2
+    pg = emit.level1_strassen_program(ms)
+    assert pg.nproducts == 7 and pg.nepilogues == 6 and pg.needs_feed == 1
+    assert max(pr.a.nterms for pr in (pg.product[i] for i in range(7))) == 2   # no operand sums more than two blocks
+    # numeric run of the program on integer blocks
+    rng = np.random.default_rng(3)
+    a = rng.integers(-3, 4, size=(8, 12)).astype(np.int64)
+    b = rng.integers(-3, 4, size=(12, 6)).astype(np.int64)
+    qa, qb = emit._quadrants(a), emit._quadrants(b)
+    views = {i: qa[i] for i in range(4)}
+    views.update({8 + i: qb[i] for i in range(4)})
+    out = {}
+    emit.run_program_numeric(pg, views, {}, out)
+    assert np.array_equal(np.block([[out[0], out[1]], [out[2], out[3]]]), a @ b)
+    sched = sbc.build(1, 8192, 8192, 8192, "f16", str(tmp_path), hw="B200", algorithm="strassen")
+    capsys.readouterr()
+    assert len(sched) == 7 and sched[0].startswith("K1(")
+    plan = json.loads((tmp_path / "schedule.json").read_text())["plan"]
+    assert plan["kernel"] == "blackwell_f16_strassen_fused_presum_2sm"
+    assert [l["program"] for l in plan["launches"]] == ["level1_strassen"]
+    assert "level1_strassen" in json.loads((tmp_path / "tile_programs.json").read_text())
+    with pytest.raises(ValueError):
+        sbc.build(2, 8192, 8192, 8192, "f16", str(tmp_path), hw="B200", algorithm="strassen")
