@@ -197,6 +197,71 @@ def gemm(kernel: str, a: torch.Tensor, b: torch.Tensor, d: Optional[torch.Tensor
     return d
 
 
+class HostPipeline:
+    """GEMMs on operands that live in pinned host memory, with the copies overlapped with the compute: while step i
+    runs its kernels, step i + 1's operands travel to the device and step i - 1's result travels back (three streams,
+    two sets of device buffers, PCIe used in both directions at once).  Every step still moves all of its bytes.
+
+        pipe = HostPipeline(kernel, m, n, k, torch.float16, device)
+        for a_host, b_host, d_host in work: pipe.submit(a_host, b_host, d_host)
+        pipe.finish()
+    """
+
+    def __init__(self, kernel: str, m: int, n: int, k: int, dtype: torch.dtype, device):
+        self.kernel, self.m, self.n, self.k, self.device = kernel, m, n, k, torch.device(device)
+        self.ws = Workspace(kernel, m, n, k, device)
+        self.s_in, self.s_mm, self.s_out = (torch.cuda.Stream(device) for _ in range(3))
+        self.slots = [{"a": torch.empty((m, k), dtype=dtype, device=device),
+                       "b": torch.empty((k, n), dtype=dtype, device=device),
+                       "d": torch.empty((m, n), dtype=dtype, device=device),
+                       "in": torch.cuda.Event(), "mm": torch.cuda.Event(), "out": torch.cuda.Event(), "used": False}
+                      for _ in range(2)]
+        self.steps = 0
+
+    def submit(self, a_host: torch.Tensor, b_host: torch.Tensor, d_host: torch.Tensor) -> None:
+        """Enqueue D = A @ B for one set of pinned host tensors; returns at once."""
+        for t in (a_host, b_host, d_host):
+            if t.is_cuda or not t.is_pinned() or not t.is_contiguous():
+                raise ValueError("HostPipeline takes contiguous tensors in pinned host memory")
+        lib = _lib.load()
+        slot = self.slots[self.steps % 2]
+        self.steps += 1
+        if slot["used"]:
+            self.s_in.wait_event(slot["mm"])    # the kernels that read this slot's operands have finished
+        with torch.cuda.stream(self.s_in):
+            slot["a"].copy_(a_host, non_blocking=True)
+            slot["b"].copy_(b_host, non_blocking=True)
+            slot["in"].record(self.s_in)
+        self.s_mm.wait_event(slot["in"])
+        if slot["used"]:
+            self.s_mm.wait_event(slot["out"])   # the slot's previous result has left
+        with torch.cuda.device(self.device):
+            rc = lib.sb200_gemm(self.kernel.encode(), slot["a"].data_ptr(), slot["b"].data_ptr(), slot["d"].data_ptr(),
+                                self.m, self.n, self.k, self.ws.ptr, self.ws.nbytes, self.s_mm.cuda_stream)
+        if rc != 0:
+            raise KernelError(self.kernel, rc)
+        slot["mm"].record(self.s_mm)
+        self.s_out.wait_event(slot["mm"])
+        with torch.cuda.stream(self.s_out):
+            d_host.copy_(slot["d"], non_blocking=True)
+            slot["out"].record(self.s_out)
+        slot["used"] = True
+
+    def join(self, stream: torch.cuda.Stream) -> None:
+        """Make `stream` wait for everything submitted so far (no host synchronisation)."""
+        for slot in self.slots:
+            if slot["used"]:
+                stream.wait_event(slot["out"])
+
+    def finish(self) -> None:
+        """Wait for everything submitted so far and check the device status word."""
+        for s in (self.s_in, self.s_mm, self.s_out):
+            s.synchronize()
+        rc = _lib.load().sb200_gemm_status(self.ws.ptr, self.s_mm.cuda_stream)
+        if rc != 0:
+            raise KernelError(self.kernel, rc)
+
+
 def gemm_colmajor(kernel: str, a_cm: torch.Tensor, b_cm: torch.Tensor, m: int, n: int, k: int) -> torch.Tensor:
     """Column-major problem: `a_cm` holds A (m x k) column-major, i.e. it is the contiguous (k x m) tensor A^T; `b_cm`
     likewise is the contiguous (n x k) tensor B^T.  Returns the contiguous (n x m) tensor D^T = column-major D."""

@@ -643,6 +643,30 @@ def test_workspace_checks(lib, cuda_device):
     assert lib.sb200_gemm_status(base, None) == 0
 
 
+def test_host_pipeline_overlaps_copies_and_keeps_results(cuda_device):
+    """Operands in pinned host memory, copies overlapped with the kernels: every step's result equals the plain call's."""
+    import torch
+
+    from subcuber_b200 import inputs, runner
+
+    kernel = "blackwell_f16_sw_interleaved_presum_2sm"
+    m, n, k = 768, 1024, 512
+    pipe = runner.HostPipeline(kernel, m, n, k, torch.float16, cuda_device)
+    work, want = [], []
+    for step in range(5):
+        a, b = inputs.operands("f16", "uniform1", m, n, k, seed=30 + step)
+        work.append((torch.from_numpy(a).pin_memory(), torch.from_numpy(b).pin_memory(),
+                     torch.full((m, n), float("nan"), dtype=torch.float16).pin_memory()))
+        want.append(_run(kernel, a, b, cuda_device))
+    for a_h, b_h, d_h in work:
+        pipe.submit(a_h, b_h, d_h)
+    pipe.finish()
+    for (_, _, d_h), w in zip(work, want):
+        assert np.array_equal(d_h.numpy(), w)
+    with pytest.raises(ValueError):
+        pipe.submit(torch.zeros((m, k), dtype=torch.float16), work[0][1], work[0][2])   # not pinned
+
+
 def test_host_buffer_call_and_determinism(oracle, cuda_device):
     from subcuber_b200 import inputs, runner
 
