@@ -40,8 +40,8 @@ UNIT = "TFLOPS"
 # DRAM bytes (read + write) per launch of the dominant kernel from one ncu capture; see profiles/.
 # key: (kernel, m, n, k).  None = not captured for that workload.
 NCU_TRAFFIC_BYTES = {
-    # profiles/sw_tile_program_pair_kernel_f16_level1_8192.md: launch 2 read 1.321 GB + write 0.325 GB
-    ("blackwell_f16_sw_interleaved_presum_2sm", 8192, 8192, 8192): 1.646e9,
+    # profiles/sw_tile_program_pair_kernel_f16_level1_8192.md: launch 2 read 1.174 GB + write 0.313 GB
+    ("blackwell_f16_sw_interleaved_presum_2sm", 8192, 8192, 8192): 1.488e9,
     # profiles/sw_tile_program_kernel_1cta_f16_level1_8192.md (earlier build): launch 2 read 1.102 GB + write 0.159 GB
     ("blackwell_f16_sw_interleaved_presum", 8192, 8192, 8192): 1.261e9,
 }

@@ -69,35 +69,48 @@ PadPlan plan(const GemmArgs& a) {
   return p;
 }
 
-// dst (rows_d x cols_d, packed) = src (rows_s x cols_s, leading dimension ld_s) in its top-left corner, zeros elsewhere.
-// Element-wise accesses: neither side needs more than element alignment.
+// dst (rows_d x cols_d, packed, cols_d a multiple of 16 bytes) = src (rows_s x cols_s, leading dimension ld_s) in its
+// top-left corner, zeros elsewhere.  Each thread gathers 16 bytes of a destination row element by element (the source
+// needs no more than element alignment) and stores them at once.
 template <typename T>
 __global__ void pad_copy_kernel(T* __restrict__ dst, int rows_d, int cols_d, const T* __restrict__ src, int rows_s,
                                 int cols_s, long long ld_s) {
-  const long long total = static_cast<long long>(rows_d) * cols_d;
+  constexpr int V = 16 / sizeof(T);
+  const int vec_per_row = cols_d / V;
+  const long long total = static_cast<long long>(rows_d) * vec_per_row;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const int r = static_cast<int>(i / cols_d);
-    const int c = static_cast<int>(i - static_cast<long long>(r) * cols_d);
-    dst[i] = (r < rows_s && c < cols_s) ? src[r * ld_s + c] : T(0);
+    const int r = static_cast<int>(i / vec_per_row);
+    const int c0 = static_cast<int>(i - static_cast<long long>(r) * vec_per_row) * V;
+    alignas(16) T tmp[V];
+#pragma unroll
+    for (int e = 0; e < V; ++e) tmp[e] = (r < rows_s && c0 + e < cols_s) ? src[r * ld_s + c0 + e] : T(0);
+    *reinterpret_cast<uint4*>(dst + static_cast<long long>(r) * cols_d + c0) = *reinterpret_cast<const uint4*>(tmp);
   }
 }
 
-// dst (rows x cols, leading dimension ld_d) = top-left corner of src (packed, cols_s columns)
+// dst (rows x cols, leading dimension ld_d) = top-left corner of src (packed, cols_s columns, a multiple of 16 bytes):
+// 16 bytes read at once, written element by element.
 template <typename T>
 __global__ void crop_copy_kernel(T* __restrict__ dst, long long ld_d, int rows, int cols, const T* __restrict__ src,
                                  int cols_s) {
-  const long long total = static_cast<long long>(rows) * cols;
+  constexpr int V = 16 / sizeof(T);
+  const int vec_per_row = (cols + V - 1) / V;
+  const long long total = static_cast<long long>(rows) * vec_per_row;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const int r = static_cast<int>(i / cols);
-    const int c = static_cast<int>(i - static_cast<long long>(r) * cols);
-    dst[r * ld_d + c] = src[static_cast<long long>(r) * cols_s + c];
+    const int r = static_cast<int>(i / vec_per_row);
+    const int c0 = static_cast<int>(i - static_cast<long long>(r) * vec_per_row) * V;
+    alignas(16) T tmp[V];
+    *reinterpret_cast<uint4*>(tmp) = *reinterpret_cast<const uint4*>(src + static_cast<long long>(r) * cols_s + c0);
+#pragma unroll
+    for (int e = 0; e < V; ++e)
+      if (c0 + e < cols) dst[r * ld_d + c0 + e] = tmp[e];
   }
 }
 
 int copy_grid(long long elements) {
-  const long long blocks = (elements + 255) / 256;
+  const long long blocks = (elements / 4 + 255) / 256;  // a thread moves 16 bytes (2 to 8 elements) per iteration
   return static_cast<int>(blocks < 148 * 16 ? (blocks < 1 ? 1 : blocks) : 148 * 16);
 }
 
