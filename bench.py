@@ -213,12 +213,17 @@ def main():
         from subcuber_b200 import multi_gpu
 
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        # the all-gather of B overlaps the GEMM of the step before: NCCL runs on a bounded number of SMs that the GEMM
+        # B is replicated by peer-to-peer copies on the copy engines (multi_gpu.PeerGather) unless SB200_GATHER=nccl
+        # asks for the NCCL all-gather (multi_gpu.PipelinedGather)
+        gather_cls = multi_gpu.PipelinedGather if os.environ.get("SB200_GATHER") == "nccl" else multi_gpu.PeerGather
+        if os.environ.get("SB200_NCCL_CTAS"):  # tuning knob: CTAs given to NCCL (and SMs kept out of the GEMM grid)
+            gather_cls.NCCL_CTAS = int(os.environ["SB200_NCCL_CTAS"])
+        # the exchange of B overlaps the GEMM of the step before: NCCL runs on a bounded number of SMs that the GEMM
         # grid leaves free (the persistent GEMM kernels would otherwise hold every SM until they end)
-        os.environ.setdefault("NCCL_MAX_CTAS", str(multi_gpu.PipelinedGather.NCCL_CTAS))
+        os.environ.setdefault("NCCL_MAX_CTAS", str(gather_cls.NCCL_CTAS))
         dist.init_process_group("nccl", device_id=device)
         sms = torch.cuda.get_device_properties(device).multi_processor_count
-        os.environ["SB200_SM_LIMIT"] = str(sms - multi_gpu.PipelinedGather.reserved_sms())
+        os.environ["SB200_SM_LIMIT"] = str(sms - gather_cls.reserved_sms())
 
     lib = _lib.load()
     kernel = args.kernel
@@ -234,7 +239,8 @@ def main():
         shard = multi_gpu.row_shard(k, world, rank)
         b_shard = b_full_ref[shard[0]:shard[1]].contiguous()
         del b_full_ref
-        gather = multi_gpu.PipelinedGather(b_shard, k, world)
+        gather = (gather_cls(b_shard, k, world, rank) if gather_cls is multi_gpu.PeerGather
+                  else gather_cls(b_shard, k, world))
         b = gather.bufs[0]
     else:
         b = inputs.fill_device(dtn, "uniform1", (k, n), seed=1, subsequence=1, device=device)
@@ -360,7 +366,7 @@ def main():
                        "seed 1" if level else f"{dtn} GEMM level 0, M=N=K={args.size}",
                        "kernel": kernel, "m": m * world, "n": n, "k": k, "level": level,
                        "l2": f"inputs larger than L2: {(m * k + k * n + m * n) * es / 2**20:.0f} MiB touched per step",
-                       "parallelism": f"row slabs x{world}" + (", B all-gathered every step over NCCL, overlapped with the GEMM of the step before" if world > 1 else "")},
+                       "parallelism": f"row slabs x{world}" + (f", B replicated every step ({'peer-to-peer copies on the copy engines' if gather_cls is multi_gpu.PeerGather else 'NCCL all-gather'}), overlapped with the GEMM of the step before" if world > 1 else "")},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches * args.steps, "roofline": roofline,
             "cpu_baseline": cpu_baseline,
         }
