@@ -277,8 +277,10 @@ def main():
     t_start = torch.cuda.Event(enable_timing=True)
     t_stop = torch.cuda.Event(enable_timing=True)
     t_start.record(stream)
+    host_t0 = time.perf_counter()
     for i in range(args.warmup, total_steps):
         step(i)
+    host_ms = (time.perf_counter() - host_t0) * 1e3 / args.steps  # host time to enqueue one step
     t_stop.record(stream)
     barrier()
     clocks = sampler.stop()
@@ -367,7 +369,7 @@ def main():
                        "kernel": kernel, "m": m * world, "n": n, "k": k, "level": level,
                        "l2": f"inputs larger than L2: {(m * k + k * n + m * n) * es / 2**20:.0f} MiB touched per step",
                        "parallelism": f"row slabs x{world}" + (f", B replicated every step ({'peer-to-peer copies on the copy engines' if gather_cls is multi_gpu.PeerGather else 'NCCL all-gather'}), overlapped with the GEMM of the step before" if world > 1 else "")},
-            "clocks": clocks, "e2e": e2e, "gpu_launches": launches * args.steps, "roofline": roofline,
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches * args.steps, "host_enqueue_ms_per_step": host_ms, "roofline": roofline,
             "cpu_baseline": cpu_baseline,
         }
         print(json.dumps(line), flush=True)
