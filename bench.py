@@ -8,7 +8,7 @@ One "step" is one GEMM D = A * B.  The default workload is the single-GPU config
 is quoted on: f16 inputs, fp32 accumulate, f16 output, Strassen-Winograd level 1 (presum variant),
 M = N = K = 8192, A and B i.i.d. uniform[-1, 1) from a seed (synthetic, generated on the device).
 With N > 1 GPUs (one process per GPU under torchrun) every rank owns an 8192-row slab of A and of C and a
-K/N-row shard of B; each step all-gathers B over NCCL (inside the timed region) and runs the local GEMM: weak
+K/N-row shard of B; each step replicates B across the GPUs (inside the timed region) and runs the local GEMM: weak
 scaling, per-GPU work fixed.
 
 The line printed by rank 0 carries: metric / value (effective TFLOPS = 2MNK / t, all GPUs), e2e (same metric
