@@ -223,7 +223,6 @@ def main():
         os.environ.setdefault("NCCL_MAX_CTAS", str(gather_cls.NCCL_CTAS))
         dist.init_process_group("nccl", device_id=device)
         sms = torch.cuda.get_device_properties(device).multi_processor_count
-        os.environ["SB200_SM_LIMIT"] = str(sms - gather_cls.reserved_sms())
 
     lib = _lib.load()
     kernel = args.kernel
@@ -239,8 +238,27 @@ def main():
         shard = multi_gpu.row_shard(k, world, rank)
         b_shard = b_full_ref[shard[0]:shard[1]].contiguous()
         del b_full_ref
-        gather = (gather_cls(b_shard, k, world, rank) if gather_cls is multi_gpu.PeerGather
-                  else gather_cls(b_shard, k, world))
+        if gather_cls is multi_gpu.PeerGather:
+            # symmetric memory needs peer mappings between all GPUs: where that cannot be set up, every rank falls back
+            # to the NCCL all-gather (the ranks agree first, so that none is left alone in a collective)
+            try:
+                gather = multi_gpu.PeerGather(b_shard, k, world, rank)
+                ok = 1
+            except Exception as exc:  # noqa: BLE001 - any setup failure means "use the other exchange"
+                print(f"[bench] rank {rank}: peer exchange unavailable ({exc}); using the NCCL all-gather", file=sys.stderr)
+                ok = 0
+            agreed = torch.tensor([ok], dtype=torch.int32, device=device)
+            dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
+            if int(agreed.item()) == 0:
+                gather_cls = multi_gpu.PipelinedGather
+                gather = None
+                # a new communicator with the all-gather's CTA bound
+                dist.destroy_process_group()
+                os.environ["NCCL_MAX_CTAS"] = str(gather_cls.NCCL_CTAS)
+                dist.init_process_group("nccl", device_id=device)
+        if gather is None:
+            gather = multi_gpu.PipelinedGather(b_shard, k, world)
+        os.environ["SB200_SM_LIMIT"] = str(sms - gather_cls.reserved_sms())
         b = gather.bufs[0]
     else:
         b = inputs.fill_device(dtn, "uniform1", (k, n), seed=1, subsequence=1, device=device)
