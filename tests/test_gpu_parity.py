@@ -213,6 +213,24 @@ def test_any_extents_uniform_inputs_f16(kernel, shape, oracle, cuda_device):
     assert _rel_fro(got, truth) <= 1.5 * _rel_fro(ref, truth)
 
 
+def test_any_extents_column_major_and_auto(oracle, cuda_device):
+    """The column-major entry point and the size-based kernel choice take the same sizes."""
+    import torch
+
+    from subcuber_b200 import inputs, runner
+
+    m, n, k = 515, 1001, 264
+    a, b = inputs.operands("f16", "harness", m, n, k, seed=12)
+    want = oracle.sw_gemm("f16", 0, a, b)
+    a_cm = torch.from_numpy(np.ascontiguousarray(a.T)).to(cuda_device)   # k x m: A stored column-major
+    b_cm = torch.from_numpy(np.ascontiguousarray(b.T)).to(cuda_device)
+    d_cm = runner.gemm_colmajor("blackwell_f16_sw_interleaved_presum_2sm", a_cm, b_cm, m, n, k)
+    torch.cuda.synchronize()
+    assert np.array_equal(d_cm.cpu().numpy().T, want)
+    got = _run("blackwell_f16_sw_auto", a, b, cuda_device)
+    assert np.array_equal(got, want)
+
+
 def test_any_extents_split_last_wave(oracle, cuda_device, monkeypatch):
     from subcuber_b200 import inputs
 

@@ -46,6 +46,9 @@ def test_rejects_other_architectures_and_levels(binary):
     ("half", "2", ["blackwell_f16_sw_level2_2sm"]),
     ("f32", "all", ["blackwell_f32_cubic_2sm_256x256", "blackwell_f32_sw_level2", "cublas_tf32"]),
     ("fp64", "all", ["blackwell_f64_cubic_dmma", "blackwell_f64_sw_level1", "blackwell_f64_sw_level2", "cublas_f64"]),
+    ("bf16", "all", ["blackwell_bf16_cubic_2sm_256x256", "blackwell_bf16_sw_interleaved_presum_2sm",
+                     "blackwell_bf16_sw_level2_2sm", "cublas_bf16"]),
+    ("f16", "1", ["blackwell_f16_strassen_fused_presum_2sm"]),
 ])
 def test_table_on_gpu(binary, dtype, level, expect):
     # both flag forms: "--flag=value" and "--flag value"; "--level" is an alias of "--strassen_level"
@@ -58,3 +61,13 @@ def test_table_on_gpu(binary, dtype, level, expect):
         rows = [ln for ln in r.stdout.splitlines() if ln.startswith(name + " ")]
         assert rows and "skipped" not in rows[0], name
     assert "Best kernel" in r.stdout or "best" in r.stdout.lower()
+
+
+@pytest.mark.gpu
+def test_sizes_off_the_tile_grid_on_gpu(binary):
+    """Every positive size runs: short last blocks, and rows off the 16-byte grid through padded copies."""
+    r = _run(binary, "--m=1001", "--n=1037", "--k=523", "--dtype=f16", "--gpu_arch=blackwell", "--level=all",
+             "--iterations=2", "--warmup=1", "--streams=1", "--kernel_regex=blackwell")
+    assert r.returncode == 0, r.stderr
+    rows = [ln for ln in r.stdout.splitlines() if ln.startswith("blackwell_f16_")]
+    assert len(rows) >= 10 and not any("skipped" in ln for ln in rows)
