@@ -2,20 +2,23 @@
 """Benchmark of the Strassen-Winograd GEMM hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--size S] [--kernel NAME] [--no-cpu-baseline]
+                    [--size S] [--kernel NAME] [--no-cpu-baseline] [--no-sustained] [--no-cublas]
 
-One "step" is one GEMM D = A * B.  The default workload is the single-GPU configuration the headline metric
-is quoted on: f16 inputs, fp32 accumulate, f16 output, Strassen-Winograd level 1 (presum variant),
-M = N = K = 8192, A and B i.i.d. uniform[-1, 1) from a seed (synthetic, generated on the device).
-With N > 1 GPUs (one process per GPU under torchrun) every rank owns an 8192-row slab of A and of C and a
-K/N-row shard of B; each step replicates B across the GPUs (inside the timed region) and runs the local GEMM: weak
-scaling, per-GPU work fixed.
+One "step" is one GEMM D = A * B.  The default workload is the configuration the headline metric is quoted on:
+f16 inputs, fp32 accumulate, f16 output, Strassen-Winograd level 1 (presum variant), M = N = K = 16384, A and B
+i.i.d. uniform[-1, 1) from a seed (synthetic, generated on the device).  With N > 1 GPUs (one process per GPU under
+torchrun) the SAME problem is divided over the GPUs (strong scaling): the GPUs form a pr x pc grid, GPU (i, j)
+computes the block C[i, j] with a local Strassen-Winograd GEMM, and every step first replicates the row slab of A
+inside each grid row and the column slab of B inside each grid column from the shards the GPUs own (inside the timed
+region, overlapped with the GEMM of the step before).
 
-The line printed by rank 0 carries: metric / value (effective TFLOPS = 2MNK / t, all GPUs), e2e (same metric
-through the C ABI with pinned HOST buffers, every step's copies inside the timed region and overlapped with the
-kernels of its neighbours), roofline of the dominant kernel
-(tensor-core bound; per-launch time from CUDA events recorded around every launch inside the timed loop),
-cpu_baseline (the CPU oracle on a bounded row sample), clocks sampled during the timed region, gpu_launches.
+The line printed by rank 0 carries: metric / value (effective TFLOPS = 2MNK / t, whole job), frac_of_dense_peak
+(value / nominal dense f16 peak per GPU), cublas (cuBLAS on the same buffers in the same process, timed in
+alternating rounds with this library so that both see the same thermal state), sustained (both again in loops of at
+least two seconds), e2e (same metric through the C ABI with pinned HOST buffers, every step's copies inside the
+timed region), roofline of the dominant kernel (tensor-core bound; per-launch time from CUDA events recorded around
+every launch inside the timed loop), cpu_baseline (the CPU oracle on a bounded row sample), clocks sampled during
+the timed region, gpu_launches.
 
 `--impl reference` times the reference project's own CPU implementation of the path (its oracle kernels compiled
 for the host, oracle/_ref) on a bounded row sample of the same workload with all host threads.
@@ -25,6 +28,7 @@ from __future__ import annotations
 import argparse
 import ctypes as C
 import json
+import math
 import os
 import statistics
 import sys
@@ -36,14 +40,17 @@ sys.path.insert(0, ROOT)
 
 METRIC = "effective TFLOPS (2MNK/t) f16/tf32 Strassen L1/L2 at 1/2/4/8 B200 vs cuBLAS"
 UNIT = "TFLOPS"
+DEFAULT_SIZE = 16384
+DEFAULT_KERNEL = "blackwell_f16_sw_interleaved_presum_2sm"
+# nominal dense tensor-core peak per GPU for the arithmetic type of the kernels (TFLOP/s)
+DENSE_PEAK = {"f16": 2250.0, "bf16": 2250.0, "f32": 1125.0, "f64": 40.0}
+CUBLAS_ROW = {"f16": "cublas_f16", "bf16": "cublas_bf16", "f32": "cublas_tf32", "f64": "cublas_f64"}
+ELEM_BYTES = {"f16": 2, "bf16": 2, "f32": 4, "f64": 8}
 
-# DRAM bytes (read + write) per launch of the dominant kernel from one ncu capture; see profiles/.
-# key: (kernel, m, n, k).  None = not captured for that workload.
+# DRAM bytes (read + write) per launch of the dominant kernel from one Nsight Compute capture of that launch
+# (dram__bytes_read.sum + dram__bytes_write.sum).  key: (kernel, m, n, k).  Absent = not captured for that workload.
 NCU_TRAFFIC_BYTES = {
-    # profiles/sw_tile_program_pair_kernel_f16_level1_8192.md: launch 2 read 1.174 GB + write 0.313 GB
     ("blackwell_f16_sw_interleaved_presum_2sm", 8192, 8192, 8192): 1.488e9,
-    # profiles/sw_tile_program_kernel_1cta_f16_level1_8192.md (earlier build): launch 2 read 1.102 GB + write 0.159 GB
-    ("blackwell_f16_sw_interleaved_presum", 8192, 8192, 8192): 1.261e9,
 }
 
 
@@ -93,6 +100,7 @@ class ClockSampler:
         if self._h is not None:
             self._thread = threading.Thread(target=self._loop, daemon=True)
             self._thread.start()
+        return self
 
     def stop(self):
         self._stop.set()
@@ -100,6 +108,18 @@ class ClockSampler:
             self._thread.join()
         return {"sm_mhz": (statistics.median(self.samples) if self.samples else None), "sm_max_mhz": self.max_mhz,
                 "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def _omp_threads(n=None):
+    """Sets (when `n` is given) and returns the OpenMP thread count of this process.  torchrun exports
+    OMP_NUM_THREADS=1 to its workers; the CPU arms use every host thread, so they set the count themselves."""
+    try:
+        gomp = C.CDLL("libgomp.so.1")
+        if n is not None:
+            gomp.omp_set_num_threads(int(n))
+        return int(gomp.omp_get_max_threads())
+    except OSError:
+        return 1
 
 
 def _cpu_run(kind, oracle, a_np, b_np, nrows):
@@ -134,17 +154,26 @@ def _cpu_calibrate(kind, oracle, a_np, b_np, target_s):
     return max(1, min(a_np.shape[0] // 2, int(target_s / per_row)))
 
 
+def _workload_text(dtn, level, m, n, k):
+    if level == 0:
+        return f"{dtn} GEMM level 0, M={m} N={n} K={k}, uniform[-1,1) from seed 1"
+    return f"{dtn} Strassen-Winograd level {level}, M={m} N={n} K={k}, uniform[-1,1) from seed 1"
+
+
 def reference_arm(args):
     """CPU reference: rank 0 alone times the reference's oracle kernels on a bounded row sample."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
-    import numpy as np
+    cores = os.cpu_count() or 1
+    os.environ["OMP_NUM_THREADS"] = str(cores)  # before the OpenMP runtime starts (torchrun sets it to 1)
+    import numpy as np  # noqa: F401
 
     from oracle import binding as ob
     from subcuber_b200 import inputs
 
     ob.build(ref=True)
+    threads = _omp_threads(cores)
     kind = "reference" if ob.ref_oracle() is not None else "port"
     if kind == "reference":
         ob.ref_oracle().ref_sw_gemm_rows.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_double,
@@ -152,7 +181,6 @@ def reference_arm(args):
                                                      C.c_int, C.c_int, C.c_int]
     size = args.size
     a_np, b_np = inputs.operands("f16", "uniform1", size, size, size, seed=1)
-    cores = os.cpu_count() or 1
     # calibrate the sample so one step takes about 1.5 s, then time exactly `steps` steps
     nrows = _cpu_calibrate(kind, ob, a_np, b_np, target_s=1.5)
     times = []
@@ -163,16 +191,18 @@ def reference_arm(args):
     tot_t = sum(t for t, _ in times)
     tot_rows = sum(r for _, r in times)
     value = 2.0 * tot_rows * size * size / tot_t / 1e12
-    sample = f"{times[0][1]} of {size} C rows per step (level-1 Strassen-Winograd, f16, {size}^3), {cores} threads"
+    sample = (f"{times[0][1]} of {size} C rows per step (level-1 Strassen-Winograd, f16, {size}^3), "
+              f"{threads} OpenMP threads on {cores} host cores")
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": 1e3 * tot_t / max(1, len(times)), "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
         # the same workload as the CUDA arm; every step covers a bounded sample of its rows (see cpu_baseline.sample)
-        "config": {"workload": f"f16 Strassen-Winograd level 1, M=N=K={size} per GPU, uniform[-1,1) from seed 1",
-                   "kernel": "reference oracle kernels compiled for the host", "m": size, "n": size, "k": size,
-                   "level": 1},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample},
+        "config": {"workload": _workload_text("f16", 1, size, size, size),
+                   "kernel": "reference oracle kernels compiled for the host" if kind == "reference"
+                   else "CPU restatement of the reference oracle", "m": size, "n": size, "k": size, "level": 1,
+                   "l2": "not applicable (CPU)", "parallelism": f"{threads} host threads"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -183,12 +213,14 @@ def reference_arm(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--size", type=int, default=8192, help="M = N = K of the per-GPU problem")
-    ap.add_argument("--kernel", default="blackwell_f16_sw_interleaved_presum_2sm")
+    ap.add_argument("--size", type=int, default=DEFAULT_SIZE, help="M = N = K of the whole problem")
+    ap.add_argument("--kernel", default=DEFAULT_KERNEL)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-sustained", action="store_true", help="skip the two-second loops")
+    ap.add_argument("--no-cublas", action="store_true", help="skip the cuBLAS comparison")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -209,89 +241,90 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: this backend has no CPU path")
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
+
+    lib = _lib.load()
+    kernel = args.kernel
+    rows_by_name = {r.name: r for r in runner.kernels()}
+    if kernel not in rows_by_name or not kernel.startswith("blackwell_"):
+        raise SystemExit(f"unknown kernel {kernel!r}: choose a blackwell_* row of the registry")
+    info = rows_by_name[kernel]
+    dtn = info.dtype                       # the registry row says which element type the kernel reads and writes
+    if dtn not in ELEM_BYTES:
+        raise SystemExit(f"bench.py cannot fill operands of type {dtn!r}")
+    tdt = runner.TORCH_DTYPE[dtn]
+    es = ELEM_BYTES[dtn]
+    M = N = K = args.size
+    resolved = kernel
+    if kernel.endswith("_sw_auto"):
+        resolved = lib.sb200_auto_kernel(dtn.encode(), M, N, K).decode()
+    level = rows_by_name[resolved].strassen_level
+
+    exchange = None
+    opts = None
+    grid_text = "1 GPU"
     if world > 1:
         from subcuber_b200 import multi_gpu
 
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        # B is replicated by peer-to-peer copies on the copy engines (multi_gpu.PeerGather) unless SB200_GATHER=nccl
-        # asks for the NCCL all-gather (multi_gpu.PipelinedGather)
-        gather_cls = multi_gpu.PipelinedGather if os.environ.get("SB200_GATHER") == "nccl" else multi_gpu.PeerGather
-        if os.environ.get("SB200_NCCL_CTAS"):  # tuning knob: CTAs given to NCCL (and SMs kept out of the GEMM grid)
-            gather_cls.NCCL_CTAS = int(os.environ["SB200_NCCL_CTAS"])
-        # the exchange of B overlaps the GEMM of the step before: NCCL runs on a bounded number of SMs that the GEMM
-        # grid leaves free (the persistent GEMM kernels would otherwise hold every SM until they end)
-        os.environ.setdefault("NCCL_MAX_CTAS", str(gather_cls.NCCL_CTAS))
+        os.environ.setdefault("NCCL_MAX_CTAS", "2")   # NCCL only carries set-up traffic and the final reductions here
         dist.init_process_group("nccl", device_id=device)
         sms = torch.cuda.get_device_properties(device).multi_processor_count
-
-    lib = _lib.load()
-    kernel = args.kernel
-    dtn = "f16" if "_f16_" in kernel else "f32"
-    tdt = torch.float16 if dtn == "f16" else torch.float32
-    es = 2 if dtn == "f16" else 4
-    m = n = k = args.size
-    # operands: this rank's A slab (subsequence 2*rank so slabs differ) and its row shard of B
-    a = inputs.fill_device(dtn, "uniform1", (m, k), seed=1, subsequence=2 * rank, device=device)
-    gather = None
-    if world > 1:
-        b_full_ref = inputs.fill_device(dtn, "uniform1", (k, n), seed=1, subsequence=1, device=device)
-        shard = multi_gpu.row_shard(k, world, rank)
-        b_shard = b_full_ref[shard[0]:shard[1]].contiguous()
-        del b_full_ref
-        if gather_cls is multi_gpu.PeerGather:
-            # symmetric memory needs peer mappings between all GPUs: where that cannot be set up, every rank falls back
-            # to the NCCL all-gather (the ranks agree first, so that none is left alone in a collective)
-            try:
-                gather = multi_gpu.PeerGather(b_shard, k, world, rank)
-                ok = 1
-            except Exception as exc:  # noqa: BLE001 - any setup failure means "use the other exchange"
-                print(f"[bench] rank {rank}: peer exchange unavailable ({exc}); using the NCCL all-gather", file=sys.stderr)
-                ok = 0
-            agreed = torch.tensor([ok], dtype=torch.int32, device=device)
-            dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
-            if int(agreed.item()) == 0:
-                gather_cls = multi_gpu.PipelinedGather
-                gather = None
-                # a new communicator with the all-gather's CTA bound
-                dist.destroy_process_group()
-                os.environ["NCCL_MAX_CTAS"] = str(gather_cls.NCCL_CTAS)
-                dist.init_process_group("nccl", device_id=device)
-        if gather is None:
-            gather = multi_gpu.PipelinedGather(b_shard, k, world)
-        os.environ["SB200_SM_LIMIT"] = str(sms - gather_cls.reserved_sms())
-        b = gather.bufs[0]
+        gp = multi_gpu.grid_plan(M, N, K, world, es, level=max(level, 1))
+        if gp.kind == "replica":
+            raise SystemExit(f"{M}x{N}x{K} does not divide over {world} GPUs")
+        m, n, k = gp.local_m, gp.local_n, K
+        # SMs left out of the GEMM grid for the few one-CTA flag kernels of the exchange (the persistent GEMM kernels
+        # would otherwise hold every SM until they end)
+        opts = runner.options(sm_limit=sms - multi_gpu.GridExchange.reserved_sms())
+        exchange = multi_gpu.GridExchange(gp, rank, dtn, device, seed=1)
+        grid_text = gp.describe()
     else:
+        m, n, k = M, N, K
+
+    if exchange is None:
+        a = inputs.fill_device(dtn, "uniform1", (m, k), seed=1, subsequence=0, device=device)
         b = inputs.fill_device(dtn, "uniform1", (k, n), seed=1, subsequence=1, device=device)
     d = torch.empty((m, n), dtype=tdt, device=device)
-    ws = runner.Workspace(kernel, m, n, k, device)
+    ws = runner.Workspace(kernel, m, n, k, device, opts)
     stream = torch.cuda.current_stream(device)
-    launches = lib.sb200_gemm_launches(kernel.encode())
+    launches = lib.sb200_gemm_launches(resolved.encode())
     total_steps = args.warmup + args.steps
     evl = lib.sb200_events_create((launches + 1) * args.steps)
+    opts_ref = C.byref(opts) if opts is not None else None
 
-    def step(i):
-        bi = gather.next() if gather else b  # replicated B of this step; the next step's all-gather is now in flight
-        if i >= args.warmup:
-            rc = lib.sb200_gemm_events(kernel.encode(), a.data_ptr(), bi.data_ptr(), d.data_ptr(), m, n, k, ws.ptr,
-                                       ws.nbytes, stream.cuda_stream, evl, (launches + 1) * (i - args.warmup))
+    def gemm(ai, bi, event_index=None):
+        if event_index is not None:
+            rc = lib.sb200_gemm_events(kernel.encode(), ai.data_ptr(), bi.data_ptr(), d.data_ptr(), m, n, k, ws.ptr,
+                                       ws.nbytes, stream.cuda_stream, evl, event_index, opts_ref)
         else:
-            rc = lib.sb200_gemm(kernel.encode(), a.data_ptr(), bi.data_ptr(), d.data_ptr(), m, n, k, ws.ptr, ws.nbytes,
-                                stream.cuda_stream)
+            rc = lib.sb200_gemm_opt(kernel.encode(), ai.data_ptr(), bi.data_ptr(), d.data_ptr(), m, n, k, ws.ptr,
+                                    ws.nbytes, stream.cuda_stream, opts_ref)
         if rc != 0:
             raise runner.KernelError(kernel, rc)
-        if gather:
-            gather.done(bi)
+
+    def step(i):
+        if exchange is not None:
+            ai, bi = exchange.next()   # this step's replicated slabs; the exchange of the step after is now in flight
+        else:
+            ai, bi = a, b
+        gemm(ai, bi, (launches + 1) * (i - args.warmup) if i >= args.warmup else None)
+        if exchange is not None:
+            exchange.done()
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize(device)
 
+    def check_status():
+        status = lib.sb200_gemm_status(ws.ptr, stream.cuda_stream)
+        if status != 0:
+            raise runner.KernelError(kernel, status)
+
     for i in range(args.warmup):
         step(i)
     barrier()
-    sampler = ClockSampler(local_rank)
-    sampler.start()
+    sampler = ClockSampler(local_rank).start()
     t_start = torch.cuda.Event(enable_timing=True)
     t_stop = torch.cuda.Event(enable_timing=True)
     t_start.record(stream)
@@ -303,14 +336,14 @@ def main():
     barrier()
     clocks = sampler.stop()
     elapsed_ms = t_start.elapsed_time(t_stop)
-    status = lib.sb200_gemm_status(ws.ptr, stream.cuda_stream)
-    if status != 0:
-        raise runner.KernelError(kernel, status)
+    check_status()
+    if exchange is not None:
+        exchange.check_status()
     if world > 1:
         t = torch.tensor([elapsed_ms], dtype=torch.float64, device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         elapsed_ms = float(t.item())
-    flops_step = 2.0 * m * n * k * world
+    flops_step = 2.0 * M * N * K            # the whole problem, however many GPUs share it
     value = flops_step * args.steps / (elapsed_ms * 1e-3) / 1e12
 
     # per-launch durations inside the timed region
@@ -324,27 +357,88 @@ def main():
     lib.sb200_events_destroy(evl)
     dom = max(range(launches), key=lambda i: per_launch[i])
     # algorithmic flops of a GEMM are 2MNK at every level; each of its 7 (49) products carries 1/7 (1/49) of them
-    level = {r.name: r.strassen_level for r in runner.kernels()}[kernel]
-    products = {0: [1], 1: {1: [7], 2: [2, 5]}.get(launches, [7]), 2: [2, 5] * 7}[level]
-    share = products[dom] / sum(products)
+    if dtn == "f64":
+        products = [0] * launches   # the fp64 path interleaves presum and product launches: whole GEMM as one unit
+        products[dom] = 1
+        share = per_launch[dom] / max(sum(per_launch), 1e-9)
+    else:
+        products = {0: [1], 1: {1: [7], 2: [2, 5]}.get(launches, [7]), 2: [2, 5] * 7}[level]
+        share = products[dom] / sum(products)
     peaks = _peaks()
     timed_s = elapsed_ms * 1e-3
     peak = peaks["burst"] if timed_s < 2.0 else peaks["sustained"]
     achieved = 2.0 * m * n * k * share / (per_launch[dom] * 1e-3) / 1e12
-    traffic = NCU_TRAFFIC_BYTES.get((kernel, m, n, k))
+    traffic = NCU_TRAFFIC_BYTES.get((resolved, m, n, k))
     roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                 "traffic": traffic, "kernel": f"launch {dom + 1} of {launches} ({products[dom]} of {sum(products)} products)",
                 "launch_ms": per_launch,
                 "peak_source": f"{peaks['source']} cuBLAS bf16 {'burst' if timed_s < 2.0 else 'sustained'}"}
 
+    # correctness evidence for the multi-GPU runs: every rank checks sampled rows of its block of the last step
+    # against the fp64 product of the operands it multiplied, and the block's checksum
+    parity = None
+    if exchange is not None:
+        ok = exchange.verify_block(d, ai_bi=exchange.last())
+        flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device=device)
+        dist.all_reduce(flag, op=dist.ReduceOp.SUM)
+        parity = {"ranks_ok": int(flag.item()), "ranks": world,
+                  "check": "sampled rows of every rank's block vs fp64 (rel. Frobenius < 2e-3) + block checksum"}
+
+    # cuBLAS on the same buffers in the same process, in alternating rounds so both arms see the same thermal state
+    cublas = None
+    sustained = None
+    blas_row = CUBLAS_ROW.get(dtn)
+    if world == 1 and blas_row and not args.no_cublas:
+        per_round = max(3, min(args.steps, 10))
+        ours_ms, blas_ms = [], []
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        for _ in range(3):
+            e0.record(stream)
+            for _ in range(per_round):
+                gemm(a, b)
+            e1.record(stream)
+            torch.cuda.synchronize(device)
+            ours_ms.append(e0.elapsed_time(e1) / per_round)
+            _, bms = runner.run_kernel(blas_row, a, b, d, warmup=1, iterations=per_round)
+            blas_ms.append(bms)
+        check_status()
+        o, c_ = statistics.median(ours_ms), statistics.median(blas_ms)
+        cublas = {"kernel": blas_row, "value": flops_step / (c_ * 1e-3) / 1e12, "ours_value": flops_step / (o * 1e-3) / 1e12,
+                  "ratio": c_ / o, "unit": UNIT, "rounds": 3, "steps_per_round": per_round,
+                  "how": "alternating rounds ours / cuBLAS on the same device buffers, median of the rounds"}
+        if not args.no_sustained:
+            n_long = max(args.steps, int(math.ceil(2200.0 / max(o, 1e-3))))
+            smp = ClockSampler(local_rank).start()
+            e0.record(stream)
+            for _ in range(n_long):
+                gemm(a, b)
+            e1.record(stream)
+            torch.cuda.synchronize(device)
+            s_clocks = smp.stop()
+            s_ours = e0.elapsed_time(e1) / n_long
+            check_status()
+            n_blas = max(args.steps, int(math.ceil(2200.0 / max(c_, 1e-3))))
+            smp = ClockSampler(local_rank).start()
+            _, s_blas = runner.run_kernel(blas_row, a, b, d, warmup=1, iterations=n_blas)
+            b_clocks = smp.stop()
+            sv = flops_step / (s_ours * 1e-3) / 1e12
+            bv = flops_step / (s_blas * 1e-3) / 1e12
+            sustained = {"value": sv, "cublas": bv, "ratio": sv / bv, "unit": UNIT,
+                         "frac": sv / peaks["sustained"], "peak": peaks["sustained"],
+                         "peak_source": f"{peaks['source']} cuBLAS bf16 sustained", "seconds": s_ours * n_long * 1e-3,
+                         "steps": n_long, "clocks": s_clocks, "cublas_clocks": b_clocks}
+
     # end to end: operands in pinned host memory, every step copies its A and B to the device and its D back, inside the
     # timed region; the copies of neighbouring steps overlap the kernels (runner.HostPipeline: three streams, two
     # sets of device buffers), so a step costs the slowest of its three parts
+    if exchange is not None:
+        a, b = exchange.last()
     e2e_steps = max(4, min(10, args.steps))
     a_host = a.cpu().pin_memory()
     b_host = b.cpu().pin_memory()
     d_host = torch.empty((m, n), dtype=tdt).pin_memory()
-    pipe = runner.HostPipeline(kernel, m, n, k, tdt, device)
+    pipe = runner.HostPipeline(kernel, m, n, k, tdt, device, opts)
     for _ in range(3):
         pipe.submit(a_host, b_host, d_host)
     pipe.finish()
@@ -364,34 +458,40 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t.item())
     e2e = {"value": flops_step * e2e_steps / (e2e_ms * 1e-3) / 1e12, "unit": UNIT,
-           "h2d_bytes_per_step": (m * k + k * n) * es, "d2h_bytes_per_step": m * n * es, "steps": e2e_steps}
+           "h2d_bytes_per_step": (m * k + k * n) * es, "d2h_bytes_per_step": m * n * es, "steps": e2e_steps,
+           "note": "bytes per GPU and step; every GPU copies the slabs it multiplies from its own pinned host memory"}
 
     cpu_baseline = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline and dtn == "f16":
+    if rank == 0 and world == 1 and not args.no_cpu_baseline and dtn == "f16" and level >= 1:
         from oracle import binding as ob
 
         ob.build(ref=False)
+        threads = _omp_threads(os.cpu_count() or 1)
         nrows = _cpu_calibrate("port", ob, a_host.numpy(), b_host.numpy(), target_s=12.0)
         dt, rows = _cpu_run("port", ob, a_host.numpy(), b_host.numpy(), nrows)
         tf = 2.0 * rows * n * k / dt / 1e12
-        cpu_baseline = {"value": tf, "unit": UNIT, "cores": os.cpu_count() or 1, "kind": "port",
-                        "sample": f"{rows} of {m} C rows of the same workload in {dt:.1f} s (CPU oracle, OpenMP)"}
+        cpu_baseline = {"value": tf, "unit": UNIT, "cores": threads, "kind": "port",
+                        "sample": f"{rows} of {m} C rows of the same workload in {dt:.1f} s (CPU oracle, level 1, OpenMP)"}
 
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": dtn, "data": "synthetic",
-            "config": {"workload": f"{dtn} Strassen-Winograd level {level}, M=N=K={args.size} per GPU, uniform[-1,1) from "
-                       "seed 1" if level else f"{dtn} GEMM level 0, M=N=K={args.size}",
-                       "kernel": kernel, "m": m * world, "n": n, "k": k, "level": level,
-                       "l2": f"inputs larger than L2: {(m * k + k * n + m * n) * es / 2**20:.0f} MiB touched per step",
-                       "parallelism": f"row slabs x{world}" + (f", B replicated every step ({'peer-to-peer copies on the copy engines' if gather_cls is multi_gpu.PeerGather else 'NCCL all-gather'}), overlapped with the GEMM of the step before" if world > 1 else "")},
-            "clocks": clocks, "e2e": e2e, "gpu_launches": launches * args.steps, "host_enqueue_ms_per_step": host_ms, "roofline": roofline,
-            "cpu_baseline": cpu_baseline,
+            "config": {"workload": _workload_text(dtn, level, M, N, K),
+                       "kernel": kernel if resolved == kernel else f"{kernel} -> {resolved}", "m": M, "n": N, "k": K,
+                       "level": level,
+                       "l2": f"inputs larger than L2: {(m * k + k * n + m * n) * es / 2**20:.0f} MiB touched per GPU and step",
+                       "parallelism": grid_text},
+            "frac_of_dense_peak": value / (DENSE_PEAK[dtn] * world),
+            "dense_peak": {"value": DENSE_PEAK[dtn] * world, "unit": "TFLOP/s", "source": "nominal, dense, per GPU x GPUs"},
+            "cublas": cublas, "sustained": sustained, "parity": parity,
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches * args.steps, "host_enqueue_ms_per_step": host_ms,
+            "roofline": roofline, "cpu_baseline": cpu_baseline,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
+        exchange.close()
         dist.destroy_process_group()
     return 0
 

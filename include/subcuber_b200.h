@@ -50,7 +50,8 @@ enum {
   SB200_STATUS_PRODUCER_TIMEOUT = 101, /* device: a bounded wait gave up (role in the code)        */
   SB200_STATUS_MMA_TIMEOUT = 102,
   SB200_STATUS_EPILOGUE_TIMEOUT = 103,
-  SB200_STATUS_PRESUM_TIMEOUT = 104
+  SB200_STATUS_PRESUM_TIMEOUT = 104,
+  SB200_STATUS_SPLIT_TIMEOUT = 105  /* the second K-half of a split tile waited in vain for the first half's sum */
 };
 
 /* ---- group 1: kernel_runner ABI (reference: src/cuda/kernel_runner.cpp:27-32) --------------------- */
@@ -152,6 +153,22 @@ size_t sb200_gemm_workspace_bytes(const char* kernel, int m, int n, int k);
  * 256-byte aligned device memory of at least sb200_gemm_workspace_bytes().  Allocates nothing. */
 int sb200_gemm(const char* kernel, const void* a, const void* b, void* d, int m, int n, int k, void* workspace,
                size_t workspace_bytes, sb200_stream_t stream);
+/* Per-call options of the tensor-core kernels (f16, bf16, f32); a NULL pointer or a zeroed struct means defaults.
+ * The reference's operators take their tuning through their Arguments struct in the same way (split_k_slices,
+ * raster order and swizzle: src/cuda/kernel_runner_support.cuh:328,341).  The workspace size depends on sm_limit and
+ * no_split (they decide which tiles are split along K), so size the workspace with the same options. */
+typedef struct sb200_gemm_options {
+  int sm_limit;         /* SMs the kernels may occupy; 0 = all.  A caller that overlaps its own kernels (e.g. a
+                           collective) with the GEMM keeps the remaining SMs free for them */
+  int no_split;         /* 1: never compute the tiles of a partial last wave as two K-halves */
+  int wait_limit_us;    /* bound of every device-side wait in microseconds; 0 = 2 s */
+  int drop_split_flags; /* test aid for the give-up path: the first K-halves of split tiles do not publish their flags,
+                           the second halves' waits run out after wait_limit_us and the status word reads
+                           SB200_STATUS_SPLIT_TIMEOUT; the output of such a call is incomplete */
+} sb200_gemm_options;
+size_t sb200_gemm_workspace_bytes_opt(const char* kernel, int m, int n, int k, const sb200_gemm_options* options);
+int sb200_gemm_opt(const char* kernel, const void* a, const void* b, void* d, int m, int n, int k, void* workspace,
+                   size_t workspace_bytes, sb200_stream_t stream, const sb200_gemm_options* options);
 /* General form D = alpha * (A * B) + beta * C (the argument set of the reference's operators,
  * include/cutlass/gemm/device/strassen_gemm.h:365-451; the reference's runner fixes alpha = 1, beta = 0).  C is m x n
  * row-major in the output type, may be the same buffer as D, and is read only when beta != 0.  The scaling is applied
@@ -182,7 +199,8 @@ int sb200_gemm_host(const char* kernel, const void* a_host, const void* b_host, 
  * resident on every GPU that uses this call until the process exits.  The call itself performs no cudaMalloc,
  * cudaFree or other allocating call.  Limits:
  *  - the problem's scratch (sb200_gemm_workspace_bytes of that kernel) must fit, else SB200_ERR_SCRATCH_TOO_LARGE
- *    is returned and nothing runs (32 MiB covers m = n = k = 2048; 3072^3 already needs 54 MiB);
+ *    is returned and nothing runs (the 33 MiB of the array cover m = n = k = 2048, which needs 32 MiB and 256 bytes;
+ *    2048 x 2048 x 2304 already needs 34 MiB, 3072^3 72 MiB, 4096^3 128 MiB);
  *  - one array per GPU, shared by all calls and never cleared between them except for what must start at zero
  *    (the status block, cleared on `stream` by every call): calls whose kernels could overlap on the GPU race on
  *    it, so order them on one stream (or otherwise serialise them);
@@ -190,7 +208,7 @@ int sb200_gemm_host(const char* kernel, const void* a_host, const void* b_host, 
  *    current) and loads the kernels: make that first call before starting any stream capture.
  * a, b, d: device pointers, packed row-major.  wait != 0: synchronise `stream` and return the device status word
  * (0 = ok); wait == 0: return after the launches are enqueued. */
-#define SB200_STATIC_SCRATCH_BYTES (32u << 20)
+#define SB200_STATIC_SCRATCH_BYTES (33u << 20)
 #define SB200_ERR_SCRATCH_TOO_LARGE 9
 int sb200_gemm_f16_sw_static_scratch(const void* a, const void* b, void* d, int m, int n, int k,
                                      sb200_stream_t stream, int wait);
@@ -218,7 +236,8 @@ sb200_event_list* sb200_events_create(int count);
 void sb200_events_destroy(sb200_event_list* list);
 int sb200_events_elapsed_ms(sb200_event_list* list, int first, int second, float* ms);
 int sb200_gemm_events(const char* kernel, const void* a, const void* b, void* d, int m, int n, int k, void* workspace,
-                      size_t workspace_bytes, sb200_stream_t stream, sb200_event_list* list, int first_index);
+                      size_t workspace_bytes, sb200_stream_t stream, sb200_event_list* list, int first_index,
+                      const sb200_gemm_options* options);
 
 /* The tile program tables the kernels interpret (csrc/tile_program.h), for inspection and tests.
  * which: "level0" | "level1_full_fly" | "level1_full_ws" | "level1_first" | "level1_first_early" | "level1_second" |

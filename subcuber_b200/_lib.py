@@ -8,8 +8,9 @@ from __future__ import annotations
 import ctypes as C
 import os
 
-_HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libsubcuber_b200.so")
+from . import build as _build
+
+LIB_PATH = _build.LIB
 
 
 class KernelRunnerBuffers(C.Structure):
@@ -38,6 +39,13 @@ class WorkspaceLayout(C.Structure):
                 ("kq", C.c_int), ("tiles_m", C.c_int), ("tiles_n", C.c_int), ("bn", C.c_int)]
 
 
+class GemmOptions(C.Structure):
+    """Mirror of `sb200_gemm_options`."""
+
+    _fields_ = [("sm_limit", C.c_int), ("no_split", C.c_int), ("wait_limit_us", C.c_int),
+                ("drop_split_flags", C.c_int)]
+
+
 _lib = None
 
 
@@ -49,9 +57,13 @@ def load(build_if_missing: bool = True) -> C.CDLL:
     if not os.path.exists(LIB_PATH):
         if not build_if_missing:
             raise RuntimeError(f"{LIB_PATH} is missing: run `python -m subcuber_b200.build`")
-        from . import build as _build
-
         _build.build()
+    elif not _build.up_to_date():
+        # a library older than its sources may no longer match the struct mirrors below
+        if build_if_missing and _build.have_nvcc():
+            _build.build()
+        else:
+            raise RuntimeError(f"{LIB_PATH} is older than its sources: run `python -m subcuber_b200.build`")
     lib = C.CDLL(LIB_PATH)
     lib.sb200_num_kernels.restype = C.c_int
     lib.sb200_kernel.restype = C.POINTER(KernelEntry)
@@ -61,6 +73,10 @@ def load(build_if_missing: bool = True) -> C.CDLL:
     lib.sb200_gemm_workspace_bytes.argtypes = [C.c_char_p, C.c_int, C.c_int, C.c_int]
     lib.sb200_gemm.argtypes = [C.c_char_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p,
                                C.c_size_t, C.c_void_p]
+    lib.sb200_gemm_workspace_bytes_opt.restype = C.c_size_t
+    lib.sb200_gemm_workspace_bytes_opt.argtypes = [C.c_char_p, C.c_int, C.c_int, C.c_int, C.POINTER(GemmOptions)]
+    lib.sb200_gemm_opt.argtypes = [C.c_char_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
+                                   C.c_void_p, C.c_size_t, C.c_void_p, C.POINTER(GemmOptions)]
     lib.sb200_gemm_ex.argtypes = [C.c_char_p, C.c_double, C.c_void_p, C.c_void_p, C.c_double, C.c_void_p, C.c_void_p,
                                   C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_size_t, C.c_void_p]
     lib.sb200_gemm_colmajor.argtypes = lib.sb200_gemm.argtypes
@@ -80,7 +96,7 @@ def load(build_if_missing: bool = True) -> C.CDLL:
     lib.sb200_events_destroy.argtypes = [C.c_void_p]
     lib.sb200_events_elapsed_ms.argtypes = [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_float)]
     lib.sb200_gemm_events.argtypes = [C.c_char_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
-                                      C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_int]
+                                      C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_int, C.POINTER(GemmOptions)]
     lib.sb200_gemm_f16_sw_static_scratch.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
                                                      C.c_void_p, C.c_int]
     _lib = lib

@@ -8,6 +8,7 @@ written next to this file (they are git-ignored build artefacts).
 """
 from __future__ import annotations
 
+import hashlib
 import os
 import shutil
 import subprocess
@@ -15,8 +16,11 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
-LIB = os.path.join(HERE, "libsubcuber_b200.so")
-RUNNER = os.path.join(HERE, "kernel_runner")
+# builds with the in-kernel measurement aids (SB200_PROFILE in the environment) go to a library of their own, so that
+# the product library never carries them
+_PROFILE = os.environ.get("SB200_PROFILE", "")
+LIB = os.path.join(HERE, "libsubcuber_b200_prof.so" if _PROFILE else "libsubcuber_b200.so")
+RUNNER = os.path.join(HERE, "kernel_runner_prof" if _PROFILE else "kernel_runner")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -39,11 +43,19 @@ def _cuda_lib_dir(nvcc: str) -> str:
     return os.path.join(os.path.dirname(os.path.dirname(os.path.realpath(nvcc))), "lib64")
 
 
-def _newer(target: str, deps) -> bool:
-    if not os.path.exists(target):
-        return False
-    t = os.path.getmtime(target)
-    return all(os.path.getmtime(d) <= t for d in deps)
+STAMP = LIB + ".srchash"
+
+
+def _source_hash() -> str:
+    """Digest of everything the binaries are made from (file times do not survive every copy of the tree)."""
+    h = hashlib.sha256()
+    for d in sorted(_all_deps()):
+        h.update(os.path.basename(d).encode())
+        with open(d, "rb") as f:
+            h.update(f.read())
+    h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(os.environ.get("SB200_PROFILE", "").encode())
+    return h.hexdigest()
 
 
 def _all_deps():
@@ -53,16 +65,28 @@ def _all_deps():
     return deps
 
 
+def have_nvcc() -> bool:
+    return bool(shutil.which("nvcc")) or os.path.exists("/usr/local/cuda/bin/nvcc")
+
+
+def up_to_date() -> bool:
+    """True when the shared library and the driver exist and were built from the present sources."""
+    if not (os.path.exists(LIB) and os.path.exists(RUNNER) and os.path.exists(STAMP)):
+        return False
+    with open(STAMP) as f:
+        return f.read().strip() == _source_hash()
+
+
 def build(force: bool = False, verbose: bool = False) -> str:
     """Compile the shared library (and the driver binary); return the library path."""
     nvcc = _nvcc()
     libdir = _cuda_lib_dir(nvcc)
-    deps = _all_deps()
     sources = [s for s in LIB_SOURCES if os.path.exists(os.path.join(CSRC, s))]
-    if force or not _newer(LIB, deps):
-        objs = []
+    stale = force or not up_to_date()
+    if stale:
+        objs, cmds = [], []
         for src in sources:
-            obj = os.path.join(CSRC, src.rsplit(".", 1)[0] + ".o")
+            obj = os.path.join(CSRC, src.rsplit(".", 1)[0] + ("_prof.o" if _PROFILE else ".o"))
             cmd = [nvcc, *NVCC_FLAGS, "-c", os.path.join(CSRC, src), "-o", obj]
             # tuning aid: compile in-kernel cycle counters in (SB200_PROFILE=1, or KSTEP / EPILOGUE / TRACE for more)
             prof = os.environ.get("SB200_PROFILE")
@@ -71,16 +95,24 @@ def build(force: bool = False, verbose: bool = False) -> str:
             if verbose:
                 cmd.insert(1, "-Xptxas")
                 cmd.insert(2, "-v")
-            subprocess.run(cmd, check=True)
+            cmds.append(cmd)
             objs.append(obj)
+        # the translation units are independent: compile them side by side
+        from concurrent.futures import ThreadPoolExecutor
+
+        with ThreadPoolExecutor(max_workers=len(cmds)) as pool:
+            list(pool.map(lambda c: subprocess.run(c, check=True), cmds))
         cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-o", LIB, *objs, "-L" + libdir, "-lcublas", "-lcublasLt", "-lcudart",
                "-Xlinker", "-rpath=" + libdir]
         subprocess.run(cmd, check=True)
     runner_srcs = [os.path.join(CSRC, s) for s in RUNNER_SOURCES if os.path.exists(os.path.join(CSRC, s))]
-    if runner_srcs and (force or not _newer(RUNNER, deps + [LIB])):
-        cmd = [nvcc, "-O2", "-std=c++17", *runner_srcs, "-o", RUNNER, "-L" + HERE, "-lsubcuber_b200",
+    if runner_srcs and stale:
+        cmd = [nvcc, "-O2", "-std=c++17", *runner_srcs, "-o", RUNNER, "-L" + HERE, "-l" + os.path.basename(LIB)[3:-3],
                "-L" + libdir, "-lcudart", "-Xlinker", "-rpath=$ORIGIN", "-Xlinker", "-rpath=" + libdir]
         subprocess.run(cmd, check=True)
+    if stale:
+        with open(STAMP, "w") as f:
+            f.write(_source_hash() + "\n")
     return LIB
 
 

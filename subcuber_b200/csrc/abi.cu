@@ -108,7 +108,8 @@ const KernelDesc* resolve_desc(const char* name, int m, int n, int k) {
   return find_desc(name);
 }
 
-GemmArgs make_args(const KernelDesc& d, const void* a, const void* b, void* out, int m, int n, int k) {
+GemmArgs make_args(const KernelDesc& d, const void* a, const void* b, void* out, int m, int n, int k,
+                   const sb200_gemm_options* opt = nullptr) {
   GemmArgs g;
   memset(&g, 0, sizeof(g));
   g.dtype = d.dt;
@@ -122,6 +123,12 @@ GemmArgs make_args(const KernelDesc& d, const void* a, const void* b, void* out,
   g.bn = d.bn;
   g.pair = d.pair;
   g.sm_limit = 0;
+  if (opt) {
+    g.sm_limit = opt->sm_limit > 0 ? opt->sm_limit : 0;
+    g.no_split = opt->no_split != 0;
+    g.wait_limit_us = opt->wait_limit_us > 0 ? opt->wait_limit_us : 0;
+    g.drop_split_flags = opt->drop_split_flags != 0;
+  }
   return g;
 }
 
@@ -443,6 +450,23 @@ extern "C" int sb200_gemm(const char* kernel, const void* a, const void* b, void
   return sb200::run(g, workspace, workspace_bytes, reinterpret_cast<cudaStream_t>(stream));
 }
 
+extern "C" size_t sb200_gemm_workspace_bytes_opt(const char* kernel, int m, int n, int k,
+                                                 const sb200_gemm_options* options) {
+  const KernelDesc* d = resolve_desc(kernel, m, n, k);
+  if (!d || m <= 0 || n <= 0 || k <= 0) return 0;
+  GemmArgs g = make_args(*d, nullptr, nullptr, nullptr, m, n, k, options);
+  return sb200::workspace_bytes(g);
+}
+
+extern "C" int sb200_gemm_opt(const char* kernel, const void* a, const void* b, void* d_out, int m, int n, int k,
+                              void* workspace, size_t workspace_bytes, sb200_stream_t stream,
+                              const sb200_gemm_options* options) {
+  const KernelDesc* d = resolve_desc(kernel, m, n, k);
+  if (!d) return SB200_ERR_NO_KERNEL;
+  GemmArgs g = make_args(*d, a, b, d_out, m, n, k, options);
+  return sb200::run(g, workspace, workspace_bytes, reinterpret_cast<cudaStream_t>(stream));
+}
+
 extern "C" int sb200_gemm_ex(const char* kernel, double alpha, const void* a, const void* b, double beta, const void* c,
                              void* d_out, int m, int n, int k, void* workspace, size_t workspace_bytes,
                              sb200_stream_t stream) {
@@ -638,10 +662,10 @@ extern "C" int sb200_events_elapsed_ms(sb200_event_list* l, int first, int secon
 
 extern "C" int sb200_gemm_events(const char* kernel, const void* a, const void* b, void* d_out, int m, int n, int k,
                                  void* workspace, size_t workspace_bytes, sb200_stream_t stream, sb200_event_list* l,
-                                 int first_index) {
+                                 int first_index, const sb200_gemm_options* options) {
   const KernelDesc* d = resolve_desc(kernel, m, n, k);
   if (!d) return SB200_ERR_NO_KERNEL;
-  GemmArgs g = make_args(*d, a, b, d_out, m, n, k);
+  GemmArgs g = make_args(*d, a, b, d_out, m, n, k, options);
   if (!l || first_index < 0 || first_index + sb200::launches_per_run(g) + 1 > l->count) return SB200_ERR_INVALID_PROBLEM;
   g.events = l->ev + first_index;
   return sb200::run(g, workspace, workspace_bytes, reinterpret_cast<cudaStream_t>(stream));

@@ -19,6 +19,7 @@
 #include <vector>
 
 #include "sw_host.h"
+#include "per_device.h"
 
 namespace sb200 {
 namespace f64 {
@@ -228,12 +229,12 @@ struct OutBlock {
 constexpr int kSmemBytes = STAGES * STAGE_DOUBLES * static_cast<int>(sizeof(double));
 
 int launch_product(const ProductParams& p, cudaStream_t stream) {
-  static bool attr_done = false;
-  if (!attr_done) {
-    cudaError_t e = cudaFuncSetAttribute(dmma_product_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    attr_done = true;
-  }
+  static PerDeviceOnce attr;  // the attribute belongs to the current device's copy of the kernel
+  const int arc = attr.run_once([] {
+    return static_cast<int>(
+        cudaFuncSetAttribute(dmma_product_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+  });
+  if (arc) return arc;
   dim3 grid((p.n + BN - 1) / BN, (p.m + BM - 1) / BM, 1);
   dmma_product_kernel<<<grid, THREADS, kSmemBytes, stream>>>(p);
   return static_cast<int>(cudaGetLastError());

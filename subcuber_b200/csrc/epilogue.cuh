@@ -64,8 +64,9 @@ __device__ __forceinline__ void raise_flag(int* flag, int epoch, int lane) {
   __syncwarp();
   if (lane == 0) asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(flag), "r"(epoch) : "memory");
 }
-// Bounded wait (2 s, or until another thread of the CTA gives up) for the flag of the matching warp of the other half.
-__device__ __forceinline__ bool wait_flag(const int* flag, int epoch, volatile int* abort_flag) {
+// Bounded wait (`limit_ns`, or until another thread of the CTA gives up) for the flag of the matching warp of the other
+// half.
+__device__ __forceinline__ bool wait_flag(const int* flag, int epoch, volatile int* abort_flag, uint64_t limit_ns) {
   const uint64_t t0 = ptx::globaltimer_ns();
   uint32_t polls = 0;
   while (true) {
@@ -74,7 +75,7 @@ __device__ __forceinline__ bool wait_flag(const int* flag, int epoch, volatile i
     const bool all_ready = __all_sync(0xffffffffu, v == epoch);
     if (all_ready) return true;
     if ((++polls & 63u) == 0) {
-      const bool give_up = *abort_flag != 0 || ptx::globaltimer_ns() - t0 > 2000000000ull;
+      const bool give_up = *abort_flag != 0 || ptx::globaltimer_ns() - t0 > limit_ns;
       if (__any_sync(0xffffffffu, give_up)) return false;
     }
     __nanosleep(100);
@@ -102,7 +103,9 @@ __device__ __forceinline__ bool epilogue_body(void* const* out, long long ldo, i
                                               WaitFn wait_slots, float alpha = 1.f, float beta = 0.f,
                                               const void* const* cin = nullptr, long long ldc = 0,
                                               long long* prof = nullptr, bool bf16 = false) {
+#ifdef SB200_PROFILE
   if (skip_body) return wait_slots();  // measurement aid
+#endif
   constexpr int NCHUNK = BN / 32;
   const int row = quarter * 32 + lane;
   // sources: the step's list (outer sources, which come last, are left to the second half of a split tile), then the

@@ -13,6 +13,8 @@
 #include <cuda_runtime.h>
 #include <math.h>
 #include <stdint.h>
+#include <thread>
+#include <vector>
 
 #include "../../include/subcuber_b200.h"
 
@@ -76,9 +78,27 @@ __global__ void fill_kernel(T* out, uint64_t n, int dist, int dtype, uint32_t su
   for (; i < n; i += stride) out[i] = convert<T>(draw(dist, dtype, i, subseq, seed));
 }
 
+// Every element is a pure function of its index, so the host fill splits the range over the host's threads.
 template <typename T>
 void fill_host_t(T* out, uint64_t n, int dist, int dtype, uint32_t subseq, uint64_t seed) {
-  for (uint64_t i = 0; i < n; ++i) out[i] = convert<T>(draw(dist, dtype, i, subseq, seed));
+  unsigned nt = std::thread::hardware_concurrency();
+  if (nt == 0) nt = 1;
+  if (nt > 64) nt = 64;
+  if (n < (1u << 16)) nt = 1;
+  auto range = [=](uint64_t lo, uint64_t hi) {
+    for (uint64_t i = lo; i < hi; ++i) out[i] = convert<T>(draw(dist, dtype, i, subseq, seed));
+  };
+  if (nt == 1) {
+    range(0, n);
+    return;
+  }
+  std::vector<std::thread> pool;
+  const uint64_t chunk = (n + nt - 1) / nt;
+  for (unsigned t = 0; t < nt; ++t) {
+    const uint64_t lo = t * chunk, hi = lo + chunk < n ? lo + chunk : n;
+    if (lo < hi) pool.emplace_back(range, lo, hi);
+  }
+  for (auto& th : pool) th.join();
 }
 
 }  // namespace

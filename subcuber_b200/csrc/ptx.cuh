@@ -66,7 +66,7 @@ __device__ __forceinline__ bool elect_one() {
 // Bounded wait.  Gives up after `limit_ns` of wall time (checked every 256 polls) or as soon as another
 // thread of the CTA has raised `*abort_flag`.  Returns false when it gave up.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                          uint64_t limit_ns = 2000000000ull) {
+                                          uint64_t limit_ns) {
   if (mbar_try_wait(bar, parity)) return true;
   uint64_t t0 = globaltimer_ns();
   uint32_t polls = 0;
@@ -259,7 +259,7 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t pa
   return ok != 0;
 }
 __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                                  uint64_t limit_ns = 2000000000ull) {
+                                                  uint64_t limit_ns) {
   if (mbar_try_wait_cluster(bar, parity)) return true;
   uint64_t t0 = globaltimer_ns();
   uint32_t polls = 0;
@@ -276,8 +276,10 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity
 // clock of the GEMM kernels.)  CLUSTER selects the cluster-scope acquire, for barriers that CTAs of the pair arrive
 // on after generic-proxy writes.
 template <bool CLUSTER>
-__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  const bool ok = CLUSTER ? mbar_wait_cluster(bar, parity, abort_flag) : mbar_wait(bar, parity, abort_flag);
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                               uint64_t limit_ns) {
+  const bool ok = CLUSTER ? mbar_wait_cluster(bar, parity, abort_flag, limit_ns)
+                          : mbar_wait(bar, parity, abort_flag, limit_ns);
   return __all_sync(0xffffffffu, ok);
 }
 
@@ -303,6 +305,42 @@ __device__ __forceinline__ void tma_load_3d_pair(void* smem_dst, const CUtensorM
       "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
       ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar) & kPeerBitMask), "r"(c0), "r"(c1),
       "r"(c2)
+      : "memory");
+}
+
+// L2 eviction-priority policies for loads that carry a cache hint.
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_normal() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+// The pair loads above with an L2 cache hint.
+__device__ __forceinline__ void tma_load_2d_pair_hint(void* smem_dst, const CUtensorMap* m, uint64_t* bar, int c0, int c1,
+                                                      uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%3, %4}], [%2], %5;"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar) & kPeerBitMask), "r"(c0), "r"(c1),
+        "l"(policy)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair_hint(void* smem_dst, const CUtensorMap* m, uint64_t* bar, int c0, int c1,
+                                                      int c2, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%3, %4, %5}], [%2], %6;"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar) & kPeerBitMask), "r"(c0), "r"(c1),
+        "r"(c2), "l"(policy)
       : "memory");
 }
 

@@ -7,6 +7,7 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include "per_device.h"
 #include "sw_kernel.cuh"
 #include "sw_kernel_pair.cuh"
 #include "sw_programs.h"
@@ -82,12 +83,12 @@ struct Layout {
 
 int level_of(Variant v) { return v == kCubic ? 0 : (v == kInterleavedLevel2 ? 2 : 1); }
 
-int sm_count();
+int sm_count() { return sm_count_of_current_device(); }
 
 // Tiles of the last wave to split: all of them when the wave is at most half full (then it lasts half as long),
 // none otherwise.  The fused-presum kernels are never split.
-int tiles_to_split(int tiles, int workers, int num_k, Variant v) {
-  if (v == kFusedPresum || v == kStrassenFused || workers <= 0 || num_k < 8 || getenv("SB200_NO_SPLIT")) return 0;
+int tiles_to_split(int tiles, int workers, int num_k, Variant v, bool no_split) {
+  if (v == kFusedPresum || v == kStrassenFused || workers <= 0 || num_k < 8 || no_split) return 0;
   const int rem = tiles % workers;
   return (rem > 0 && 2 * rem <= workers) ? rem : 0;
 }
@@ -124,13 +125,12 @@ Layout make_layout(const GemmArgs& a) {
     L.off_pb = off;
     off = align_up(off + size_t(4) * L.kq * L.nq * L.esize, 256);
   }
-  int cap = a.sm_limit > 0 ? a.sm_limit : sm_count();
-  if (const char* lim = getenv("SB200_SM_LIMIT"))  // test aid: run on fewer SMs (exercises multi-wave paths on small shapes)
-    if (atoi(lim) > 0 && atoi(lim) < cap) cap = atoi(lim);
+  int cap = sm_count();
+  if (a.sm_limit > 0 && a.sm_limit < cap) cap = a.sm_limit;  // the caller keeps the other SMs for its own kernels
   if (a.pair) cap /= 2;  // one pair per two SMs
   if (cap < 1) cap = 1;
   L.workers = L.tiles_m * L.tiles_n < cap ? L.tiles_m * L.tiles_n : cap;
-  L.split_tiles = tiles_to_split(L.tiles_m * L.tiles_n, L.workers, L.num_k, a.variant);
+  L.split_tiles = tiles_to_split(L.tiles_m * L.tiles_n, L.workers, L.num_k, a.variant, a.no_split != 0);
   const int nws = a.variant == kCubic ? 0 : (a.variant == kFusedPresum ? 2 : (a.variant == kStrassenFused ? 3 : 4));
   const size_t tile_bytes = size_t(128) * L.bn * sizeof(float) * (a.pair ? 2 : 1);  // per tile of the grid
   const size_t quadrant_bytes = size_t(L.tiles_m) * L.tiles_n * tile_bytes;
@@ -158,13 +158,12 @@ Layout make_layout(const GemmArgs& a) {
 
 template <typename Cfg>
 int launch(const KernelParams& p, int grid, cudaStream_t stream) {
-  static bool attr_done = false;
-  if (!attr_done) {
-    cudaError_t e = cudaFuncSetAttribute(sw_tile_program_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         Cfg::SMEM_BYTES);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    attr_done = true;
-  }
+  static PerDeviceOnce attr;  // the attribute belongs to the current device's copy of the kernel
+  const int arc = attr.run_once([] {
+    return static_cast<int>(cudaFuncSetAttribute(sw_tile_program_kernel<Cfg>,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+  });
+  if (arc) return arc;
   sw_tile_program_kernel<Cfg><<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(p);
   return static_cast<int>(cudaGetLastError());
 }
@@ -205,13 +204,12 @@ int launch_any(int esize, int bn, int mode, const KernelParams& p, int grid, cud
 
 template <typename Cfg>
 int launch_pair(const KernelParams& p, int pairs, cudaStream_t stream) {
-  static bool attr_done = false;
-  if (!attr_done) {
-    cudaError_t e = cudaFuncSetAttribute(sw_tile_program_pair_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         Cfg::SMEM_BYTES);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    attr_done = true;
-  }
+  static PerDeviceOnce smem_attr;  // the attribute belongs to the current device's copy of the kernel
+  const int arc = smem_attr.run_once([] {
+    return static_cast<int>(cudaFuncSetAttribute(sw_tile_program_pair_kernel<Cfg>,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+  });
+  if (arc) return arc;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3(2 * pairs, 1, 1);
@@ -244,16 +242,6 @@ int launch_pair_mode(int mode, const KernelParams& p, int pairs, cudaStream_t st
     case kPresumJob: return launch_pair<PairConfig<ESIZE, STAGES, kPresumJob>>(p, pairs, stream);
   }
   return kErrInternal;
-}
-
-int sm_count() {
-  static int n = 0;
-  if (!n) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-  }
-  return n;
 }
 
 int launch_any_pair(int esize, int mode, const KernelParams& p, int pairs, cudaStream_t stream) {
@@ -340,6 +328,8 @@ struct LaunchSpec {
   float* split_buf;
   int* split_flags;
   int* split_epoch;          // counter shared by the launches of one run
+  unsigned long long wait_ns;  // bound of every device-side wait
+  int drop_split_flags;        // test aid, see GemmArgs
 };
 
 // Block (br, bc) of a matrix cut at multiples of (rows, cols): the last block row / column keeps what is left.
@@ -351,6 +341,74 @@ View block_of(const View& w, int br, int bc, int rows, int cols, int es) {
   v.cols = w.cols - bc * cols < cols ? w.cols - bc * cols : cols;
   return v;
 }
+
+#ifdef SB200_PROFILE
+// Measurement aids of builds with -DSB200_PROFILE (never compiled into the product library): environment knobs for the
+// raster band and the debug flags, and the in-kernel cycle counters, printed by the next launch.
+void apply_tuning_aids(KernelParams& p) {
+  if (const char* bd = getenv("SB200_BAND")) p.band = atoi(bd) > 0 ? atoi(bd) : p.band;
+  if (const char* dbg = getenv("SB200_DEBUG_FLAGS")) p.debug_flags = atoi(dbg);
+  if (const char* hm = getenv("SB200_HINT")) p.hint_mode = atoi(hm);
+  if (getenv("SB200_PROF")) {
+    // measurement aid: per-CTA cycle counters of the CTA-pair kernels (library built with SB200_PROFILE), printed by
+    // the next call
+    static long long* prof_dev = nullptr;
+    static long long prof_host[4096 + 128 * 128];
+    if (!prof_dev) {
+      cudaMalloc(&prof_dev, sizeof(prof_host));
+    } else {
+      cudaDeviceSynchronize();
+      cudaMemcpy(prof_host, prof_dev, sizeof(prof_host), cudaMemcpyDeviceToHost);
+      double sum[8] = {0};
+      int n = 0;
+      for (int c = 0; c < 148; c += 2, ++n)
+        for (int i = 0; i < 8; ++i) sum[i] += double(prof_host[c * 8 + i]);
+      fprintf(stderr, "[prof] leader mma thread: total %.0f = wait_full %.0f + wait_free %.0f + issue %.0f + rest | "
+              "producer: wait_empty %.0f issue %.0f total %.0f\n",
+              sum[0] / n, sum[1] / n, sum[2] / n, sum[5] / n, sum[3] / n, sum[7] / n, sum[4] / n);
+      if (prof_host[1191])
+        fprintf(stderr, "[prof] tcgen05.ld 32x32 + wait: %.0f cycles per load (%lld loads)\n",
+                double(prof_host[1190]) / double(prof_host[1191]), prof_host[1191]);
+      fprintf(stderr, "[prof] epilogue segments (cycles, whole launch, warp 2 of CTA 0): sources %lld, tmem+add %lld, "
+              "convert/stage or fp32 store %lld, output store %lld\n", prof_host[1192], prof_host[1193], prof_host[1194],
+              prof_host[1195]);
+      for (int es = 0; es < 16; ++es)
+        if (prof_host[1200 + es * 2 + 1])
+          fprintf(stderr, "[prof] epilogue step %d: %.0f cycles per call (%lld calls)\n", es,
+                  double(prof_host[1200 + es * 2]) / double(prof_host[1200 + es * 2 + 1]), prof_host[1200 + es * 2 + 1]);
+      {
+        // start-time spread of the pairs, wave by wave
+        const long long* ts = prof_host + 4096;
+        for (int it = 0; it < 128; it += 4) {
+          long long lo = 0, hi = 0;
+          int cnt = 0;
+          for (int pr = 0; pr < 74; ++pr) {
+            const long long v = ts[pr * 128 + it];
+            if (!v) continue;
+            if (!cnt || v < lo) lo = v;
+            if (!cnt || v > hi) hi = v;
+            ++cnt;
+          }
+          if (cnt > 1) fprintf(stderr, "[skew] tile %3d of each pair: %d pairs, start spread %.1f us (first at +%.1f us)\n", it, cnt,
+                               (hi - lo) * 1e-3, (lo - ts[0]) * 1e-3);
+        }
+      }
+      if (getenv("SB200_PROF_TRACE")) {
+        // per k-step of one tile of CTA 0 (cycles relative to the first entry): producer saw the stage empty / issued
+        // its loads, an observer saw the stage full, the MMA thread started waiting / got the stage / had issued
+        const long long* t = prof_host + 2048;
+        long long base = t[0];
+        fprintf(stderr, "[trace] kk: prod_empty prod_issued full_seen | mma_wait_start mma_got mma_issued | load_latency\n");
+        for (int kk = 0; kk < 64; ++kk, t += 8)
+          fprintf(stderr, "[trace] %2d: %7lld %7lld %7lld | %7lld %7lld %7lld | %6lld\n", kk, t[0] - base, t[1] - base,
+                  t[2] - base, t[3] - base, t[4] - base, t[5] - base, t[2] - t[1]);
+      }
+    }
+    cudaMemset(prof_dev, 0, sizeof(prof_host));
+    p.prof = prof_dev;
+  }
+}
+#endif
 
 template <typename MarkFn>
 int launch_group(const LaunchSpec& s, cudaStream_t stream, MarkFn mark) {
@@ -423,49 +481,11 @@ int launch_group(const LaunchSpec& s, cudaStream_t stream, MarkFn mark) {
   // raster band height in tile rows: the tiles of a wave share A row tiles and B column tiles through L2; taller bands
   // for tall tile grids read less from HBM (measured at 16384^3 f16: 19.4 GB with 16 against 23.9 GB with 8)
   p.band = s.tiles_m >= 32 ? 16 : 8;
-  if (const char* bd = getenv("SB200_BAND")) p.band = atoi(bd) > 0 ? atoi(bd) : p.band;
-  if (const char* dbg = getenv("SB200_DEBUG_FLAGS")) p.debug_flags = atoi(dbg);
-  if (getenv("SB200_PROF")) {
-    // measurement aid: per-CTA cycle counters of the CTA-pair kernels (library built with SB200_PROFILE), printed by
-    // the next call
-    static long long* prof_dev = nullptr;
-    static long long prof_host[8 * 256 + 64 * 8];
-    if (!prof_dev) {
-      cudaMalloc(&prof_dev, sizeof(prof_host));
-    } else {
-      cudaDeviceSynchronize();
-      cudaMemcpy(prof_host, prof_dev, sizeof(prof_host), cudaMemcpyDeviceToHost);
-      double sum[8] = {0};
-      int n = 0;
-      for (int c = 0; c < 148; c += 2, ++n)
-        for (int i = 0; i < 8; ++i) sum[i] += double(prof_host[c * 8 + i]);
-      fprintf(stderr, "[prof] leader mma thread: total %.0f = wait_full %.0f + wait_free %.0f + issue %.0f + rest | "
-              "producer: wait_empty %.0f issue %.0f total %.0f\n",
-              sum[0] / n, sum[1] / n, sum[2] / n, sum[5] / n, sum[3] / n, sum[7] / n, sum[4] / n);
-      if (prof_host[1191])
-        fprintf(stderr, "[prof] tcgen05.ld 32x32 + wait: %.0f cycles per load (%lld loads)\n",
-                double(prof_host[1190]) / double(prof_host[1191]), prof_host[1191]);
-      fprintf(stderr, "[prof] epilogue segments (cycles, whole launch, warp 2 of CTA 0): sources %lld, tmem+add %lld, "
-              "convert/stage or fp32 store %lld, output store %lld\n", prof_host[1192], prof_host[1193], prof_host[1194],
-              prof_host[1195]);
-      for (int es = 0; es < 16; ++es)
-        if (prof_host[1200 + es * 2 + 1])
-          fprintf(stderr, "[prof] epilogue step %d: %.0f cycles per call (%lld calls)\n", es,
-                  double(prof_host[1200 + es * 2]) / double(prof_host[1200 + es * 2 + 1]), prof_host[1200 + es * 2 + 1]);
-      if (getenv("SB200_PROF_TRACE")) {
-        // per k-step of one tile of CTA 0 (cycles relative to the first entry): producer saw the stage empty / issued
-        // its loads, an observer saw the stage full, the MMA thread started waiting / got the stage / had issued
-        const long long* t = prof_host + 2048;
-        long long base = t[0];
-        fprintf(stderr, "[trace] kk: prod_empty prod_issued full_seen | mma_wait_start mma_got mma_issued | load_latency\n");
-        for (int kk = 0; kk < 64; ++kk, t += 8)
-          fprintf(stderr, "[trace] %2d: %7lld %7lld %7lld | %7lld %7lld %7lld | %6lld\n", kk, t[0] - base, t[1] - base,
-                  t[2] - base, t[3] - base, t[4] - base, t[5] - base, t[2] - t[1]);
-      }
-    }
-    cudaMemset(prof_dev, 0, sizeof(prof_host));
-    p.prof = prof_dev;
-  }
+  p.wait_ns = s.wait_ns;
+  p.drop_split_flags = s.drop_split_flags;
+#ifdef SB200_PROFILE
+  apply_tuning_aids(p);
+#endif
   if (s.variant == kInterleavedPresum) {
     p.njobs = 2;
     for (int q = 0; q < 4; ++q) {
@@ -495,8 +515,7 @@ int launch_group(const LaunchSpec& s, cudaStream_t stream, MarkFn mark) {
       break;
     case kInterleavedPresum: {
       const sb200_program_t first = s.linked ? programs::level1_first() : programs::level1_first_early();
-      const sb200_program_t second =
-          getenv("SB200_L1_PLAIN") && !s.linked ? programs::level1_second() : programs::level1_second_taps();
+      const sb200_program_t second = programs::level1_second_taps();
       p.prog = s.linked ? programs::link_outer(first, s.link, 1) : first;
       p.split_epoch = ++*s.split_epoch;
       rc = launch_any(es, bn_sel, kPresumJob, p, s.grid, stream);
@@ -559,6 +578,8 @@ int run(const GemmArgs& a, void* workspace, size_t workspace_size, cudaStream_t 
   for (int i = 0; i < 4; ++i) s.ws_inner[i] = reinterpret_cast<float*>(wsb + L.off_ws[i]);
   s.quadrant_floats = L.quadrant_floats;
   s.status = status;
+  s.wait_ns = a.wait_limit_us > 0 ? 1000ull * static_cast<unsigned long long>(a.wait_limit_us) : 2000000000ull;
+  s.drop_split_flags = a.drop_split_flags;
   s.alpha = a.scaled ? static_cast<float>(a.alpha) : 1.f;
   s.beta = a.scaled ? static_cast<float>(a.beta) : 0.f;
   const char* Cin = (a.scaled && a.beta != 0.0) ? static_cast<const char*>(a.c) : nullptr;

@@ -41,7 +41,11 @@ struct GemmArgs {
   void* d;        // m x n row-major, ldd = n;  D = A * B
   int bn;         // tile width: 256 (default when 0) or 128
   int pair;       // 1: CTA-pair kernels (256 x 256 tiles on two SMs, cta_group::2); requires bn == 256
-  int sm_limit;   // CTAs to launch at most (0: one per SM of the current device)
+  int sm_limit;   // SMs the kernels may occupy (0: every SM of the current device)
+  int no_split;   // 1: never compute the tiles of a partial last wave as two K-halves
+  int wait_limit_us;     // bound of every device-side wait in microseconds (0: 2 s)
+  int drop_split_flags;  // test aid for the give-up path: the first K-halves of split tiles do not publish their
+                         // flags, so the second halves' bounded waits run out and the call reports status 105
   cudaEvent_t* events;  // optional: launches_per_run()+1 events, recorded before the first and after each launch
   // D = alpha * (A * B) + beta * C when `scaled` is set (else alpha = 1, beta = 0 and `c` is never read), the general
   // form of the reference's operators (include/cutlass/gemm/device/strassen_gemm.h:365-451).  C is m x n row-major,

@@ -91,15 +91,30 @@ struct KernelParams {
   float* split_buf;         // [split tile][quadrant 4][CTA of the tile][128 x BN] fp32, hand-off tile order
   int* split_flags;         // [split tile][quadrant 4][CTA of the tile 2][epilogue warp 4]
   int* status;              // device status word, 0 = ok
+  unsigned long long wait_ns;  // bound of every wait in the kernel (mbarrier, split flag), in nanoseconds
+  int drop_split_flags;     // test aid for the give-up path: first halves of split tiles do not raise their flags
+#ifdef SB200_PROFILE
   int debug_flags;          // measurement aids (results are garbage): bit 0 = issue no MMA, bit 1 = issue no TMA load,
                             // bit 3 = load only while the ring fills for the first time (pairs), bit 4 = skip the
                             // presum job (pairs), bit 5 = skip the epilogue bodies
   long long* prof;          // measurement aid (CTA-pair kernels): 8 cycle counters per CTA, or null
+  int hint_mode;            // measurement aid: L2 cache hints of the operand loads (pairs): tens digit = A, units = B;
+                            // 0 none, 1 evict_first, 2 evict_last, 3 evict_normal
+#endif
   // presum jobs (mode JOB), run by the presum warps of the whole grid one after the other
   int njobs;
   PresumSideJob job[SB200_MAX_JOBS];
   sb200_program_t prog;
 };
+
+// Measurement aids exist only in builds with -DSB200_PROFILE; the product kernels carry none of their branches.
+#ifdef SB200_PROFILE
+#define SB200_DEBUG_BIT(p, bit) (((p).debug_flags & (bit)) != 0)
+#define SB200_PROF_PTR(p) ((p).prof)
+#else
+#define SB200_DEBUG_BIT(p, bit) false
+#define SB200_PROF_PTR(p) (static_cast<long long*>(nullptr))
+#endif
 
 template <int ESIZE_, int BN_, int STAGES_, int MODE_, bool SCALED_ = false>
 struct KernelConfig {
@@ -188,9 +203,12 @@ __device__ __forceinline__ WorkUnit unit_of(const KernelParams& p, int u) {
   return w;
 }
 
+// The first code to arrive stays in the status word.  The code is published before the CTA-wide abort flag, so that
+// roles which give up only because they saw the flag cannot overwrite the code of the wait that actually ran out.
 __device__ __forceinline__ void raise_abort(const KernelParams& p, volatile int* abort_flag, int code) {
-  *abort_flag = 1;
-  atomicCAS(p.status, 0, code);
+  const int before = atomicCAS(p.status, 0, code);
+  __threadfence();
+  *abort_flag = before == 0 ? 1 : 2;  // the store depends on the atomic's result, so it cannot pass it
 }
 
 // ---------------------------------------------------------------------------------------------------
@@ -448,7 +466,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_kernel(const 
           const uint32_t tx = (a_tma ? Cfg::A_BYTES : 0) + (b_tma ? Cfg::B_BYTES : 0);
           const CUtensorMap* ma = &p.tmap[pr.a.view[0]];
           const CUtensorMap* mb = &p.tmap[pr.b.view[0]];
-          const bool no_load = (p.debug_flags & 2) != 0;  // measurement aid
+          const bool no_load = SB200_DEBUG_BIT(p, 2);  // measurement aid
           for (int kk = wu.k0; kk < wu.k1; ++kk) {
             const bool mine = (turn == my_turn);
             if (++turn == 3u) turn = 0;
@@ -456,7 +474,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_kernel(const 
               if (++stage == STAGES) { stage = 0; phase ^= 1u; }
               continue;
             }
-            bool got = ptx::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag);
+            bool got = ptx::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.wait_ns);
             got = __all_sync(0xffffffffu, got);
             if (!got) {
               if (lane == 0) raise_abort(p, abort_flag, kStatusProducerTimeout);
@@ -502,7 +520,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_kernel(const 
           const sb200_product_t& pr = p.prog.product[ps];
           const uint32_t slot = pr.slot ^ sx;
           if (pr.wait_free) {
-            bool got = ptx::mbar_wait(&slot_free[slot], ((free_bits >> slot) & 1u) ^ 1u, abort_flag);
+            bool got = ptx::mbar_wait(&slot_free[slot], ((free_bits >> slot) & 1u) ^ 1u, abort_flag, p.wait_ns);
             got = __all_sync(0xffffffffu, got);
             if (!got) {
               if (lane == 0) raise_abort(p, abort_flag, kStatusMmaTimeout);
@@ -514,13 +532,13 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_kernel(const 
           }
           const uint32_t idesc = ptx::umma_idesc((ESIZE == 2 && p.bf16) ? 1u : Cfg::FMT, Cfg::BM, BN, pr.negate != 0);
           const uint32_t tmem_d = tmem_base + slot * BN;
-          const bool skip_mma = (p.debug_flags & 1) != 0;  // measurement aid
+          const bool skip_mma = SB200_DEBUG_BIT(p, 1);  // measurement aid
           // descriptors differ between stages and k-substeps only in the start-address field (low word, 16-byte units)
           const uint64_t adesc0 = ptx::umma_desc_sw128(ptx::smem_u32(smem), 16, 1024);
           const uint64_t bdesc0 =
               ptx::umma_desc_sw128(ptx::smem_u32(smem) + Cfg::A_BYTES, Cfg::BLK_BYTES, Cfg::B_SBO, Cfg::B_LAYOUT_TYPE);
           for (int kk = 0; ok && kk < nk; ++kk) {
-            bool got = ptx::mbar_wait(&full_bar[stage], phase, abort_flag);
+            bool got = ptx::mbar_wait(&full_bar[stage], phase, abort_flag, p.wait_ns);
             got = __all_sync(0xffffffffu, got);
             if (!got) {
               if (lane == 0) raise_abort(p, abort_flag, kStatusMmaTimeout);
@@ -574,7 +592,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_kernel(const 
           for (int s = 0; s < SLOTS; ++s) {
             if ((ep.wait_full_mask >> s) & 1u) {
               const uint32_t slot = s ^ sx;
-              bool got = ptx::mbar_wait(&slot_full[slot], (full_bits >> slot) & 1u, abort_flag);
+              bool got = ptx::mbar_wait(&slot_full[slot], (full_bits >> slot) & 1u, abort_flag, p.wait_ns);
               got = __all_sync(0xffffffffu, got);
               if (!got) {
                 if (lane == 0) raise_abort(p, abort_flag, kStatusEpilogueTimeout);
@@ -583,7 +601,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_kernel(const 
               full_bits ^= (1u << slot);
             }
           }
-          if (sp.add_partial && !wait_flag(flag, p.split_epoch, abort_flag)) {
+          if (sp.add_partial && !wait_flag(flag, p.split_epoch, abort_flag, p.wait_ns)) {
             if (lane == 0) raise_abort(p, abort_flag, kStatusSplitTimeout);
             return false;
           }
@@ -599,10 +617,10 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_kernel(const 
                                                      staging + (warp - 2) * kStagingWarpBytes,
                                                      sp.redirect ? split_tile_buf : nullptr,
                                                      sp.add_partial ? split_tile_buf : nullptr,
-                                                     (p.debug_flags & 32) != 0, wait_slots, p.alpha, p.beta, p.cin, p.ldc, nullptr,
+                                                     SB200_DEBUG_BIT(p, 32), wait_slots, p.alpha, p.beta, p.cin, p.ldc, nullptr,
                                                      ESIZE == 2 && p.bf16 != 0);
         if (!ok) break;
-        if (sp.redirect) raise_flag(flag, p.split_epoch, lane);
+        if (sp.redirect && !p.drop_split_flags) raise_flag(flag, p.split_epoch, lane);
         ptx::tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) {
@@ -627,7 +645,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_kernel(const 
           const bool a_mt = pr.a.nterms > 1;
           const bool b_mt = pr.b.nterms > 1;
           for (int kk = wu.k0; kk < wu.k1; ++kk) {
-            bool got = ptx::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag);
+            bool got = ptx::mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.wait_ns);
             got = __all_sync(0xffffffffu, got);
             if (!got) {
               if (lane == 0) raise_abort(p, abort_flag, kStatusPresumTimeout);

@@ -159,7 +159,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
           const uint32_t tx = 2u * ((a_tma ? Cfg::A_BYTES : 0) + (b_tma ? Cfg::B_BYTES : 0));  // both CTAs' bytes
           const CUtensorMap* ma = &p.tmap[pr.a.view[0]];
           const CUtensorMap* mb = &p.tmap[pr.b.view[0]];
-          const bool no_load_all = (p.debug_flags & 2) != 0;
+          const bool no_load_all = SB200_DEBUG_BIT(p, 2);
           for (int kk = wu.k0; kk < wu.k1; ++kk) {
             const bool mine = (turn == my_turn);
             if (++turn == 3u) turn = 0;
@@ -169,7 +169,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
             }
             const long long tw = SB200_CLOCK();
             // the stage-empty barrier is signalled by tcgen05.commit only: no cluster-scope acquire needed
-            const bool got = ptx::mbar_wait_warp<false>(&empty_bar[stage], phase ^ 1u, abort_flag);
+            const bool got = ptx::mbar_wait_warp<false>(&empty_bar[stage], phase ^ 1u, abort_flag, p.wait_ns);
             if (!got) {
               if (lane == 0) raise_abort(p, abort_flag, kStatusProducerTimeout);
               ok = false;
@@ -184,12 +184,30 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
             uint8_t* sa = smem + stage * Cfg::STAGE_BYTES;
             uint8_t* sb = sa + Cfg::A_BYTES;
             // measurement aids: bit 1 = never load; bit 3 = load only while the ring fills for the first time
-            const bool no_load = no_load_all || ((p.debug_flags & 8) != 0 && (w != pair || ps > 0 || kk >= wu.k0 + STAGES));
+            const bool no_load = no_load_all || (SB200_DEBUG_BIT(p, 8) && (w != pair || ps > 0 || kk >= wu.k0 + STAGES));
             if (ptx::elect_one()) {
               if (rank == 0) {
                 if (tx && !no_load) ptx::mbar_arrive_expect_tx(&full_bar[stage], tx);
                 else ptx::mbar_arrive(&full_bar[stage]);
               }
+#ifdef SB200_PROFILE
+              if (p.hint_mode && p.b_blocked && !no_load) {
+                auto policy_of = [](int code) {
+                  return code == 1 ? ptx::l2_policy_evict_first()
+                                   : (code == 2 ? ptx::l2_policy_evict_last() : ptx::l2_policy_evict_normal());
+                };
+                const int ha = p.hint_mode / 10, hb = p.hint_mode % 10;
+                if (a_tma) {
+                  if (ha) ptx::tma_load_2d_pair_hint(sa, ma, &full_bar[stage], kk * BK, row0, policy_of(ha));
+                  else ptx::tma_load_2d_pair(sa, ma, &full_bar[stage], kk * BK, row0);
+                }
+                if (b_tma) {
+                  if (hb) ptx::tma_load_3d_pair_hint(sb, mb, &full_bar[stage], 0, kk * BK, col0 / BK, policy_of(hb));
+                  else ptx::tma_load_3d_pair(sb, mb, &full_bar[stage], 0, kk * BK, col0 / BK);
+                }
+              } else
+#endif
+              {
               if (a_tma && !no_load) ptx::tma_load_2d_pair(sa, ma, &full_bar[stage], kk * BK, row0);
               if (b_tma && !no_load) {
                 if (p.b_blocked) {
@@ -199,6 +217,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
                   for (int nb = 0; nb < Cfg::NBLK; ++nb)
                     ptx::tma_load_2d_pair(sb + nb * Cfg::BLK_BYTES, mb, &full_bar[stage], col0 + nb * BK, kk * BK);
                 }
+              }
               }
             }
             __syncwarp();
@@ -210,11 +229,15 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
           }
         }
       }
+#ifdef SB200_PROFILE
       if (p.prof && warp == 0 && lane == 0) {
         p.prof[blockIdx.x * 8 + 7] = pw_issue;
         p.prof[blockIdx.x * 8 + 3] = pw_empty;
         p.prof[blockIdx.x * 8 + 4] = SB200_CLOCK() - pt0;
       }
+#else
+      (void)pw_issue; (void)pw_empty; (void)pt0;
+#endif
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (leader CTA only)
@@ -231,12 +254,16 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
         const WorkUnit wu = unit_of(p, w);
         const int nk = wu.k1 - wu.k0;
         const uint32_t sx = p.prog.alternate_slots ? (iter & 1u) : 0u;
+#ifdef SB200_PROFILE
+        // wall-clock time at which this pair starts its iter-th tile (skew between the pairs of a wave)
+        if (p.prof && lane == 0 && iter < 128) p.prof[4096 + pair * 128 + iter] = static_cast<long long>(ptx::globaltimer_ns());
+#endif
         for (int ps = 0; ok && ps < nproducts; ++ps) {
           const sb200_product_t& pr = p.prog.product[ps];
           const uint32_t slot = pr.slot ^ sx;
           if (pr.wait_free) {
             const long long tw = SB200_CLOCK_LIGHT();
-            const bool got = ptx::mbar_wait_warp<true>(&slot_free[slot], ((free_bits >> slot) & 1u) ^ 1u, abort_flag);
+            const bool got = ptx::mbar_wait_warp<true>(&slot_free[slot], ((free_bits >> slot) & 1u) ^ 1u, abort_flag, p.wait_ns);
             if (!got) {
               if (lane == 0) raise_abort(p, abort_flag, kStatusMmaTimeout);
               ok = false;
@@ -248,7 +275,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
           }
           const uint32_t idesc = ptx::umma_idesc((ESIZE == 2 && p.bf16) ? 1u : Cfg::FMT, Cfg::PAIR_M, BN, pr.negate != 0);
           const uint32_t tmem_d = tmem_base + slot * BN;
-          const bool skip_mma = (p.debug_flags & 1) != 0;
+          const bool skip_mma = SB200_DEBUG_BIT(p, 1);
           // descriptors differ between stages and k-substeps only in the start-address field (low word, 16-byte units)
           const uint64_t adesc0 = ptx::umma_desc_sw128(ptx::smem_u32(smem), 16, 1024);
           const uint64_t bdesc0 =
@@ -258,8 +285,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
             // in FEED mode the peer's presum warps arrive on this barrier after writing their own shared memory
             // through the generic proxy: that hand-over needs the cluster-scope acquire; TMA-only stages do not
             const bool got = (Cfg::MODE == kPresumFeed)
-                                 ? ptx::mbar_wait_warp<true>(&full_bar[stage], phase, abort_flag)
-                                 : ptx::mbar_wait_warp<false>(&full_bar[stage], phase, abort_flag);
+                                 ? ptx::mbar_wait_warp<true>(&full_bar[stage], phase, abort_flag, p.wait_ns)
+                                 : ptx::mbar_wait_warp<false>(&full_bar[stage], phase, abort_flag, p.wait_ns);
             if (!got) {
               if (lane == 0) raise_abort(p, abort_flag, kStatusMmaTimeout);
               ok = false;
@@ -299,12 +326,16 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
           }
         }
       }
+#ifdef SB200_PROFILE
       if (p.prof && lane == 0) {
         p.prof[blockIdx.x * 8 + 0] = SB200_CLOCK_LIGHT() - mt0;
         p.prof[blockIdx.x * 8 + 1] = mw_full;
         p.prof[blockIdx.x * 8 + 2] = mw_free;
         p.prof[blockIdx.x * 8 + 5] = mw_issue;
       }
+#else
+      (void)mw_full; (void)mw_free; (void)mw_issue; (void)mt0;
+#endif
     }
 #ifdef SB200_PROFILE_TRACE
   } else if (warp == 8 && Cfg::MODE == kPresumNone) {
@@ -317,7 +348,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
         const WorkUnit wu = unit_of(p, w);
         for (int ps = 0; ok && ps < nproducts; ++ps)
           for (int kk = 0; kk < wu.k1 - wu.k0; ++kk) {
-            if (!ptx::mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+            if (!ptx::mbar_wait(&full_bar[stage], phase, abort_flag, p.wait_ns)) { ok = false; break; }
             if (blockIdx.x == 0 && w == pair + 3 * num_pairs && ps == 0 && kk < 64) p.prof[2048 + kk * 8 + 2] = clock64();
             if (++stage == STAGES) { stage = 0; phase ^= 1u; }
           }
@@ -348,7 +379,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
             if ((ep.wait_full_mask >> s0) & 1u) {
               const uint32_t s = s0 ^ sx;
               const long long tw = SB200_CLOCK();
-              const bool got = ptx::mbar_wait_warp<true>(&slot_full[s], (full_bits >> s) & 1u, abort_flag);
+              const bool got = ptx::mbar_wait_warp<true>(&slot_full[s], (full_bits >> s) & 1u, abort_flag, p.wait_ns);
               ew_full += SB200_CLOCK() - tw;
               if (!got) {
                 if (lane == 0) raise_abort(p, abort_flag, kStatusEpilogueTimeout);
@@ -357,7 +388,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
               full_bits ^= (1u << s);
             }
           }
-          if (sp.add_partial && !wait_flag(flag, p.split_epoch, abort_flag)) {
+          if (sp.add_partial && !wait_flag(flag, p.split_epoch, abort_flag, p.wait_ns)) {
             if (lane == 0) raise_abort(p, abort_flag, kStatusSplitTimeout);
             return false;
           }
@@ -377,8 +408,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
                                                      staging + (warp - 2) * kStagingWarpBytes,
                                                      sp.redirect ? split_tile_buf : nullptr,
                                                      sp.add_partial ? split_tile_buf : nullptr,
-                                                     (p.debug_flags & 32) != 0, wait_slots, p.alpha, p.beta, p.cin, p.ldc,
-                                                     (p.prof && blockIdx.x == 0 && warp == 2) ? p.prof + 1190 : nullptr,
+                                                     SB200_DEBUG_BIT(p, 32), wait_slots, p.alpha, p.beta, p.cin, p.ldc,
+                                                     (SB200_PROF_PTR(p) && blockIdx.x == 0 && warp == 2) ? SB200_PROF_PTR(p) + 1190 : nullptr,
                                                      ESIZE == 2 && p.bf16 != 0);
         if (!ok) break;
 #ifdef SB200_PROFILE_EPILOGUE
@@ -388,7 +419,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
           p.prof[1200 + es * 2 + 1] += 1;
         }
 #endif
-        if (sp.redirect) raise_flag(flag, p.split_epoch, lane);
+        if (sp.redirect && !p.drop_split_flags) raise_flag(flag, p.split_epoch, lane);
         ptx::tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) {
@@ -417,7 +448,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
           const bool a_mt = pr.a.nterms > 1;
           const bool b_mt = pr.b.nterms > 1;
           for (int kk = wu.k0; kk < wu.k1; ++kk) {
-            bool got = ptx::mbar_wait_cluster(&empty_bar[stage], phase ^ 1u, abort_flag);
+            bool got = ptx::mbar_wait_cluster(&empty_bar[stage], phase ^ 1u, abort_flag, p.wait_ns);
             got = __all_sync(0xffffffffu, got);
             if (!got) {
               if (lane == 0) raise_abort(p, abort_flag, kStatusPresumTimeout);
@@ -437,7 +468,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
           }
         }
       }
-    } else if (Cfg::MODE == kPresumJob && !(p.debug_flags & 16)) {  // bit 4: measurement aid, skip the presum job
+    } else if (Cfg::MODE == kPresumJob && !SB200_DEBUG_BIT(p, 16)) {  // bit 4: measurement aid, skip the presum job
       const int ptid = threadIdx.x - Cfg::FIRST_PRESUM_WARP * 32;
       constexpr int PT = Cfg::PRESUM_WARPS * 32;
       presum_job<ESIZE>(p, blockIdx.x * PT + ptid, gridDim.x * PT);

@@ -27,6 +27,7 @@ ERROR_NAMES = {
     102: "device: mma wait timed out",
     103: "device: epilogue wait timed out",
     104: "device: presum wait timed out",
+    105: "device: split-tile wait timed out",
 }
 
 TORCH_DTYPE = {"f16": torch.float16, "f32": torch.float32, "f64": torch.float64, "bf16": torch.bfloat16}
@@ -147,36 +148,52 @@ def run_kernel(name: str, a: torch.Tensor, b: torch.Tensor, d: Optional[torch.Te
     return d, float(avg.value)
 
 
-class Workspace:
-    """Device workspace for `gemm`, sized for one (kernel, m, n, k); reusable across calls of that shape."""
+def options(sm_limit: int = 0, no_split: bool = False, wait_limit_us: int = 0,
+            drop_split_flags: bool = False) -> "_lib.GemmOptions":
+    """Per-call options of the tensor-core kernels (`sb200_gemm_options`): SMs the kernels may occupy, no K-split of a
+    partial last wave, the bound of the device-side waits, and the test aid that makes a split wait run out."""
+    return _lib.GemmOptions(int(sm_limit), int(bool(no_split)), int(wait_limit_us), int(bool(drop_split_flags)))
 
-    def __init__(self, kernel: str, m: int, n: int, k: int, device):
+
+def _options_key(opts) -> tuple:
+    return (0, 0) if opts is None else (int(opts.sm_limit), int(opts.no_split))
+
+
+class Workspace:
+    """Device workspace for `gemm`, sized for one (kernel, m, n, k, options); reusable across calls of that shape."""
+
+    def __init__(self, kernel: str, m: int, n: int, k: int, device, opts=None):
         lib = _lib.load()
         rc = lib.sb200_gemm_can_implement(kernel.encode(), m, n, k)
         if rc != 0:
             raise KernelError(kernel, rc)
-        self.nbytes = int(lib.sb200_gemm_workspace_bytes(kernel.encode(), m, n, k))
+        with torch.cuda.device(device):  # the layout depends on the SM count of the device that will run the call
+            self.nbytes = int(lib.sb200_gemm_workspace_bytes_opt(kernel.encode(), m, n, k,
+                                                                 C.byref(opts) if opts is not None else None))
         self.buf = torch.empty(self.nbytes + 256, dtype=torch.uint8, device=device)
         off = (-self.buf.data_ptr()) % 256
         self.ptr = self.buf.data_ptr() + off
-        self.key = (kernel, m, n, k)
+        self.key = (kernel, m, n, k) + _options_key(opts)
 
 
 def gemm(kernel: str, a: torch.Tensor, b: torch.Tensor, d: Optional[torch.Tensor] = None,
          workspace: Optional[Workspace] = None, check: bool = True, alpha: float = 1.0, beta: float = 0.0,
-         c: Optional[torch.Tensor] = None) -> torch.Tensor:
+         c: Optional[torch.Tensor] = None, opts=None) -> torch.Tensor:
     """D = A @ B, or D = alpha * (A @ B) + beta * C when alpha / beta / c are given, with the named kernel;
-    asynchronous on the current stream (synchronises only if `check`).  C may be D itself."""
+    asynchronous on the current stream (synchronises only if `check`).  C may be D itself.  `opts` (see `options`)
+    applies to the plain form only."""
     lib = _lib.load()
     _check_inputs(a, b)
     m, k = a.shape
     n = b.shape[1]
     if d is None:
         d = torch.empty((m, n), dtype=a.dtype, device=a.device)
-    if workspace is None or workspace.key != (kernel, m, n, k):
-        workspace = Workspace(kernel, m, n, k, a.device)
+    if workspace is None or workspace.key != (kernel, m, n, k) + _options_key(opts):
+        workspace = Workspace(kernel, m, n, k, a.device, opts)
     s = torch.cuda.current_stream(a.device).cuda_stream
     scaled = alpha != 1.0 or beta != 0.0
+    if scaled and opts is not None:
+        raise ValueError("options are not supported together with alpha / beta")
     if scaled and beta != 0.0:
         if c is None or not c.is_cuda or not c.is_contiguous() or c.shape != d.shape or c.dtype != d.dtype:
             raise ValueError("beta != 0 needs a contiguous CUDA tensor C with the shape and dtype of D")
@@ -186,8 +203,8 @@ def gemm(kernel: str, a: torch.Tensor, b: torch.Tensor, d: Optional[torch.Tensor
                                    c.data_ptr() if c is not None else None, d.data_ptr(), m, n, k, workspace.ptr,
                                    workspace.nbytes, s)
         else:
-            rc = lib.sb200_gemm(kernel.encode(), a.data_ptr(), b.data_ptr(), d.data_ptr(), m, n, k, workspace.ptr,
-                                workspace.nbytes, s)
+            rc = lib.sb200_gemm_opt(kernel.encode(), a.data_ptr(), b.data_ptr(), d.data_ptr(), m, n, k, workspace.ptr,
+                                    workspace.nbytes, s, C.byref(opts) if opts is not None else None)
         if rc != 0:
             raise KernelError(kernel, rc)
         if check:
@@ -207,9 +224,10 @@ class HostPipeline:
         pipe.finish()
     """
 
-    def __init__(self, kernel: str, m: int, n: int, k: int, dtype: torch.dtype, device):
+    def __init__(self, kernel: str, m: int, n: int, k: int, dtype: torch.dtype, device, opts=None):
         self.kernel, self.m, self.n, self.k, self.device = kernel, m, n, k, torch.device(device)
-        self.ws = Workspace(kernel, m, n, k, device)
+        self.opts = opts
+        self.ws = Workspace(kernel, m, n, k, device, opts)
         self.s_in, self.s_mm, self.s_out = (torch.cuda.Stream(device) for _ in range(3))
         self.slots = [{"a": torch.empty((m, k), dtype=dtype, device=device),
                        "b": torch.empty((k, n), dtype=dtype, device=device),
@@ -236,8 +254,9 @@ class HostPipeline:
         if slot["used"]:
             self.s_mm.wait_event(slot["out"])   # the slot's previous result has left
         with torch.cuda.device(self.device):
-            rc = lib.sb200_gemm(self.kernel.encode(), slot["a"].data_ptr(), slot["b"].data_ptr(), slot["d"].data_ptr(),
-                                self.m, self.n, self.k, self.ws.ptr, self.ws.nbytes, self.s_mm.cuda_stream)
+            rc = lib.sb200_gemm_opt(self.kernel.encode(), slot["a"].data_ptr(), slot["b"].data_ptr(),
+                                    slot["d"].data_ptr(), self.m, self.n, self.k, self.ws.ptr, self.ws.nbytes,
+                                    self.s_mm.cuda_stream, C.byref(self.opts) if self.opts is not None else None)
         if rc != 0:
             raise KernelError(self.kernel, rc)
         slot["mm"].record(self.s_mm)

@@ -18,7 +18,7 @@ def main():
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     dist.init_process_group("nccl", device_id=dev)
     sms = torch.cuda.get_device_properties(dev).multi_processor_count
-    os.environ["SB200_SM_LIMIT"] = str(sms - multi_gpu.PeerGather.reserved_sms())
+    opts = runner.options(sm_limit=sms - multi_gpu.PeerGather.reserved_sms())  # SMs left free for the exchange
     kernel = "blackwell_f16_sw_interleaved_presum_2sm"
     m, n, k = 512, 1024, 1024 * world
     gen = torch.Generator(device="cpu").manual_seed(5)
@@ -27,7 +27,7 @@ def main():
     lo, hi = multi_gpu.row_shard(k, world, rank)
     shard = b_steps[0][lo:hi].to(dev).contiguous()
     gather = multi_gpu.PeerGather(shard, k, world, rank)
-    ws = runner.Workspace(kernel, m, n, k, dev)
+    ws = runner.Workspace(kernel, m, n, k, dev, opts)
     ok = True
     for step in range(5):
         # the first call of next() starts the exchanges of steps 0 and 1, every later call the one of the step after:
@@ -35,7 +35,7 @@ def main():
         if step > 0:
             gather.update_shard(b_steps[step][lo:hi].to(dev))
         b = gather.next()
-        d = runner.gemm(kernel, a, b, workspace=ws, check=False)
+        d = runner.gemm(kernel, a, b, workspace=ws, check=False, opts=opts)
         gather.done(b)
         want_b = b_steps[max(0, step - 1)]
         torch.cuda.synchronize(dev)

@@ -41,7 +41,7 @@ def _level(kernel):
     return 0 if "cubic" in kernel else (2 if "level2" in kernel else 1)
 
 
-def _run(kernel, a_np, b_np, device):
+def _run(kernel, a_np, b_np, device, opts=None):
     import torch
 
     from subcuber_b200 import runner
@@ -49,7 +49,7 @@ def _run(kernel, a_np, b_np, device):
     a = runner.to_torch(a_np, device)
     b = runner.to_torch(b_np, device)
     d = torch.full((a.shape[0], b.shape[1]), float("nan"), dtype=a.dtype, device=device)
-    runner.gemm(kernel, a, b, d)
+    runner.gemm(kernel, a, b, d, opts=opts)
     torch.cuda.synchronize()
     return runner.to_numpy(d)
 
@@ -231,14 +231,13 @@ def test_any_extents_column_major_and_auto(oracle, cuda_device):
     assert np.array_equal(got, want)
 
 
-def test_any_extents_split_last_wave(oracle, cuda_device, monkeypatch):
-    from subcuber_b200 import inputs
+def test_any_extents_split_last_wave(oracle, cuda_device):
+    from subcuber_b200 import inputs, runner
 
     kernel = "blackwell_f16_sw_interleaved_presum_2sm"
     m, n, k = 1001, 2568, 1160
     a, b = inputs.operands("f16", "harness", m, n, k, seed=4)
-    monkeypatch.setenv("SB200_SM_LIMIT", "16")
-    got = _run(kernel, a, b, cuda_device)
+    got = _run(kernel, a, b, cuda_device, runner.options(sm_limit=16))
     assert np.array_equal(got, oracle.sw_gemm("f16", 0, a, b))
 
 
@@ -358,18 +357,15 @@ SPLIT_CASES = [
 
 
 @pytest.mark.parametrize("kernel,sms,shape", SPLIT_CASES)
-def test_split_last_wave_bit_exact_on_harness_values(kernel, sms, shape, oracle, cuda_device, monkeypatch):
-    from subcuber_b200 import inputs
+def test_split_last_wave_bit_exact_on_harness_values(kernel, sms, shape, oracle, cuda_device):
+    from subcuber_b200 import inputs, runner
 
     m, n, k = shape
     dt = _dt(kernel)
     level = _level(kernel)
     a, b = inputs.operands(dt, "harness", m, n, k, seed=4)
-    if sms:
-        monkeypatch.setenv("SB200_SM_LIMIT", str(sms))
-    got = _run(kernel, a, b, cuda_device)
-    monkeypatch.setenv("SB200_NO_SPLIT", "1")
-    unsplit = _run(kernel, a, b, cuda_device)
+    got = _run(kernel, a, b, cuda_device, runner.options(sm_limit=sms))
+    unsplit = _run(kernel, a, b, cuda_device, runner.options(sm_limit=sms, no_split=True))
     assert not np.isnan(got).any()
     assert np.array_equal(got, unsplit)
     if m * n * k <= 2 ** 34:
@@ -380,14 +376,13 @@ def test_split_last_wave_bit_exact_on_harness_values(kernel, sms, shape, oracle,
 
 
 @pytest.mark.parametrize("kernel", ["blackwell_f16_sw_interleaved_presum_2sm", "blackwell_f16_sw_level2_2sm"])
-def test_split_last_wave_uniform_inputs(kernel, oracle, cuda_device, monkeypatch):
+def test_split_last_wave_uniform_inputs(kernel, oracle, cuda_device):
     """On inexact inputs the split changes only the order of fp32 additions: the result stays within the error gate."""
-    from subcuber_b200 import inputs
+    from subcuber_b200 import inputs, runner
 
     m, n, k = (512, 2560, 1024) if _level(kernel) == 1 else (1024, 5120, 2048)
     a, b = inputs.operands("f16", "uniform1", m, n, k, seed=6)
-    monkeypatch.setenv("SB200_SM_LIMIT", "8")
-    got = _run(kernel, a, b, cuda_device)
+    got = _run(kernel, a, b, cuda_device, runner.options(sm_limit=8))
     truth = a.astype(np.float64) @ b.astype(np.float64)
     ref = oracle.sw_gemm("f16", _level(kernel), a, b)
     assert _rel_fro(got, truth) <= 1.5 * _rel_fro(ref, truth)
@@ -560,6 +555,140 @@ def test_full_size_properties(kernel, size, oracle, cuda_device):
         assert err <= 1.5 * ref_err, f"{err:.3e} vs reference routine {ref_err:.3e}"
     else:
         assert _rel_fro(got, truth) < 3e-3
+
+
+def _checksum_ok(a, b, d, tol):
+    """sum(D) = colsum(A) . rowsum(B) over the whole matrix, in double on the device."""
+    total_dev = float(d.double().sum())
+    total = float(a.double().sum(dim=0) @ b.double().sum(dim=1))
+    scale = float(a.double().abs().sum(dim=0) @ b.double().abs().sum(dim=1))
+    return abs(total_dev - total) <= tol * scale, (total_dev, total, scale)
+
+
+# The configurations the headline metric is quoted on, at their full sizes.  The CPU oracle cannot form whole
+# matrices of this size in test time, so: sampled rows against the fp64 product and against the reference routine (or
+# the TF32 model), and the checksum identity over every element.
+def test_target_config_f16_level1_16384(oracle, cuda_device):
+    """f16 Strassen-Winograd level 1 at M = N = K = 16384 (the reference's own test lists reach 16384:
+    tests/hopper_f16_tensorop_strassen_winograd_presum.cu:10-35)."""
+    import torch
+
+    from subcuber_b200 import inputs, runner
+
+    size = 16384
+    kernel = "blackwell_f16_sw_interleaved_presum_2sm"
+    a = inputs.fill_device("f16", "uniform1", (size, size), 1, 0, cuda_device)
+    b = inputs.fill_device("f16", "uniform1", (size, size), 1, 1, cuda_device)
+    d = runner.gemm(kernel, a, b)
+    torch.cuda.synchronize()
+    ok, info = _checksum_ok(a, b, d, 2e-5)
+    assert ok, info
+    a_np, b_np = a.cpu().numpy(), b.cpu().numpy()
+    rows = np.array([0, 131, size // 4 + 5, size // 2 - 1], dtype=np.int32)   # quadrant rows
+    all_rows = np.concatenate([rows, rows + size // 2])
+    truth = oracle.truth_rows("f16", a_np, b_np, all_rows)
+    got = d[torch.from_numpy(all_rows).long().to(cuda_device)].cpu().numpy()
+    ref = oracle.sw_gemm("f16", 1, a_np, b_np, rows=rows)[all_rows]
+    err, ref_err = _rel_fro(got, truth), _rel_fro(ref, truth)
+    assert err <= 1.5 * ref_err, f"{err:.3e} vs reference routine {ref_err:.3e}"
+    # harness tolerance element by element against the reference routine (tests/base_test.cuh:92-93 in the reference)
+    diff = np.abs(got.astype(np.float64) - ref.astype(np.float64))
+    assert ((diff <= 4.0) | (diff <= 1e-2 * np.abs(ref.astype(np.float64)))).all()
+
+
+def test_config_f16_level2_16384(oracle, cuda_device):
+    """f16 level 2 (49 products) at 16384^3 (the reference's level-2 shapes:
+    tests/ampere_f16_tensorop_strassen_winograd_presum_level_2.cu:8-11).  The reference checks its level-2 kernels
+    against the level-1 routine (tests/base_test.cuh:290-302); so does this: sampled rows within 1.5x the level-1
+    routine's error against fp64, the whole matrix by checksum."""
+    import torch
+
+    from subcuber_b200 import inputs, runner
+
+    size = 16384
+    a = inputs.fill_device("f16", "uniform1", (size, size), 1, 0, cuda_device)
+    b = inputs.fill_device("f16", "uniform1", (size, size), 1, 1, cuda_device)
+    d = runner.gemm("blackwell_f16_sw_level2_2sm", a, b)
+    torch.cuda.synchronize()
+    ok, info = _checksum_ok(a, b, d, 2e-5)
+    assert ok, info
+    a_np, b_np = a.cpu().numpy(), b.cpu().numpy()
+    rows = np.array([3, size // 8 + 1, size // 4 + 77, size // 2 - 2], dtype=np.int32)
+    all_rows = np.concatenate([rows, rows + size // 2])
+    truth = oracle.truth_rows("f16", a_np, b_np, all_rows)
+    got = d[torch.from_numpy(all_rows).long().to(cuda_device)].cpu().numpy()
+    ref = oracle.sw_gemm("f16", 1, a_np, b_np, rows=rows)[all_rows]
+    err, ref_err = _rel_fro(got, truth), _rel_fro(ref, truth)
+    assert err <= 1.5 * ref_err, f"{err:.3e} vs level-1 reference routine {ref_err:.3e}"
+
+
+@pytest.mark.parametrize("kernel", ["blackwell_f32_sw_interleaved_presum_2sm", "blackwell_f32_sw_level2_2sm"])
+def test_config_tf32_rectangular_k_heavy(kernel, oracle, cuda_device):
+    """f32 storage, TF32 math, M = 16384, N = 8192, K = 32768, normal(0, 1) inputs, levels 1 and 2 (the reference's
+    only TF32 tensor-op instantiation: example/strassen_gemm_ampere_tf32_tensorop/
+    strassen_ampere_tf32_tensorop_gemm.cu:185-237).  Sampled rows against the fp64 product within 4x the error of the
+    round-to-nearest TF32 level-1 model (the tensor core truncates), whole matrix by checksum."""
+    import torch
+
+    from subcuber_b200 import inputs, runner
+
+    m, n, k = 16384, 8192, 32768
+    a = inputs.fill_device("f32", "normal", (m, k), 1, 0, cuda_device)
+    b = inputs.fill_device("f32", "normal", (k, n), 1, 1, cuda_device)
+    d = runner.gemm(kernel, a, b)
+    torch.cuda.synchronize()
+    ok, info = _checksum_ok(a, b, d, 2e-4)
+    assert ok, info
+    a_np, b_np = a.cpu().numpy(), b.cpu().numpy()
+    rows = np.array([1, m // 4 + 9, m // 2 - 1], dtype=np.int32)
+    all_rows = np.concatenate([rows, rows + m // 2])
+    truth = oracle.truth_rows("f32", a_np, b_np, all_rows)
+    got = d[torch.from_numpy(all_rows).long().to(cuda_device)].cpu().numpy()
+    model = oracle.sw_gemm("tf32", 1, a_np, b_np, rows=rows)[all_rows]
+    err, model_err = _rel_fro(got, truth), _rel_fro(model, truth)
+    level = _level(kernel)
+    assert err <= (4.0 if level == 1 else 8.0) * model_err + 1e-6, f"{err:.3e} vs TF32 model {model_err:.3e}"
+    assert err < (3e-3 if level == 1 else 6e-3)
+
+
+def test_config_f32_level1_2048_against_fp64(oracle, cuda_device):
+    """f32 level 1 at M = N = K = 2048, uniform[-1, 1) inputs, the whole matrix against the fp64 product (the
+    reference's f32 gtest shape, tests/base_test.cuh:290-302 with its host fp64 check)."""
+    from subcuber_b200 import inputs
+
+    m = n = k = 2048
+    a, b = inputs.operands("f32", "uniform1", m, n, k, seed=1)
+    truth = a.astype(np.float64) @ b.astype(np.float64)
+    model = oracle.sw_gemm("tf32", 1, a, b)
+    for kernel in ("blackwell_f32_sw_interleaved_presum_2sm", "blackwell_f32_sw_interleaved_presum"):
+        got = _run(kernel, a, b, cuda_device)
+        err, model_err = _rel_fro(got, truth), _rel_fro(model, truth)
+        assert err <= 4.0 * model_err + 1e-6, f"{kernel}: {err:.3e} vs TF32 model {model_err:.3e}"
+        assert err < 3e-3
+
+
+# ------------------------------------------------------------------------------------- bounded waits
+def test_bounded_wait_gives_up_and_the_device_stays_usable(oracle, cuda_device):
+    """Every device-side wait is bounded (the reference's PostsumSemaphore spins without a bound,
+    include/cutlass/postsum_semaphore.h:102-110).  Here one such wait is made to run out: the first K-halves of the
+    split tiles do not publish their flags, the second halves give up after the (shortened) limit, unwind their CTAs
+    and report status 105.  Nothing faults and nothing spins past its limit; the same GEMM then runs normally on the
+    same device and is bit-exact."""
+    import torch
+
+    from subcuber_b200 import inputs, runner
+
+    kernel = "blackwell_f16_sw_interleaved_presum_2sm"
+    m, n, k = 512, 2560, 1024          # quadrant 1 x 5 pair tiles on 4 pairs: the last wave is one tile, split along K
+    a_np, b_np = inputs.operands("f16", "harness", m, n, k, seed=4)
+    a, b = runner.to_torch(a_np, cuda_device), runner.to_torch(b_np, cuda_device)
+    d = torch.zeros((m, n), dtype=torch.float16, device=cuda_device)
+    with pytest.raises(runner.KernelError) as exc:
+        runner.gemm(kernel, a, b, d, opts=runner.options(sm_limit=8, wait_limit_us=1000, drop_split_flags=True))
+    assert exc.value.code == 105
+    torch.cuda.synchronize()
+    got = _run(kernel, a_np, b_np, cuda_device, runner.options(sm_limit=8))
+    assert np.array_equal(got, oracle.sw_gemm("f16", 1, a_np, b_np))
 
 
 def test_level0_agrees_with_cublas(cuda_device):

@@ -2,10 +2,11 @@
 
 For callers that may not allocate device memory (a process whose pool owns the GPU, a loop that cannot afford
 the device-wide synchronisation of cudaMalloc/cudaFree) the library keeps the level-1 kernels' scratch in a fixed
-32 MiB array of its own.  The test calls the entry point through the C ABI twice in a row, with different operands
+33 MiB array of its own.  The test calls the entry point through the C ABI twice in a row, with different operands
 and shapes, so the second call starts from the scratch the first one left behind, and compares each result with
 the output of `sb200_gemm` on a caller-provided workspace: same kernels, same operands, so the outputs must be
-identical bit for bit.  It also checks that a problem whose scratch does not fit is refused before anything runs.
+identical bit for bit.  It also checks that the device's free memory does not change across a call, that the largest
+documented problem (2048^3) runs, and that a problem whose scratch does not fit is refused before anything runs.
 This file sorts last so that a run that stops at the first failure has already run every other test.
 """
 import numpy as np
@@ -50,10 +51,45 @@ def test_static_scratch_matches_workspace_path_twice_in_a_row(lib, cuda_device):
     assert np.allclose(got2[:4].astype(np.float64), truth, rtol=1e-2, atol=0.05)
 
 
+def test_static_scratch_allocates_nothing_and_covers_its_documented_limit(lib, cuda_device):
+    """After a first call (which loads the kernels and looks up the array's address) a call must leave the device's
+    free memory exactly as it found it.  2048^3 is the largest cube the header promises."""
+    import torch
+
+    m = n = k = 2048
+    from subcuber_b200 import inputs, runner
+
+    a = inputs.fill_device("f16", "uniform1", (m, k), 41, 0, cuda_device)
+    b = inputs.fill_device("f16", "uniform1", (k, n), 41, 1, cuda_device)
+    want = runner.gemm(KERNEL, a, b)
+    got = torch.full((m, n), float("nan"), dtype=torch.float16, device=cuda_device)
+    stream = torch.cuda.current_stream(cuda_device).cuda_stream
+    with torch.cuda.device(cuda_device):
+        assert lib.sb200_gemm_f16_sw_static_scratch(a.data_ptr(), b.data_ptr(), got.data_ptr(), m, n, k, stream, 1) == 0
+        torch.cuda.synchronize()
+        free_before, _ = torch.cuda.mem_get_info(cuda_device)
+        assert lib.sb200_gemm_f16_sw_static_scratch(a.data_ptr(), b.data_ptr(), got.data_ptr(), m, n, k, stream, 1) == 0
+        torch.cuda.synchronize()
+        free_after, _ = torch.cuda.mem_get_info(cuda_device)
+    assert free_after == free_before, "the allocation-free entry point changed the device's free memory"
+    assert torch.equal(got, want)
+
+
 def test_static_scratch_rejects_what_does_not_fit(lib, cuda_device):
     import torch
 
-    m = n = k = 4096  # needs 96 MiB of scratch, the array holds 32 MiB
+    # just above the limit: 2048 x 2048 x 2304 needs 34 MiB of scratch, the array holds 33 MiB
+    m, n, k = 2048, 2048, 2304
+    a = torch.zeros((m, k), dtype=torch.float16, device=cuda_device)
+    b = torch.zeros((k, n), dtype=torch.float16, device=cuda_device)
+    d = torch.full((m, n), 7.0, dtype=torch.float16, device=cuda_device)
+    with torch.cuda.device(cuda_device):
+        rc = lib.sb200_gemm_f16_sw_static_scratch(a.data_ptr(), b.data_ptr(), d.data_ptr(), m, n, k, None, 1)
+    assert rc == ERR_SCRATCH_TOO_LARGE
+    torch.cuda.synchronize()
+    assert float(d.min()) == 7.0 and float(d.max()) == 7.0  # nothing ran
+
+    m = n = k = 4096  # needs 128 MiB of scratch
     a = torch.zeros((m, k), dtype=torch.float16, device=cuda_device)
     b = torch.zeros((k, n), dtype=torch.float16, device=cuda_device)
     d = torch.full((m, n), 7.0, dtype=torch.float16, device=cuda_device)
