@@ -169,6 +169,15 @@ typedef struct sb200_gemm_options {
 size_t sb200_gemm_workspace_bytes_opt(const char* kernel, int m, int n, int k, const sb200_gemm_options* options);
 int sb200_gemm_opt(const char* kernel, const void* a, const void* b, void* d, int m, int n, int k, void* workspace,
                    size_t workspace_bytes, sb200_stream_t stream, const sb200_gemm_options* options);
+/* The plan by which the output tiles of one launch of a tensor-core kernel are dealt to its workers (CTAs or CTA
+ * pairs) on a device of `sms` SMs (0 = the current device): whole tiles round-robin, and - where the last wave would
+ * not be full - tiles cut once along K so that every worker gets an equal share (the role the reference gives to
+ * split_k_slices, src/cuda/kernel_runner.cpp:244-255).  Writes 8 ints per unit, in the order each worker runs them:
+ * worker, tile, part (0 = whole tile or the part that publishes its partial sum, 1 = the part that adds it), parts
+ * (1 or 2), first k-step, end k-step, hand-off slot, split slot.  Returns the number of units (negative: error code);
+ * *workers = CTAs or pairs launched.  Host arithmetic only. */
+int sb200_gemm_deal(const char* kernel, int m, int n, int k, const sb200_gemm_options* options, int sms, int* units,
+                    int max_units, int* workers);
 /* General form D = alpha * (A * B) + beta * C (the argument set of the reference's operators,
  * include/cutlass/gemm/device/strassen_gemm.h:365-451; the reference's runner fixes alpha = 1, beta = 0).  C is m x n
  * row-major in the output type, may be the same buffer as D, and is read only when beta != 0.  The scaling is applied

@@ -73,8 +73,9 @@ def sw_gemm(dtype: str, level: int, A: np.ndarray, B: np.ndarray, rows=None, alp
             interim_round: bool = False) -> np.ndarray:
     """D = alpha * (A @ B by Strassen-Winograd at `level`) + beta * Cin in the type set `dtype`.
 
-    With `rows` (level 0: C rows; level 1: quadrant rows r, producing C rows r and r + M/2) only those rows
-    of the returned matrix are meaningful; the rest are zero.
+    With `rows` (level 0: C rows; level 1: quadrant rows r, producing C rows r and r + M/2; level 2: rows r of the
+    innermost quadrants, producing C rows r, r + M/4, r + M/2 and r + 3M/4) only those rows of the returned matrix
+    are meaningful; the rest are zero.
     """
     npd = NP_DTYPE[dtype]
     A = np.ascontiguousarray(A, dtype=npd)

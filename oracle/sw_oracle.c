@@ -46,8 +46,9 @@
  *
  * Row sampling: every routine takes (nrows, rows).  rows == NULL means all rows of the (quadrant) row
  * space.  For orc_gemm a listed row r produces C row r.  For orc_sw_gemm at level 1 a listed row r in
- * [0, M/2) produces C rows r and r + M/2.  Output is always written at its natural place in C
- * (leading dimension ldc); unlisted rows are not touched.
+ * [0, M/2) produces C rows r and r + M/2; at level 2 a listed row r in [0, M/4) produces C rows r,
+ * r + M/4, r + M/2 and r + 3M/4.  Output is always written at its natural place in C (leading
+ * dimension ldc); unlisted rows are not touched.
  */
 #include <math.h>
 #include <stdint.h>
@@ -219,9 +220,12 @@ static inline float tf32_round(float x) {
     free(pb);                                                                                           \
   }                                                                                                     \
                                                                                                         \
-  /* Level 2: outer Winograd formulas, each outer product by a level-1 recursion (all rows). */         \
+  /* Level 2: outer Winograd formulas, each outer product by a level-1 recursion.  With a row list      \
+   * (rows q of the innermost quadrants, in [0, M/4)) only C rows q, q + M/4, q + M/2 and q + 3M/4 are  \
+   * formed. */                                                                                         \
   static int sw2_##SUFFIX(int M, int N, int K, TACC alpha, const TIN *A, int lda, const TIN *B,         \
-                          int ldb, TACC beta, const TOUT *Cin, TOUT *C, int ldc, int interim_round) {   \
+                          int ldb, TACC beta, const TOUT *Cin, TOUT *C, int ldc, int interim_round,     \
+                          int nrows, const int *rows) {                                                 \
     int hm = M / 2, hn = N / 2, hk = K / 2;                                                             \
     size_t qa = (size_t)hm * hk, qb = (size_t)hk * hn, qc = (size_t)hm * hn;                            \
     TIN *pa = (TIN *)malloc(sizeof(TIN) * 4 * qa);                                                      \
@@ -236,8 +240,10 @@ static inline float tf32_round(float x) {
     int oldb[7] = {ldb, ldb, hn, hn, hn, ldb, hn};                                                      \
     for (int p = 0; p < 7; ++p)                                                                         \
       sw1_rows_##SUFFIX(hm, hn, hk, (TACC)1, opa[p], olda[p], opb[p], oldb[p], (TACC)0, NULL, NULL, 0,  \
-                        0, NULL, mm + p * qc);                                                          \
-    _Pragma("omp parallel for") for (int r = 0; r < hm; ++r) for (int j = 0; j < hn; ++j) {             \
+                        nrows, rows, mm + p * qc);                                                      \
+    int R2 = rows ? 2 * nrows : hm;                                                                     \
+    _Pragma("omp parallel for") for (int ri = 0; ri < R2; ++ri) for (int j = 0; j < hn; ++j) {          \
+      int r = rows ? rows[ri >> 1] + ((ri & 1) ? hm / 2 : 0) : ri;                                      \
       size_t o = (size_t)r * hn + j;                                                                    \
       TACC m0 = mm[o], m1 = mm[qc + o], m2 = mm[2 * qc + o], m3 = mm[3 * qc + o];                       \
       TACC m4 = mm[4 * qc + o], m5 = mm[5 * qc + o], m6 = mm[6 * qc + o];                               \
@@ -316,13 +322,13 @@ int orc_sw_gemm(int dtype, int level, int M, int N, int K, double alpha, const v
     return 1;
   }
   if (level == 2) {
-    if ((M % 4) || (N % 4) || (K % 4) || rows) return 1;
+    if ((M % 4) || (N % 4) || (K % 4)) return 1;
     switch (dtype) {
-      case 0: return sw2_f16(M, N, K, (float)alpha, A, lda, B, ldb, (float)beta, Cin, C, ldc, interim_round);
-      case 1: return sw2_f32(M, N, K, (float)alpha, A, lda, B, ldb, (float)beta, Cin, C, ldc, interim_round);
-      case 2: return sw2_f64(M, N, K, alpha, A, lda, B, ldb, beta, Cin, C, ldc, interim_round);
-      case 3: return sw2_tf32(M, N, K, (float)alpha, A, lda, B, ldb, (float)beta, Cin, C, ldc, interim_round);
-      case 4: return sw2_bf16(M, N, K, (float)alpha, A, lda, B, ldb, (float)beta, Cin, C, ldc, interim_round);
+      case 0: return sw2_f16(M, N, K, (float)alpha, A, lda, B, ldb, (float)beta, Cin, C, ldc, interim_round, nrows, rows);
+      case 1: return sw2_f32(M, N, K, (float)alpha, A, lda, B, ldb, (float)beta, Cin, C, ldc, interim_round, nrows, rows);
+      case 2: return sw2_f64(M, N, K, alpha, A, lda, B, ldb, beta, Cin, C, ldc, interim_round, nrows, rows);
+      case 3: return sw2_tf32(M, N, K, (float)alpha, A, lda, B, ldb, (float)beta, Cin, C, ldc, interim_round, nrows, rows);
+      case 4: return sw2_bf16(M, N, K, (float)alpha, A, lda, B, ldb, (float)beta, Cin, C, ldc, interim_round, nrows, rows);
     }
   }
   return 1;

@@ -77,6 +77,8 @@ def load(build_if_missing: bool = True) -> C.CDLL:
     lib.sb200_gemm_workspace_bytes_opt.argtypes = [C.c_char_p, C.c_int, C.c_int, C.c_int, C.POINTER(GemmOptions)]
     lib.sb200_gemm_opt.argtypes = [C.c_char_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
                                    C.c_void_p, C.c_size_t, C.c_void_p, C.POINTER(GemmOptions)]
+    lib.sb200_gemm_deal.argtypes = [C.c_char_p, C.c_int, C.c_int, C.c_int, C.POINTER(GemmOptions), C.c_int,
+                                    C.POINTER(C.c_int), C.c_int, C.POINTER(C.c_int)]
     lib.sb200_gemm_ex.argtypes = [C.c_char_p, C.c_double, C.c_void_p, C.c_void_p, C.c_double, C.c_void_p, C.c_void_p,
                                   C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_size_t, C.c_void_p]
     lib.sb200_gemm_colmajor.argtypes = lib.sb200_gemm.argtypes

@@ -458,6 +458,15 @@ extern "C" size_t sb200_gemm_workspace_bytes_opt(const char* kernel, int m, int 
   return sb200::workspace_bytes(g);
 }
 
+extern "C" int sb200_gemm_deal(const char* kernel, int m, int n, int k, const sb200_gemm_options* options, int sms,
+                               int* units, int max_units, int* workers) {
+  const KernelDesc* d = resolve_desc(kernel, m, n, k);
+  if (!d) return -SB200_ERR_NO_KERNEL;
+  if (!units || max_units < 0 || m <= 0 || n <= 0 || k <= 0 || d->dt == sb200::kF64) return -SB200_ERR_INVALID_PROBLEM;
+  GemmArgs g = make_args(*d, nullptr, nullptr, nullptr, m, n, k, options);
+  return sb200::tc::deal_units(g, sms, units, max_units, workers);
+}
+
 extern "C" int sb200_gemm_opt(const char* kernel, const void* a, const void* b, void* d_out, int m, int n, int k,
                               void* workspace, size_t workspace_bytes, sb200_stream_t stream,
                               const sb200_gemm_options* options) {

@@ -75,9 +75,10 @@ struct Layout {
   // level 2 only: outer presums [4][m/2][k/2], [4][k/2][n/2] and three outer chain buffers (fp32, tile-contiguous,
   // four inner quadrants each)
   size_t off_opa, off_opb, off_x[3], quadrant_floats;
-  // K-split of the last wave (WorkUnit in sw_kernel.cuh)
+  // how the tiles are dealt to the workers (WorkUnit in sw_kernel.cuh)
   int workers;       // CTAs (1-CTA kernels) or CTA pairs launched
-  int split_tiles;   // tiles of the last wave computed as two K-halves (0: none)
+  int whole_tiles, region_tiles, region_mode, region_snap;
+  int split_slots;   // tiles that may be cut along K (0: none): slots of the split buffer and of the flag array
   size_t off_split_buf, off_split_flags, split_flag_bytes;
 };
 
@@ -85,15 +86,38 @@ int level_of(Variant v) { return v == kCubic ? 0 : (v == kInterleavedLevel2 ? 2 
 
 int sm_count() { return sm_count_of_current_device(); }
 
-// Tiles of the last wave to split: all of them when the wave is at most half full (then it lasts half as long),
-// none otherwise.  The fused-presum kernels are never split.
-int tiles_to_split(int tiles, int workers, int num_k, Variant v, bool no_split) {
-  if (v == kFusedPresum || v == kStrassenFused || workers <= 0 || num_k < 8 || no_split) return 0;
-  const int rem = tiles % workers;
-  return (rem > 0 && 2 * rem <= workers) ? rem : 0;
+// Deals `tiles` output tiles to at most `cap` workers (see WorkUnit in sw_kernel.cuh for the three ways).
+//   fewer tiles than workers: every tile is cut into two K-halves when that still fits the workers;
+//   a last wave that is not full: the last full wave and the partial one are streamed over all workers, unless the
+//   partial wave is so nearly full (more than 9/10) that cutting tiles costs more than it saves.
+// The fused-presum kernels are never cut, nor are products of fewer than 8 k-steps.
+void deal_tiles(Layout& L, int tiles, int cap, Variant v, bool no_split) {
+  L.workers = tiles < cap ? tiles : cap;
+  L.whole_tiles = tiles;
+  L.region_tiles = 0;
+  L.region_mode = kRegionNone;
+  L.region_snap = 0;
+  L.split_slots = 0;
+  if (v == kFusedPresum || v == kStrassenFused || no_split || L.num_k < 8 || cap < 2) return;
+  if (tiles < cap) {
+    if (2 * tiles > cap) return;
+    L.workers = 2 * tiles;
+    L.whole_tiles = 0;
+    L.region_tiles = tiles;
+    L.region_mode = kRegionHalves;
+    L.split_slots = tiles;
+    return;
+  }
+  const int q = tiles / cap, rem = tiles % cap;
+  if (rem == 0 || 10 * rem > 9 * cap) return;
+  L.whole_tiles = (q - 1) * cap;
+  L.region_tiles = cap + rem;
+  L.region_mode = kRegionStream;
+  L.region_snap = L.num_k / 16 > 2 ? L.num_k / 16 : 2;
+  L.split_slots = cap;
 }
 
-Layout make_layout(const GemmArgs& a) {
+Layout make_layout(const GemmArgs& a, int cap_override = 0) {
   Layout L;
   memset(&L, 0, sizeof(L));
   L.esize = esize_of(a.dtype);
@@ -125,26 +149,31 @@ Layout make_layout(const GemmArgs& a) {
     L.off_pb = off;
     off = align_up(off + size_t(4) * L.kq * L.nq * L.esize, 256);
   }
-  int cap = sm_count();
+  int cap = cap_override > 0 ? cap_override : sm_count();
   if (a.sm_limit > 0 && a.sm_limit < cap) cap = a.sm_limit;  // the caller keeps the other SMs for its own kernels
   if (a.pair) cap /= 2;  // one pair per two SMs
   if (cap < 1) cap = 1;
-  L.workers = L.tiles_m * L.tiles_n < cap ? L.tiles_m * L.tiles_n : cap;
-  L.split_tiles = tiles_to_split(L.tiles_m * L.tiles_n, L.workers, L.num_k, a.variant, a.no_split != 0);
+  bool no_split = a.no_split != 0;
+#ifdef SB200_PROFILE
+  if (getenv("SB200_NO_SPLIT")) no_split = true;  // measurement aid of profile builds
+#endif
+  deal_tiles(L, L.tiles_m * L.tiles_n, cap, a.variant, no_split);
   const int nws = a.variant == kCubic ? 0 : (a.variant == kFusedPresum ? 2 : (a.variant == kStrassenFused ? 3 : 4));
   const size_t tile_bytes = size_t(128) * L.bn * sizeof(float) * (a.pair ? 2 : 1);  // per tile of the grid
   const size_t quadrant_bytes = size_t(L.tiles_m) * L.tiles_n * tile_bytes;
   L.quadrant_floats = quadrant_bytes / sizeof(float);
   for (int i = 0; i < nws; ++i) {
     L.off_ws[i] = off;
-    // the second half of every split tile keeps its level-1 hand-off tiles in extra slots behind the grid's
-    off = align_up(off + quadrant_bytes + size_t(L.split_tiles) * tile_bytes, 256);
+    // buffer 0 (M0) is indexed by tile: the finisher of every cut tile keeps its hand-off tile in an extra slot behind
+    // the grid's; buffers 1..3 are indexed by worker
+    const size_t bytes = i == 0 ? quadrant_bytes + size_t(L.split_slots) * tile_bytes : size_t(L.workers) * tile_bytes;
+    off = align_up(off + bytes, 256);
   }
-  if (L.split_tiles) {
+  if (L.split_slots) {
     L.off_split_buf = off;
-    off = align_up(off + size_t(L.split_tiles) * 4 * tile_bytes, 256);
+    off = align_up(off + size_t(L.split_slots) * 4 * tile_bytes, 256);
     L.off_split_flags = off;
-    L.split_flag_bytes = size_t(L.split_tiles) * 4 * 8 * sizeof(int);
+    L.split_flag_bytes = size_t(L.split_slots) * 4 * 8 * sizeof(int);
     off = align_up(off + L.split_flag_bytes, 256);
   }
   if (L.level == 2)
@@ -291,6 +320,27 @@ WorkspaceLayout workspace_layout(const GemmArgs& a) {
   return w;
 }
 
+int deal_units(const GemmArgs& a, int sms, int* out, int max_units, int* workers) {
+  const Layout L = make_layout(a, sms);
+  KernelParams p;
+  memset(&p, 0, sizeof(p));
+  p.tiles_m = L.tiles_m; p.tiles_n = L.tiles_n; p.num_k = L.num_k;
+  p.whole_tiles = L.whole_tiles; p.region_tiles = L.region_tiles; p.region_mode = L.region_mode;
+  p.region_snap = L.region_snap;
+  if (workers) *workers = L.workers;
+  int n = 0;
+  for (int w = 0; w < L.workers; ++w) {
+    const int mine = units_of_worker(p, w, L.workers);
+    for (int it = 0; it < mine; ++it, ++n) {
+      if (n >= max_units) continue;
+      const WorkUnit u = unit_of(p, w, L.workers, it);
+      int* o = out + size_t(n) * 8;
+      o[0] = w; o[1] = u.tile; o[2] = u.part; o[3] = u.nparts; o[4] = u.k0; o[5] = u.k1; o[6] = u.ws_slot; o[7] = u.split_idx;
+    }
+  }
+  return n;
+}
+
 int launches_per_run(const GemmArgs& a) {
   return a.variant == kInterleavedLevel2 ? 14 : (a.variant == kInterleavedPresum ? 2 : 1);
 }
@@ -324,7 +374,7 @@ struct LaunchSpec {
   PresumSideJob more_jobs[2];  // presum jobs of the level above, run by launch 1's presum warps
   int n_more_jobs;
   int* status;
-  int split_from;            // first split tile (= number of tiles when nothing is split)
+  int whole_tiles, region_tiles, region_mode, region_snap;  // how the tiles are dealt (Layout)
   float* split_buf;
   int* split_flags;
   int* split_epoch;          // counter shared by the launches of one run
@@ -391,6 +441,15 @@ void apply_tuning_aids(KernelParams& p) {
           }
           if (cnt > 1) fprintf(stderr, "[skew] tile %3d of each pair: %d pairs, start spread %.1f us (first at +%.1f us)\n", it, cnt,
                                (hi - lo) * 1e-3, (lo - ts[0]) * 1e-3);
+        }
+        if (getenv("SB200_PROF_DUMP")) {
+          // per pair: SM id of its leader CTA, then the durations of its first tiles in us
+          for (int pr = 0; pr < 74; ++pr) {
+            fprintf(stderr, "[dump] pair %2d sm %3lld start0 %+6.1f:", pr, prof_host[3000 + pr], (ts[pr * 128] - ts[0]) * 1e-3);
+            for (int it = 0; it + 1 < 24 && ts[pr * 128 + it + 1]; ++it)
+              fprintf(stderr, " %6.1f", (ts[pr * 128 + it + 1] - ts[pr * 128 + it]) * 1e-3);
+            fprintf(stderr, "\n");
+          }
         }
       }
       if (getenv("SB200_PROF_TRACE")) {
@@ -475,7 +534,10 @@ int launch_group(const LaunchSpec& s, cudaStream_t stream, MarkFn mark) {
   p.tiles_m = s.tiles_m;
   p.tiles_n = s.tiles_n;
   p.num_k = s.num_k;
-  p.split_from = s.split_from;
+  p.whole_tiles = s.whole_tiles;
+  p.region_tiles = s.region_tiles;
+  p.region_mode = s.region_mode;
+  p.region_snap = s.region_snap;
   p.split_buf = s.split_buf;
   p.split_flags = s.split_flags;
   // raster band height in tile rows: the tiles of a wave share A row tiles and B column tiles through L2; taller bands
@@ -564,8 +626,11 @@ int run(const GemmArgs& a, void* workspace, size_t workspace_size, cudaStream_t 
   s.grid = L.workers;
   int epoch = 0;
   s.split_epoch = &epoch;
-  s.split_from = L.tiles_m * L.tiles_n - L.split_tiles;
-  if (L.split_tiles) {
+  s.whole_tiles = L.whole_tiles;
+  s.region_tiles = L.region_tiles;
+  s.region_mode = L.region_mode;
+  s.region_snap = L.region_snap;
+  if (L.split_slots) {
     s.split_buf = reinterpret_cast<float*>(wsb + L.off_split_buf);
     s.split_flags = reinterpret_cast<int*>(wsb + L.off_split_flags);
     ce = cudaMemsetAsync(s.split_flags, 0, L.split_flag_bytes, stream);

@@ -103,7 +103,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
   const uint32_t rank = ptx::cluster_ctarank();   // 0 = leader
   const int pair = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
-  const int total_tiles = total_units(p);  // work units: pair tiles, or K-halves of the tiles of a split last wave
+  const int my_units = units_of_worker(p, pair, num_pairs);  // pair tiles, or parts of tiles cut along K
   const int nproducts = p.prog.nproducts;
 
   if (threadIdx.x == 0) {
@@ -147,8 +147,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
       bool ok = true;
       const long long pt0 = SB200_CLOCK();
       long long pw_empty = 0, pw_issue = 0;
-      for (int w = pair; ok && w < total_tiles; w += num_pairs) {
-        const WorkUnit wu = unit_of(p, w);
+      for (int it = 0; ok && it < my_units; ++it) {
+        const WorkUnit wu = unit_of(p, pair, num_pairs, it);
         const TileCoord tile = tile_of(wu.tile, p.tiles_m, p.tiles_n, p.band);
         const int row0 = tile.i * Cfg::PAIR_M + static_cast<int>(rank) * Cfg::BM;
         const int col0 = tile.j * BN + static_cast<int>(rank) * Cfg::BN_CTA;
@@ -178,13 +178,13 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
             const long long tw2 = SB200_CLOCK();
             pw_empty += tw2 - tw;
 #ifdef SB200_PROFILE_TRACE
-            const bool traced = p.prof && lane == 0 && blockIdx.x == 0 && w == pair + 3 * num_pairs && ps == 0 && kk < 64;
+            const bool traced = p.prof && lane == 0 && blockIdx.x == 0 && it == 3 && ps == 0 && kk < 64;
             if (traced) p.prof[2048 + kk * 8 + 0] = tw2;
 #endif
             uint8_t* sa = smem + stage * Cfg::STAGE_BYTES;
             uint8_t* sb = sa + Cfg::A_BYTES;
             // measurement aids: bit 1 = never load; bit 3 = load only while the ring fills for the first time
-            const bool no_load = no_load_all || (SB200_DEBUG_BIT(p, 8) && (w != pair || ps > 0 || kk >= wu.k0 + STAGES));
+            const bool no_load = no_load_all || (SB200_DEBUG_BIT(p, 8) && (it != 0 || ps > 0 || kk >= wu.k0 + STAGES));
             if (ptx::elect_one()) {
               if (rank == 0) {
                 if (tx && !no_load) ptx::mbar_arrive_expect_tx(&full_bar[stage], tx);
@@ -250,13 +250,20 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
       bool ok = true;
       const long long mt0 = SB200_CLOCK_LIGHT();
       long long mw_full = 0, mw_free = 0, mw_issue = 0;
-      for (int w = pair; ok && w < total_tiles; w += num_pairs, ++iter) {
-        const WorkUnit wu = unit_of(p, w);
+      for (int it = 0; ok && it < my_units; ++it, ++iter) {
+        const WorkUnit wu = unit_of(p, pair, num_pairs, it);
         const int nk = wu.k1 - wu.k0;
         const uint32_t sx = p.prog.alternate_slots ? (iter & 1u) : 0u;
 #ifdef SB200_PROFILE
         // wall-clock time at which this pair starts its iter-th tile (skew between the pairs of a wave)
-        if (p.prof && lane == 0 && iter < 128) p.prof[4096 + pair * 128 + iter] = static_cast<long long>(ptx::globaltimer_ns());
+        if (p.prof && lane == 0 && iter < 128) {
+          p.prof[4096 + pair * 128 + iter] = static_cast<long long>(ptx::globaltimer_ns());
+          if (iter == 0) {
+            unsigned smid;
+            asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+            p.prof[3000 + pair] = smid;
+          }
+        }
 #endif
         for (int ps = 0; ok && ps < nproducts; ++ps) {
           const sb200_product_t& pr = p.prog.product[ps];
@@ -344,12 +351,12 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int w = pair; ok && w < total_tiles; w += num_pairs) {
-        const WorkUnit wu = unit_of(p, w);
+      for (int it = 0; ok && it < my_units; ++it) {
+        const WorkUnit wu = unit_of(p, pair, num_pairs, it);
         for (int ps = 0; ok && ps < nproducts; ++ps)
           for (int kk = 0; kk < wu.k1 - wu.k0; ++kk) {
             if (!ptx::mbar_wait(&full_bar[stage], phase, abort_flag, p.wait_ns)) { ok = false; break; }
-            if (blockIdx.x == 0 && w == pair + 3 * num_pairs && ps == 0 && kk < 64) p.prof[2048 + kk * 8 + 2] = clock64();
+            if (blockIdx.x == 0 && it == 3 && ps == 0 && kk < 64) p.prof[2048 + kk * 8 + 2] = clock64();
             if (++stage == STAGES) { stage = 0; phase ^= 1u; }
           }
       }
@@ -363,8 +370,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
     bool ok = true;
     const long long et0 = SB200_CLOCK();
     long long ew_full = 0;
-    for (int w = pair; ok && w < total_tiles; w += num_pairs, ++iter) {
-      const WorkUnit wu = unit_of(p, w);
+    for (int it = 0; ok && it < my_units; ++it, ++iter) {
+      const WorkUnit wu = unit_of(p, pair, num_pairs, it);
       const TileCoord tile = tile_of(wu.tile, p.tiles_m, p.tiles_n, p.band);
       const uint32_t sx = p.prog.alternate_slots ? (iter & 1u) : 0u;
       for (int es = 0; ok && es < p.prog.nepilogues; ++es) {
@@ -438,8 +445,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int w = pair; ok && w < total_tiles; w += num_pairs) {
-        const WorkUnit wu = unit_of(p, w);
+      for (int it = 0; ok && it < my_units; ++it) {
+        const WorkUnit wu = unit_of(p, pair, num_pairs, it);
         const TileCoord tile = tile_of(wu.tile, p.tiles_m, p.tiles_n, p.band);
         const int row0 = tile.i * Cfg::PAIR_M + static_cast<int>(rank) * Cfg::BM;
         const int col0 = tile.j * BN + static_cast<int>(rank) * Cfg::BN_CTA;

@@ -106,7 +106,11 @@ def test_workspace_layout(lib):
     q = 4096 * 4096 * 2
     assert w.presum_a == 256 and w.presum_b == 256 + 4 * q and w.handoff[0] == 256 + 8 * q
     tile = 128 * 256 * 4
-    assert w.handoff[1] - w.handoff[0] == 32 * 16 * tile and w.total == w.handoff[3] + 32 * 16 * tile
+    # buffer 0 (M0) holds one tile per tile of the grid (plus slots for cut tiles), buffers 1..3 one tile per worker
+    assert w.handoff[1] - w.handoff[0] >= 32 * 16 * tile and (w.handoff[1] - w.handoff[0]) % tile == 0
+    per_worker = w.handoff[2] - w.handoff[1]
+    assert per_worker >= tile and per_worker % tile == 0 and w.handoff[3] - w.handoff[2] == per_worker
+    assert w.total >= w.handoff[3] + per_worker
     assert lib.sb200_gemm_workspace_bytes(b"blackwell_f16_sw_interleaved_presum", 8192, 8192, 8192) == w.total
     assert lib.sb200_gemm_workspace_bytes(b"blackwell_f16_cubic_128x256", 8192, 8192, 8192) == 256
     assert lib.sb200_gemm_workspace_bytes(b"nope", 8, 8, 8) == 0

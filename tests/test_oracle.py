@@ -135,6 +135,20 @@ def test_row_sampling_matches_full(oracle):
     assert np.allclose(t, (a.astype(np.float64) @ b.astype(np.float64))[[3, 47]], rtol=0, atol=1e-12)
 
 
+def test_row_sampling_matches_full_at_level2(oracle):
+    rng = np.random.default_rng(12)
+    a = rng.uniform(-1, 1, (96, 80)).astype(np.float16)
+    b = rng.uniform(-1, 1, (80, 112)).astype(np.float16)
+    rows = [0, 7, 23]   # rows of the innermost quadrants: each yields four C rows
+    for interim_round in (False, True):
+        full = oracle.sw_gemm("f16", 2, a, b, interim_round=interim_round)
+        part = oracle.sw_gemm("f16", 2, a, b, rows=rows, interim_round=interim_round)
+        for r in rows:
+            for blk in range(4):
+                assert np.array_equal(part[r + 24 * blk], full[r + 24 * blk])
+        assert not part[1].any()
+
+
 def test_level2_interim_rounding_is_the_less_accurate_variant(oracle):
     rng = np.random.default_rng(2)
     a = rng.uniform(-1, 1, (128, 128)).astype(np.float16)
