@@ -169,13 +169,13 @@ typedef struct sb200_gemm_options {
 size_t sb200_gemm_workspace_bytes_opt(const char* kernel, int m, int n, int k, const sb200_gemm_options* options);
 int sb200_gemm_opt(const char* kernel, const void* a, const void* b, void* d, int m, int n, int k, void* workspace,
                    size_t workspace_bytes, sb200_stream_t stream, const sb200_gemm_options* options);
-/* The plan by which the output tiles of one launch of a tensor-core kernel are dealt to its workers (CTAs or CTA
- * pairs) on a device of `sms` SMs (0 = the current device): whole tiles round-robin, and - where the last wave would
- * not be full - tiles cut once along K so that every worker gets an equal share (the role the reference gives to
- * split_k_slices, src/cuda/kernel_runner.cpp:244-255).  Writes 8 ints per unit, in the order each worker runs them:
- * worker, tile, part (0 = whole tile or the part that publishes its partial sum, 1 = the part that adds it), parts
- * (1 or 2), first k-step, end k-step, hand-off slot, split slot.  Returns the number of units (negative: error code);
- * *workers = CTAs or pairs launched.  Host arithmetic only. */
+/* The unit list of one launch of a tensor-core kernel on a device of `sms` SMs (0 = the current device): whole output
+ * tiles in raster order and, where the last wave would be at most half full (or there are fewer tiles than half the
+ * workers), tiles cut into two K-halves that run at the same time (the role the reference gives to split_k_slices,
+ * src/cuda/kernel_runner.cpp:244-255).  Writes 8 ints per unit in list order: worker under a round-robin deal, tile,
+ * part (0 = whole tile or the half that publishes its partial sum, 1 = the half that adds it), parts (1 or 2), first
+ * k-step, end k-step, hand-off slot, split slot.  Returns the number of units (negative: error code); *workers = CTAs
+ * or CTA pairs launched.  Host arithmetic only. */
 int sb200_gemm_deal(const char* kernel, int m, int n, int k, const sb200_gemm_options* options, int sms, int* units,
                     int max_units, int* workers);
 /* General form D = alpha * (A * B) + beta * C (the argument set of the reference's operators,
@@ -207,7 +207,8 @@ int sb200_gemm_host(const char* kernel, const void* a_host, const void* b_host, 
  * The scratch memory the kernels need lives in a fixed array of SB200_STATIC_SCRATCH_BYTES inside the library,
  * resident on every GPU that uses this call until the process exits.  The call itself performs no cudaMalloc,
  * cudaFree or other allocating call.  Limits:
- *  - the problem's scratch (sb200_gemm_workspace_bytes of that kernel) must fit, else SB200_ERR_SCRATCH_TOO_LARGE
+ *  - the problem's scratch (sb200_gemm_workspace_bytes_opt of that kernel with no_split = 1: this call never cuts
+ *    tiles along K, so that its scratch does not depend on the GPU's SM count) must fit, else SB200_ERR_SCRATCH_TOO_LARGE
  *    is returned and nothing runs (the 33 MiB of the array cover m = n = k = 2048, which needs 32 MiB and 256 bytes;
  *    2048 x 2048 x 2304 already needs 34 MiB, 3072^3 72 MiB, 4096^3 128 MiB);
  *  - one array per GPU, shared by all calls and never cleared between them except for what must start at zero

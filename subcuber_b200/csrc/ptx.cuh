@@ -245,6 +245,17 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint64_t* bar, uint32_t cta)
       "r"(cta)
       : "memory");
 }
+// 32-bit store into the shared memory of CTA `cta` of the cluster, at the offset of `local` in this CTA.
+__device__ __forceinline__ void st_shared_cluster_u32(const void* local, uint32_t cta, uint32_t value) {
+  asm volatile(
+      "{\n\t"
+      ".reg .b32 ra;\n\t"
+      "mapa.shared::cluster.u32 ra, %0, %1;\n\t"
+      "st.shared::cluster.u32 [ra], %2;\n\t"
+      "}\n" ::"r"(smem_u32(local)),
+      "r"(cta), "r"(value)
+      : "memory");
+}
 __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(

@@ -69,6 +69,7 @@ extern "C" int sb200_gemm_f16_sw_static_scratch(const void* a, const void* b, vo
   g.b = b;
   g.d = d;
   g.bn = 256;
+  g.no_split = 1;  // no tile is cut along K: the scratch stays small and its size does not depend on the GPU's SM count
   int rc = sb200::can_implement(g);
   if (rc) return rc;
   if (sb200::workspace_bytes(g) > static_cast<size_t>(SB200_STATIC_SCRATCH_BYTES)) return SB200_ERR_SCRATCH_TOO_LARGE;

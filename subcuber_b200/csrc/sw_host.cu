@@ -75,10 +75,10 @@ struct Layout {
   // level 2 only: outer presums [4][m/2][k/2], [4][k/2][n/2] and three outer chain buffers (fp32, tile-contiguous,
   // four inner quadrants each)
   size_t off_opa, off_opb, off_x[3], quadrant_floats;
-  // how the tiles are dealt to the workers (WorkUnit in sw_kernel.cuh)
+  // the unit list (WorkUnit in sw_kernel.cuh)
   int workers;       // CTAs (1-CTA kernels) or CTA pairs launched
-  int whole_tiles, region_tiles, region_mode, region_snap;
-  int split_slots;   // tiles that may be cut along K (0: none): slots of the split buffer and of the flag array
+  int whole_tiles;   // tiles handed out whole
+  int region_tiles;  // tiles that follow, each handed out as two K-halves (0: none)
   size_t off_split_buf, off_split_flags, split_flag_bytes;
 };
 
@@ -86,35 +86,26 @@ int level_of(Variant v) { return v == kCubic ? 0 : (v == kInterleavedLevel2 ? 2 
 
 int sm_count() { return sm_count_of_current_device(); }
 
-// Deals `tiles` output tiles to at most `cap` workers (see WorkUnit in sw_kernel.cuh for the three ways).
-//   fewer tiles than workers: every tile is cut into two K-halves when that still fits the workers;
-//   a last wave that is not full: the last full wave and the partial one are streamed over all workers, unless the
-//   partial wave is so nearly full (more than 9/10) that cutting tiles costs more than it saves.
+// Builds the unit list for `tiles` output tiles on at most `cap` workers (see WorkUnit in sw_kernel.cuh):
+//   fewer tiles than half the workers: every tile is cut into two K-halves;
+//   a last wave that is at most half full: its tiles are cut, so that it lasts half as long.
 // The fused-presum kernels are never cut, nor are products of fewer than 8 k-steps.
 void deal_tiles(Layout& L, int tiles, int cap, Variant v, bool no_split) {
   L.workers = tiles < cap ? tiles : cap;
   L.whole_tiles = tiles;
   L.region_tiles = 0;
-  L.region_mode = kRegionNone;
-  L.region_snap = 0;
-  L.split_slots = 0;
   if (v == kFusedPresum || v == kStrassenFused || no_split || L.num_k < 8 || cap < 2) return;
   if (tiles < cap) {
     if (2 * tiles > cap) return;
     L.workers = 2 * tiles;
     L.whole_tiles = 0;
     L.region_tiles = tiles;
-    L.region_mode = kRegionHalves;
-    L.split_slots = tiles;
     return;
   }
-  const int q = tiles / cap, rem = tiles % cap;
-  if (rem == 0 || 10 * rem > 9 * cap) return;
-  L.whole_tiles = (q - 1) * cap;
-  L.region_tiles = cap + rem;
-  L.region_mode = kRegionStream;
-  L.region_snap = L.num_k / 16 > 2 ? L.num_k / 16 : 2;
-  L.split_slots = cap;
+  const int rem = tiles % cap;
+  if (rem == 0 || 2 * rem > cap) return;
+  L.whole_tiles = tiles - rem;
+  L.region_tiles = rem;
 }
 
 Layout make_layout(const GemmArgs& a, int cap_override = 0) {
@@ -164,16 +155,16 @@ Layout make_layout(const GemmArgs& a, int cap_override = 0) {
   L.quadrant_floats = quadrant_bytes / sizeof(float);
   for (int i = 0; i < nws; ++i) {
     L.off_ws[i] = off;
-    // buffer 0 (M0) is indexed by tile: the finisher of every cut tile keeps its hand-off tile in an extra slot behind
-    // the grid's; buffers 1..3 are indexed by worker
-    const size_t bytes = i == 0 ? quadrant_bytes + size_t(L.split_slots) * tile_bytes : size_t(L.workers) * tile_bytes;
+    // buffer 0 (M0) is indexed by tile: the second half of every cut tile keeps its hand-off tile in an extra slot
+    // behind the grid's; buffers 1..3 are indexed by worker
+    const size_t bytes = i == 0 ? quadrant_bytes + size_t(L.region_tiles) * tile_bytes : size_t(L.workers) * tile_bytes;
     off = align_up(off + bytes, 256);
   }
-  if (L.split_slots) {
+  if (L.region_tiles) {
     L.off_split_buf = off;
-    off = align_up(off + size_t(L.split_slots) * 4 * tile_bytes, 256);
+    off = align_up(off + size_t(L.region_tiles) * 4 * tile_bytes, 256);
     L.off_split_flags = off;
-    L.split_flag_bytes = size_t(L.split_slots) * 4 * 8 * sizeof(int);
+    L.split_flag_bytes = size_t(L.region_tiles) * 4 * 8 * sizeof(int);
     off = align_up(off + L.split_flag_bytes, 256);
   }
   if (L.level == 2)
@@ -325,18 +316,14 @@ int deal_units(const GemmArgs& a, int sms, int* out, int max_units, int* workers
   KernelParams p;
   memset(&p, 0, sizeof(p));
   p.tiles_m = L.tiles_m; p.tiles_n = L.tiles_n; p.num_k = L.num_k;
-  p.whole_tiles = L.whole_tiles; p.region_tiles = L.region_tiles; p.region_mode = L.region_mode;
-  p.region_snap = L.region_snap;
+  p.whole_tiles = L.whole_tiles; p.region_tiles = L.region_tiles;
   if (workers) *workers = L.workers;
-  int n = 0;
-  for (int w = 0; w < L.workers; ++w) {
-    const int mine = units_of_worker(p, w, L.workers);
-    for (int it = 0; it < mine; ++it, ++n) {
-      if (n >= max_units) continue;
-      const WorkUnit u = unit_of(p, w, L.workers, it);
-      int* o = out + size_t(n) * 8;
-      o[0] = w; o[1] = u.tile; o[2] = u.part; o[3] = u.nparts; o[4] = u.k0; o[5] = u.k1; o[6] = u.ws_slot; o[7] = u.split_idx;
-    }
+  const int n = total_units(p);
+  for (int u = 0; u < n && u < max_units; ++u) {
+    const WorkUnit w = unit_of(p, u);
+    int* o = out + size_t(u) * 8;
+    o[0] = u % L.workers; o[1] = w.tile; o[2] = w.part; o[3] = w.nparts; o[4] = w.k0; o[5] = w.k1; o[6] = w.ws_slot;
+    o[7] = w.split_idx;
   }
   return n;
 }
@@ -349,6 +336,10 @@ namespace {
 
 // One launch group over (A, B) -> D with quadrant extents (mq, nq, kq): level 0 (whole matrices, one launch), level 1
 // fused (one launch) or level 1 interleaved (two launches), optionally tied into an outer recursion step.
+// The 256-byte status block at the head of the workspace is cleared on the stream by every run: word 0 is the device
+// status, words kUnitCounterBase + 1 .. + 14 are the unit counters of the run's launches (UnitCursor).
+constexpr int kUnitCounterBase = 8;
+
 struct LaunchSpec {
   Variant variant;
   int es, bn, pair, grid;
@@ -374,7 +365,8 @@ struct LaunchSpec {
   PresumSideJob more_jobs[2];  // presum jobs of the level above, run by launch 1's presum warps
   int n_more_jobs;
   int* status;
-  int whole_tiles, region_tiles, region_mode, region_snap;  // how the tiles are dealt (Layout)
+  int whole_tiles, region_tiles;  // the unit list (Layout)
+  int dynamic;                    // CTA pairs draw their units from a counter instead of taking them round-robin
   float* split_buf;
   int* split_flags;
   int* split_epoch;          // counter shared by the launches of one run
@@ -446,9 +438,12 @@ void apply_tuning_aids(KernelParams& p) {
           // per pair: SM id of its leader CTA, then the durations of its first tiles in us
           for (int pr = 0; pr < 74; ++pr) {
             fprintf(stderr, "[dump] pair %2d sm %3lld start0 %+6.1f:", pr, prof_host[3000 + pr], (ts[pr * 128] - ts[0]) * 1e-3);
-            for (int it = 0; it + 1 < 24 && ts[pr * 128 + it + 1]; ++it)
+            int it = 0;
+            for (; it + 1 < 24 && ts[pr * 128 + it + 1]; ++it)
               fprintf(stderr, " %6.1f", (ts[pr * 128 + it + 1] - ts[pr * 128 + it]) * 1e-3);
-            fprintf(stderr, "\n");
+            fprintf(stderr, " | last unit to MMAs issued %6.1f, to last epilogue %6.1f, flag waits (CTA 0 of the pair) %6.1f\n",
+                    (ts[pr * 128 + 127] - ts[pr * 128 + it]) * 1e-3, (ts[pr * 128 + 126] - ts[pr * 128 + it]) * 1e-3,
+                    prof_host[2 * pr * 8 + 6] * 1e-3);
           }
         }
       }
@@ -536,8 +531,6 @@ int launch_group(const LaunchSpec& s, cudaStream_t stream, MarkFn mark) {
   p.num_k = s.num_k;
   p.whole_tiles = s.whole_tiles;
   p.region_tiles = s.region_tiles;
-  p.region_mode = s.region_mode;
-  p.region_snap = s.region_snap;
   p.split_buf = s.split_buf;
   p.split_flags = s.split_flags;
   // raster band height in tile rows: the tiles of a wave share A row tiles and B column tiles through L2; taller bands
@@ -565,6 +558,7 @@ int launch_group(const LaunchSpec& s, cudaStream_t stream, MarkFn mark) {
     case kCubic:
       p.prog = programs::level0();
       p.split_epoch = ++*s.split_epoch;
+      p.unit_counter = s.dynamic ? s.status + kUnitCounterBase + p.split_epoch : nullptr;
       rc = launch_any(es, bn_sel, kPresumNone, p, s.grid, stream);
       break;
     case kFusedPresum:
@@ -580,11 +574,13 @@ int launch_group(const LaunchSpec& s, cudaStream_t stream, MarkFn mark) {
       const sb200_program_t second = programs::level1_second_taps();
       p.prog = s.linked ? programs::link_outer(first, s.link, 1) : first;
       p.split_epoch = ++*s.split_epoch;
+      p.unit_counter = s.dynamic ? s.status + kUnitCounterBase + p.split_epoch : nullptr;
       rc = launch_any(es, bn_sel, kPresumJob, p, s.grid, stream);
       if (rc) return rc;
       if ((rc = mark())) return rc;
       p.prog = s.linked ? programs::link_outer(second, s.link, 2) : second;
       p.split_epoch = ++*s.split_epoch;
+      p.unit_counter = s.dynamic ? s.status + kUnitCounterBase + p.split_epoch : nullptr;
       p.njobs = 0;
       rc = launch_any(es, bn_sel, kPresumNone, p, s.grid, stream);
       break;
@@ -628,9 +624,12 @@ int run(const GemmArgs& a, void* workspace, size_t workspace_size, cudaStream_t 
   s.split_epoch = &epoch;
   s.whole_tiles = L.whole_tiles;
   s.region_tiles = L.region_tiles;
-  s.region_mode = L.region_mode;
-  s.region_snap = L.region_snap;
-  if (L.split_slots) {
+  // more units than workers: the pairs draw units in raster order as they become free (UnitCursor)
+  s.dynamic = a.pair && L.whole_tiles + 2 * L.region_tiles > L.workers;
+#ifdef SB200_PROFILE
+  if (const char* sc = getenv("SB200_SCHED")) s.dynamic = s.dynamic && atoi(sc) != 0;  // measurement aid
+#endif
+  if (L.region_tiles) {
     s.split_buf = reinterpret_cast<float*>(wsb + L.off_split_buf);
     s.split_flags = reinterpret_cast<int*>(wsb + L.off_split_flags);
     ce = cudaMemsetAsync(s.split_flags, 0, L.split_flag_bytes, stream);

@@ -87,9 +87,9 @@ size_t workspace_bytes(const GemmArgs& args);
 WorkspaceLayout workspace_layout(const GemmArgs& args);
 int run(const GemmArgs& args, void* workspace, size_t workspace_size, cudaStream_t stream);
 int launches_per_run(const GemmArgs& args);
-// How the output tiles of one launch are dealt to the workers on a device of `sms` SMs (0: the current device): writes
-// 8 ints per unit (worker, tile, part, parts, k0, k1, hand-off slot, split slot) in the order the workers run them,
-// returns the number of units and the worker count.  Host arithmetic only (tests read the plan through this).
+// The unit list of one launch on a device of `sms` SMs (0: the current device): writes 8 ints per unit (worker under
+// the round-robin deal, tile, part, parts, k0, k1, hand-off slot, split slot) in list order, returns the number of
+// units and the worker count.  Host arithmetic only (tests read the plan through this).
 int deal_units(const GemmArgs& args, int sms, int* out, int max_units, int* workers);
 }  // namespace tc
 

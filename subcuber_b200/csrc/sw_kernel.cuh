@@ -84,12 +84,12 @@ struct KernelParams {
   int num_k;                // k-steps per product
   int band;                 // raster band height in tiles
   int b_blocked;            // 1: the B tensor maps are 3-D [128-byte column block][row][block]: one load per B tile
-  // How the tiles are dealt to the workers (see WorkUnit): the first whole_tiles tiles go round-robin, the other
-  // region_tiles are cut along K; a publisher hands its partial sums over through split_buf and raises split_flags.
-  int whole_tiles;          // tiles dealt whole
-  int region_tiles;         // tiles of the region that follows (0 when region_mode is kRegionNone)
-  int region_mode;          // RegionMode
-  int region_snap;          // stream: a share boundary closer than this many k-steps to a tile boundary moves onto it
+  // The unit list (see WorkUnit): whole_tiles whole tiles, then the two K-halves of each of the region_tiles tiles
+  // that follow; a first half hands its partial sums over through split_buf and raises split_flags.
+  int whole_tiles;
+  int region_tiles;
+  int* unit_counter;        // CTA-pair kernels: units are drawn from this counter (zero at launch) in list order by
+                            // whichever pair is free; null: dealt round-robin
   int split_epoch;          // value a raised flag holds in this launch (flags are zeroed once per run)
   float* split_buf;         // [split slot][quadrant 4][CTA of the tile][128 x BN] fp32, hand-off tile order
   int* split_flags;         // [split slot][quadrant 4][CTA of the tile 2][epilogue warp 4]
@@ -172,24 +172,19 @@ __device__ __forceinline__ TileCoord tile_of(int w, int tiles_m, int tiles_n, in
   return t;
 }
 
-// Work units of the persistent loop.  A unit is one output tile, or one part of a tile cut in two along K.  Every
-// postsum is linear in the products, so both parts of a tile run the whole tile program on their K range with private
-// hand-off tiles; at each step that leaves the tile (an output quadrant or a buffer of the level above) the part
-// called the publisher writes its partial sum to a split buffer and raises a flag, and the part called the finisher
-// waits (bounded) for the flag and adds the partial sum.  Three ways of dealing tiles to the W workers (CTAs or CTA
-// pairs), chosen by the host:
-//   whole   every tile goes to one worker, round-robin, wave after wave (tile t -> worker t mod W);
-//   halves  fewer tiles than half the workers: every tile is cut into two equal K-halves that run at the same time;
-//           the first half publishes, the second finishes;
-//   stream  T = q W + r tiles with 0 < r < W: the first (q - 1) W tiles are dealt whole; the last W + r tiles form a
-//           region of (W + r) * num_k k-steps that is cut into W equal, contiguous shares (boundaries that come close
-//           to a tile boundary snap onto it).  A share is longer than a tile, so a tile is cut at most once.  A worker
-//           runs its share in order: first the TAIL of the tile it shares with its predecessor (the publisher), then
-//           whole tiles, last the HEAD of the tile it shares with its successor (the finisher) - the partial sum a
-//           finisher needs was published more than a tile's time earlier, so it never waits in practice.
-//           Every worker is busy for (W + r) / W tile times instead of two.
-enum RegionMode { kRegionNone = 0, kRegionHalves = 1, kRegionStream = 2 };
-
+// Work units of the persistent loop.  A unit is one output tile, or one K-half of a tile.  Every postsum is linear in
+// the products, so both halves of a tile run the whole tile program on their K range with private hand-off tiles; at
+// each step that leaves the tile (an output quadrant or a buffer of the level above) the first half (the publisher)
+// writes its partial sum to a split buffer and raises a flag, and the second half (the finisher) waits (bounded) for
+// the flag and adds the partial sum.  The unit list, in the order units are handed out:
+//   units 0 .. whole_tiles - 1            whole tiles in raster order
+//   then 2 units per tile of the region   first half, second half of tiles whole_tiles .. whole_tiles + region_tiles - 1
+// The host cuts the tiles of a last wave that is at most half full (and all tiles when there are fewer than half as
+// many as workers): that wave then lasts half as long.  Both halves of a tile start at the same time on two workers,
+// at the same phase as every other half: workers that share operand panels stay close in K, which is what lets them
+// share those panels through L2.  (Cutting tiles at uneven points to give every worker an exactly equal share of a
+// partial wave was tried and is much slower: workers at different K phases stop sharing panels and the launch
+// becomes memory bound.)
 struct WorkUnit {
   int tile;       // linear tile index (argument of tile_of)
   int part;       // 0 = whole tile or publisher, 1 = finisher
@@ -199,67 +194,25 @@ struct WorkUnit {
   int split_idx;  // slot of the cut tile in the split buffer and the flag array
 };
 
-// Start of worker w's share of the stream region, in k-steps from the region's start.
-__host__ __device__ __forceinline__ long long region_bound(const KernelParams& p, int w, int nw) {
-  if (w >= nw) return static_cast<long long>(p.region_tiles) * p.num_k;
-  long long b = static_cast<long long>(w) * p.region_tiles * p.num_k / nw;
-  const int r = static_cast<int>(b % p.num_k);
-  if (r < p.region_snap) b -= r;
-  else if (p.num_k - r < p.region_snap) b += p.num_k - r;
-  return b;
-}
+__host__ __device__ __forceinline__ int total_units(const KernelParams& p) { return p.whole_tiles + 2 * p.region_tiles; }
 
-// Units worker `w` of `nw` runs, and its `it`-th unit.
-__host__ __device__ __forceinline__ int units_of_worker(const KernelParams& p, int w, int nw) {
-  int n = p.whole_tiles / nw + (w < p.whole_tiles % nw ? 1 : 0);
-  if (p.region_mode == kRegionHalves) {
-    n += (w < 2 * p.region_tiles) ? 1 : 0;
-  } else if (p.region_mode == kRegionStream) {
-    const long long b0 = region_bound(p, w, nw), b1 = region_bound(p, w + 1, nw);
-    if (b1 > b0) n += static_cast<int>((b1 - 1) / p.num_k - b0 / p.num_k) + 1;
-  }
-  return n;
-}
-__host__ __device__ __forceinline__ WorkUnit unit_of(const KernelParams& p, int w, int nw, int it) {
-  WorkUnit u;
-  const int n_whole = p.whole_tiles / nw + (w < p.whole_tiles % nw ? 1 : 0);
-  const int total_tiles = p.tiles_m * p.tiles_n;
-  u.part = 0; u.nparts = 1; u.k0 = 0; u.k1 = p.num_k; u.split_idx = 0;
-  if (it < n_whole) {
-    u.tile = it * nw + w;
-    u.ws_slot = u.tile;
-    return u;
-  }
-  if (p.region_mode == kRegionHalves) {
+// Unit number `u` of the list.
+__host__ __device__ __forceinline__ WorkUnit unit_of(const KernelParams& p, int u) {
+  WorkUnit w;
+  if (u < p.whole_tiles) {
+    w.tile = u; w.part = 0; w.nparts = 1; w.k0 = 0; w.k1 = p.num_k; w.ws_slot = u; w.split_idx = 0;
+  } else {
+    const int v = u - p.whole_tiles;
     const int h = p.num_k >> 1;
-    u.split_idx = w >> 1;
-    u.tile = p.whole_tiles + u.split_idx;
-    u.part = w & 1;
-    u.nparts = 2;
-    u.k0 = u.part ? h : 0;
-    u.k1 = u.part ? p.num_k : h;
-    u.ws_slot = u.part ? total_tiles + u.split_idx : u.tile;
-    return u;
+    w.split_idx = v >> 1;
+    w.tile = p.whole_tiles + w.split_idx;
+    w.part = v & 1;
+    w.nparts = 2;
+    w.k0 = w.part ? h : 0;
+    w.k1 = w.part ? p.num_k : h;
+    w.ws_slot = w.part ? p.tiles_m * p.tiles_n + w.split_idx : w.tile;
   }
-  // stream region: the (it - n_whole)-th tile that worker w's share [b0, b1) touches
-  const long long b0 = region_bound(p, w, nw), b1 = region_bound(p, w + 1, nw);
-  const int t = static_cast<int>(b0 / p.num_k) + (it - n_whole);
-  const long long t0 = static_cast<long long>(t) * p.num_k;
-  u.tile = p.whole_tiles + t;
-  u.k0 = b0 > t0 ? static_cast<int>(b0 - t0) : 0;
-  u.k1 = b1 < t0 + p.num_k ? static_cast<int>(b1 - t0) : p.num_k;
-  u.ws_slot = u.tile;
-  if (u.k0 > 0) {            // tail of the tile shared with worker w - 1: the publisher
-    u.nparts = 2;
-    u.part = 0;
-    u.split_idx = w - 1;
-  } else if (u.k1 < p.num_k) {  // head of the tile shared with worker w + 1: the finisher
-    u.nparts = 2;
-    u.part = 1;
-    u.split_idx = w;
-    u.ws_slot = total_tiles + u.split_idx;
-  }
-  return u;
+  return w;
 }
 
 // The first code to arrive stays in the status word.  The code is published before the CTA-wide abort flag, so that
@@ -480,7 +433,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_kernel(const 
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int my_units = units_of_worker(p, blockIdx.x, gridDim.x);  // tiles, or parts of tiles cut along K
+  const int num_units = total_units(p);  // tiles, or K-halves of tiles, dealt round-robin
   const int nproducts = p.prog.nproducts;
 
   if (threadIdx.x == 0) {
@@ -515,8 +468,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_kernel(const 
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int it = 0; ok && it < my_units; ++it) {
-        const WorkUnit wu = unit_of(p, blockIdx.x, gridDim.x, it);
+      for (int u = blockIdx.x; ok && u < num_units; u += gridDim.x) {
+        const WorkUnit wu = unit_of(p, u);
         const TileCoord tile = tile_of(wu.tile, p.tiles_m, p.tiles_n, p.band);
         for (int ps = 0; ok && ps < nproducts; ++ps) {
           const sb200_product_t& pr = p.prog.product[ps];
@@ -571,8 +524,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_kernel(const 
       uint32_t free_bits = 0;
       uint32_t iter = 0;
       bool ok = true;
-      for (int it = 0; ok && it < my_units; ++it, ++iter) {
-        const WorkUnit wu = unit_of(p, blockIdx.x, gridDim.x, it);
+      for (int u = blockIdx.x; ok && u < num_units; u += gridDim.x, ++iter) {
+        const WorkUnit wu = unit_of(p, u);
         const int nk = wu.k1 - wu.k0;
         const uint32_t sx = p.prog.alternate_slots ? (iter & 1u) : 0u;
         for (int ps = 0; ok && ps < nproducts; ++ps) {
@@ -636,8 +589,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_kernel(const 
     uint32_t full_bits = 0;
     uint32_t iter = 0;
     bool ok = true;
-    for (int it = 0; ok && it < my_units; ++it, ++iter) {
-      const WorkUnit wu = unit_of(p, blockIdx.x, gridDim.x, it);
+    for (int u = blockIdx.x; ok && u < num_units; u += gridDim.x, ++iter) {
+      const WorkUnit wu = unit_of(p, u);
       const TileCoord tile = tile_of(wu.tile, p.tiles_m, p.tiles_n, p.band);
       const uint32_t sx = p.prog.alternate_slots ? (iter & 1u) : 0u;
       for (int es = 0; ok && es < p.prog.nepilogues; ++es) {
@@ -696,8 +649,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_kernel(const 
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int it = 0; ok && it < my_units; ++it) {
-        const WorkUnit wu = unit_of(p, blockIdx.x, gridDim.x, it);
+      for (int u = blockIdx.x; ok && u < num_units; u += gridDim.x) {
+        const WorkUnit wu = unit_of(p, u);
         const TileCoord tile = tile_of(wu.tile, p.tiles_m, p.tiles_n, p.band);
         for (int ps = 0; ok && ps < nproducts; ++ps) {
           const sb200_product_t& pr = p.prog.product[ps];

@@ -79,6 +79,72 @@ struct PairConfig {
   static constexpr uint32_t B_SBO = B_SWZ32 ? 512u : 1024u;
 };
 
+// How the roles of a CTA pair learn which unit comes next.
+//   static   unit = pair + i * pairs: round-robin, wave after wave;
+//   dynamic  the first producer warp of the leader CTA (the scheduler) draws the next unit number from a counter in
+//            global memory when it needs one and publishes it to both CTAs through a small ring in shared memory;
+//            every other role of both CTAs reads the ring in order.  Units are then started in raster order by
+//            whichever pair is free: a pair on a faster part of the chip simply takes more tiles, and - what matters
+//            more - tiles that are neighbours in raster order start close together in time, so the pairs that share
+//            operand panels stay close in K and find them in L2.  (With the static deal the pairs drift apart by up to
+//            a whole tile's time within a dozen tiles - measured on B200: their speeds differ by up to 6 % with their
+//            position on the chip - and DRAM traffic doubles.)
+// Ring protocol: sched_full[s] (one arrival: the scheduler, after it wrote the unit number into both CTAs' slot s) and
+// the leader's sched_empty[s] (one arrival per consumer warp of the pair when it is done with the unit of slot s).
+constexpr int kSchedSlots = 4;
+
+struct UnitCursor {
+  uint64_t* full;        // this CTA's sched_full[kSchedSlots]
+  uint64_t* empty;       // sched_empty[kSchedSlots] (the leader's copy is the one that counts)
+  int* slots;            // this CTA's unit numbers
+  int* counter;          // global unit counter of this launch (dynamic), or null (static)
+  volatile int* abort_flag;
+  unsigned long long wait_ns;
+  int pair, num_pairs, num_units;
+  uint32_t i;            // units taken so far
+  bool scheduler;        // this warp draws the units
+
+  __device__ __forceinline__ void init(uint64_t* full_, uint64_t* empty_, int* slots_, const KernelParams& p, int pair_,
+                                       int num_pairs_, bool scheduler_, volatile int* abort_flag_) {
+    full = full_; empty = empty_; slots = slots_; counter = p.unit_counter; abort_flag = abort_flag_;
+    wait_ns = p.wait_ns; pair = pair_; num_pairs = num_pairs_; num_units = total_units(p); i = 0;
+    scheduler = scheduler_;
+  }
+  // Next unit number of this pair, the same in every lane; -1: no more units (or a wait was given up: *ok = false).
+  __device__ __forceinline__ int next(bool* ok) {
+    if (!counter) {
+      const int u = pair + static_cast<int>(i) * num_pairs;
+      return u < num_units ? u : -1;
+    }
+    const uint32_t s = i % kSchedSlots, round = i / kSchedSlots;
+    int u = 0;
+    if (scheduler) {
+      bool got = true;
+      if (round > 0) got = ptx::mbar_wait_warp<true>(&empty[s], (round - 1) & 1u, abort_flag, wait_ns);
+      if (!got) { *ok = false; return -1; }
+      if (ptx::elect_one()) {
+        u = atomicAdd(counter, 1);
+        slots[s] = u;
+        ptx::st_shared_cluster_u32(&slots[s], 1, static_cast<uint32_t>(u));
+        ptx::mbar_arrive_cluster(&full[s], 1);
+        ptx::mbar_arrive_cluster(&full[s], 0);
+      }
+      __syncwarp();
+    }
+    if (!ptx::mbar_wait_warp<true>(&full[s], round & 1u, abort_flag, wait_ns)) { *ok = false; return -1; }
+    u = slots[s];
+    return u < num_units ? u : -1;
+  }
+  // This warp is done with the unit it took last.
+  __device__ __forceinline__ void done(int lane) {
+    if (counter) {
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive_cluster(&empty[i % kSchedSlots], 0);
+    }
+    ++i;
+  }
+};
+
 template <typename Cfg>
 __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(const __grid_constant__ KernelParams p) {
   constexpr int ESIZE = Cfg::ESIZE;
@@ -94,8 +160,11 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
   uint64_t* empty_bar = full_bar + STAGES;
   uint64_t* slot_full = empty_bar + STAGES;
   uint64_t* slot_free = slot_full + SLOTS;
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(slot_free + SLOTS);
+  uint64_t* sched_full = slot_free + SLOTS;
+  uint64_t* sched_empty = sched_full + kSchedSlots;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(sched_empty + kSchedSlots);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  int* sched_slots = reinterpret_cast<int*>(tmem_holder + 2);
   const uint32_t staging = ptx::smem_u32(bar_base + Cfg::BAR_BYTES);  // epilogue staging rows (epilogue.cuh)
 
   const int warp = threadIdx.x >> 5;
@@ -103,8 +172,12 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
   const uint32_t rank = ptx::cluster_ctarank();   // 0 = leader
   const int pair = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
-  const int my_units = units_of_worker(p, pair, num_pairs);  // pair tiles, or parts of tiles cut along K
   const int nproducts = p.prog.nproducts;
+  // warps of the pair that read the unit ring: 3 producers and 4 epilogue warps per CTA, the leader's MMA warp, and
+  // the presum warps when they feed the stage ring
+  constexpr int kRingReaders = 2 * (3 + 4 + (Cfg::MODE == kPresumFeed ? Cfg::PRESUM_WARPS : 0)) + 1;
+  UnitCursor cursor;
+  cursor.init(sched_full, sched_empty, sched_slots, p, pair, num_pairs, rank == 0 && warp == 0, abort_flag);
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -116,6 +189,10 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
     for (int s = 0; s < SLOTS; ++s) {
       ptx::mbar_init(&slot_full[s], 1);
       ptx::mbar_init(&slot_free[s], 8);  // 4 epilogue warps of each CTA
+    }
+    for (int s = 0; s < kSchedSlots; ++s) {
+      ptx::mbar_init(&sched_full[s], 1);
+      ptx::mbar_init(&sched_empty[s], kRingReaders);
     }
     ptx::fence_mbar_init();
   }
@@ -147,8 +224,10 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
       bool ok = true;
       const long long pt0 = SB200_CLOCK();
       long long pw_empty = 0, pw_issue = 0;
-      for (int it = 0; ok && it < my_units; ++it) {
-        const WorkUnit wu = unit_of(p, pair, num_pairs, it);
+      for (int it = 0; ok; ++it, cursor.done(lane)) {
+        const int unit = cursor.next(&ok);
+        if (unit < 0) break;
+        const WorkUnit wu = unit_of(p, unit);
         const TileCoord tile = tile_of(wu.tile, p.tiles_m, p.tiles_n, p.band);
         const int row0 = tile.i * Cfg::PAIR_M + static_cast<int>(rank) * Cfg::BM;
         const int col0 = tile.j * BN + static_cast<int>(rank) * Cfg::BN_CTA;
@@ -250,8 +329,10 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
       bool ok = true;
       const long long mt0 = SB200_CLOCK_LIGHT();
       long long mw_full = 0, mw_free = 0, mw_issue = 0;
-      for (int it = 0; ok && it < my_units; ++it, ++iter) {
-        const WorkUnit wu = unit_of(p, pair, num_pairs, it);
+      for (int it = 0; ok; ++it, ++iter, cursor.done(lane)) {
+        const int unit = cursor.next(&ok);
+        if (unit < 0) break;
+        const WorkUnit wu = unit_of(p, unit);
         const int nk = wu.k1 - wu.k0;
         const uint32_t sx = p.prog.alternate_slots ? (iter & 1u) : 0u;
 #ifdef SB200_PROFILE
@@ -335,6 +416,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
       }
 #ifdef SB200_PROFILE
       if (p.prof && lane == 0) {
+        p.prof[4096 + pair * 128 + 127] = static_cast<long long>(ptx::globaltimer_ns());  // all MMAs issued
         p.prof[blockIdx.x * 8 + 0] = SB200_CLOCK_LIGHT() - mt0;
         p.prof[blockIdx.x * 8 + 1] = mw_full;
         p.prof[blockIdx.x * 8 + 2] = mw_free;
@@ -351,8 +433,10 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int it = 0; ok && it < my_units; ++it) {
-        const WorkUnit wu = unit_of(p, pair, num_pairs, it);
+      for (int it = 0; ok; ++it) {   // tracing runs with the static deal only
+        const int unit = pair + it * num_pairs;
+        if (unit >= total_units(p)) break;
+        const WorkUnit wu = unit_of(p, unit);
         for (int ps = 0; ok && ps < nproducts; ++ps)
           for (int kk = 0; kk < wu.k1 - wu.k0; ++kk) {
             if (!ptx::mbar_wait(&full_bar[stage], phase, abort_flag, p.wait_ns)) { ok = false; break; }
@@ -370,8 +454,10 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
     bool ok = true;
     const long long et0 = SB200_CLOCK();
     long long ew_full = 0;
-    for (int it = 0; ok && it < my_units; ++it, ++iter) {
-      const WorkUnit wu = unit_of(p, pair, num_pairs, it);
+    for (int it = 0; ok; ++it, ++iter, cursor.done(lane)) {
+      const int unit = cursor.next(&ok);
+      if (unit < 0) break;
+      const WorkUnit wu = unit_of(p, unit);
       const TileCoord tile = tile_of(wu.tile, p.tiles_m, p.tiles_n, p.band);
       const uint32_t sx = p.prog.alternate_slots ? (iter & 1u) : 0u;
       for (int es = 0; ok && es < p.prog.nepilogues; ++es) {
@@ -395,10 +481,17 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
               full_bits ^= (1u << s);
             }
           }
+#ifdef SB200_PROFILE
+          const unsigned long long tf0 = ptx::globaltimer_ns();
+#endif
           if (sp.add_partial && !wait_flag(flag, p.split_epoch, abort_flag, p.wait_ns)) {
             if (lane == 0) raise_abort(p, abort_flag, kStatusSplitTimeout);
             return false;
           }
+#ifdef SB200_PROFILE
+          if (p.prof && sp.add_partial && warp == 2 && lane == 0)
+            p.prof[blockIdx.x * 8 + 6] += static_cast<long long>(ptx::globaltimer_ns() - tf0);
+#endif
           ptx::tc_fence_after_sync();
           return true;
         };
@@ -435,6 +528,10 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
         }
       }
     }
+#ifdef SB200_PROFILE
+    if (p.prof && warp == 2 && lane == 0 && rank == 0)
+      p.prof[4096 + pair * 128 + 126] = static_cast<long long>(ptx::globaltimer_ns());  // last epilogue step done
+#endif
     (void)ew_full;
     (void)et0;
   } else if (warp >= Cfg::FIRST_PRESUM_WARP) {
@@ -445,8 +542,10 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int it = 0; ok && it < my_units; ++it) {
-        const WorkUnit wu = unit_of(p, pair, num_pairs, it);
+      for (int it = 0; ok; ++it, cursor.done(lane)) {
+        const int unit = cursor.next(&ok);
+        if (unit < 0) break;
+        const WorkUnit wu = unit_of(p, unit);
         const TileCoord tile = tile_of(wu.tile, p.tiles_m, p.tiles_n, p.band);
         const int row0 = tile.i * Cfg::PAIR_M + static_cast<int>(rank) * Cfg::BM;
         const int col0 = tile.j * BN + static_cast<int>(rank) * Cfg::BN_CTA;

@@ -18,6 +18,14 @@ KERNEL = "blackwell_f16_sw_interleaved_presum"
 ERR_SCRATCH_TOO_LARGE = 9
 
 
+def NO_SPLIT():
+    """The entry point never cuts tiles along K (its scratch must not depend on the GPU); the comparison run on a
+    caller's workspace is told to do the same, so that both add the same numbers in the same order."""
+    from subcuber_b200 import runner
+
+    return runner.options(no_split=True)
+
+
 def _both(lib, cuda_device, m, n, k, seed):
     import torch
 
@@ -25,7 +33,7 @@ def _both(lib, cuda_device, m, n, k, seed):
 
     a = inputs.fill_device("f16", "uniform1", (m, k), seed, 0, cuda_device)
     b = inputs.fill_device("f16", "uniform1", (k, n), seed, 1, cuda_device)
-    want = runner.gemm(KERNEL, a, b)
+    want = runner.gemm(KERNEL, a, b, opts=NO_SPLIT())
     got = torch.full((m, n), float("nan"), dtype=torch.float16, device=cuda_device)
     stream = torch.cuda.current_stream(cuda_device).cuda_stream
     with torch.cuda.device(cuda_device):
@@ -61,7 +69,7 @@ def test_static_scratch_allocates_nothing_and_covers_its_documented_limit(lib, c
 
     a = inputs.fill_device("f16", "uniform1", (m, k), 41, 0, cuda_device)
     b = inputs.fill_device("f16", "uniform1", (k, n), 41, 1, cuda_device)
-    want = runner.gemm(KERNEL, a, b)
+    want = runner.gemm(KERNEL, a, b, opts=NO_SPLIT())
     got = torch.full((m, n), float("nan"), dtype=torch.float16, device=cuda_device)
     stream = torch.cuda.current_stream(cuda_device).cuda_stream
     with torch.cuda.device(cuda_device):
