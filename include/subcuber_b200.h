@@ -51,7 +51,8 @@ enum {
   SB200_STATUS_MMA_TIMEOUT = 102,
   SB200_STATUS_EPILOGUE_TIMEOUT = 103,
   SB200_STATUS_PRESUM_TIMEOUT = 104,
-  SB200_STATUS_SPLIT_TIMEOUT = 105  /* the second K-half of a split tile waited in vain for the first half's sum */
+  SB200_STATUS_SPLIT_TIMEOUT = 105, /* the second K-half of a split tile waited in vain for the first half's sum */
+  SB200_STATUS_PEER_TIMEOUT = 201   /* sb200_peer_wait: a counter another GPU should have raised did not arrive      */
 };
 
 /* ---- group 1: kernel_runner ABI (reference: src/cuda/kernel_runner.cpp:27-32) --------------------- */
@@ -255,6 +256,20 @@ int sb200_gemm_events(const char* kernel, const void* a, const void* b, void* d,
  * "level2_<child>_launch<1|2>" with child in m0, m1, m2, m4, m5, m3, m6. */
 int sb200_tile_program(const char* which, void* out, size_t out_bytes);
 size_t sb200_tile_program_bytes(void);
+
+/* ---- flags between the GPUs of one box (the multi-GPU plan's operand exchange; the reference is single-GPU,
+ *      src/cuda/kernel_runner_support.cuh:312, and has no counterpart) ----------------------------------------------
+ * The exchange moves operand shards with the copy engines; these two calls order it.  A flag is a 32-bit counter in
+ * the receiving GPU's memory; the sender reaches it through a peer mapping (plain stores over NVLink).
+ * sb200_peer_signal enqueues a one-block kernel that stores `value` (release, system scope) to each of `count` flag
+ * addresses; behind copies on the same stream it announces that they have landed.  sb200_peer_wait enqueues a
+ * one-block kernel that waits until each of `count` local flags is >= `value`; the wait is bounded (wait_limit_us
+ * microseconds, 0 = 2 s): when it runs out the kernel stores SB200_STATUS_PEER_TIMEOUT to *status (a device int the
+ * caller zeroed) and returns, so a peer that never arrives cannot hang this GPU. */
+#define SB200_MAX_PEERS 16
+int sb200_peer_signal(int* const* peer_flags, int count, int value, sb200_stream_t stream);
+int sb200_peer_wait(int* const* local_flags, int count, int value, unsigned wait_limit_us, int* status,
+                    sb200_stream_t stream);
 
 /* Seeded synthetic inputs, bit-identical on host and device for dist 0 and 2 (dist 1 uses libm / device
  * math and agrees to rounding).  dtype: 0 f16, 1 f32, 2 f64, 3 bf16.  dist: 0 uniform[-1,1), 1 normal(0,1),

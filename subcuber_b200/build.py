@@ -28,7 +28,7 @@ NVCC_FLAGS = [
     "-Xcompiler", "-fPIC",
 ]
 
-LIB_SOURCES = ["sw_host.cu", "any_size.cu", "dgemm_sw.cu", "abi.cu", "fill.cu", "static_scratch.cu"]
+LIB_SOURCES = ["sw_host.cu", "any_size.cu", "dgemm_sw.cu", "abi.cu", "fill.cu", "static_scratch.cu", "peer_flags.cu"]
 RUNNER_SOURCES = ["kernel_runner.cpp"]
 
 

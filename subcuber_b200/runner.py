@@ -28,6 +28,7 @@ ERROR_NAMES = {
     103: "device: epilogue wait timed out",
     104: "device: presum wait timed out",
     105: "device: split-tile wait timed out",
+    201: "device: a flag from another GPU did not arrive in time",
 }
 
 TORCH_DTYPE = {"f16": torch.float16, "f32": torch.float32, "f64": torch.float64, "bf16": torch.bfloat16}

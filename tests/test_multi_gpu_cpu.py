@@ -128,3 +128,66 @@ def test_pipelined_gather_alternates_buffers_on_two_ranks():
         ptrs = [ptr for ptr, _ in results[rank]]
         assert ptrs[0] != ptrs[1] and ptrs[0::2] == [ptrs[0]] * 3 and ptrs[1::2] == [ptrs[1]] * 2
     assert multi_gpu.PipelinedGather.reserved_sms() == 2 * multi_gpu.PipelinedGather.NCCL_CTAS
+
+
+def test_grid_plan_moves_fewer_bytes_than_slabs():
+    gp = multi_gpu.grid_plan(16384, 16384, 16384, 8, esize=2, level=1)
+    assert (gp.kind, gp.pr, gp.pc, gp.local_m, gp.local_n) == ("grid", 4, 2, 4096, 8192)
+    assert gp.a_recv_bytes + gp.b_recv_bytes == 256 << 20          # against 448 MiB for eight row slabs
+    assert gp.row_group(5) == [4, 5] and gp.col_group(5) == [1, 3, 5, 7] and gp.coords(5) == (2, 1)
+    gp = multi_gpu.grid_plan(16384, 16384, 16384, 4, esize=2, level=1)
+    assert (gp.pr, gp.pc) == (2, 2) and gp.a_recv_bytes == gp.b_recv_bytes == 128 << 20
+    gp = multi_gpu.grid_plan(16384, 16384, 16384, 2, esize=2, level=1)
+    assert (gp.pr, gp.pc, gp.a_recv_bytes) == (2, 1, 0)
+    assert multi_gpu.grid_plan(16384, 16384, 16384, 1, esize=2).a_recv_bytes == 0
+    assert multi_gpu.grid_plan(1000, 1000, 1000, 8, esize=2).kind == "replica"
+
+
+def _grid_worker(rank, world, port, out):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        m, n, k = 2048, 2048, 512
+        gp = multi_gpu.grid_plan(m, n, k, world, esize=4, level=1)
+        ex = multi_gpu.CollectiveGridExchange(gp, rank, "f32", "cpu", seed=3)
+        a, b = ex.next()
+        ex.done()
+        want_a, want_b = multi_gpu.expected_slabs(gp, rank, "f32", "cpu", seed=3)
+        ok = torch.equal(a, want_a) and torch.equal(b, want_b)
+        ok = ok and tuple(a.shape) == (gp.local_m, k) and tuple(b.shape) == (k, gp.local_n)
+        # the blocks of all ranks assemble to the product of the assembled operands
+        i, j = gp.coords(rank)
+        block = a.double() @ b.double()
+        blocks = [torch.empty_like(block) for _ in range(world)]
+        dist.all_gather(blocks, block)
+        slabs_a = [torch.empty_like(a) for _ in range(world)]
+        slabs_b = [torch.empty_like(b) for _ in range(world)]
+        dist.all_gather(slabs_a, a)
+        dist.all_gather(slabs_b, b)
+        full_a = torch.cat([slabs_a[ii * gp.pc] for ii in range(gp.pr)])
+        full_b = torch.cat([slabs_b[jj] for jj in range(gp.pc)], dim=1)
+        full_c = torch.cat([torch.cat([blocks[ii * gp.pc + jj] for jj in range(gp.pc)], dim=1) for ii in range(gp.pr)])
+        ok = ok and torch.allclose(full_c, full_a.double() @ full_b.double(), rtol=0, atol=1e-9)
+        # ranks of one grid row hold the same A slab, ranks of one grid column the same B slab
+        ok = ok and all(torch.equal(slabs_a[r], a) for r in gp.row_group(rank))
+        ok = ok and all(torch.equal(slabs_b[r], b) for r in gp.col_group(rank))
+        out.put((rank, bool(ok), (gp.pr, gp.pc)))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_grid_exchange_on_gloo_ranks(world):
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_grid_worker, args=(r, world, port, out)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [out.get(timeout=180) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert all(ok for _, ok, _ in results)
+    assert {g for _, _, g in results} == {(2, 1) if world == 2 else (2, 2)}

@@ -22,6 +22,21 @@ def test_peer_gather_on_two_gpus():
     assert "PEER_GATHER_OK" in out.stdout, out.stdout[-2000:] + out.stderr[-2000:]
 
 
+def test_grid_exchange_on_two_gpus():
+    """multi_gpu.GridExchange on two real GPUs: the slabs every rank multiplies are the shards their owners generated,
+    in place, at every step, and the block GEMMs equal the same GEMMs on private copies bit for bit."""
+    import torch
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    here = os.path.dirname(os.path.abspath(__file__))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+           "127.0.0.1", "--master-port", "29573", os.path.join(here, "grid_exchange_worker.py")]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr[-2000:]
+    assert "GRID_EXCHANGE_OK" in out.stdout, out.stdout[-2000:] + out.stderr[-2000:]
+
+
 def test_two_devices_in_one_process(oracle):
     """Kernel attributes and the SM count are kept per device: one process runs a GEMM on cuda:0 and then on cuda:1
     (every launch needs more than the default dynamic shared memory, an attribute of each device's copy of a kernel)."""
