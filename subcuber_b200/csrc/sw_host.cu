@@ -533,9 +533,11 @@ int launch_group(const LaunchSpec& s, cudaStream_t stream, MarkFn mark) {
   p.region_tiles = s.region_tiles;
   p.split_buf = s.split_buf;
   p.split_flags = s.split_flags;
-  // raster band height in tile rows: the tiles of a wave share A row tiles and B column tiles through L2; taller bands
-  // for tall tile grids read less from HBM (measured at 16384^3 f16: 19.4 GB with 16 against 23.9 GB with 8)
-  p.band = s.tiles_m >= 32 ? 16 : 8;
+  // Raster band height in tile rows.  Units are handed out band by band, column by column inside a band, so the
+  // tiles in flight cover `band` A row panels and about workers / band B column panels, and tiles that share a panel
+  // start close together.  Measured on B200 at 16384^3 (f16, CTA pairs, units drawn in order): 8 rows read the least
+  // from DRAM (level 0: 9.1 GB against 10.4 with 16 and 11.2 with 4; cuBLAS reads 8.9) and run fastest.
+  p.band = 8;
   p.wait_ns = s.wait_ns;
   p.drop_split_flags = s.drop_split_flags;
 #ifdef SB200_PROFILE

@@ -274,7 +274,7 @@ class GridExchange:
         from . import _lib
 
         self.C, self.lib = C, _lib.load()
-        self.gp, self.rank, self.device = gp, rank, torch.device(device)
+        self.gp, self.rank, self.device, self.seed = gp, rank, torch.device(device), seed
         self.a_shard, self.b_shard = make_shards(gp, rank, dtype, device, seed)
         tdt = self.a_shard.dtype
         world = gp.world
@@ -282,8 +282,8 @@ class GridExchange:
         self.share_a, self.share_b = gp.pc > 1, gp.pr > 1
         a_shape, b_shape = (gp.local_m, gp.k), (gp.k, gp.local_n)
         # symmetric allocations are collective: every rank makes the same ones in the same order
-        self.a_bufs = [symm_mem.empty(a_shape, dtype=tdt, device=device) for _ in range(2)]
-        self.b_bufs = [symm_mem.empty(b_shape, dtype=tdt, device=device) for _ in range(2)]
+        self.a_bufs = [symm_mem.empty(a_shape, dtype=tdt, device=device) for _ in range(2)] if self.share_a else []
+        self.b_bufs = [symm_mem.empty(b_shape, dtype=tdt, device=device) for _ in range(2)] if self.share_b else []
         self.flags = symm_mem.empty((2 * 2 * world,), dtype=torch.int32, device=device)   # [kind][buffer][rank]
         self.flags.zero_()
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
@@ -300,13 +300,27 @@ class GridExchange:
         self.peer_flags = {r: f_h.get_buffer(r, (2 * 2 * world,), torch.int32) for r in self.peers}
         self.a_row0 = row.index(rank) * gp.a_shard_rows()
         self.b_row0 = col.index(rank) * gp.b_shard_rows()
+        self.a_rows = slice(self.a_row0, self.a_row0 + gp.a_shard_rows())
+        self.b_rows = slice(self.b_row0, self.b_row0 + gp.b_shard_rows())
         self.comm = torch.cuda.Stream(device=device)
         self.copy_streams = {r: torch.cuda.Stream(device=device) for r in self.peers}
-        self.local_stream = torch.cuda.Stream(device=device)
+        self.local_streams = [torch.cuda.Stream(device=device) for _ in range(2)]   # own A shard, own B shard
         self.consumed_local = [torch.cuda.Event() for _ in range(2)]
-        self.filled_local = [torch.cuda.Event() for _ in range(2)]
+        self.filled_local = [[torch.cuda.Event() for _ in range(2)] for _ in range(2)]
+        self.free_ev = [torch.cuda.Event() for _ in range(2)]
         for ev in self.consumed_local:
             ev.record(torch.cuda.current_stream(device))
+        # flag addresses, fixed for the life of the exchange: [kind][buffer] -> pointer array
+        C_ = C
+        def pointers(pairs):
+            arr = (C_.c_void_p * max(1, len(pairs)))()
+            for n_, (t, idx) in enumerate(pairs):
+                arr[n_] = t.data_ptr() + 4 * idx
+            return arr
+        self.signal_ptrs = [[pointers([(self.peer_flags[r], self._flag_index(kind, buf, rank)) for r in self.peers])
+                             for buf in range(2)] for kind in range(2)]
+        self.wait_ptrs = [[pointers([(self.flags, self._flag_index(kind, buf, r)) for r in self.peers])
+                           for buf in range(2)] for kind in range(2)]
         self.issued = 0
         self.taken = 0
         self._last = None
@@ -316,19 +330,11 @@ class GridExchange:
     def _flag_index(self, kind: int, buf: int, rank: int) -> int:
         return (kind * 2 + buf) * self.gp.world + rank
 
-    def _pointers(self, tensors_and_indices):
-        C = self.C
-        arr = (C.c_void_p * len(tensors_and_indices))()
-        for n, (t, idx) in enumerate(tensors_and_indices):
-            arr[n] = t.data_ptr() + 4 * idx
-        return arr
-
     def _signal(self, kind: int, buf: int, value: int, stream) -> None:
         """Raise my counter (kind, buf) in every peer's flag array to `value`, behind the work queued on `stream`."""
         if not self.peers:
             return
-        ptrs = self._pointers([(self.peer_flags[r], self._flag_index(kind, buf, self.rank)) for r in self.peers])
-        rc = self.lib.sb200_peer_signal(ptrs, len(self.peers), value, stream.cuda_stream)
+        rc = self.lib.sb200_peer_signal(self.signal_ptrs[kind][buf], len(self.peers), value, stream.cuda_stream)
         if rc:
             raise RuntimeError(f"sb200_peer_signal failed with {rc}")
 
@@ -336,36 +342,36 @@ class GridExchange:
         """Make `stream` wait until every peer's counter (kind, buf) in my flag array has reached `value`."""
         if not self.peers or value <= 0:
             return
-        ptrs = self._pointers([(self.flags, self._flag_index(kind, buf, r)) for r in self.peers])
-        rc = self.lib.sb200_peer_wait(ptrs, len(self.peers), value, self.WAIT_LIMIT_US, self.status.data_ptr(),
-                                      stream.cuda_stream)
+        rc = self.lib.sb200_peer_wait(self.wait_ptrs[kind][buf], len(self.peers), value, self.WAIT_LIMIT_US,
+                                      self.status.data_ptr(), stream.cuda_stream)
         if rc:
             raise RuntimeError(f"sb200_peer_wait failed with {rc}")
 
     def _start(self) -> None:
         s = self.issued
         j = s % 2
-        gp = self.gp
         with torch.cuda.device(self.device):
             self.comm.wait_event(self.consumed_local[j])        # my GEMM that read buffer j is over
             self._wait(1, j, s - 1, self.comm)                  # ... and so are the peers' (their step s - 2)
-            free = torch.cuda.Event()
+            free = self.free_ev[j]
             free.record(self.comm)
-            a_rows = slice(self.a_row0, self.a_row0 + gp.a_shard_rows())
-            b_rows = slice(self.b_row0, self.b_row0 + gp.b_shard_rows())
-            self.local_stream.wait_event(free)
-            with torch.cuda.stream(self.local_stream):          # my own shards into my own buffers
-                self.a_bufs[j][a_rows].copy_(self.a_shard, non_blocking=True)
-                self.b_bufs[j][b_rows].copy_(self.b_shard, non_blocking=True)
-                self.filled_local[j].record(self.local_stream)
+            # my own shards into my own buffers (a slab that is not shared is the shard itself: nothing to copy)
+            for which, (shared, bufs, rows, shard) in enumerate(((self.share_a, self.a_bufs, self.a_rows, self.a_shard),
+                                                                 (self.share_b, self.b_bufs, self.b_rows, self.b_shard))):
+                if shared:
+                    st = self.local_streams[which]
+                    st.wait_event(free)
+                    with torch.cuda.stream(st):
+                        bufs[j][rows].copy_(shard, non_blocking=True)
+                        self.filled_local[which][j].record(st)
             for r in self.peers:
                 st = self.copy_streams[r]
                 st.wait_event(free)
                 with torch.cuda.stream(st):
                     if r in self.a_dst:
-                        self.a_dst[r][j][a_rows].copy_(self.a_shard, non_blocking=True)
+                        self.a_dst[r][j][self.a_rows].copy_(self.a_shard, non_blocking=True)
                     if r in self.b_dst:
-                        self.b_dst[r][j][b_rows].copy_(self.b_shard, non_blocking=True)
+                        self.b_dst[r][j][self.b_rows].copy_(self.b_shard, non_blocking=True)
                 self.comm.wait_stream(st)
             self._signal(0, j, s + 1, self.comm)                # my pushes for step s have landed everywhere
         self.issued += 1
@@ -377,11 +383,14 @@ class GridExchange:
         s = self.taken
         j = s % 2
         cur = torch.cuda.current_stream(self.device)
-        cur.wait_event(self.filled_local[j])
+        if self.share_a:
+            cur.wait_event(self.filled_local[0][j])
+        if self.share_b:
+            cur.wait_event(self.filled_local[1][j])
         with torch.cuda.device(self.device):
             self._wait(0, j, s + 1, cur)
         self.taken += 1
-        self._last = (self.a_bufs[j], self.b_bufs[j])
+        self._last = (self.a_bufs[j] if self.share_a else self.a_shard, self.b_bufs[j] if self.share_b else self.b_shard)
         return self._last
 
     def done(self) -> None:
@@ -407,7 +416,7 @@ class GridExchange:
         agree with the fp64 product of those slabs, as does the block's checksum."""
         a, b = ai_bi
         dtype = {torch.float16: "f16", torch.bfloat16: "bf16", torch.float32: "f32"}[a.dtype]
-        want_a, want_b = expected_slabs(self.gp, self.rank, dtype, self.device)
+        want_a, want_b = expected_slabs(self.gp, self.rank, dtype, self.device, self.seed)
         ok = bool(torch.equal(a, want_a)) and bool(torch.equal(b, want_b))
         del want_a, want_b
         rows = torch.tensor([0, d.shape[0] // 3, d.shape[0] // 2 + 1, d.shape[0] - 1], device=self.device)
