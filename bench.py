@@ -337,8 +337,10 @@ def main():
     clocks = sampler.stop()
     elapsed_ms = t_start.elapsed_time(t_stop)
     check_status()
+    exchange_wait_ms = None
     if exchange is not None:
         exchange.check_status()
+        exchange_wait_ms = exchange.wait_ms(args.steps)
     if world > 1:
         t = torch.tensor([elapsed_ms], dtype=torch.float64, device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -495,6 +497,7 @@ def main():
             "frac_of_dense_peak": value / (DENSE_PEAK[dtn] * world),
             "dense_peak": {"value": DENSE_PEAK[dtn] * world, "unit": "TFLOP/s", "source": "nominal, dense, per GPU x GPUs"},
             "cublas": cublas, "sustained": sustained, "parity": parity,
+            "exchange_wait_ms_per_step": exchange_wait_ms,
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches * args.steps, "host_enqueue_ms_per_step": host_ms,
             "roofline": roofline, "cpu_baseline": cpu_baseline,
         }

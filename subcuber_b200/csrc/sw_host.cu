@@ -125,9 +125,22 @@ Layout make_layout(const GemmArgs& a, int cap_override = 0) {
   L.tiles_m = ceil_div(L.mq, a.pair ? 256 : 128);
   L.tiles_n = ceil_div(L.nq, L.bn);
   L.num_k = ceil_div(L.kq, 128 / L.esize);
+  int cap = cap_override > 0 ? cap_override : sm_count();
+  if (a.sm_limit > 0 && a.sm_limit < cap) cap = a.sm_limit;  // the caller keeps the other SMs for its own kernels
+  if (a.pair) cap /= 2;  // one pair per two SMs
+  if (cap < 1) cap = 1;
+  bool no_split = a.no_split != 0;
+#ifdef SB200_PROFILE
+  if (getenv("SB200_NO_SPLIT")) no_split = true;  // measurement aid of profile builds
+#endif
+  deal_tiles(L, L.tiles_m * L.tiles_n, cap, a.variant, no_split);
+  // the status block and the flags of the cut tiles sit together at the head: one memset clears both for a run
   size_t off = 0;
   L.off_status = off;
   off += 256;
+  L.off_split_flags = off;
+  L.split_flag_bytes = size_t(L.region_tiles) * 4 * 8 * sizeof(int);
+  off = align_up(off + L.split_flag_bytes, 256);
   if (L.level == 2) {
     L.off_opa = off;
     off = align_up(off + size_t(4) * (2 * L.mq) * (2 * L.kq) * L.esize, 256);
@@ -140,15 +153,6 @@ Layout make_layout(const GemmArgs& a, int cap_override = 0) {
     L.off_pb = off;
     off = align_up(off + size_t(4) * L.kq * L.nq * L.esize, 256);
   }
-  int cap = cap_override > 0 ? cap_override : sm_count();
-  if (a.sm_limit > 0 && a.sm_limit < cap) cap = a.sm_limit;  // the caller keeps the other SMs for its own kernels
-  if (a.pair) cap /= 2;  // one pair per two SMs
-  if (cap < 1) cap = 1;
-  bool no_split = a.no_split != 0;
-#ifdef SB200_PROFILE
-  if (getenv("SB200_NO_SPLIT")) no_split = true;  // measurement aid of profile builds
-#endif
-  deal_tiles(L, L.tiles_m * L.tiles_n, cap, a.variant, no_split);
   const int nws = a.variant == kCubic ? 0 : (a.variant == kFusedPresum ? 2 : (a.variant == kStrassenFused ? 3 : 4));
   const size_t tile_bytes = size_t(128) * L.bn * sizeof(float) * (a.pair ? 2 : 1);  // per tile of the grid
   const size_t quadrant_bytes = size_t(L.tiles_m) * L.tiles_n * tile_bytes;
@@ -163,9 +167,6 @@ Layout make_layout(const GemmArgs& a, int cap_override = 0) {
   if (L.region_tiles) {
     L.off_split_buf = off;
     off = align_up(off + size_t(L.region_tiles) * 4 * tile_bytes, 256);
-    L.off_split_flags = off;
-    L.split_flag_bytes = size_t(L.region_tiles) * 4 * 8 * sizeof(int);
-    off = align_up(off + L.split_flag_bytes, 256);
   }
   if (L.level == 2)
     for (int i = 0; i < 3; ++i) {
@@ -606,7 +607,7 @@ int run(const GemmArgs& a, void* workspace, size_t workspace_size, cudaStream_t 
   const int es = L.esize;
 
   int* status = reinterpret_cast<int*>(wsb + L.off_status);
-  cudaError_t ce = cudaMemsetAsync(status, 0, 256, stream);
+  cudaError_t ce = cudaMemsetAsync(status, 0, 256 + L.split_flag_bytes, stream);  // status, unit counters, split flags
   if (ce != cudaSuccess) return static_cast<int>(ce);
 
   int nev = 0;
@@ -634,8 +635,6 @@ int run(const GemmArgs& a, void* workspace, size_t workspace_size, cudaStream_t 
   if (L.region_tiles) {
     s.split_buf = reinterpret_cast<float*>(wsb + L.off_split_buf);
     s.split_flags = reinterpret_cast<int*>(wsb + L.off_split_flags);
-    ce = cudaMemsetAsync(s.split_flags, 0, L.split_flag_bytes, stream);
-    if (ce != cudaSuccess) return static_cast<int>(ce);
   }
   s.mq = L.mq; s.nq = L.nq; s.kq = L.kq;
   s.tiles_m = L.tiles_m; s.tiles_n = L.tiles_n; s.num_k = L.num_k;

@@ -245,22 +245,27 @@ class CollectiveGridExchange:
 
 
 class GridExchange:
-    """The grid exchange on real GPUs, double-buffered and overlapped with compute.
+    """The grid exchange on real GPUs, buffered three deep and overlapped with compute.
 
     The A-slab and B-slab buffers live in symmetric memory (torch.distributed._symmetric_memory: every rank's buffer
-    is mapped into every process).  For step s every rank pushes its A shard into buffer s % 2 of the ranks of its
-    grid row and its B shard into buffer s % 2 of the ranks of its grid column: device-to-device copies whose
-    destination is peer memory, one stream per destination, so the copy engines move the bytes over NVLink and the
+    is mapped into every process).  A rank's own shard lives IN PLACE inside its own slab buffers (`shard_views(j)`
+    is where the producer of the shard writes it for a step that uses buffer j); a slab that nobody shares is just
+    the shard.  For step s every rank pushes its A shard into buffer s % 3 of the other ranks of its grid row and its
+    B shard into buffer s % 3 of the other ranks of its grid column: device-to-device copies whose destination is peer
+    memory, in several row blocks on streams of their own, so the copy engines move the bytes over NVLink and the
     GEMM keeps its SMs.  Ordering between GPUs uses counters in symmetric memory and the library's bounded flag
     kernels, never a collective:
       filled[j][r]    raised by rank r behind its pushes into my buffer j; my GEMM of step s waits for s + 1
       consumed[j][r]  raised by rank r behind its GEMM that read its buffer j; my pushes for step s into r's buffer
-                      wait for s - 1 (the GEMM of step s - 2 is over)
-    The push for step s + 1 is started when step s is handed to compute, so it runs under the GEMM of step s.  The
-    caller leaves `reserved_sms()` SMs out of the GEMM grid for the one-block flag kernels that run beside it.
+                      wait for s - 2 (the GEMM of step s - 3 is over)
+    The pushes for steps s + 1 and s + 2 are in flight while step s computes.  The caller leaves `reserved_sms()` SMs
+    out of the GEMM grid for the one-block flag kernels that run beside it.
     """
 
     WAIT_LIMIT_US = 5_000_000   # bound of every flag wait (first steps include lazy set-up on the peers)
+    PIECES = 2                  # every shard travels as this many row blocks on streams of their own: under the GEMM's
+                                # memory load one copy is latency-bound, several copy engines together are not
+    NBUF = 3                    # slab buffers per operand: a push has two steps' time to land
 
     @staticmethod
     def reserved_sms() -> int:
@@ -273,18 +278,18 @@ class GridExchange:
 
         from . import _lib
 
-        self.C, self.lib = C, _lib.load()
+        self.lib = _lib.load()
         self.gp, self.rank, self.device, self.seed = gp, rank, torch.device(device), seed
-        self.a_shard, self.b_shard = make_shards(gp, rank, dtype, device, seed)
-        tdt = self.a_shard.dtype
-        world = gp.world
+        a_shard, b_shard = make_shards(gp, rank, dtype, device, seed)
+        tdt = a_shard.dtype
+        world, nbuf = gp.world, self.NBUF
         pg = dist.group.WORLD
         self.share_a, self.share_b = gp.pc > 1, gp.pr > 1
         a_shape, b_shape = (gp.local_m, gp.k), (gp.k, gp.local_n)
         # symmetric allocations are collective: every rank makes the same ones in the same order
-        self.a_bufs = [symm_mem.empty(a_shape, dtype=tdt, device=device) for _ in range(2)] if self.share_a else []
-        self.b_bufs = [symm_mem.empty(b_shape, dtype=tdt, device=device) for _ in range(2)] if self.share_b else []
-        self.flags = symm_mem.empty((2 * 2 * world,), dtype=torch.int32, device=device)   # [kind][buffer][rank]
+        self.a_bufs = [symm_mem.empty(a_shape, dtype=tdt, device=device) for _ in range(nbuf)] if self.share_a else []
+        self.b_bufs = [symm_mem.empty(b_shape, dtype=tdt, device=device) for _ in range(nbuf)] if self.share_b else []
+        self.flags = symm_mem.empty((2 * nbuf * world,), dtype=torch.int32, device=device)   # [kind][buffer][rank]
         self.flags.zero_()
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
         a_h = [symm_mem.rendezvous(t, pg) for t in self.a_bufs]
@@ -297,30 +302,36 @@ class GridExchange:
         # peer views of the buffers this rank pushes into, and of the flag arrays it raises
         self.a_dst = {r: [h.get_buffer(r, a_shape, tdt) for h in a_h] for r in self.a_peers}
         self.b_dst = {r: [h.get_buffer(r, b_shape, tdt) for h in b_h] for r in self.b_peers}
-        self.peer_flags = {r: f_h.get_buffer(r, (2 * 2 * world,), torch.int32) for r in self.peers}
-        self.a_row0 = row.index(rank) * gp.a_shard_rows()
-        self.b_row0 = col.index(rank) * gp.b_shard_rows()
-        self.a_rows = slice(self.a_row0, self.a_row0 + gp.a_shard_rows())
-        self.b_rows = slice(self.b_row0, self.b_row0 + gp.b_shard_rows())
+        self.peer_flags = {r: f_h.get_buffer(r, (2 * nbuf * world,), torch.int32) for r in self.peers}
+        self.a_rows = slice(row.index(rank) * gp.a_shard_rows(), (row.index(rank) + 1) * gp.a_shard_rows())
+        self.b_rows = slice(col.index(rank) * gp.b_shard_rows(), (col.index(rank) + 1) * gp.b_shard_rows())
+        # the shards in place: every buffer of a shared slab holds this rank's rows; an unshared slab is the shard
+        self.a_own = [buf[self.a_rows] for buf in self.a_bufs] if self.share_a else [a_shard] * nbuf
+        self.b_own = [buf[self.b_rows] for buf in self.b_bufs] if self.share_b else [b_shard] * nbuf
+        for j in range(nbuf):
+            if self.share_a:
+                self.a_own[j].copy_(a_shard)
+            if self.share_b:
+                self.b_own[j].copy_(b_shard)
         self.comm = torch.cuda.Stream(device=device)
-        self.copy_streams = {r: torch.cuda.Stream(device=device) for r in self.peers}
-        self.local_streams = [torch.cuda.Stream(device=device) for _ in range(2)]   # own A shard, own B shard
-        self.consumed_local = [torch.cuda.Event() for _ in range(2)]
-        self.filled_local = [[torch.cuda.Event() for _ in range(2)] for _ in range(2)]
-        self.free_ev = [torch.cuda.Event() for _ in range(2)]
+        self.copy_streams = {r: [torch.cuda.Stream(device=device) for _ in range(self.PIECES)] for r in self.peers}
+        self.consumed_local = [torch.cuda.Event() for _ in range(nbuf)]
+        self.free_ev = [torch.cuda.Event() for _ in range(nbuf)]
+        self.wait_events = []   # (before, after) event pairs around the compute stream's wait for a step's slabs
         for ev in self.consumed_local:
             ev.record(torch.cuda.current_stream(device))
+
         # flag addresses, fixed for the life of the exchange: [kind][buffer] -> pointer array
-        C_ = C
         def pointers(pairs):
-            arr = (C_.c_void_p * max(1, len(pairs)))()
+            arr = (C.c_void_p * max(1, len(pairs)))()
             for n_, (t, idx) in enumerate(pairs):
                 arr[n_] = t.data_ptr() + 4 * idx
             return arr
+
         self.signal_ptrs = [[pointers([(self.peer_flags[r], self._flag_index(kind, buf, rank)) for r in self.peers])
-                             for buf in range(2)] for kind in range(2)]
+                             for buf in range(nbuf)] for kind in range(2)]
         self.wait_ptrs = [[pointers([(self.flags, self._flag_index(kind, buf, r)) for r in self.peers])
-                           for buf in range(2)] for kind in range(2)]
+                           for buf in range(nbuf)] for kind in range(2)]
         self.issued = 0
         self.taken = 0
         self._last = None
@@ -328,7 +339,12 @@ class GridExchange:
         dist.barrier()  # every process has mapped every buffer and zeroed its flags before the first push
 
     def _flag_index(self, kind: int, buf: int, rank: int) -> int:
-        return (kind * 2 + buf) * self.gp.world + rank
+        return (kind * self.NBUF + buf) * self.gp.world + rank
+
+    def shard_views(self, j: int):
+        """Where this rank's A shard and B shard live for a step that uses buffer j (write new shard values here
+        before the step's `next`: the pushes read them from here)."""
+        return self.a_own[j], self.b_own[j]
 
     def _signal(self, kind: int, buf: int, value: int, stream) -> None:
         """Raise my counter (kind, buf) in every peer's flag array to `value`, behind the work queued on `stream`."""
@@ -349,54 +365,50 @@ class GridExchange:
 
     def _start(self) -> None:
         s = self.issued
-        j = s % 2
+        j = s % self.NBUF
         with torch.cuda.device(self.device):
-            self.comm.wait_event(self.consumed_local[j])        # my GEMM that read buffer j is over
-            self._wait(1, j, s - 1, self.comm)                  # ... and so are the peers' (their step s - 2)
+            self.comm.wait_event(self.consumed_local[j])                  # my GEMM that read buffer j is over
+            self._wait(1, j, s - self.NBUF + 1, self.comm)                # ... and so are the peers' (step s - NBUF)
             free = self.free_ev[j]
             free.record(self.comm)
-            # my own shards into my own buffers (a slab that is not shared is the shard itself: nothing to copy)
-            for which, (shared, bufs, rows, shard) in enumerate(((self.share_a, self.a_bufs, self.a_rows, self.a_shard),
-                                                                 (self.share_b, self.b_bufs, self.b_rows, self.b_shard))):
-                if shared:
-                    st = self.local_streams[which]
+            for r in self.peers:
+                for piece, st in enumerate(self.copy_streams[r]):
                     st.wait_event(free)
                     with torch.cuda.stream(st):
-                        bufs[j][rows].copy_(shard, non_blocking=True)
-                        self.filled_local[which][j].record(st)
-            for r in self.peers:
-                st = self.copy_streams[r]
-                st.wait_event(free)
-                with torch.cuda.stream(st):
-                    if r in self.a_dst:
-                        self.a_dst[r][j][self.a_rows].copy_(self.a_shard, non_blocking=True)
-                    if r in self.b_dst:
-                        self.b_dst[r][j][self.b_rows].copy_(self.b_shard, non_blocking=True)
-                self.comm.wait_stream(st)
-            self._signal(0, j, s + 1, self.comm)                # my pushes for step s have landed everywhere
+                        for dst, rows, shard in ((self.a_dst.get(r), self.a_rows, self.a_own[j]),
+                                                 (self.b_dst.get(r), self.b_rows, self.b_own[j])):
+                            if dst is None:
+                                continue
+                            n_rows = shard.shape[0]
+                            lo = piece * n_rows // self.PIECES
+                            hi = (piece + 1) * n_rows // self.PIECES
+                            dst[j][rows.start + lo:rows.start + hi].copy_(shard[lo:hi], non_blocking=True)
+                    self.comm.wait_stream(st)
+            self._signal(0, j, s + 1, self.comm)                          # my pushes for step s have landed everywhere
         self.issued += 1
 
     def next(self):
-        """(A slab, B slab) of this step, valid on the current stream; the pushes for the next step are started."""
-        while self.issued < self.taken + 2:
+        """(A slab, B slab) of this step, valid on the current stream; the pushes for the steps after are started."""
+        while self.issued < self.taken + self.NBUF:
             self._start()
         s = self.taken
-        j = s % 2
+        j = s % self.NBUF
         cur = torch.cuda.current_stream(self.device)
-        if self.share_a:
-            cur.wait_event(self.filled_local[0][j])
-        if self.share_b:
-            cur.wait_event(self.filled_local[1][j])
+        before = torch.cuda.Event(enable_timing=True)
+        after = torch.cuda.Event(enable_timing=True)
+        before.record(cur)
         with torch.cuda.device(self.device):
             self._wait(0, j, s + 1, cur)
+        after.record(cur)
+        self.wait_events.append((before, after))
         self.taken += 1
-        self._last = (self.a_bufs[j] if self.share_a else self.a_shard, self.b_bufs[j] if self.share_b else self.b_shard)
+        self._last = (self.a_bufs[j] if self.share_a else self.a_own[j], self.b_bufs[j] if self.share_b else self.b_own[j])
         return self._last
 
     def done(self) -> None:
         """Call after the GEMM of the step handed out last has been enqueued on the current stream."""
         s = self.taken - 1
-        j = s % 2
+        j = s % self.NBUF
         cur = torch.cuda.current_stream(self.device)
         self.consumed_local[j].record(cur)
         with torch.cuda.device(self.device):
@@ -404,6 +416,12 @@ class GridExchange:
 
     def last(self):
         return self._last
+
+    def wait_ms(self, last_steps: int) -> float:
+        """Mean device time per step the compute stream spent waiting for its slabs, over the last `last_steps` steps
+        (call after a synchronize)."""
+        pairs = self.wait_events[-last_steps:]
+        return sum(b.elapsed_time(a) for b, a in pairs) / max(1, len(pairs))
 
     def check_status(self) -> None:
         code = int(self.status.item())
