@@ -605,30 +605,7 @@ extern "C" int sb200_gemm_timed(const char* kernel, const void* a, const void* b
 extern "C" int sb200_tile_program(const char* which, void* out, size_t out_bytes) {
   if (!which || !out || out_bytes < sizeof(sb200_program_t)) return SB200_ERR_INVALID_PROBLEM;
   sb200_program_t pg;
-  if (strcmp(which, "level0") == 0) pg = sb200::programs::level0();
-  else if (strcmp(which, "level1_full_fly") == 0) pg = sb200::programs::level1_full(true);
-  else if (strcmp(which, "level1_full_ws") == 0) pg = sb200::programs::level1_full(false);
-  else if (strcmp(which, "level1_strassen") == 0) pg = sb200::programs::level1_strassen();
-  else if (strcmp(which, "level1_first") == 0) pg = sb200::programs::level1_first();
-  else if (strcmp(which, "level1_first_early") == 0) pg = sb200::programs::level1_first_early();
-  else if (strcmp(which, "level1_second") == 0) pg = sb200::programs::level1_second();
-  else if (strcmp(which, "level1_second_taps") == 0) pg = sb200::programs::level1_second_taps();
-  else if (strncmp(which, "level2_", 7) == 0) {
-    // "level2_<child>_launch<1|2>", child = m0, m1, m2, m4, m5, m3, m6 (execution order)
-    const sb200::programs::Level2Child* ch = sb200::programs::level2_children();
-    int found = -1, launch = 0;
-    for (int c = 0; c < 7 && found < 0; ++c) {
-      const size_t len = strlen(ch[c].name);
-      if (strncmp(which + 7, ch[c].name, len) == 0 && strncmp(which + 7 + len, "_launch", 7) == 0) {
-        found = c;
-        launch = which[7 + len + 7] - '0';
-      }
-    }
-    if (found < 0 || (launch != 1 && launch != 2)) return SB200_ERR_NO_KERNEL;
-    pg = sb200::programs::link_outer(launch == 1 ? sb200::programs::level1_first() : sb200::programs::level1_second_taps(),
-                                     ch[found].link, launch);
-  }
-  else return SB200_ERR_NO_KERNEL;
+  if (!sb200::programs::find(which, &pg)) return SB200_ERR_NO_KERNEL;
   memcpy(out, &pg, sizeof(pg));
   return 0;
 }

@@ -79,6 +79,7 @@ struct Layout {
   int workers;       // CTAs (1-CTA kernels) or CTA pairs launched
   int whole_tiles;   // tiles handed out whole
   int region_tiles;  // tiles that follow, each handed out as two K-halves (0: none)
+  bool dynamic;      // units are drawn from a counter by whichever pair is free (else dealt round-robin)
   size_t off_split_buf, off_split_flags, split_flag_bytes;
 };
 
@@ -86,20 +87,29 @@ int level_of(Variant v) { return v == kCubic ? 0 : (v == kInterleavedLevel2 ? 2 
 
 int sm_count() { return sm_count_of_current_device(); }
 
-// Builds the unit list for `tiles` output tiles on at most `cap` workers (see WorkUnit in sw_kernel.cuh):
+// Builds the unit list for `tiles` output tiles on at most `cap` workers (see WorkUnit in sw_kernel.cuh).
+// CTA pairs with more tiles than workers draw their units from a counter as they become free (UnitCursor): they end
+// within one unit's time of each other, so with two waves or more the last `cap` tiles are handed out as K-halves,
+// which halves that spread.  Otherwise units are dealt round-robin, and
 //   fewer tiles than half the workers: every tile is cut into two K-halves;
 //   a last wave that is at most half full: its tiles are cut, so that it lasts half as long.
 // The fused-presum kernels are never cut, nor are products of fewer than 8 k-steps.
-void deal_tiles(Layout& L, int tiles, int cap, Variant v, bool no_split) {
+void deal_tiles(Layout& L, int tiles, int cap, Variant v, bool no_split, bool pair) {
   L.workers = tiles < cap ? tiles : cap;
   L.whole_tiles = tiles;
   L.region_tiles = 0;
+  L.dynamic = pair && tiles > cap;
   if (v == kFusedPresum || v == kStrassenFused || no_split || L.num_k < 8 || cap < 2) return;
   if (tiles < cap) {
     if (2 * tiles > cap) return;
     L.workers = 2 * tiles;
     L.whole_tiles = 0;
     L.region_tiles = tiles;
+    return;
+  }
+  if (L.dynamic && tiles >= 2 * cap) {
+    L.whole_tiles = tiles - cap;
+    L.region_tiles = cap;
     return;
   }
   const int rem = tiles % cap;
@@ -133,7 +143,13 @@ Layout make_layout(const GemmArgs& a, int cap_override = 0) {
 #ifdef SB200_PROFILE
   if (getenv("SB200_NO_SPLIT")) no_split = true;  // measurement aid of profile builds
 #endif
-  deal_tiles(L, L.tiles_m * L.tiles_n, cap, a.variant, no_split);
+  deal_tiles(L, L.tiles_m * L.tiles_n, cap, a.variant, no_split, a.pair != 0);
+#ifdef SB200_PROFILE
+  if (const char* sc = getenv("SB200_SCHED")) {  // measurement aid: 0 = round-robin deal, 2 = drawn but no final halves
+    if (atoi(sc) == 0) { L.dynamic = false; deal_tiles(L, L.tiles_m * L.tiles_n, cap, a.variant, true, false); }
+    if (atoi(sc) == 2) deal_tiles(L, L.tiles_m * L.tiles_n, cap, a.variant, true, a.pair != 0);
+  }
+#endif
   // the status block and the flags of the cut tiles sit together at the head: one memset clears both for a run
   size_t off = 0;
   L.off_status = off;
@@ -361,7 +377,7 @@ struct LaunchSpec {
   float* outer_src;
   float* outer_src2;
   float* extra_dst;
-  programs::OuterLink link;
+  int child;                 // group of a level-2 run (0..6), or -1: a level-1 GEMM of its own
   bool linked;
   PresumSideJob more_jobs[2];  // presum jobs of the level above, run by launch 1's presum warps
   int n_more_jobs;
@@ -565,7 +581,7 @@ int launch_group(const LaunchSpec& s, cudaStream_t stream, MarkFn mark) {
       rc = launch_any(es, bn_sel, kPresumNone, p, s.grid, stream);
       break;
     case kFusedPresum:
-      p.prog = programs::level1_full(true);
+      p.prog = programs::level1_fused();
       rc = launch_any(es, bn_sel, kPresumFeed, p, s.grid, stream);
       break;
     case kStrassenFused:
@@ -573,15 +589,13 @@ int launch_group(const LaunchSpec& s, cudaStream_t stream, MarkFn mark) {
       rc = launch_any(es, bn_sel, kPresumFeed, p, s.grid, stream);
       break;
     case kInterleavedPresum: {
-      const sb200_program_t first = s.linked ? programs::level1_first() : programs::level1_first_early();
-      const sb200_program_t second = programs::level1_second_taps();
-      p.prog = s.linked ? programs::link_outer(first, s.link, 1) : first;
+      p.prog = s.linked ? programs::level2_launch(s.child, 1) : programs::level1_first();
       p.split_epoch = ++*s.split_epoch;
       p.unit_counter = s.dynamic ? s.status + kUnitCounterBase + p.split_epoch : nullptr;
       rc = launch_any(es, bn_sel, kPresumJob, p, s.grid, stream);
       if (rc) return rc;
       if ((rc = mark())) return rc;
-      p.prog = s.linked ? programs::link_outer(second, s.link, 2) : second;
+      p.prog = s.linked ? programs::level2_launch(s.child, 2) : programs::level1_second();
       p.split_epoch = ++*s.split_epoch;
       p.unit_counter = s.dynamic ? s.status + kUnitCounterBase + p.split_epoch : nullptr;
       p.njobs = 0;
@@ -627,11 +641,7 @@ int run(const GemmArgs& a, void* workspace, size_t workspace_size, cudaStream_t 
   s.split_epoch = &epoch;
   s.whole_tiles = L.whole_tiles;
   s.region_tiles = L.region_tiles;
-  // more units than workers: the pairs draw units in raster order as they become free (UnitCursor)
-  s.dynamic = a.pair && L.whole_tiles + 2 * L.region_tiles > L.workers;
-#ifdef SB200_PROFILE
-  if (const char* sc = getenv("SB200_SCHED")) s.dynamic = s.dynamic && atoi(sc) != 0;  // measurement aid
-#endif
+  s.dynamic = L.dynamic;
   if (L.region_tiles) {
     s.split_buf = reinterpret_cast<float*>(wsb + L.off_split_buf);
     s.split_flags = reinterpret_cast<int*>(wsb + L.off_split_flags);
@@ -690,7 +700,7 @@ int run(const GemmArgs& a, void* workspace, size_t workspace_size, cudaStream_t 
     const programs::Level2Child& ch = children[c];
     s.a = operand_a(ch.a);
     s.b = operand_b(ch.b);
-    s.link = ch.link;
+    s.child = c;
     const long long out_off = ch.out_quadrant >= 0 ? ((ch.out_quadrant >> 1) * mh * ldd + (ch.out_quadrant & 1) * nh) * es : 0;
     s.out = ch.out_quadrant >= 0 ? D + out_off : nullptr;
     s.out_rows = (ch.out_quadrant >= 0 && (ch.out_quadrant >> 1)) ? a.m - mh : mh;

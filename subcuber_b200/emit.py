@@ -4,8 +4,9 @@ The reference front end prints its schedules and copies pre-written example sour
 646-653); nothing downstream reads the schedule.  Here the schedule selects a launch plan of this library's
 kernels, and the per-tile programs of every launch (product order, operand term lists, tensor-memory slot plan,
 postsum steps) are GENERATED from the DSL expressions and checked (`tile_program.check_program`) before they are
-written out.  The tables compiled into the CUDA library (csrc/sw_programs.h) are the same tables; a test compares
-them byte for byte.
+written out.  The tables the CUDA library runs are these tables: the build (subcuber_b200/build.py) calls
+`generate_tables` and compiles its output (csrc/sw_tile_programs.inc, included by csrc/sw_programs.h) into the
+library; no tile program is written by hand on the C++ side.
 """
 from __future__ import annotations
 
@@ -163,17 +164,18 @@ def level1_second_program(ms) -> tp.Program:
 
 def level1_second_taps_program(ms) -> tp.Program:
     """Launch 2, the plan in use: no product waits for an epilogue step that has not had a whole product's time.
-    A slot that keeps accumulating is tapped into a hand-off tile while the other slot's product runs; m6 goes to
-    slot Q (c2 = v - Q) so that the tap after m3 overlaps it; slot roles swap from tile to tile.  Hand-offs: m4,
-    u = m0 + m2, v = m0 + (m2 + m3), and m0 from launch 1.  No step reads more than two hand-off tiles."""
+    Every product's slot is read by an epilogue step while the other slot's product runs; m6 goes to slot Q
+    (c2 = v - Q) so that the step after m3 overlaps it; slot roles swap from tile to tile.  Hand-offs: m4,
+    u = m0 + m2, v = u + m3 (written over u, which is dead once c1 is formed), and m0 from launch 1, which is read
+    once - it is the one hand-off that comes from DRAM.  No step reads more than two hand-off tiles."""
     b = ProgramBuilder(_products_by_name(ms), fly=False)
     b.pg.alternate_slots = 1
     b.product("m4", Q).product("m2", P)
     b.epilogue([Q], [], wait=[Q], release=[Q], dst_kind=1, dst=WS_M4)
     b.epilogue([P], [WS_M0], wait=[P], release=[P], dst_kind=1, dst=WS_U)            # u = m0 + m2
-    b.product("m5", Q).product("m3", P, accumulate=1)
+    b.product("m5", Q).product("m3", P)
     b.epilogue([Q], [WS_U, WS_M4], wait=[Q], release=[Q], dst_kind=0, dst=1)         # c1 = u + m4 + m5
-    b.epilogue([P], [WS_M0], wait=[P], release=[P], dst_kind=1, dst=WS_V)            # v = m0 + m2 + m3
+    b.epilogue([P], [WS_U], wait=[P], release=[P], dst_kind=1, dst=WS_V)             # v = u + m3
     b.product("m6", Q)
     b.epilogue([], [WS_V, WS_M4], wait=[], release=[], dst_kind=0, dst=3)            # c3 = v + m4
     b.epilogue([Q], [WS_V], wait=[Q], release=[Q], dst_kind=0, dst=2, signs=[-1])    # c2 = v - m6
@@ -498,6 +500,38 @@ def program_to_c(name: str, pg: tp.Program) -> str:
         lines.append("  " + ", ".join(str(b) for b in raw[i:i + 24]) + ",")
     lines.append("};")
     return "\n".join(lines) + "\n"
+
+
+def generate_tables() -> str:
+    """The C text the library compiles in (csrc/sw_tile_programs.inc): every tile program as the bytes of an
+    `sb200_program_t`, a name index, and the seven groups of a level-2 run.  The programs are checked first."""
+    from .algos.strassen_winograd_level1 import strassen_winograd
+
+    programs = all_programs()
+    verify_programs(programs)
+    size = C.sizeof(tp.Program)
+    out = ["/* Generated by subcuber_b200/emit.py from the algorithm DSL (subcuber_b200/algos) - do not edit.\n"
+           "   Tile programs as the bytes of sb200_program_t (csrc/tile_program.h). */\n",
+           f"#define SB200_EMITTED_PROGRAM_BYTES {size}\n"]
+    for name in sorted(programs):
+        out.append(program_to_c(name, programs[name]))
+    out.append("static const struct sb200_emitted_program { const char* name; const unsigned char* bytes; } "
+               "sb200_emitted_programs[] = {\n")
+    for name in sorted(programs):
+        out.append(f'  {{"{name}", sb200_program_{name}}},\n')
+    out.append("};\n")
+    out.append(f"#define SB200_NUM_EMITTED_PROGRAMS {len(programs)}\n")
+    _, ms = strassen_winograd(4, 4, 4)
+    out.append("/* The seven level-1 groups of a level-2 run in execution order.  a, b: operand codes (0..3 raw outer "
+               "quadrant, 4..7 outer presum);\n   dst, src, src2, extra_dst: outer chain buffers X0..X2 (-1 none); "
+               "out_quadrant: quadrant of C written in the output type (-1 none). */\n")
+    out.append("static const struct sb200_level2_child { const char* name; int a, b, dst, src, src2, extra_dst, "
+               "out_quadrant; } sb200_level2_children[7] = {\n")
+    for ch in level2_children(ms):
+        out.append(f'  {{"{ch["name"]}", {ch["a"]}, {ch["b"]}, {ch["dst"]}, {ch["src"]}, {ch["src2"]}, {ch["extra_dst"]}, '
+                   f'{ch["out_quadrant"]}}},\n')
+    out.append("};\n")
+    return "".join(out)
 
 
 def artefacts(schedule: list, fusion: Optional[dict], plan: dict) -> Dict[str, str]:
