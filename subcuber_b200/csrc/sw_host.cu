@@ -88,9 +88,9 @@ int level_of(Variant v) { return v == kCubic ? 0 : (v == kInterleavedLevel2 ? 2 
 int sm_count() { return sm_count_of_current_device(); }
 
 // Builds the unit list for `tiles` output tiles on at most `cap` workers (see WorkUnit in sw_kernel.cuh).
-// CTA pairs with more tiles than workers draw their units from a counter as they become free (UnitCursor): they end
-// within one unit's time of each other, so with two waves or more the last `cap` tiles are handed out as K-halves,
-// which halves that spread.  Otherwise units are dealt round-robin, and
+// CTA pairs with more tiles than workers draw whole tiles from a counter as they become free (UnitCursor); cutting
+// their last tiles into K-halves to even out the end was measured and costs more than it saves (f16 level 1 on B200:
+// -2.5 % at 16384^3, -10 % at 8192^3).  Otherwise units are dealt round-robin, and
 //   fewer tiles than half the workers: every tile is cut into two K-halves;
 //   a last wave that is at most half full: its tiles are cut, so that it lasts half as long.
 // The fused-presum kernels are never cut, nor are products of fewer than 8 k-steps.
@@ -107,11 +107,7 @@ void deal_tiles(Layout& L, int tiles, int cap, Variant v, bool no_split, bool pa
     L.region_tiles = tiles;
     return;
   }
-  if (L.dynamic && tiles >= 2 * cap) {
-    L.whole_tiles = tiles - cap;
-    L.region_tiles = cap;
-    return;
-  }
+  if (L.dynamic) return;
   const int rem = tiles % cap;
   if (rem == 0 || 2 * rem > cap) return;
   L.whole_tiles = tiles - rem;
@@ -145,10 +141,8 @@ Layout make_layout(const GemmArgs& a, int cap_override = 0) {
 #endif
   deal_tiles(L, L.tiles_m * L.tiles_n, cap, a.variant, no_split, a.pair != 0);
 #ifdef SB200_PROFILE
-  if (const char* sc = getenv("SB200_SCHED")) {  // measurement aid: 0 = round-robin deal, 2 = drawn but no final halves
-    if (atoi(sc) == 0) { L.dynamic = false; deal_tiles(L, L.tiles_m * L.tiles_n, cap, a.variant, true, false); }
-    if (atoi(sc) == 2) deal_tiles(L, L.tiles_m * L.tiles_n, cap, a.variant, true, a.pair != 0);
-  }
+  if (const char* sc = getenv("SB200_SCHED"))  // measurement aid: 0 = round-robin deal
+    if (atoi(sc) == 0) deal_tiles(L, L.tiles_m * L.tiles_n, cap, a.variant, no_split, false);
 #endif
   // the status block and the flags of the cut tiles sit together at the head: one memset clears both for a run
   size_t off = 0;

@@ -64,16 +64,13 @@ def test_every_k_step_of_every_tile_is_handed_out_once(kernel, shape, sms, lib):
     assert (whole[:, 3] == 1).all() and len(whole) == tiles
 
 
-def test_the_last_tiles_are_cut(lib):
-    """CTA pairs draw their units as they become free: with two waves or more the last 74 tiles go out as halves
-    (8192^3 at level 1: 256 pair tiles = 182 whole + 148 halves).  The 1-CTA kernels deal round-robin and cut a last
-    wave only when it is at most half full."""
+def test_which_tiles_are_cut(lib):
+    """CTA pairs with more tiles than pairs draw whole tiles as they become free: nothing is cut.  The 1-CTA kernels
+    deal round-robin and cut a last wave that is at most half full."""
     kernel = "blackwell_f16_sw_interleaved_presum_2sm"
-    units, workers = _deal(lib, kernel, 8192, 8192, 8192, 148)
-    assert workers == 74 and len(units) == 182 + 148
-    assert (units[:182, 3] == 1).all() and (units[182:, 3] == 2).all()
-    units, workers = _deal(lib, kernel, 16384, 16384, 16384, 148)
-    assert workers == 74 and len(units) == 950 + 148 and (units[:950, 3] == 1).all()
+    for size, tiles in ((8192, 256), (16384, 1024)):
+        units, workers = _deal(lib, kernel, size, size, size, 148)
+        assert workers == 74 and len(units) == tiles and (units[:, 3] == 1).all()
     # 1-CTA kernels, 8192^3: 512 tiles on 148 CTAs = 3 waves + 68: less than half a wave, cut
     units, workers = _deal(lib, "blackwell_f16_sw_interleaved_presum", 8192, 8192, 8192, 148)
     assert workers == 148 and len(units) == 444 + 136
