@@ -171,9 +171,9 @@ size_t sb200_gemm_workspace_bytes_opt(const char* kernel, int m, int n, int k, c
 int sb200_gemm_opt(const char* kernel, const void* a, const void* b, void* d, int m, int n, int k, void* workspace,
                    size_t workspace_bytes, sb200_stream_t stream, const sb200_gemm_options* options);
 /* The unit list of one launch of a tensor-core kernel on a device of `sms` SMs (0 = the current device): whole output
- * tiles in raster order and, where the last wave would be at most half full (or there are fewer tiles than half the
- * workers), tiles cut into two K-halves that run at the same time (the role the reference gives to split_k_slices,
- * src/cuda/kernel_runner.cpp:244-255).  Writes 8 ints per unit in list order: worker under a round-robin deal, tile,
+ * tiles in raster order and, for the kernels that deal tiles round-robin, the tiles of a last wave that is at most
+ * half full cut into two K-halves that run at the same time (the role the reference gives to split_k_slices,
+ * src/cuda/kernel_runner.cpp:244-255); the CTA-pair kernels draw whole tiles as they become free instead.  Writes 8 ints per unit in list order: worker under a round-robin deal, tile,
  * part (0 = whole tile or the half that publishes its partial sum, 1 = the half that adds it), parts (1 or 2), first
  * k-step, end k-step, hand-off slot, split slot.  Returns the number of units (negative: error code); *workers = CTAs
  * or CTA pairs launched.  Host arithmetic only. */

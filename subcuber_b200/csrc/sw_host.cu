@@ -88,26 +88,19 @@ int level_of(Variant v) { return v == kCubic ? 0 : (v == kInterleavedLevel2 ? 2 
 int sm_count() { return sm_count_of_current_device(); }
 
 // Builds the unit list for `tiles` output tiles on at most `cap` workers (see WorkUnit in sw_kernel.cuh).
-// CTA pairs with more tiles than workers draw whole tiles from a counter as they become free (UnitCursor); cutting
-// their last tiles into K-halves to even out the end was measured and costs more than it saves (f16 level 1 on B200:
-// -2.5 % at 16384^3, -10 % at 8192^3).  Otherwise units are dealt round-robin, and
-//   fewer tiles than half the workers: every tile is cut into two K-halves;
-//   a last wave that is at most half full: its tiles are cut, so that it lasts half as long.
+//   CTA pairs with more tiles than pairs draw whole tiles from a counter as they become free (UnitCursor).
+//   Otherwise tiles are dealt round-robin, and the tiles of a last wave that is at most half full are cut into two
+//   K-halves, so that the wave lasts half as long.
+// Measured on B200 (f16 level 1) and therefore NOT done: cutting the last tiles of the drawn order (-2.5 % at 16384^3,
+// -10 % at 8192^3); cutting every tile when there are fewer than half as many as workers (-6 % at 2048^3, -12 % at
+// 3072^3): a half tile costs a whole tile's epilogue, and the halves' partial sums travel through memory.
 // The fused-presum kernels are never cut, nor are products of fewer than 8 k-steps.
 void deal_tiles(Layout& L, int tiles, int cap, Variant v, bool no_split, bool pair) {
   L.workers = tiles < cap ? tiles : cap;
   L.whole_tiles = tiles;
   L.region_tiles = 0;
   L.dynamic = pair && tiles > cap;
-  if (v == kFusedPresum || v == kStrassenFused || no_split || L.num_k < 8 || cap < 2) return;
-  if (tiles < cap) {
-    if (2 * tiles > cap) return;
-    L.workers = 2 * tiles;
-    L.whole_tiles = 0;
-    L.region_tiles = tiles;
-    return;
-  }
-  if (L.dynamic) return;
+  if (v == kFusedPresum || v == kStrassenFused || no_split || L.num_k < 8 || L.dynamic || tiles <= cap) return;
   const int rem = tiles % cap;
   if (rem == 0 || 2 * rem > cap) return;
   L.whole_tiles = tiles - rem;

@@ -179,8 +179,8 @@ __device__ __forceinline__ TileCoord tile_of(int w, int tiles_m, int tiles_n, in
 // the flag and adds the partial sum.  The unit list, in the order units are handed out:
 //   units 0 .. whole_tiles - 1            whole tiles in raster order
 //   then 2 units per tile of the region   first half, second half of tiles whole_tiles .. whole_tiles + region_tiles - 1
-// The host cuts the tiles of a last wave that is at most half full (and all tiles when there are fewer than half as
-// many as workers): that wave then lasts half as long.  Both halves of a tile start at the same time on two workers,
+// The host cuts the tiles of a last wave that is at most half full when tiles are dealt round-robin: that wave then
+// lasts half as long.  Both halves of a tile start at the same time on two workers,
 // at the same phase as every other half: workers that share operand panels stay close in K, which is what lets them
 // share those panels through L2.  (Cutting tiles at uneven points to give every worker an exactly equal share of a
 // partial wave was tried and is much slower: workers at different K phases stop sharing panels and the launch

@@ -343,14 +343,10 @@ def test_f64_agrees_with_cublas(cuda_device):
 
 # ------------------------------------------------------------------------------- K-split of the last wave
 SPLIT_CASES = [
-    # CTA pairs cut tiles only when there are at most half as many tiles as pairs (else they draw whole tiles)
-    ("blackwell_f16_sw_interleaved_presum_2sm", 8, (512, 1024, 1024)),  # quadrant 1 x 2 pair tiles -> 4 halves on 4 pairs
-    ("blackwell_f16_sw_interleaved_presum_2sm", 0, (2048, 2048, 1024)),  # quadrant 4 x 4 pair tiles -> 32 halves
-    ("blackwell_f32_sw_interleaved_presum_2sm", 0, (2048, 2048, 2048)),  # 16 tiles -> 32 halves
-    ("blackwell_f16_cubic_2sm_256x256", 16, (1024, 768, 1024)),          # 4 x 3 pair tiles... on 8 pairs: drawn whole
-    ("blackwell_f16_cubic_2sm_256x256", 0, (2048, 2048, 2048)),          # 64 tiles on 74 pairs: whole
-    ("blackwell_f16_cubic_2sm_256x256", 0, (1024, 1536, 2048)),          # 24 tiles -> 48 halves
-    ("blackwell_f16_sw_level2_2sm", 8, (1024, 2048, 2048)),              # every group: 1 x 2 pair tiles -> 4 halves
+    # CTA pairs draw whole tiles (nothing is cut): these check that their drawn order gives the same bits
+    ("blackwell_f16_sw_interleaved_presum_2sm", 8, (512, 2560, 2048)),  # quadrant 1 x 5 pair tiles drawn by 4 pairs
+    ("blackwell_f16_cubic_2sm_256x256", 16, (1024, 768, 1024)),          # 4 x 3 pair tiles drawn by 8 pairs
+    ("blackwell_f16_sw_level2_2sm", 8, (1024, 5120, 4096)),              # every group: 1 x 5 pair tiles drawn by 4 pairs
     # kernel, SMs, shape: the tile count leaves a last wave at most half full, whose tiles are split in two K-halves
     ("blackwell_f16_cubic_128x256", 8, (384, 768, 1024)),              # 3 x 3 = 9 tiles on 8 CTAs
     ("blackwell_f16_cubic_2sm_256x256", 8, (512, 640, 1024)),          # 2 x 3 = 6 pair tiles on 4 pairs... 2 left
@@ -690,8 +686,8 @@ def test_bounded_wait_gives_up_and_the_device_stays_usable(oracle, cuda_device):
 
     from subcuber_b200 import inputs, runner
 
-    kernel = "blackwell_f16_sw_interleaved_presum_2sm"
-    m, n, k = 512, 1024, 2048          # quadrant 1 x 2 pair tiles on 4 pairs: both tiles are cut into two K-halves
+    kernel = "blackwell_f16_sw_interleaved_presum"
+    m, n, k = 768, 1536, 2048          # quadrant 3 x 3 tiles on 8 CTAs: the ninth tile is cut into two K-halves
     a_np, b_np = inputs.operands("f16", "harness", m, n, k, seed=4)
     a, b = runner.to_torch(a_np, cuda_device), runner.to_torch(b_np, cuda_device)
     d = torch.zeros((m, n), dtype=torch.float16, device=cuda_device)
