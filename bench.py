@@ -50,7 +50,8 @@ ELEM_BYTES = {"f16": 2, "bf16": 2, "f32": 4, "f64": 8}
 # DRAM bytes (read + write) per launch of the dominant kernel from one Nsight Compute capture of that launch
 # (dram__bytes_read.sum + dram__bytes_write.sum).  key: (kernel, m, n, k).  Absent = not captured for that workload.
 NCU_TRAFFIC_BYTES = {
-    ("blackwell_f16_sw_interleaved_presum_2sm", 8192, 8192, 8192): 1.488e9,
+    ("blackwell_f16_sw_interleaved_presum_2sm", 16384, 16384, 16384): 9.71e9,   # launch 2: read 8.52 GB + write 1.19 GB
+    ("blackwell_f16_sw_interleaved_presum_2sm", 8192, 8192, 8192): 1.307e9,     # launch 2: read 1.033 GB + write 0.274 GB
 }
 
 
