@@ -15,7 +15,10 @@ import json
 import os
 import sys
 
-ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+# the reference tree: first argument, else REFERENCE_ROOT, else a directory "reference" beside this repository
+ref = sys.argv[1] if len(sys.argv) > 1 else os.environ.get(
+    "REFERENCE_ROOT", os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.dirname(
+        os.path.abspath(__file__))))), "reference"))
 sys.dont_write_bytecode = True
 sys.path.insert(0, os.path.join(ref, "src"))
 
