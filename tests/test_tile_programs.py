@@ -64,3 +64,24 @@ def test_checker_rejects_broken_tables(lib):
     pg.epilogue[1].release_mask = 0  # never gives the slot back
     with pytest.raises(tp.ProgramError):
         tp.check_program(pg, level=1)
+
+
+def test_the_library_runs_the_generated_tables(lib):
+    """The C++ side holds no schedule of its own: every table the library reports is the front end's, byte for byte,
+    and csrc/sw_programs.h only looks tables up."""
+    import os
+
+    from subcuber_b200 import emit
+
+    programs = emit.all_programs()
+    assert len(programs) >= 8 + 14
+    for name, pg in programs.items():
+        assert bytes(tp.to_bytes(tp.from_library(name))) == bytes(tp.to_bytes(pg)), name
+    here = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    text = open(os.path.join(here, "subcuber_b200", "csrc", "sw_programs.h")).read()
+    assert "sw_tile_programs.inc" in text and "add_product" not in text and "add_epilogue" not in text
+    # m0 comes from DRAM: the second launch reads it exactly once
+    second = programs["level1_second_taps"]
+    reads_m0 = sum(1 for i in range(second.nepilogues) for t in range(second.epilogue[i].nsrc)
+                   if second.epilogue[i].src[t] == 0)
+    assert reads_m0 == 1
