@@ -276,9 +276,21 @@ def main():
         m, n, k = gp.local_m, gp.local_n, K
         # SMs left out of the GEMM grid for the few one-CTA flag kernels of the exchange (the persistent GEMM kernels
         # would otherwise hold every SM until they end)
-        opts = runner.options(sm_limit=sms - multi_gpu.GridExchange.reserved_sms())
-        exchange = multi_gpu.GridExchange(gp, rank, dtn, device, seed=1)
-        grid_text = gp.describe()
+        # symmetric memory needs peer mappings between all GPUs: where they cannot be set up every rank falls back to
+        # all-gathers in the grid's groups (the ranks agree first, so that none is left alone in a collective)
+        try:
+            exchange = multi_gpu.GridExchange(gp, rank, dtn, device, seed=1)
+            ok = 1
+        except Exception as exc:  # noqa: BLE001 - any set-up failure means "use the other exchange"
+            print(f"[bench] rank {rank}: peer exchange unavailable ({exc}); using collectives", file=sys.stderr)
+            ok = 0
+        agreed = torch.tensor([ok], dtype=torch.int32, device=device)
+        dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
+        if int(agreed.item()) == 0:
+            exchange = multi_gpu.CollectiveGridExchange(gp, rank, dtn, device, seed=1)
+        reserved = type(exchange).reserved_sms()
+        opts = runner.options(sm_limit=sms - reserved) if reserved else None
+        grid_text = gp.describe() + "; exchange: " + exchange.describe()
     else:
         m, n, k = M, N, K
 

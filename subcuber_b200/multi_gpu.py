@@ -137,8 +137,7 @@ class GridPlan:
             return f"{self.world} independent replicas"
         return (f"{self.pr} x {self.pc} grid of GPUs, local {self.local_m}x{self.local_n}x{self.k}; per step every GPU "
                 f"receives {(self.a_recv_bytes + self.b_recv_bytes) / 2**20:.0f} MiB "
-                f"(A slab {self.a_recv_bytes / 2**20:.0f}, B slab {self.b_recv_bytes / 2**20:.0f}) pushed by its peers' "
-                "copy engines over NVLink, overlapped with the GEMM of the step before")
+                f"(A slab {self.a_recv_bytes / 2**20:.0f}, B slab {self.b_recv_bytes / 2**20:.0f}) over NVLink")
 
 
 def grid_plan(m: int, n: int, k: int, world: int, esize: int, level: int = 1, tile: int = 256) -> GridPlan:
@@ -197,12 +196,35 @@ def expected_slabs(gp: GridPlan, rank: int, dtype: str, device, seed: int = 1):
     return a, b
 
 
+def verify_block(gp: GridPlan, rank: int, seed: int, d: torch.Tensor, ai_bi, tol: float = 2e-3) -> bool:
+    """Correctness evidence for one step of a grid exchange: the slabs this rank multiplied equal the shards their
+    owners generated (bit for bit: the exchange delivered the right bytes to the right place), and sampled rows of the
+    block D agree with the fp64 product of those slabs, as does the block's checksum."""
+    a, b = ai_bi
+    dtype = {torch.float16: "f16", torch.bfloat16: "bf16", torch.float32: "f32", torch.float64: "f64"}[a.dtype]
+    want_a, want_b = expected_slabs(gp, rank, dtype, a.device, seed)
+    ok = bool(torch.equal(a, want_a)) and bool(torch.equal(b, want_b))
+    del want_a, want_b
+    rows = torch.tensor([0, d.shape[0] // 3, d.shape[0] // 2 + 1, d.shape[0] - 1], device=a.device)
+    truth = a[rows].double() @ b.double()
+    err = float((d[rows].double() - truth).norm() / truth.norm())
+    ok = ok and err < tol
+    total = float(d.double().sum())
+    want = float(a.double().sum(dim=0) @ b.double().sum(dim=1))
+    scale = float(a.double().abs().sum(dim=0) @ b.double().abs().sum(dim=1))
+    return ok and abs(total - want) <= 2e-5 * scale
+
+
 class CollectiveGridExchange:
     """The grid exchange with collectives: an all-gather of the A shards inside every grid row and of the B shards
     inside every grid column, on any torch.distributed backend.  Synchronous with the compute stream."""
 
+    @staticmethod
+    def reserved_sms() -> int:
+        return 0   # the collectives run between the GEMMs, not beside them
+
     def __init__(self, gp: GridPlan, rank: int, dtype: str, device, seed: int = 1):
-        self.gp, self.rank = gp, rank
+        self.gp, self.rank, self.seed = gp, rank, seed
         self.a_shard, self.b_shard = make_shards(gp, rank, dtype, device, seed)
         # every rank creates every sub-group, in the same order
         self.row_pg = self.col_pg = None
@@ -239,6 +261,15 @@ class CollectiveGridExchange:
 
     def check_status(self) -> None:
         pass
+
+    def wait_ms(self, last_steps: int):
+        return None   # the exchange is part of the compute stream's own work
+
+    def verify_block(self, d: torch.Tensor, ai_bi, tol: float = 2e-3) -> bool:
+        return verify_block(self.gp, self.rank, self.seed, d, ai_bi, tol)
+
+    def describe(self) -> str:
+        return "all-gathers in the grid's row and column groups before every GEMM (no overlap)"
 
     def close(self) -> None:
         pass
@@ -429,22 +460,10 @@ class GridExchange:
             raise RuntimeError(f"grid exchange: device status {code} (a flag from another GPU did not arrive in time)")
 
     def verify_block(self, d: torch.Tensor, ai_bi, tol: float = 2e-3) -> bool:
-        """Correctness evidence for one step: the slabs this rank multiplied equal the shards their owners generated
-        (bit for bit: the exchange delivered the right bytes to the right place), and sampled rows of the block D
-        agree with the fp64 product of those slabs, as does the block's checksum."""
-        a, b = ai_bi
-        dtype = {torch.float16: "f16", torch.bfloat16: "bf16", torch.float32: "f32"}[a.dtype]
-        want_a, want_b = expected_slabs(self.gp, self.rank, dtype, self.device, self.seed)
-        ok = bool(torch.equal(a, want_a)) and bool(torch.equal(b, want_b))
-        del want_a, want_b
-        rows = torch.tensor([0, d.shape[0] // 3, d.shape[0] // 2 + 1, d.shape[0] - 1], device=self.device)
-        truth = a[rows].double() @ b.double()
-        err = float((d[rows].double() - truth).norm() / truth.norm())
-        ok = ok and err < tol
-        total = float(d.double().sum())
-        want = float(a.double().sum(dim=0) @ b.double().sum(dim=1))
-        scale = float(a.double().abs().sum(dim=0) @ b.double().abs().sum(dim=1))
-        return ok and abs(total - want) <= 2e-5 * scale
+        return verify_block(self.gp, self.rank, self.seed, d, ai_bi, tol)
+
+    def describe(self) -> str:
+        return "copy-engine pushes into symmetric memory, ordered by bounded flag kernels, under the GEMM before"
 
     def close(self) -> None:
         torch.cuda.synchronize(self.device)
