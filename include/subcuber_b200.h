@@ -81,6 +81,12 @@ SB200_DECLARE_RUN(run_blackwell_f16_sw_fused_presum_2sm);
 SB200_DECLARE_RUN(run_blackwell_f32_sw_fused_presum_2sm);
 SB200_DECLARE_RUN(run_blackwell_f16_sw_interleaved_presum_2sm);
 SB200_DECLARE_RUN(run_blackwell_f32_sw_interleaved_presum_2sm);
+/* Level 1 in ONE launch: the seven products of a tile run back to back in one CTA pair while the presum warps of the
+ * same launch materialise the presums and publish them panel by panel (the reference runs several Mi in one CTA with
+ * FusedMiGroup, include/cutlass/gemm/device/strassen_decls.h:1466-1539, but always launches its presum step first). */
+SB200_DECLARE_RUN(run_blackwell_f16_sw_merged_presum_2sm);
+SB200_DECLARE_RUN(run_blackwell_f32_sw_merged_presum_2sm);
+SB200_DECLARE_RUN(run_blackwell_bf16_sw_merged_presum_2sm);
 /* Level 2 (49 products): seven level-1 interleaved-presum groups over half-size operands, 14 launches, chained through
  * fp32 buffers.  Stands where the reference has StrassenGemmLevel2 (include/cutlass/gemm/device/strassen_gemm.h:
  * 1300-2008) behind its "*_level_2" runner entries. */

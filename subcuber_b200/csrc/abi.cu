@@ -40,6 +40,9 @@ const KernelDesc kDescs[] = {
     {"blackwell_f32_sw_fused_presum_2sm", "f32", 1, sb200::kF32, sb200::kFusedPresum, 256, 1},
     {"blackwell_f16_sw_interleaved_presum_2sm", "f16", 1, sb200::kF16, sb200::kInterleavedPresum, 256, 1},
     {"blackwell_f32_sw_interleaved_presum_2sm", "f32", 1, sb200::kF32, sb200::kInterleavedPresum, 256, 1},
+    {"blackwell_f16_sw_merged_presum_2sm", "f16", 1, sb200::kF16, sb200::kMergedPresum, 256, 1},
+    {"blackwell_f32_sw_merged_presum_2sm", "f32", 1, sb200::kF32, sb200::kMergedPresum, 256, 1},
+    {"blackwell_bf16_sw_merged_presum_2sm", "bf16", 1, sb200::kBF16, sb200::kMergedPresum, 256, 1},
     {"blackwell_f16_sw_level2", "f16", 2, sb200::kF16, sb200::kInterleavedLevel2, 256, 0},
     {"blackwell_f32_sw_level2", "f32", 2, sb200::kF32, sb200::kInterleavedLevel2, 256, 0},
     {"blackwell_f16_sw_level2_2sm", "f16", 2, sb200::kF16, sb200::kInterleavedLevel2, 256, 1},
@@ -336,6 +339,9 @@ SB200_DEFINE_RUN(blackwell_f16_sw_fused_presum_2sm)
 SB200_DEFINE_RUN(blackwell_f32_sw_fused_presum_2sm)
 SB200_DEFINE_RUN(blackwell_f16_sw_interleaved_presum_2sm)
 SB200_DEFINE_RUN(blackwell_f32_sw_interleaved_presum_2sm)
+SB200_DEFINE_RUN(blackwell_f16_sw_merged_presum_2sm)
+SB200_DEFINE_RUN(blackwell_f32_sw_merged_presum_2sm)
+SB200_DEFINE_RUN(blackwell_bf16_sw_merged_presum_2sm)
 SB200_DEFINE_RUN(blackwell_f16_sw_level2)
 SB200_DEFINE_RUN(blackwell_f32_sw_level2)
 SB200_DEFINE_RUN(blackwell_f16_sw_level2_2sm)
@@ -396,6 +402,9 @@ static const sb200_kernel_entry kRegistry[] = {
     {"blackwell_f32_sw_fused_presum_2sm", "blackwell", "f32", 1, run_blackwell_f32_sw_fused_presum_2sm},
     {"blackwell_f16_sw_interleaved_presum_2sm", "blackwell", "f16", 1, run_blackwell_f16_sw_interleaved_presum_2sm},
     {"blackwell_f32_sw_interleaved_presum_2sm", "blackwell", "f32", 1, run_blackwell_f32_sw_interleaved_presum_2sm},
+    {"blackwell_f16_sw_merged_presum_2sm", "blackwell", "f16", 1, run_blackwell_f16_sw_merged_presum_2sm},
+    {"blackwell_f32_sw_merged_presum_2sm", "blackwell", "f32", 1, run_blackwell_f32_sw_merged_presum_2sm},
+    {"blackwell_bf16_sw_merged_presum_2sm", "blackwell", "bf16", 1, run_blackwell_bf16_sw_merged_presum_2sm},
     {"blackwell_f16_sw_level2", "blackwell", "f16", 2, run_blackwell_f16_sw_level2},
     {"blackwell_f32_sw_level2", "blackwell", "f32", 2, run_blackwell_f32_sw_level2},
     {"blackwell_f16_sw_level2_2sm", "blackwell", "f16", 2, run_blackwell_f16_sw_level2_2sm},

@@ -81,6 +81,7 @@ struct Layout {
   int region_tiles;  // tiles that follow, each handed out as two K-halves (0: none)
   bool dynamic;      // units are drawn from a counter by whichever pair is free (else dealt round-robin)
   size_t off_split_buf, off_split_flags, split_flag_bytes;
+  size_t off_panel_flags, panel_flag_bytes;  // one-launch plan: chunk counter + per-panel counters, cleared per run
 };
 
 int level_of(Variant v) { return v == kCubic ? 0 : (v == kInterleavedLevel2 ? 2 : 1); }
@@ -100,7 +101,7 @@ void deal_tiles(Layout& L, int tiles, int cap, Variant v, bool no_split, bool pa
   L.whole_tiles = tiles;
   L.region_tiles = 0;
   L.dynamic = pair && tiles > cap;
-  if (v == kFusedPresum || v == kStrassenFused || no_split || L.num_k < 8 || L.dynamic || tiles <= cap) return;
+  if (v == kFusedPresum || v == kStrassenFused || v == kMergedPresum || no_split || L.num_k < 8 || L.dynamic || tiles <= cap) return;
   const int rem = tiles % cap;
   if (rem == 0 || 2 * rem > cap) return;
   L.whole_tiles = tiles - rem;
@@ -144,13 +145,16 @@ Layout make_layout(const GemmArgs& a, int cap_override = 0) {
   L.off_split_flags = off;
   L.split_flag_bytes = size_t(L.region_tiles) * 4 * 8 * sizeof(int);
   off = align_up(off + L.split_flag_bytes, 256);
+  L.off_panel_flags = off;
+  L.panel_flag_bytes = a.variant == kMergedPresum ? align_up(size_t(1 + L.tiles_m + L.tiles_n) * sizeof(int), 256) : 0;
+  off += L.panel_flag_bytes;
   if (L.level == 2) {
     L.off_opa = off;
     off = align_up(off + size_t(4) * (2 * L.mq) * (2 * L.kq) * L.esize, 256);
     L.off_opb = off;
     off = align_up(off + size_t(4) * (2 * L.kq) * (2 * L.nq) * L.esize, 256);
   }
-  if (a.variant == kInterleavedPresum || L.level == 2) {
+  if (a.variant == kInterleavedPresum || a.variant == kMergedPresum || L.level == 2) {
     L.off_pa = off;
     off = align_up(off + size_t(4) * L.mq * L.kq * L.esize, 256);
     L.off_pb = off;
@@ -164,7 +168,9 @@ Layout make_layout(const GemmArgs& a, int cap_override = 0) {
     L.off_ws[i] = off;
     // buffer 0 (M0) is indexed by tile: the second half of every cut tile keeps its hand-off tile in an extra slot
     // behind the grid's; buffers 1..3 are indexed by worker
-    const size_t bytes = i == 0 ? quadrant_bytes + size_t(L.region_tiles) * tile_bytes : size_t(L.workers) * tile_bytes;
+    // (the one-launch plan keeps M0 in a per-worker buffer too and leaves buffer 0 empty)
+    const size_t bytes = i == 0 ? (a.variant == kMergedPresum ? 256 : quadrant_bytes + size_t(L.region_tiles) * tile_bytes)
+                                : size_t(L.workers) * tile_bytes;
     off = align_up(off + bytes, 256);
   }
   if (L.region_tiles) {
@@ -284,6 +290,7 @@ int can_implement(const GemmArgs& a) {
   if (a.scaled && a.beta != 0.0 && (!a.c || (reinterpret_cast<uintptr_t>(a.c) & 15))) return kErrInvalidProblem;
   if (a.bn != 0 && a.bn != 128 && a.bn != 256) return kErrNotSupported;
   if (a.pair && a.bn == 128) return kErrNotSupported;
+  if (a.variant == kMergedPresum && !a.pair) return kErrNotSupported;
   const int es = esize_of(a.dtype);
   const int vec = 16 / es;  // elements per 16 bytes
   const int div = 1 << level_of(a.variant);
@@ -333,7 +340,7 @@ int deal_units(const GemmArgs& a, int sms, int* out, int max_units, int* workers
 }
 
 int launches_per_run(const GemmArgs& a) {
-  return a.variant == kInterleavedLevel2 ? 14 : (a.variant == kInterleavedPresum ? 2 : 1);
+  return a.variant == kInterleavedLevel2 ? 14 : (a.variant == kInterleavedPresum ? 2 : 1);  // one-launch plans: 1
 }
 
 namespace {
@@ -376,6 +383,7 @@ struct LaunchSpec {
   int* split_epoch;          // counter shared by the launches of one run
   unsigned long long wait_ns;  // bound of every device-side wait
   int drop_split_flags;        // test aid, see GemmArgs
+  int* panel_flags;            // one-launch plan: [chunk counter][tiles_m A panels][tiles_n B panels]
 };
 
 // Block (br, bc) of a matrix cut at multiples of (rows, cols): the last block row / column keeps what is left.
@@ -489,7 +497,7 @@ int launch_group(const LaunchSpec& s, cudaStream_t stream, MarkFn mark) {
       p.view[SB200_VIEW_B0 + q] = block_of(s.b, q >> 1, q & 1, s.kq, s.nq, es);
       p.out[q] = s.out ? s.out + ((q >> 1) * s.mq * s.ldo + (q & 1) * s.nq) * es : nullptr;
       p.cin[q] = (s.out && s.cin) ? s.cin + ((q >> 1) * s.mq * s.ldo + (q & 1) * s.nq) * es : nullptr;
-      if (s.variant == kInterleavedPresum) {
+      if (s.variant == kInterleavedPresum || s.variant == kMergedPresum) {
         p.view[SB200_VIEW_PA0 + q] =
             View{s.presum_a + size_t(q) * s.mq * s.kq * es, static_cast<long long>(s.kq), s.mq, s.kq};
         p.view[SB200_VIEW_PB0 + q] =
@@ -547,7 +555,7 @@ int launch_group(const LaunchSpec& s, cudaStream_t stream, MarkFn mark) {
 #ifdef SB200_PROFILE
   apply_tuning_aids(p);
 #endif
-  if (s.variant == kInterleavedPresum) {
+  if (s.variant == kInterleavedPresum || s.variant == kMergedPresum) {
     p.njobs = 2;
     for (int q = 0; q < 4; ++q) {
       p.job[0].src[q] = p.view[SB200_VIEW_A0 + q].ptr;
@@ -574,6 +582,21 @@ int launch_group(const LaunchSpec& s, cudaStream_t stream, MarkFn mark) {
     case kStrassenFused:
       p.prog = programs::level1_strassen();
       rc = launch_any(es, bn_sel, kPresumFeed, p, s.grid, stream);
+      break;
+    case kMergedPresum:
+      // one launch: the presum warps publish the presums panel by panel in the order of the tile raster
+      p.prog = programs::level1_merged();
+      p.split_epoch = ++*s.split_epoch;
+      p.unit_counter = s.dynamic ? s.status + kUnitCounterBase + p.split_epoch : nullptr;
+      p.panels.enabled = 1;
+      p.panels.chunk_k = 512;
+      p.panels.chunks = ceil_div(s.kq, p.panels.chunk_k);
+      p.panels.panel_rows = s.pair ? 256 : 128;
+      p.panels.panel_cols = s.bn;
+      p.panels.next_chunk = s.panel_flags;
+      p.panels.ready_a = s.panel_flags + 1;
+      p.panels.ready_b = s.panel_flags + 1 + s.tiles_m;
+      rc = launch_any(es, bn_sel, kPresumJob, p, s.grid, stream);
       break;
     case kInterleavedPresum: {
       p.prog = s.linked ? programs::level2_launch(s.child, 1) : programs::level1_first();
@@ -608,7 +631,8 @@ int run(const GemmArgs& a, void* workspace, size_t workspace_size, cudaStream_t 
   const int es = L.esize;
 
   int* status = reinterpret_cast<int*>(wsb + L.off_status);
-  cudaError_t ce = cudaMemsetAsync(status, 0, 256 + L.split_flag_bytes, stream);  // status, unit counters, split flags
+  // status, unit counters, split flags, panel counters: adjacent, one memset
+  cudaError_t ce = cudaMemsetAsync(status, 0, 256 + align_up(L.split_flag_bytes, 256) + L.panel_flag_bytes, stream);
   if (ce != cudaSuccess) return static_cast<int>(ce);
 
   int nev = 0;
@@ -640,6 +664,7 @@ int run(const GemmArgs& a, void* workspace, size_t workspace_size, cudaStream_t 
   for (int i = 0; i < 4; ++i) s.ws_inner[i] = reinterpret_cast<float*>(wsb + L.off_ws[i]);
   s.quadrant_floats = L.quadrant_floats;
   s.status = status;
+  s.panel_flags = reinterpret_cast<int*>(wsb + L.off_panel_flags);
   s.wait_ns = a.wait_limit_us > 0 ? 1000ull * static_cast<unsigned long long>(a.wait_limit_us) : 2000000000ull;
   s.drop_split_flags = a.drop_split_flags;
   s.alpha = a.scaled ? static_cast<float>(a.alpha) : 1.f;

@@ -18,6 +18,8 @@ enum Variant {
   kInterleavedPresum = 2, // level 1, two launches, presums materialised by the first launch's presum warps
   kInterleavedLevel2 = 3, // level 2, seven level-1 interleaved groups (14 launches) chained through fp32 buffers
   kStrassenFused = 4,     // level 1 of Strassen's original algorithm, one launch, operand sums formed in shared memory
+  kMergedPresum = 5,      // level 1, ONE launch: presums materialised by the launch's presum warps and published panel
+                          // by panel to the products that read them (CTA-pair kernels only)
 };
 
 // Error codes returned across the C ABI.  Small values keep the meaning of the reference's

@@ -65,6 +65,22 @@ struct PresumSideJob {
 };
 constexpr int SB200_MAX_JOBS = 4;
 
+// One-launch plan: the presum warps publish the presums panel by panel, and the TMA producers wait for the two panels
+// a tile reads before its first product on presum operands.  A panel is the block of rows of the four A-side presums
+// that one tile row reads (or the block of columns of the four B-side presums that one tile column reads); it is
+// produced in `chunks` pieces along K, each by the presum warps of one CTA, drawn from a list that follows the tile
+// raster: the A panels of the first band, every B panel, then the A panels of the other bands.
+struct PresumPanels {
+  int enabled;
+  int chunks;        // pieces per panel; a panel is ready when its counter has reached this
+  int chunk_k;       // extent of a piece along K, in elements
+  int panel_rows;    // rows of an A panel (tile rows of a worker)
+  int panel_cols;    // columns of a B panel
+  int* next_chunk;   // global counter over the chunk list (zero at launch)
+  int* ready_a;      // [tiles_m] pieces finished per A panel (zero at launch)
+  int* ready_b;      // [tiles_n]
+};
+
 struct KernelParams {
   CUtensorMap tmap[SB200_NUM_VIEWS];
   View view[SB200_NUM_VIEWS];
@@ -104,6 +120,7 @@ struct KernelParams {
   int hint_mode;            // measurement aid: L2 cache hints of the operand loads (pairs): tens digit = A, units = B;
                             // 0 none, 1 evict_first, 2 evict_last, 3 evict_normal
 #endif
+  PresumPanels panels;      // mode JOB, one-launch plan only
   // presum jobs (mode JOB), run by the presum warps of the whole grid one after the other
   int njobs;
   PresumSideJob job[SB200_MAX_JOBS];
@@ -341,12 +358,14 @@ __device__ __forceinline__ void build_operand_tile(uint32_t smem_tile, uint32_t 
 // Global presum jobs: every presum thread of the grid takes 16-byte vector positions of a quadrant in a grid-stride
 // loop; per position it reads the four raw quadrant vectors and writes the four combinations of that side.
 // Sums are formed from the raw values left to right in fp32 and rounded once (VecAcc).
+// `presum_rect` does this for the rectangle [row0, row1) x [col0, col1) of the quadrant (columns on 16-byte vectors).
 template <int ESIZE>
-__device__ __forceinline__ void presum_side_job(const PresumSideJob& j, int gtid, int gthreads, bool bf) {
+__device__ __forceinline__ void presum_rect(const PresumSideJob& j, int row0, int row1, int col0, int col1, int gtid,
+                                            int gthreads, bool bf) {
   constexpr int EPV = 16 / ESIZE;
   constexpr int U = 4;  // vector positions per thread per iteration: 16 loads in flight hide the memory latency
-  const int vec_per_row = j.cols / EPV;
-  const long long total = static_cast<long long>(j.rows) * vec_per_row;
+  const int vec_per_row = (col1 - col0) / EPV;
+  const long long total = static_cast<long long>(row1 - row0) * vec_per_row;
   const long long q = static_cast<long long>(j.rows) * j.cols * ESIZE;  // bytes per result matrix
   const char* s0 = static_cast<const char*>(j.src[0]);
   const char* s1 = static_cast<const char*>(j.src[1]);
@@ -361,8 +380,9 @@ __device__ __forceinline__ void presum_side_job(const PresumSideJob& j, int gtid
       const long long v = v0 + static_cast<long long>(u) * gthreads;
       o[u] = -1;
       if (v < total) {
-        const int r = static_cast<int>(v / vec_per_row);
-        const int c = static_cast<int>(v - static_cast<long long>(r) * vec_per_row) * EPV;
+        const int rr = static_cast<int>(v / vec_per_row);
+        const int r = row0 + rr;
+        const int c = col0 + static_cast<int>(v - static_cast<long long>(rr) * vec_per_row) * EPV;
         const long long in = (r * j.ld + c) * ESIZE;
         const bool has_r = r < j.rows2, has_c = c < j.cols2;
         const uint4 zero = make_uint4(0, 0, 0, 0);
@@ -403,6 +423,69 @@ __device__ __forceinline__ void presum_side_job(const PresumSideJob& j, int gtid
         *reinterpret_cast<uint4*>(out + 3 * q + o[u]) = t.pack();
       }
     }
+  }
+}
+
+template <int ESIZE>
+__device__ __forceinline__ void presum_side_job(const PresumSideJob& j, int gtid, int gthreads, bool bf) {
+  presum_rect<ESIZE>(j, 0, j.rows, 0, j.cols, gtid, gthreads, bf);
+}
+
+// One-launch plan: the presum warps of a CTA (PT threads, `ptid` among them) draw chunks until the list is exhausted.
+// `slot` is a word of shared memory for handing the drawn chunk number to the other presum threads; the two named
+// barriers (ids 1 and 2) are used by the presum warps only.
+template <int ESIZE, int PT>
+__device__ __forceinline__ void presum_panels_job(const KernelParams& p, int ptid, volatile int* slot) {
+  const PresumPanels& pp = p.panels;
+  const int band0 = p.band < p.tiles_m ? p.band : p.tiles_m;   // A panels of the first raster band come first
+  const int total = (p.tiles_m + p.tiles_n) * pp.chunks;
+  const PresumSideJob& ja = p.job[0];
+  const PresumSideJob& jb = p.job[1];
+  while (true) {
+    if (ptid == 0) *slot = atomicAdd(pp.next_chunk, 1);
+    asm volatile("bar.sync 1, %0;" ::"r"(PT) : "memory");
+    const int c = *slot;
+    asm volatile("bar.sync 2, %0;" ::"r"(PT) : "memory");
+    if (c >= total) break;
+    int side, panel;
+    const int piece = c % pp.chunks;
+    const int q = c / pp.chunks;
+    if (q < band0) { side = 0; panel = q; }
+    else if (q < band0 + p.tiles_n) { side = 1; panel = q - band0; }
+    else { side = 0; panel = q - p.tiles_n; }
+    const int k0 = piece * pp.chunk_k;
+    if (side == 0) {
+      const int r0 = panel * pp.panel_rows;
+      const int r1 = r0 + pp.panel_rows < ja.rows ? r0 + pp.panel_rows : ja.rows;
+      const int k1 = k0 + pp.chunk_k < ja.cols ? k0 + pp.chunk_k : ja.cols;
+      if (r0 < r1 && k0 < k1) presum_rect<ESIZE>(ja, r0, r1, k0, k1, ptid, PT, p.bf16 != 0);
+    } else {
+      const int c0 = panel * pp.panel_cols;
+      const int c1 = c0 + pp.panel_cols < jb.cols ? c0 + pp.panel_cols : jb.cols;
+      const int k1 = k0 + pp.chunk_k < jb.rows ? k0 + pp.chunk_k : jb.rows;
+      if (c0 < c1 && k0 < k1) presum_rect<ESIZE>(jb, k0, k1, c0, c1, ptid, PT, p.bf16 != 0);
+    }
+    // every thread's stores are made visible device-wide (to TMA readers too), then one thread counts the piece
+    asm volatile("fence.proxy.async;" ::: "memory");
+    __threadfence();
+    asm volatile("bar.sync 1, %0;" ::"r"(PT) : "memory");
+    if (ptid == 0) atomicAdd(side == 0 ? pp.ready_a + panel : pp.ready_b + panel, 1);
+  }
+}
+
+// Bounded wait of a whole warp until the counter at `ctr` has reached `target`.
+__device__ __forceinline__ bool wait_counter(const int* ctr, int target, volatile int* abort_flag, uint64_t limit_ns) {
+  const uint64_t t0 = ptx::globaltimer_ns();
+  uint32_t polls = 0;
+  while (true) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(ctr) : "memory");
+    if (__all_sync(0xffffffffu, v >= target)) return true;
+    if ((++polls & 63u) == 0) {
+      const bool give_up = *abort_flag != 0 || ptx::globaltimer_ns() - t0 > limit_ns;
+      if (__any_sync(0xffffffffu, give_up)) return false;
+    }
+    __nanosleep(100);
   }
 }
 

@@ -165,6 +165,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(sched_empty + kSchedSlots);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
   int* sched_slots = reinterpret_cast<int*>(tmem_holder + 2);
+  volatile int* presum_slot = sched_slots + kSchedSlots;   // chunk number handed around the presum warps
   const uint32_t staging = ptx::smem_u32(bar_base + Cfg::BAR_BYTES);  // epilogue staging rows (epilogue.cuh)
 
   const int warp = threadIdx.x >> 5;
@@ -231,11 +232,26 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
         const TileCoord tile = tile_of(wu.tile, p.tiles_m, p.tiles_n, p.band);
         const int row0 = tile.i * Cfg::PAIR_M + static_cast<int>(rank) * Cfg::BM;
         const int col0 = tile.j * BN + static_cast<int>(rank) * Cfg::BN_CTA;
+        bool panels_seen = !(Cfg::MODE == kPresumJob && p.panels.enabled);
         for (int ps = 0; ok && ps < nproducts; ++ps) {
           const sb200_product_t& pr = p.prog.product[ps];
           const bool a_tma = pr.a.nterms == 1;
           const bool b_tma = pr.b.nterms == 1;
           const uint32_t tx = 2u * ((a_tma ? Cfg::A_BYTES : 0) + (b_tma ? Cfg::B_BYTES : 0));  // both CTAs' bytes
+          if (!panels_seen && ((pr.a.view[0] >= SB200_VIEW_PA0 && pr.a.view[0] < SB200_VIEW_B0) ||
+                               pr.b.view[0] >= SB200_VIEW_PB0)) {
+            // one-launch plan: the first product of a tile that reads presums waits (bounded) until the presum
+            // warps of the grid have published the tile's A panel and B panel; TMA reads them through the async proxy
+            const bool got = wait_counter(p.panels.ready_a + tile.i, p.panels.chunks, abort_flag, p.wait_ns) &&
+                             wait_counter(p.panels.ready_b + tile.j, p.panels.chunks, abort_flag, p.wait_ns);
+            if (!got) {
+              if (lane == 0) raise_abort(p, abort_flag, kStatusPresumTimeout);
+              ok = false;
+              break;
+            }
+            ptx::fence_proxy_async_all();
+            panels_seen = true;
+          }
           const CUtensorMap* ma = &p.tmap[pr.a.view[0]];
           const CUtensorMap* mb = &p.tmap[pr.b.view[0]];
           const bool no_load_all = SB200_DEBUG_BIT(p, 2);
@@ -577,7 +593,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
     } else if (Cfg::MODE == kPresumJob && !SB200_DEBUG_BIT(p, 16)) {  // bit 4: measurement aid, skip the presum job
       const int ptid = threadIdx.x - Cfg::FIRST_PRESUM_WARP * 32;
       constexpr int PT = Cfg::PRESUM_WARPS * 32;
-      presum_job<ESIZE>(p, blockIdx.x * PT + ptid, gridDim.x * PT);
+      if (p.panels.enabled) presum_panels_job<ESIZE, PT>(p, ptid, presum_slot);
+      else presum_job<ESIZE>(p, blockIdx.x * PT + ptid, gridDim.x * PT);
     }
   }
 

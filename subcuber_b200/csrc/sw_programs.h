@@ -44,6 +44,8 @@ inline sb200_program_t level1_strassen() { return get("level1_strassen"); }
 // the two launches of the interleaved-presum plan
 inline sb200_program_t level1_first() { return get("level1_first_early"); }
 inline sb200_program_t level1_second() { return get("level1_second_taps"); }
+// all seven products in one launch, presums read from the workspace as the launch's presum warps publish them
+inline sb200_program_t level1_merged() { return get("level1_merged"); }
 
 // Level 2: the outer recursion step applies the same seven-product scheme to half-size blocks, and each outer product
 // is a level-1 GEMM (two launches) whose epilogue steps also carry the outer postsums through three fp32 chain

@@ -25,6 +25,7 @@ PRESUM_VIEW = {"s1": 4, "s2": 5, "a02": 6, "a1s2": 7, "b10": 12, "b31": 13, "s3"
 P, Q = 0, 1
 WS_M0, WS_M4, WS_U, WS_V = 0, 1, 2, 2  # u is dead once c1 is formed, before v is written: one buffer
 WS_T1, WS_T4 = 1, 2                     # Strassen's original algorithm: taps of m1 and m4 (per-CTA scratch tiles)
+WS_M0_CTA = 3                           # one-launch plan: m0 never leaves the CTA, it lives in a per-CTA scratch tile
 
 
 # ------------------------------------------------------------------------------------------- algebra from the DSL
@@ -179,6 +180,31 @@ def level1_second_taps_program(ms) -> tp.Program:
     b.product("m6", Q)
     b.epilogue([], [WS_V, WS_M4], wait=[], release=[], dst_kind=0, dst=3)            # c3 = v + m4
     b.epilogue([Q], [WS_V], wait=[Q], release=[Q], dst_kind=0, dst=2, signs=[-1])    # c2 = v - m6
+    return b.pg
+
+
+def level1_merged_program(ms) -> tp.Program:
+    """All seven products of a tile in ONE launch with materialised presums (the presum warps of the same launch
+    publish them panel by panel; m0 and m1, which read raw quadrants, come first and cover the start).  Every product
+    goes to the slot the step before last has released, every slot is read by an epilogue step while the other slot's
+    product runs, and with seven products the slot roles swap from tile to tile.  Hand-offs stay in per-CTA scratch
+    tiles: m0, m4, u = m0 + m2, v = u + m3 (over u).  No step reads more than two of them."""
+    b = ProgramBuilder(_products_by_name(ms), fly=False)
+    b.pg.alternate_slots = 1
+    b.product("m0", P).product("m1", Q)
+    b.epilogue([P], [], wait=[P], release=[P], dst_kind=1, dst=WS_M0_CTA)             # m0            (during m1)
+    b.product("m4", P)
+    b.epilogue([Q], [WS_M0_CTA], wait=[Q], release=[Q], dst_kind=0, dst=0)            # c0 = m0 + m1  (during m4)
+    b.product("m2", Q)
+    b.epilogue([P], [], wait=[P], release=[P], dst_kind=1, dst=WS_M4)                 # m4            (during m2)
+    b.product("m5", P)
+    b.epilogue([Q], [WS_M0_CTA], wait=[Q], release=[Q], dst_kind=1, dst=WS_U)         # u = m0 + m2   (during m5)
+    b.product("m3", Q)
+    b.epilogue([P], [WS_U, WS_M4], wait=[P], release=[P], dst_kind=0, dst=1)          # c1 = u + m4 + m5 (during m3)
+    b.product("m6", P)
+    b.epilogue([Q], [WS_U], wait=[Q], release=[Q], dst_kind=1, dst=WS_V)              # v = u + m3    (during m6)
+    b.epilogue([], [WS_V, WS_M4], wait=[], release=[], dst_kind=0, dst=3)             # c3 = v + m4
+    b.epilogue([P], [WS_V], wait=[P], release=[P], dst_kind=0, dst=2, signs=[-1])     # c2 = v - m6   (during next m0)
     return b.pg
 
 
@@ -376,6 +402,7 @@ def all_programs() -> Dict[str, tp.Program]:
         "level1_first_early": level1_first_early_program(ms),
         "level1_second": level1_second_program(ms),
         "level1_second_taps": level1_second_taps_program(ms),
+        "level1_merged": level1_merged_program(ms),
         **{f"level2_{ch['name']}_launch{launch}":
            link_outer(level1_first_program(ms) if launch == 1 else level1_second_taps_program(ms), ch["link"], launch)
            for ch in level2_children(ms) for launch in (1, 2)},
@@ -389,8 +416,8 @@ def verify_programs(programs: Dict[str, tp.Program]) -> None:
     c, _ = strassen_winograd(4, 4, 4)
     want = {q: bilinear_form(part) for q, part in enumerate(c.parts)}
     tp.check_program(programs["level0"], level=0)
-    for name in ("level1_full_fly", "level1_full_ws"):
-        got = tp.check_program(programs[name], level=1)["outputs"]
+    for name in ("level1_full_fly", "level1_full_ws", "level1_merged"):
+        got = tp.check_program(programs[name], level=1, tiles=5)["outputs"]
         for q in range(4):
             assert np.array_equal(got[q], want[q]), (name, q)
     # Strassen's original algorithm: its own postsum expressions must give the same four blocks

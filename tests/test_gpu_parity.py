@@ -15,9 +15,11 @@ import pytest
 pytestmark = pytest.mark.gpu
 
 L1_F16 = ["blackwell_f16_sw_interleaved_presum", "blackwell_f16_sw_fused_presum",
-          "blackwell_f16_sw_interleaved_presum_2sm", "blackwell_f16_sw_fused_presum_2sm"]
+          "blackwell_f16_sw_interleaved_presum_2sm", "blackwell_f16_sw_fused_presum_2sm",
+          "blackwell_f16_sw_merged_presum_2sm"]
 L1_F32 = ["blackwell_f32_sw_interleaved_presum", "blackwell_f32_sw_fused_presum",
-          "blackwell_f32_sw_interleaved_presum_2sm", "blackwell_f32_sw_fused_presum_2sm"]
+          "blackwell_f32_sw_interleaved_presum_2sm", "blackwell_f32_sw_fused_presum_2sm",
+          "blackwell_f32_sw_merged_presum_2sm"]
 L2_F16 = ["blackwell_f16_sw_level2", "blackwell_f16_sw_level2_2sm"]
 L2_F32 = ["blackwell_f32_sw_level2", "blackwell_f32_sw_level2_2sm"]
 # Strassen's original algorithm: the same products of blocks summed another way, checked against the same oracle
@@ -25,7 +27,8 @@ STRASSEN_F16 = ["blackwell_f16_strassen_fused_presum", "blackwell_f16_strassen_f
 STRASSEN_F32 = ["blackwell_f32_strassen_fused_presum", "blackwell_f32_strassen_fused_presum_2sm"]
 # bfloat16 storage: the f16 kernels with the other 16-bit format
 BF16 = ["blackwell_bf16_cubic_128x256", "blackwell_bf16_cubic_2sm_256x256", "blackwell_bf16_sw_fused_presum_2sm",
-        "blackwell_bf16_sw_interleaved_presum", "blackwell_bf16_sw_interleaved_presum_2sm"]
+        "blackwell_bf16_sw_interleaved_presum", "blackwell_bf16_sw_interleaved_presum_2sm",
+        "blackwell_bf16_sw_merged_presum_2sm"]
 L2_BF16 = ["blackwell_bf16_sw_level2", "blackwell_bf16_sw_level2_2sm"]
 L0_F16 = ["blackwell_f16_cubic_128x256", "blackwell_f16_cubic_128x128", "blackwell_f16_cubic_2sm_256x256"]
 L0_F32 = ["blackwell_f32_cubic_128x256", "blackwell_f32_cubic_128x128", "blackwell_f32_cubic_2sm_256x256"]
@@ -346,6 +349,8 @@ SPLIT_CASES = [
     # CTA pairs draw whole tiles (nothing is cut): these check that their drawn order gives the same bits
     ("blackwell_f16_sw_interleaved_presum_2sm", 8, (512, 2560, 2048)),  # quadrant 1 x 5 pair tiles drawn by 4 pairs
     ("blackwell_f16_cubic_2sm_256x256", 16, (1024, 768, 1024)),          # 4 x 3 pair tiles drawn by 8 pairs
+    ("blackwell_f16_sw_merged_presum_2sm", 8, (1536, 2560, 2048)),       # quadrant 3 x 5 pair tiles drawn by 4 pairs
+    ("blackwell_f32_sw_merged_presum_2sm", 0, (4608, 5120, 1024)),       # quadrant 9 x 10 = 90 pair tiles on 74 pairs
     ("blackwell_f16_sw_level2_2sm", 8, (1024, 5120, 4096)),              # every group: 1 x 5 pair tiles drawn by 4 pairs
     # kernel, SMs, shape: the tile count leaves a last wave at most half full, whose tiles are split in two K-halves
     ("blackwell_f16_cubic_128x256", 8, (384, 768, 1024)),              # 3 x 3 = 9 tiles on 8 CTAs
@@ -529,6 +534,7 @@ def test_uniform_inputs_tf32(kernel, dist, oracle, cuda_device):
 # ----------------------------------------------------------------------------------------- full size
 @pytest.mark.parametrize("kernel,size", [("blackwell_f16_sw_interleaved_presum", 8192),
                                          ("blackwell_f16_sw_interleaved_presum_2sm", 8192),
+                                         ("blackwell_f16_sw_merged_presum_2sm", 8192),
                                          ("blackwell_f16_cubic_128x256", 8192),
                                          ("blackwell_f32_sw_interleaved_presum", 4096)])
 def test_full_size_properties(kernel, size, oracle, cuda_device):
