@@ -228,12 +228,16 @@ def main():
     if args.impl == "reference":
         return reference_arm(args)
 
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world > 1:
+        # one hardware work queue per stream of the exchange (the driver reads this when it is initialised)
+        os.environ.setdefault("CUDA_DEVICE_MAX_CONNECTIONS", "32")
+
     import torch
     import torch.distributed as dist
 
     from subcuber_b200 import _lib, inputs, runner
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if world != args.gpus:

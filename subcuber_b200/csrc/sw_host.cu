@@ -593,6 +593,10 @@ int launch_group(const LaunchSpec& s, cudaStream_t stream, MarkFn mark) {
       p.panels.chunks = ceil_div(s.kq, p.panels.chunk_k);
       p.panels.panel_rows = s.pair ? 256 : 128;
       p.panels.panel_cols = s.bn;
+      p.panels.group_cols = s.pair ? ceil_div(s.grid, p.band) : 0;  // s.grid = pairs for the CTA-pair kernels
+#ifdef SB200_PROFILE
+      if (const char* g = getenv("SB200_PANEL_GROUP")) p.panels.group_cols = atoi(g);
+#endif
       p.panels.next_chunk = s.panel_flags;
       p.panels.ready_a = s.panel_flags + 1;
       p.panels.ready_b = s.panel_flags + 1 + s.tiles_m;
@@ -609,6 +613,12 @@ int launch_group(const LaunchSpec& s, cudaStream_t stream, MarkFn mark) {
       p.split_epoch = ++*s.split_epoch;
       p.unit_counter = s.dynamic ? s.status + kUnitCounterBase + p.split_epoch : nullptr;
       p.njobs = 0;
+#ifdef SB200_PROFILE
+      if (getenv("SB200_SECOND_AS_JOB")) {  // measurement aid: the second launch in the 384-thread configuration
+        rc = launch_any(es, bn_sel, kPresumJob, p, s.grid, stream);
+        break;
+      }
+#endif
       rc = launch_any(es, bn_sel, kPresumNone, p, s.grid, stream);
       break;
     }

@@ -76,6 +76,7 @@ struct PresumPanels {
   int chunk_k;       // extent of a piece along K, in elements
   int panel_rows;    // rows of an A panel (tile rows of a worker)
   int panel_cols;    // columns of a B panel
+  int group_cols;    // tile columns in flight at once (workers / band, rounded up): see the producer's wait
   int* next_chunk;   // global counter over the chunk list (zero at launch)
   int* ready_a;      // [tiles_m] pieces finished per A panel (zero at launch)
   int* ready_b;      // [tiles_n]

@@ -241,8 +241,18 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
           if (!panels_seen && ((pr.a.view[0] >= SB200_VIEW_PA0 && pr.a.view[0] < SB200_VIEW_B0) ||
                                pr.b.view[0] >= SB200_VIEW_PB0)) {
             // one-launch plan: the first product of a tile that reads presums waits (bounded) until the presum
-            // warps of the grid have published the tile's A panel and B panel; TMA reads them through the async proxy
-            const bool got = wait_counter(p.panels.ready_a + tile.i, p.panels.chunks, abort_flag, p.wait_ns) &&
+            // warps of the grid have published the tile's A panel and B panel; TMA reads them through the async proxy.
+            // It waits first for the LAST B panel of the group of tile columns that are in flight together: B panels
+            // are published in column order, so without this the tiles of one wave would resume a few microseconds
+            // apart per column and stay apart in K for the rest of the launch (tiles that share an operand panel find
+            // it in L2 only while they read the same K range at the same time).
+            int last_j = tile.j;
+            if (p.panels.group_cols > 0) {
+              last_j = (tile.j / p.panels.group_cols + 1) * p.panels.group_cols - 1;
+              if (last_j >= p.tiles_n) last_j = p.tiles_n - 1;
+            }
+            const bool got = wait_counter(p.panels.ready_b + last_j, p.panels.chunks, abort_flag, p.wait_ns) &&
+                             wait_counter(p.panels.ready_a + tile.i, p.panels.chunks, abort_flag, p.wait_ns) &&
                              wait_counter(p.panels.ready_b + tile.j, p.panels.chunks, abort_flag, p.wait_ns);
             if (!got) {
               if (lane == 0) raise_abort(p, abort_flag, kStatusPresumTimeout);

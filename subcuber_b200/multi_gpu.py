@@ -297,6 +297,11 @@ class GridExchange:
     PIECES = 2                  # every shard travels as this many row blocks on streams of their own: under the GEMM's
                                 # memory load one copy is latency-bound, several copy engines together are not
     NBUF = 3                    # slab buffers per operand: a push has two steps' time to land
+    MAX_COPY_STREAMS = 4        # the copies of a step are dealt over at most this many streams.  A process has a small
+                                # number of hardware work queues (8 unless CUDA_DEVICE_MAX_CONNECTIONS says otherwise);
+                                # with more streams than queues the GEMM's launches share a queue with copies that
+                                # wait for another GPU and start late (measured on 4 and 8 B200s: the first launch of
+                                # a step took 2.6 ms instead of 0.65 with two streams per peer)
 
     @staticmethod
     def reserved_sms() -> int:
@@ -345,7 +350,8 @@ class GridExchange:
             if self.share_b:
                 self.b_own[j].copy_(b_shard)
         self.comm = torch.cuda.Stream(device=device)
-        self.copy_streams = {r: [torch.cuda.Stream(device=device) for _ in range(self.PIECES)] for r in self.peers}
+        n_copies = self.PIECES * (len(self.a_peers) + len(self.b_peers))
+        self.copy_streams = [torch.cuda.Stream(device=device) for _ in range(min(self.MAX_COPY_STREAMS, max(1, n_copies)))]
         self.consumed_local = [torch.cuda.Event() for _ in range(nbuf)]
         self.free_ev = [torch.cuda.Event() for _ in range(nbuf)]
         self.wait_events = []   # (before, after) event pairs around the compute stream's wait for a step's slabs
@@ -402,19 +408,20 @@ class GridExchange:
             self._wait(1, j, s - self.NBUF + 1, self.comm)                # ... and so are the peers' (step s - NBUF)
             free = self.free_ev[j]
             free.record(self.comm)
-            for r in self.peers:
-                for piece, st in enumerate(self.copy_streams[r]):
-                    st.wait_event(free)
-                    with torch.cuda.stream(st):
-                        for dst, rows, shard in ((self.a_dst.get(r), self.a_rows, self.a_own[j]),
-                                                 (self.b_dst.get(r), self.b_rows, self.b_own[j])):
-                            if dst is None:
-                                continue
-                            n_rows = shard.shape[0]
-                            lo = piece * n_rows // self.PIECES
-                            hi = (piece + 1) * n_rows // self.PIECES
-                            dst[j][rows.start + lo:rows.start + hi].copy_(shard[lo:hi], non_blocking=True)
-                    self.comm.wait_stream(st)
+            for st in self.copy_streams:
+                st.wait_event(free)
+            turn = 0
+            for piece in range(self.PIECES):
+                for dsts, rows, shard in ((self.a_dst, self.a_rows, self.a_own[j]), (self.b_dst, self.b_rows, self.b_own[j])):
+                    n_rows = shard.shape[0]
+                    lo = piece * n_rows // self.PIECES
+                    hi = (piece + 1) * n_rows // self.PIECES
+                    for r in sorted(dsts):
+                        with torch.cuda.stream(self.copy_streams[turn % len(self.copy_streams)]):
+                            dsts[r][j][rows.start + lo:rows.start + hi].copy_(shard[lo:hi], non_blocking=True)
+                        turn += 1
+            for st in self.copy_streams:
+                self.comm.wait_stream(st)
             self._signal(0, j, s + 1, self.comm)                          # my pushes for step s have landed everywhere
         self.issued += 1
 
