@@ -177,12 +177,14 @@ size_t sb200_gemm_workspace_bytes_opt(const char* kernel, int m, int n, int k, c
 int sb200_gemm_opt(const char* kernel, const void* a, const void* b, void* d, int m, int n, int k, void* workspace,
                    size_t workspace_bytes, sb200_stream_t stream, const sb200_gemm_options* options);
 /* The unit list of one launch of a tensor-core kernel on a device of `sms` SMs (0 = the current device): whole output
- * tiles in raster order and, for the kernels that deal tiles round-robin, the tiles of a last wave that is at most
- * half full cut into two K-halves that run at the same time (the role the reference gives to split_k_slices,
- * src/cuda/kernel_runner.cpp:244-255); the CTA-pair kernels draw whole tiles as they become free instead.  Writes 8 ints per unit in list order: worker under a round-robin deal, tile,
- * part (0 = whole tile or the half that publishes its partial sum, 1 = the half that adds it), parts (1 or 2), first
- * k-step, end k-step, hand-off slot, split slot.  Returns the number of units (negative: error code); *workers = CTAs
- * or CTA pairs launched.  Host arithmetic only. */
+ * tiles in raster order, then two units for each tile of a last wave that is at most half full - the tile's two
+ * column halves (CTA-pair kernels: independent units, drawn with the whole tiles by whichever pair is free) or its
+ * two K-halves that run at the same time (1-CTA kernels, dealt round-robin; the role the reference gives to
+ * split_k_slices, src/cuda/kernel_runner.cpp:244-255).  Writes 10 ints per unit in list order: worker under a
+ * round-robin deal, tile, part (0 = all of K or the K-half that publishes its partial sum, 1 = the K-half that adds
+ * it), parts (1 or 2), first k-step, end k-step, hand-off slot, split slot, column half (0 or 1), column parts (1 or
+ * 2).  Returns the number of units (negative: error code); *workers = CTAs or CTA pairs launched.  Host arithmetic
+ * only. */
 int sb200_gemm_deal(const char* kernel, int m, int n, int k, const sb200_gemm_options* options, int sms, int* units,
                     int max_units, int* workers);
 /* General form D = alpha * (A * B) + beta * C (the argument set of the reference's operators,

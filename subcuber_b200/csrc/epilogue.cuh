@@ -102,11 +102,11 @@ __device__ __forceinline__ bool epilogue_body(void* const* out, long long ldo, i
                                               float* redirect, const float* late_src, bool skip_body,
                                               WaitFn wait_slots, float alpha = 1.f, float beta = 0.f,
                                               const void* const* cin = nullptr, long long ldc = 0,
-                                              long long* prof = nullptr, bool bf16 = false) {
+                                              long long* prof = nullptr, bool bf16 = false, int nchunk = BN / 32) {
 #ifdef SB200_PROFILE
   if (skip_body) return wait_slots();  // measurement aid
 #endif
-  constexpr int NCHUNK = BN / 32;
+  const int NCHUNK = nchunk;  // 32-column chunks of the unit: BN / 32, or half of that for a column half of a tile
   const int row = quarter * 32 + lane;
   // sources: the step's list (outer sources, which come last, are left to the second half of a split tile), then the
   // late source

@@ -78,7 +78,8 @@ struct Layout {
   // the unit list (WorkUnit in sw_kernel.cuh)
   int workers;       // CTAs (1-CTA kernels) or CTA pairs launched
   int whole_tiles;   // tiles handed out whole
-  int region_tiles;  // tiles that follow, each handed out as two K-halves (0: none)
+  int region_tiles;  // tiles that follow, each handed out as two units (0: none)
+  int region_cols;   // 1: those units are column halves of the tile (CTA pairs), 0: K-halves
   bool dynamic;      // units are drawn from a counter by whichever pair is free (else dealt round-robin)
   size_t off_split_buf, off_split_flags, split_flag_bytes;
   size_t off_panel_flags, panel_flag_bytes;  // one-launch plan: chunk counter + per-panel counters, cleared per run
@@ -89,21 +90,35 @@ int level_of(Variant v) { return v == kCubic ? 0 : (v == kInterleavedLevel2 ? 2 
 int sm_count() { return sm_count_of_current_device(); }
 
 // Builds the unit list for `tiles` output tiles on at most `cap` workers (see WorkUnit in sw_kernel.cuh).
-//   CTA pairs with more tiles than pairs draw whole tiles from a counter as they become free (UnitCursor).
-//   Otherwise tiles are dealt round-robin, and the tiles of a last wave that is at most half full are cut into two
-//   K-halves, so that the wave lasts half as long.
-// Measured on B200 (f16 level 1) and therefore NOT done: cutting the last tiles of the drawn order (-2.5 % at 16384^3,
-// -10 % at 8192^3); cutting every tile when there are fewer than half as many as workers (-6 % at 2048^3, -12 % at
-// 3072^3): a half tile costs a whole tile's epilogue, and the halves' partial sums travel through memory.
-// The fused-presum kernels are never cut, nor are products of fewer than 8 k-steps.
+//   CTA pairs: the tiles of a last wave that is at most half full (all tiles, when there are at most half as many as
+//   pairs) are cut into two column halves, independent units with a whole tile's ratio of MMA work to epilogue
+//   work, so that this wave lasts half as long; with more units than pairs, units are drawn from a counter by
+//   whichever pair is free (UnitCursor).
+//   1-CTA kernels: tiles are dealt round-robin, and the tiles of a last wave that is at most half full are cut into
+//   two K-halves.
+// Measured on B200 (f16 level 1, CTA pairs) and therefore NOT done: K-halves for the last tiles of the drawn order
+// (-2.5 % at 16384^3, -10 % at 8192^3) or for every tile when tiles are few (-6 % at 2048^3, -12 % at 3072^3): a K-half
+// costs a whole tile's epilogue, and the halves' partial sums travel through memory.
+// The fused-presum and one-launch kernels are never cut, nor are products of fewer than 8 k-steps cut along K.
 void deal_tiles(Layout& L, int tiles, int cap, Variant v, bool no_split, bool pair) {
   L.workers = tiles < cap ? tiles : cap;
   L.whole_tiles = tiles;
   L.region_tiles = 0;
+  L.region_cols = 0;
   L.dynamic = pair && tiles > cap;
-  if (v == kFusedPresum || v == kStrassenFused || v == kMergedPresum || no_split || L.num_k < 8 || L.dynamic || tiles <= cap) return;
-  const int rem = tiles % cap;
+  if (v == kFusedPresum || v == kStrassenFused || v == kMergedPresum || no_split) return;
+  const int rem = tiles % cap;  // tiles of the last wave (all of them when they are fewer than the workers)
   if (rem == 0 || 2 * rem > cap) return;
+  if (pair) {
+    L.whole_tiles = tiles - rem;
+    L.region_tiles = rem;
+    L.region_cols = 1;
+    const int units = L.whole_tiles + 2 * rem;
+    L.workers = units < cap ? units : cap;
+    L.dynamic = units > cap;
+    return;
+  }
+  if (L.num_k < 8 || tiles <= cap) return;
   L.whole_tiles = tiles - rem;
   L.region_tiles = rem;
 }
@@ -143,7 +158,8 @@ Layout make_layout(const GemmArgs& a, int cap_override = 0) {
   L.off_status = off;
   off += 256;
   L.off_split_flags = off;
-  L.split_flag_bytes = size_t(L.region_tiles) * 4 * 8 * sizeof(int);
+  const int k_regions = L.region_cols ? 0 : L.region_tiles;  // tiles cut along K: flags, partial sums, extra slots
+  L.split_flag_bytes = size_t(k_regions) * 4 * 8 * sizeof(int);
   off = align_up(off + L.split_flag_bytes, 256);
   L.off_panel_flags = off;
   L.panel_flag_bytes = a.variant == kMergedPresum ? align_up(size_t(1 + L.tiles_m + L.tiles_n) * sizeof(int), 256) : 0;
@@ -169,13 +185,13 @@ Layout make_layout(const GemmArgs& a, int cap_override = 0) {
     // buffer 0 (M0) is indexed by tile: the second half of every cut tile keeps its hand-off tile in an extra slot
     // behind the grid's; buffers 1..3 are indexed by worker
     // (the one-launch plan keeps M0 in a per-worker buffer too and leaves buffer 0 empty)
-    const size_t bytes = i == 0 ? (a.variant == kMergedPresum ? 256 : quadrant_bytes + size_t(L.region_tiles) * tile_bytes)
+    const size_t bytes = i == 0 ? (a.variant == kMergedPresum ? 256 : quadrant_bytes + size_t(k_regions) * tile_bytes)
                                 : size_t(L.workers) * tile_bytes;
     off = align_up(off + bytes, 256);
   }
-  if (L.region_tiles) {
+  if (k_regions) {
     L.off_split_buf = off;
-    off = align_up(off + size_t(L.region_tiles) * 4 * tile_bytes, 256);
+    off = align_up(off + size_t(k_regions) * 4 * tile_bytes, 256);
   }
   if (L.level == 2)
     for (int i = 0; i < 3; ++i) {
@@ -327,14 +343,14 @@ int deal_units(const GemmArgs& a, int sms, int* out, int max_units, int* workers
   KernelParams p;
   memset(&p, 0, sizeof(p));
   p.tiles_m = L.tiles_m; p.tiles_n = L.tiles_n; p.num_k = L.num_k;
-  p.whole_tiles = L.whole_tiles; p.region_tiles = L.region_tiles;
+  p.whole_tiles = L.whole_tiles; p.region_tiles = L.region_tiles; p.region_cols = L.region_cols;
   if (workers) *workers = L.workers;
   const int n = total_units(p);
   for (int u = 0; u < n && u < max_units; ++u) {
     const WorkUnit w = unit_of(p, u);
-    int* o = out + size_t(u) * 8;
+    int* o = out + size_t(u) * 10;
     o[0] = u % L.workers; o[1] = w.tile; o[2] = w.part; o[3] = w.nparts; o[4] = w.k0; o[5] = w.k1; o[6] = w.ws_slot;
-    o[7] = w.split_idx;
+    o[7] = w.split_idx; o[8] = w.col_part; o[9] = w.col_parts;
   }
   return n;
 }
@@ -376,7 +392,7 @@ struct LaunchSpec {
   PresumSideJob more_jobs[2];  // presum jobs of the level above, run by launch 1's presum warps
   int n_more_jobs;
   int* status;
-  int whole_tiles, region_tiles;  // the unit list (Layout)
+  int whole_tiles, region_tiles, region_cols;  // the unit list (Layout)
   int dynamic;                    // CTA pairs draw their units from a counter instead of taking them round-robin
   float* split_buf;
   int* split_flags;
@@ -521,6 +537,10 @@ int launch_group(const LaunchSpec& s, cudaStream_t stream, MarkFn mark) {
     rc = p.b_blocked ? make_tmap_b_blocked(&p.tmap[v], es, p.view[v], 128 / es, b_nblk, b_swz)
                      : make_tmap(&p.tmap[v], es, p.view[v], 128 / es, b_swz);
     if (rc) return rc;
+    if (p.b_blocked && s.pair && s.region_cols) {
+      // a column half loads half as many column blocks of a B tile
+      if ((rc = make_tmap_b_blocked(&p.tmap_half_b[v - 8], es, p.view[v], 128 / es, b_nblk / 2, b_swz))) return rc;
+    }
   }
   p.ldo = s.ldo;
   p.ldc = s.ldo;
@@ -543,6 +563,7 @@ int launch_group(const LaunchSpec& s, cudaStream_t stream, MarkFn mark) {
   p.num_k = s.num_k;
   p.whole_tiles = s.whole_tiles;
   p.region_tiles = s.region_tiles;
+  p.region_cols = s.region_cols;
   p.split_buf = s.split_buf;
   p.split_flags = s.split_flags;
   // Raster band height in tile rows.  Units are handed out band by band, column by column inside a band, so the
@@ -662,8 +683,9 @@ int run(const GemmArgs& a, void* workspace, size_t workspace_size, cudaStream_t 
   s.split_epoch = &epoch;
   s.whole_tiles = L.whole_tiles;
   s.region_tiles = L.region_tiles;
+  s.region_cols = L.region_cols;
   s.dynamic = L.dynamic;
-  if (L.region_tiles) {
+  if (L.region_tiles && !L.region_cols) {
     s.split_buf = reinterpret_cast<float*>(wsb + L.off_split_buf);
     s.split_flags = reinterpret_cast<int*>(wsb + L.off_split_flags);
   }

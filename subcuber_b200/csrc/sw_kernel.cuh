@@ -84,6 +84,9 @@ struct PresumPanels {
 
 struct KernelParams {
   CUtensorMap tmap[SB200_NUM_VIEWS];
+  // CTA-pair kernels whose unit list has column halves, blocked B maps: the B-side views (SB200_VIEW_B0 ...) once
+  // more with half as many column blocks per box, for the loads of a column half
+  CUtensorMap tmap_half_b[SB200_NUM_VIEWS - SB200_VIEW_B0];
   View view[SB200_NUM_VIEWS];
   void* out[4];       // output quadrant base pointers (level 0: out[0] = D)
   long long ldo;      // leading dimension of the output in elements
@@ -101,10 +104,12 @@ struct KernelParams {
   int num_k;                // k-steps per product
   int band;                 // raster band height in tiles
   int b_blocked;            // 1: the B tensor maps are 3-D [128-byte column block][row][block]: one load per B tile
-  // The unit list (see WorkUnit): whole_tiles whole tiles, then the two K-halves of each of the region_tiles tiles
-  // that follow; a first half hands its partial sums over through split_buf and raises split_flags.
+  // The unit list (see WorkUnit): whole_tiles whole tiles, then two units for each of the region_tiles tiles that
+  // follow: its column halves (region_cols = 1) or its K-halves (region_cols = 0; the first half hands its partial
+  // sums over through split_buf and raises split_flags).
   int whole_tiles;
   int region_tiles;
+  int region_cols;
   int* unit_counter;        // CTA-pair kernels: units are drawn from this counter (zero at launch) in list order by
                             // whichever pair is free; null: dealt round-robin
   int split_epoch;          // value a raised flag holds in this launch (flags are zeroed once per run)
@@ -190,7 +195,12 @@ __device__ __forceinline__ TileCoord tile_of(int w, int tiles_m, int tiles_n, in
   return t;
 }
 
-// Work units of the persistent loop.  A unit is one output tile, or one K-half of a tile.  Every postsum is linear in
+// Work units of the persistent loop.  A unit is one output tile, one column half of a tile, or one K-half of a tile.
+// Column halves (CTA-pair kernels): the two halves are independent units that run the tile program on 128 of the
+// tile's 256 columns (MMA N = 128, half the B columns, half the epilogue chunks); a half has a whole unit's ratio of
+// MMA work to epilogue work, and its results are bit-identical to the whole tile's.  The host cuts the tiles of a last
+// wave that is at most half full into column halves, so that this wave lasts half as long.
+// K-halves (1-CTA kernels, tiles dealt round-robin): every postsum is linear in
 // the products, so both halves of a tile run the whole tile program on their K range with private hand-off tiles; at
 // each step that leaves the tile (an output quadrant or a buffer of the level above) the first half (the publisher)
 // writes its partial sum to a split buffer and raises a flag, and the second half (the finisher) waits (bounded) for
@@ -210,6 +220,8 @@ struct WorkUnit {
   int k0, k1;     // k-step range [k0, k1)
   int ws_slot;    // tile slot of this unit in the level-1 hand-off buffers (a finisher uses an extra slot)
   int split_idx;  // slot of the cut tile in the split buffer and the flag array
+  int col_part;   // column half of the tile this unit computes (0 when the tile's columns are not cut)
+  int col_parts;  // 1 = all columns of the tile, 2 = one half
 };
 
 __host__ __device__ __forceinline__ int total_units(const KernelParams& p) { return p.whole_tiles + 2 * p.region_tiles; }
@@ -217,8 +229,14 @@ __host__ __device__ __forceinline__ int total_units(const KernelParams& p) { ret
 // Unit number `u` of the list.
 __host__ __device__ __forceinline__ WorkUnit unit_of(const KernelParams& p, int u) {
   WorkUnit w;
+  w.col_part = 0; w.col_parts = 1;
   if (u < p.whole_tiles) {
     w.tile = u; w.part = 0; w.nparts = 1; w.k0 = 0; w.k1 = p.num_k; w.ws_slot = u; w.split_idx = 0;
+  } else if (p.region_cols) {
+    const int v = u - p.whole_tiles;
+    w.tile = p.whole_tiles + (v >> 1);
+    w.part = 0; w.nparts = 1; w.k0 = 0; w.k1 = p.num_k; w.ws_slot = w.tile; w.split_idx = 0;
+    w.col_part = v & 1; w.col_parts = 2;
   } else {
     const int v = u - p.whole_tiles;
     const int h = p.num_k >> 1;

@@ -231,13 +231,15 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
         const WorkUnit wu = unit_of(p, unit);
         const TileCoord tile = tile_of(wu.tile, p.tiles_m, p.tiles_n, p.band);
         const int row0 = tile.i * Cfg::PAIR_M + static_cast<int>(rank) * Cfg::BM;
-        const int col0 = tile.j * BN + static_cast<int>(rank) * Cfg::BN_CTA;
+        // a column half of a tile: each CTA brings 64 of the half's 128 columns (half the column blocks of a B tile)
+        const int col0 = tile.j * BN + wu.col_part * (BN / 2) + static_cast<int>(rank) * (Cfg::BN_CTA / wu.col_parts);
         bool panels_seen = !(Cfg::MODE == kPresumJob && p.panels.enabled);
         for (int ps = 0; ok && ps < nproducts; ++ps) {
           const sb200_product_t& pr = p.prog.product[ps];
           const bool a_tma = pr.a.nterms == 1;
           const bool b_tma = pr.b.nterms == 1;
-          const uint32_t tx = 2u * ((a_tma ? Cfg::A_BYTES : 0) + (b_tma ? Cfg::B_BYTES : 0));  // both CTAs' bytes
+          const int nblk = Cfg::NBLK / wu.col_parts;  // column blocks of B this CTA loads per k-step
+          const uint32_t tx = 2u * ((a_tma ? Cfg::A_BYTES : 0) + (b_tma ? nblk * Cfg::BLK_BYTES : 0));  // both CTAs' bytes
           if (!panels_seen && ((pr.a.view[0] >= SB200_VIEW_PA0 && pr.a.view[0] < SB200_VIEW_B0) ||
                                pr.b.view[0] >= SB200_VIEW_PB0)) {
             // one-launch plan: the first product of a tile that reads presums waits (bounded) until the presum
@@ -263,7 +265,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
             panels_seen = true;
           }
           const CUtensorMap* ma = &p.tmap[pr.a.view[0]];
-          const CUtensorMap* mb = &p.tmap[pr.b.view[0]];
+          const CUtensorMap* mb = (wu.col_parts == 2 && p.b_blocked) ? &p.tmap_half_b[pr.b.view[0] - SB200_VIEW_B0]
+                                                                     : &p.tmap[pr.b.view[0]];
           const bool no_load_all = SB200_DEBUG_BIT(p, 2);
           for (int kk = wu.k0; kk < wu.k1; ++kk) {
             const bool mine = (turn == my_turn);
@@ -320,7 +323,8 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
                 } else {
 #pragma unroll
                   for (int nb = 0; nb < Cfg::NBLK; ++nb)
-                    ptx::tma_load_2d_pair(sb + nb * Cfg::BLK_BYTES, mb, &full_bar[stage], col0 + nb * BK, kk * BK);
+                    if (nb < nblk)
+                      ptx::tma_load_2d_pair(sb + nb * Cfg::BLK_BYTES, mb, &full_bar[stage], col0 + nb * BK, kk * BK);
                 }
               }
               }
@@ -387,7 +391,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
             free_bits ^= (1u << slot);
             ptx::tc_fence_after_sync();
           }
-          const uint32_t idesc = ptx::umma_idesc((ESIZE == 2 && p.bf16) ? 1u : Cfg::FMT, Cfg::PAIR_M, BN, pr.negate != 0);
+          const uint32_t idesc = ptx::umma_idesc((ESIZE == 2 && p.bf16) ? 1u : Cfg::FMT, Cfg::PAIR_M, BN / wu.col_parts, pr.negate != 0);
           const uint32_t tmem_d = tmem_base + slot * BN;
           const bool skip_mma = SB200_DEBUG_BIT(p, 1);
           // descriptors differ between stages and k-substeps only in the start-address field (low word, 16-byte units)
@@ -521,8 +525,10 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
           ptx::tc_fence_after_sync();
           return true;
         };
-        const long long tile_off = (static_cast<long long>(wu.ws_slot) * 2 + rank) * (128 * BN);
-        const long long outer_off = (static_cast<long long>(wu.tile) * 2 + rank) * (128 * BN);
+        // hand-off tiles are [32-column chunk][float4 index][128 rows][4]: a column half uses its half of the chunks
+        const long long half_off = static_cast<long long>(wu.col_part) * (128 * BN / 2);
+        const long long tile_off = (static_cast<long long>(wu.ws_slot) * 2 + rank) * (128 * BN) + half_off;
+        const long long outer_off = (static_cast<long long>(wu.tile) * 2 + rank) * (128 * BN) + half_off;
 #ifdef SB200_PROFILE_EPILOGUE
         const long long te0 = SB200_CLOCK();
         const long long ew0 = ew_full;
@@ -530,13 +536,14 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1) sw_tile_program_pair_kernel(c
         ok = epilogue_body<ESIZE, BN, Cfg::NSRC_MAX, Cfg::NSLOT_MAX, Cfg::SCALED>(p.out, p.ldo, (ep.dst & 2) ? p.out_rows2 : p.out_rows,
                                                      (ep.dst & 1) ? p.out_cols2 : p.out_cols, p.ws, ep, sx, tmem_base, quarter,
                                                      lane, tile_off, static_cast<long long>(blockIdx.x) * (128 * BN), outer_off,
-                                                     tile.i * Cfg::PAIR_M + static_cast<int>(rank) * Cfg::BM, tile.j * BN,
+                                                     tile.i * Cfg::PAIR_M + static_cast<int>(rank) * Cfg::BM,
+                                                     tile.j * BN + wu.col_part * (BN / 2),
                                                      staging + (warp - 2) * kStagingWarpBytes,
                                                      sp.redirect ? split_tile_buf : nullptr,
                                                      sp.add_partial ? split_tile_buf : nullptr,
                                                      SB200_DEBUG_BIT(p, 32), wait_slots, p.alpha, p.beta, p.cin, p.ldc,
                                                      (SB200_PROF_PTR(p) && blockIdx.x == 0 && warp == 2) ? SB200_PROF_PTR(p) + 1190 : nullptr,
-                                                     ESIZE == 2 && p.bf16 != 0);
+                                                     ESIZE == 2 && p.bf16 != 0, (BN / 32) / wu.col_parts);
         if (!ok) break;
 #ifdef SB200_PROFILE_EPILOGUE
         if (p.prof && blockIdx.x == 0 && warp == 2 && lane == 0 && es < 16) {
