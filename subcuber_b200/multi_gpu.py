@@ -290,7 +290,8 @@ class GridExchange:
       consumed[j][r]  raised by rank r behind its GEMM that read its buffer j; my pushes for step s into r's buffer
                       wait for s - 2 (the GEMM of step s - 3 is over)
     The pushes for steps s + 1 and s + 2 are in flight while step s computes.  The caller leaves `reserved_sms()` SMs
-    out of the GEMM grid for the one-block flag kernels that run beside it.
+    out of the GEMM grid for the one-block flag kernels that run beside it; those run on streams of their own and
+    meet the compute stream through events, so the GEMM launches of consecutive steps follow one another directly.
     """
 
     WAIT_LIMIT_US = 5_000_000   # bound of every flag wait (first steps include lazy set-up on the peers)
@@ -350,6 +351,10 @@ class GridExchange:
             if self.share_b:
                 self.b_own[j].copy_(b_shard)
         self.comm = torch.cuda.Stream(device=device)
+        # the flag kernels of the compute side run on streams of their own, tied to the compute stream by events, so
+        # that the GEMM launches of consecutive steps follow one another without a flag kernel in between
+        self.arrivals = torch.cuda.Stream(device=device)   # waits for the slabs of step s, one step after the other
+        self.releases = torch.cuda.Stream(device=device)   # tells the peers that a buffer has been read
         n_copies = self.PIECES * (len(self.a_peers) + len(self.b_peers))
         self.copy_streams = [torch.cuda.Stream(device=device) for _ in range(min(self.MAX_COPY_STREAMS, max(1, n_copies)))]
         self.consumed_local = [torch.cuda.Event() for _ in range(nbuf)]
@@ -436,7 +441,10 @@ class GridExchange:
         after = torch.cuda.Event(enable_timing=True)
         before.record(cur)
         with torch.cuda.device(self.device):
-            self._wait(0, j, s + 1, cur)
+            self._wait(0, j, s + 1, self.arrivals)
+            arrived = torch.cuda.Event()
+            arrived.record(self.arrivals)
+            cur.wait_event(arrived)
         after.record(cur)
         self.wait_events.append((before, after))
         self.taken += 1
@@ -450,7 +458,8 @@ class GridExchange:
         cur = torch.cuda.current_stream(self.device)
         self.consumed_local[j].record(cur)
         with torch.cuda.device(self.device):
-            self._signal(1, j, s + 1, cur)
+            self.releases.wait_event(self.consumed_local[j])
+            self._signal(1, j, s + 1, self.releases)
 
     def last(self):
         return self._last
