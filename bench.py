@@ -222,6 +222,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-sustained", action="store_true", help="skip the two-second loops")
     ap.add_argument("--no-cublas", action="store_true", help="skip the cuBLAS comparison")
+    ap.add_argument("--copy-streams", type=int, default=0, help="N > 1: streams the exchange deals its copies over (0 = its default)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -283,7 +284,7 @@ def main():
         # symmetric memory needs peer mappings between all GPUs: where they cannot be set up every rank falls back to
         # all-gathers in the grid's groups (the ranks agree first, so that none is left alone in a collective)
         try:
-            exchange = multi_gpu.GridExchange(gp, rank, dtn, device, seed=1)
+            exchange = multi_gpu.GridExchange(gp, rank, dtn, device, seed=1, max_copy_streams=args.copy_streams)
             ok = 1
         except Exception as exc:  # noqa: BLE001 - any set-up failure means "use the other exchange"
             print(f"[bench] rank {rank}: peer exchange unavailable ({exc}); using collectives", file=sys.stderr)

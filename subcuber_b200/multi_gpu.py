@@ -308,7 +308,7 @@ class GridExchange:
     def reserved_sms() -> int:
         return 2
 
-    def __init__(self, gp: GridPlan, rank: int, dtype: str, device, seed: int = 1):
+    def __init__(self, gp: GridPlan, rank: int, dtype: str, device, seed: int = 1, max_copy_streams: int = 0):
         import ctypes as C
 
         import torch.distributed._symmetric_memory as symm_mem
@@ -356,7 +356,8 @@ class GridExchange:
         self.arrivals = torch.cuda.Stream(device=device)   # waits for the slabs of step s, one step after the other
         self.releases = torch.cuda.Stream(device=device)   # tells the peers that a buffer has been read
         n_copies = self.PIECES * (len(self.a_peers) + len(self.b_peers))
-        self.copy_streams = [torch.cuda.Stream(device=device) for _ in range(min(self.MAX_COPY_STREAMS, max(1, n_copies)))]
+        limit = max_copy_streams if max_copy_streams > 0 else self.MAX_COPY_STREAMS
+        self.copy_streams = [torch.cuda.Stream(device=device) for _ in range(min(limit, max(1, n_copies)))]
         self.consumed_local = [torch.cuda.Event() for _ in range(nbuf)]
         self.free_ev = [torch.cuda.Event() for _ in range(nbuf)]
         self.wait_events = []   # (before, after) event pairs around the compute stream's wait for a step's slabs
