@@ -112,6 +112,9 @@ SB200_DECLARE_RUN(run_blackwell_f16_strassen_fused_presum);
 SB200_DECLARE_RUN(run_blackwell_f32_strassen_fused_presum);
 SB200_DECLARE_RUN(run_blackwell_f16_strassen_fused_presum_2sm);
 SB200_DECLARE_RUN(run_blackwell_f32_strassen_fused_presum_2sm);
+/* the same algorithm on materialised presums (a launch without products forms them, a second launch multiplies) */
+SB200_DECLARE_RUN(run_blackwell_f16_strassen_presum_2sm);
+SB200_DECLARE_RUN(run_blackwell_f32_strassen_presum_2sm);
 /* fp64 on the double-precision tensor-core instruction (mma.sync.m16n8k16.f64): plain GEMM, level 1 (2 standalone
  * presum launches + 7 product launches whose epilogue adds the postsums) and level 2 (2 + 7 x 9 launches).  Stand where the reference has its f64 DMMA kernels
  * (src/cuda/kernels/ampere_f64_*.cu via kernel_runner.cpp:99-180). */

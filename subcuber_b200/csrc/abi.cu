@@ -58,6 +58,8 @@ const KernelDesc kDescs[] = {
     {"blackwell_f32_strassen_fused_presum", "f32", 1, sb200::kF32, sb200::kStrassenFused, 256, 0},
     {"blackwell_f16_strassen_fused_presum_2sm", "f16", 1, sb200::kF16, sb200::kStrassenFused, 256, 1},
     {"blackwell_f32_strassen_fused_presum_2sm", "f32", 1, sb200::kF32, sb200::kStrassenFused, 256, 1},
+    {"blackwell_f16_strassen_presum_2sm", "f16", 1, sb200::kF16, sb200::kStrassenPresum, 256, 1},
+    {"blackwell_f32_strassen_presum_2sm", "f32", 1, sb200::kF32, sb200::kStrassenPresum, 256, 1},
     {"blackwell_f64_cubic_dmma", "f64", 0, sb200::kF64, sb200::kCubic, 0, 0},
     {"blackwell_f64_sw_level1", "f64", 1, sb200::kF64, sb200::kFusedPresum, 0, 0},
     {"blackwell_f64_sw_level2", "f64", 2, sb200::kF64, sb200::kInterleavedLevel2, 0, 0},
@@ -358,6 +360,8 @@ SB200_DEFINE_RUN(blackwell_f16_strassen_fused_presum)
 SB200_DEFINE_RUN(blackwell_f32_strassen_fused_presum)
 SB200_DEFINE_RUN(blackwell_f16_strassen_fused_presum_2sm)
 SB200_DEFINE_RUN(blackwell_f32_strassen_fused_presum_2sm)
+SB200_DEFINE_RUN(blackwell_f16_strassen_presum_2sm)
+SB200_DEFINE_RUN(blackwell_f32_strassen_presum_2sm)
 SB200_DEFINE_RUN(blackwell_f64_cubic_dmma)
 SB200_DEFINE_RUN(blackwell_f64_sw_level1)
 SB200_DEFINE_RUN(blackwell_f64_sw_level2)
@@ -420,6 +424,8 @@ static const sb200_kernel_entry kRegistry[] = {
     {"blackwell_f32_strassen_fused_presum", "blackwell", "f32", 1, run_blackwell_f32_strassen_fused_presum},
     {"blackwell_f16_strassen_fused_presum_2sm", "blackwell", "f16", 1, run_blackwell_f16_strassen_fused_presum_2sm},
     {"blackwell_f32_strassen_fused_presum_2sm", "blackwell", "f32", 1, run_blackwell_f32_strassen_fused_presum_2sm},
+    {"blackwell_f16_strassen_presum_2sm", "blackwell", "f16", 1, run_blackwell_f16_strassen_presum_2sm},
+    {"blackwell_f32_strassen_presum_2sm", "blackwell", "f32", 1, run_blackwell_f32_strassen_presum_2sm},
     {"blackwell_f64_cubic_dmma", "blackwell", "f64", 0, run_blackwell_f64_cubic_dmma},
     {"blackwell_f64_sw_level1", "blackwell", "f64", 1, run_blackwell_f64_sw_level1},
     {"blackwell_f64_sw_level2", "blackwell", "f64", 2, run_blackwell_f64_sw_level2},

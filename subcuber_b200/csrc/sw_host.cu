@@ -77,6 +77,7 @@ struct Layout {
   size_t off_opa, off_opb, off_x[3], quadrant_floats;
   // the unit list (WorkUnit in sw_kernel.cuh)
   int workers;       // CTAs (1-CTA kernels) or CTA pairs launched
+  int cap;           // most workers a launch may have (SMs, or pairs of SMs, left to this call)
   int whole_tiles;   // tiles handed out whole
   int region_tiles;  // tiles that follow, each handed out as two units (0: none)
   int region_cols;   // 1: those units are column halves of the tile (CTA pairs), 0: K-halves
@@ -148,6 +149,7 @@ Layout make_layout(const GemmArgs& a, int cap_override = 0) {
 #ifdef SB200_PROFILE
   if (getenv("SB200_NO_SPLIT")) no_split = true;  // measurement aid of profile builds
 #endif
+  L.cap = cap;
   deal_tiles(L, L.tiles_m * L.tiles_n, cap, a.variant, no_split, a.pair != 0);
 #ifdef SB200_PROFILE
   if (const char* sc = getenv("SB200_SCHED"))  // measurement aid: 0 = round-robin deal
@@ -170,13 +172,15 @@ Layout make_layout(const GemmArgs& a, int cap_override = 0) {
     L.off_opb = off;
     off = align_up(off + size_t(4) * (2 * L.kq) * (2 * L.nq) * L.esize, 256);
   }
-  if (a.variant == kInterleavedPresum || a.variant == kMergedPresum || L.level == 2) {
+  if (a.variant == kInterleavedPresum || a.variant == kMergedPresum || a.variant == kStrassenPresum || L.level == 2) {
+    const size_t npre = a.variant == kStrassenPresum ? programs::kStrassenPresumsPerSide : 4;  // presums per side
     L.off_pa = off;
-    off = align_up(off + size_t(4) * L.mq * L.kq * L.esize, 256);
+    off = align_up(off + npre * L.mq * L.kq * L.esize, 256);
     L.off_pb = off;
-    off = align_up(off + size_t(4) * L.kq * L.nq * L.esize, 256);
+    off = align_up(off + npre * L.kq * L.nq * L.esize, 256);
   }
-  const int nws = a.variant == kCubic ? 0 : (a.variant == kFusedPresum ? 2 : (a.variant == kStrassenFused ? 3 : 4));
+  const bool strassen = a.variant == kStrassenFused || a.variant == kStrassenPresum;
+  const int nws = a.variant == kCubic ? 0 : (a.variant == kFusedPresum ? 2 : (strassen ? 3 : 4));
   const size_t tile_bytes = size_t(128) * L.bn * sizeof(float) * (a.pair ? 2 : 1);  // per tile of the grid
   const size_t quadrant_bytes = size_t(L.tiles_m) * L.tiles_n * tile_bytes;
   L.quadrant_floats = quadrant_bytes / sizeof(float);
@@ -306,7 +310,7 @@ int can_implement(const GemmArgs& a) {
   if (a.scaled && a.beta != 0.0 && (!a.c || (reinterpret_cast<uintptr_t>(a.c) & 15))) return kErrInvalidProblem;
   if (a.bn != 0 && a.bn != 128 && a.bn != 256) return kErrNotSupported;
   if (a.pair && a.bn == 128) return kErrNotSupported;
-  if (a.variant == kMergedPresum && !a.pair) return kErrNotSupported;
+  if ((a.variant == kMergedPresum || a.variant == kStrassenPresum) && !a.pair) return kErrNotSupported;
   const int es = esize_of(a.dtype);
   const int vec = 16 / es;  // elements per 16 bytes
   const int div = 1 << level_of(a.variant);
@@ -356,7 +360,8 @@ int deal_units(const GemmArgs& a, int sms, int* out, int max_units, int* workers
 }
 
 int launches_per_run(const GemmArgs& a) {
-  return a.variant == kInterleavedLevel2 ? 14 : (a.variant == kInterleavedPresum ? 2 : 1);  // one-launch plans: 1
+  if (a.variant == kInterleavedLevel2) return 14;
+  return (a.variant == kInterleavedPresum || a.variant == kStrassenPresum) ? 2 : 1;  // one-launch plans: 1
 }
 
 namespace {
@@ -370,6 +375,7 @@ constexpr int kUnitCounterBase = 8;
 struct LaunchSpec {
   Variant variant;
   int es, bn, pair, grid;
+  int cap;                   // most workers a launch may have (a launch without products uses them all)
   int bf16;                  // 16-bit operands are bfloat16
   View a, b;                 // whole operands of this group (extents up to twice the block extents)
   int mq, nq, kq;            // extents of one block (level 0: of the whole problem)
@@ -524,6 +530,15 @@ int launch_group(const LaunchSpec& s, cudaStream_t stream, MarkFn mark) {
       }
     }
   }
+  if (s.variant == kStrassenPresum) {
+    // the ten presums of Strassen's original algorithm, read through the view slots the generated table names
+    for (int r = 0; r < programs::kStrassenPresumsPerSide; ++r) {
+      p.view[programs::strassen_presums(0)[r].view] =
+          View{s.presum_a + size_t(r) * s.mq * s.kq * es, static_cast<long long>(s.kq), s.mq, s.kq};
+      p.view[programs::strassen_presums(1)[r].view] =
+          View{s.presum_b + size_t(r) * s.kq * s.nq * es, static_cast<long long>(s.nq), s.kq, s.nq};
+    }
+  }
   for (int v = 0; v < 8; ++v)
     if ((rc = make_tmap(&p.tmap[v], es, p.view[v], 128, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
   // B tiles of 32-bit elements are deposited with 32-byte swizzle atoms (see KernelConfig::B_SWZ32)
@@ -588,6 +603,24 @@ int launch_group(const LaunchSpec& s, cudaStream_t stream, MarkFn mark) {
     p.job[1].rows2 = s.b.rows - s.kq; p.job[1].cols2 = s.b.cols - s.nq;
     for (int j = 0; j < s.n_more_jobs; ++j) p.job[p.njobs++] = s.more_jobs[j];
   }
+  if (s.variant == kStrassenPresum) {
+    // two table-driven presum jobs over the raw quadrants (view slots 1 and 9 hold presums in this plan)
+    p.njobs = 2;
+    for (int side = 0; side < 2; ++side) {
+      PresumSideJob& j = p.job[side];
+      const View& whole = side == 0 ? s.a : s.b;
+      const int rows = side == 0 ? s.mq : s.kq, cols = side == 0 ? s.kq : s.nq;
+      for (int q = 0; q < 4; ++q) j.src[q] = block_of(whole, q >> 1, q & 1, rows, cols, es).ptr;
+      j.ld = whole.ld; j.dst = side == 0 ? s.presum_a : s.presum_b; j.rows = rows; j.cols = cols; j.side = side;
+      j.rows2 = whole.rows - rows; j.cols2 = whole.cols - cols;
+      j.npairs = programs::kStrassenPresumsPerSide;
+      for (int r = 0; r < j.npairs; ++r) {
+        const programs::PresumPair& pp = programs::strassen_presums(side)[r];
+        j.pair_q[r][0] = static_cast<signed char>(pp.q0); j.pair_c[r][0] = static_cast<signed char>(pp.c0);
+        j.pair_q[r][1] = static_cast<signed char>(pp.q1); j.pair_c[r][1] = static_cast<signed char>(pp.c1);
+      }
+    }
+  }
   const int bn_sel = s.pair ? -1 : s.bn;  // -1 routes launch_any to the CTA-pair kernels (grid = pairs)
   switch (s.variant) {
     case kCubic:
@@ -604,6 +637,29 @@ int launch_group(const LaunchSpec& s, cudaStream_t stream, MarkFn mark) {
       p.prog = programs::level1_strassen();
       rc = launch_any(es, bn_sel, kPresumFeed, p, s.grid, stream);
       break;
+    case kStrassenPresum: {
+      // launch 1: no products, the presum warps of every worker materialise the ten presums; launch 2: the products
+      const sb200_program_t products = programs::level1_strassen_presum();
+      const int whole = p.whole_tiles, region = p.region_tiles;
+      memset(&p.prog, 0, sizeof(p.prog));
+      p.whole_tiles = 0;
+      p.region_tiles = 0;
+      p.unit_counter = nullptr;
+      p.split_epoch = ++*s.split_epoch;
+      rc = launch_any(es, bn_sel, kPresumJob, p, s.cap, stream);
+      if (rc) return rc;
+      if ((rc = mark())) return rc;
+      p.prog = products;
+      p.whole_tiles = whole;
+      p.region_tiles = region;
+      p.njobs = 0;
+      p.split_epoch = ++*s.split_epoch;
+      p.unit_counter = s.dynamic ? s.status + kUnitCounterBase + p.split_epoch : nullptr;
+      // this program's epilogue steps sum two TMEM slots: of the kernels that read operands by TMA only, the
+      // configuration with presum warps is the one compiled for that (its presum warps find no job here)
+      rc = launch_any(es, bn_sel, kPresumJob, p, s.grid, stream);
+      break;
+    }
     case kMergedPresum:
       // one launch: the presum warps publish the presums panel by panel in the order of the tile raster
       p.prog = programs::level1_merged();
@@ -679,6 +735,7 @@ int run(const GemmArgs& a, void* workspace, size_t workspace_size, cudaStream_t 
   s.bn = L.bn;
   s.pair = a.pair;
   s.grid = L.workers;
+  s.cap = L.cap;
   int epoch = 0;
   s.split_epoch = &epoch;
   s.whole_tiles = L.whole_tiles;

@@ -20,6 +20,8 @@ enum Variant {
   kStrassenFused = 4,     // level 1 of Strassen's original algorithm, one launch, operand sums formed in shared memory
   kMergedPresum = 5,      // level 1, ONE launch: presums materialised by the launch's presum warps and published panel
                           // by panel to the products that read them (CTA-pair kernels only)
+  kStrassenPresum = 6,    // level 1 of Strassen's original algorithm, two launches: its ten presums materialised by
+                          // the presum warps of a launch without products, then all seven products (CTA pairs only)
 };
 
 // Error codes returned across the C ABI.  Small values keep the meaning of the reference's

@@ -54,14 +54,21 @@ struct View {
 
 // One presum job: the four combinations of one operand's quadrants, written as four packed matrices.
 //   side 0 (A): S1, S2, A02, A1S2      side 1 (B): B10, B31, S3, S3B2
+//   npairs > 0: instead, `npairs` two-term combinations given by table, result r = c0 * quadrant q0 + c1 * quadrant q1
+//               with pair_q[r] = {q0, q1}, pair_c[r] = {c0, c1} (coefficients +1 or -1): the presums of algorithms
+//               whose operand sums have two terms (Strassen's original algorithm)
+constexpr int SB200_MAX_PRESUM_PAIRS = 6;
 struct PresumSideJob {
   const void* src[4];  // quadrant base pointers, row-major with a common leading dimension
   long long ld;        // in elements
-  void* dst;           // [4][rows][cols], packed
+  void* dst;           // [4 or npairs][rows][cols], packed
   int rows, cols;      // extent of one quadrant (and of each result)
   int rows2, cols2;    // rows present in quadrants 2, 3 and columns present in quadrants 1, 3 (<= rows, cols): an
                        // operand whose extents are not twice the block extents reads as if padded with zeros
   int side;
+  int npairs;
+  signed char pair_q[SB200_MAX_PRESUM_PAIRS][2];
+  signed char pair_c[SB200_MAX_PRESUM_PAIRS][2];
 };
 constexpr int SB200_MAX_JOBS = 4;
 
@@ -415,7 +422,18 @@ __device__ __forceinline__ void presum_rect(const PresumSideJob& j, int row0, in
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       if (o[u] < 0) continue;
-      if (j.side == 0) {
+      if (j.npairs > 0) {
+        // table-driven two-term presums: fp32 sum of the raw values, one rounding
+        for (int r = 0; r < j.npairs; ++r) {
+          const int q0 = j.pair_q[r][0], q1 = j.pair_q[r][1];
+          const uint4 y0 = q0 == 0 ? x0[u] : (q0 == 1 ? x1[u] : (q0 == 2 ? x2[u] : x3[u]));
+          const uint4 y1 = q1 == 0 ? x0[u] : (q1 == 1 ? x1[u] : (q1 == 2 ? x2[u] : x3[u]));
+          VecAcc<ESIZE> s(bf);
+          s.set(y0, j.pair_c[r][0]);
+          s.add(y1, j.pair_c[r][1]);
+          *reinterpret_cast<uint4*>(out + r * q + o[u]) = s.pack();
+        }
+      } else if (j.side == 0) {
         // A side: S1 = A2 + A3, S2 = S1 - A0, A02 = A0 - A2, A1S2 = A1 - S2
         VecAcc<ESIZE> s(bf);
         s.set(x2[u], 1); s.add(x3[u], 1);                             // S1

@@ -41,6 +41,12 @@ inline sb200_program_t level0() { return get("level0"); }
 // all seven products of a tile in one launch, operand sums formed in shared memory
 inline sb200_program_t level1_fused() { return get("level1_full_fly"); }
 inline sb200_program_t level1_strassen() { return get("level1_strassen"); }
+// Strassen's original algorithm on materialised presums: the program, and the ten presums (five per side) with the
+// view slots they are read through
+inline sb200_program_t level1_strassen_presum() { return get("level1_strassen_presum"); }
+typedef sb200_presum_pair PresumPair;
+constexpr int kStrassenPresumsPerSide = 5;
+inline const PresumPair* strassen_presums(int side) { return sb200_strassen_presums[side]; }
 // the two launches of the interleaved-presum plan
 inline sb200_program_t level1_first() { return get("level1_first_early"); }
 inline sb200_program_t level1_second() { return get("level1_second_taps"); }

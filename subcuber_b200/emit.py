@@ -22,6 +22,11 @@ from .dsl import BinOp, Matrix, expand_terms
 # operand view indices (csrc/tile_program.h)
 QUADRANT_VIEW = {"a0": 0, "a1": 1, "a2": 2, "a3": 3, "b0": 8, "b1": 9, "b2": 10, "b3": 11}
 PRESUM_VIEW = {"s1": 4, "s2": 5, "a02": 6, "a1s2": 7, "b10": 12, "b31": 13, "s3": 14, "s3b2": 15}
+# Strassen's original algorithm with materialised presums: ten two-term presums, five per side.  Four use the presum
+# view slots of their side; the fifth takes the slot of a raw quadrant that no product of the algorithm reads alone
+# (a1 and b1).  The order of a side's list is the order of the presum workspace.
+STRASSEN_PRESUM_VIEW = {"a03": 4, "a23": 5, "a01": 6, "a20": 7, "a13": 1,
+                        "b03": 12, "b13": 13, "b20": 14, "b01": 15, "b23": 9}
 P, Q = 0, 1
 WS_M0, WS_M4, WS_U, WS_V = 0, 1, 2, 2  # u is dead once c1 is formed, before v is written: one buffer
 WS_T1, WS_T4 = 1, 2                     # Strassen's original algorithm: taps of m1 and m4 (per-CTA scratch tiles)
@@ -48,14 +53,14 @@ def bilinear_form(expr: Matrix) -> np.ndarray:
 
 
 # --------------------------------------------------------------------------------------------- program building
-def _operand(expr: Matrix, fly: bool) -> tp.Operand:
+def _operand(expr: Matrix, fly: bool, presum_view: Optional[Dict[str, int]] = None) -> tp.Operand:
     op = tp.Operand()
     if not isinstance(expr, BinOp):
         terms = [(1, QUADRANT_VIEW[expr.name])]
     elif fly:
         terms = [(coef, QUADRANT_VIEW[leaf.name]) for coef, leaf in expand_terms(expr)]
     else:
-        terms = [(1, PRESUM_VIEW[expr.name])]
+        terms = [(1, (presum_view or PRESUM_VIEW)[expr.name])]
     op.nterms = len(terms)
     for i, (coef, view) in enumerate(terms):
         op.view[i] = view
@@ -64,17 +69,19 @@ def _operand(expr: Matrix, fly: bool) -> tp.Operand:
 
 
 class ProgramBuilder:
-    def __init__(self, products: Dict[str, BinOp], fly: bool):
+    def __init__(self, products: Dict[str, BinOp], fly: bool, presum_view: Optional[Dict[str, int]] = None):
         self.pg = tp.Program()
         self.products = products
         self.fly = fly
+        self.presum_view = presum_view
 
     def product(self, name: str, slot: int, accumulate: int = 0, negate: int = 0, wait_free: int = 1, commit: int = 1,
                 a_view: Optional[int] = None, b_view: Optional[int] = None):
         pr = self.pg.product[self.pg.nproducts]
         if name in self.products:
             node = self.products[name]
-            pr.a, pr.b = _operand(node.op1, self.fly), _operand(node.op2, self.fly)
+            pr.a = _operand(node.op1, self.fly, self.presum_view)
+            pr.b = _operand(node.op2, self.fly, self.presum_view)
         else:  # level 0: whole operands
             pr.a.nterms, pr.a.view[0], pr.a.coef[0] = 1, a_view, 1
             pr.b.nterms, pr.b.view[0], pr.b.coef[0] = 1, b_view, 1
@@ -208,12 +215,13 @@ def level1_merged_program(ms) -> tp.Program:
     return b.pg
 
 
-def level1_strassen_program(ms) -> tp.Program:
-    """Strassen's original algorithm (algos/strassen_level1.py), all seven products of a tile in one CTA, operand sums
-    formed on the fly.  Slot P accumulates m1 + m7, then m3 + m6; slot Q accumulates m4 - m5, then holds m2; m1 and
-    m4 are tapped into fp32 tiles before their slots go on accumulating:
+def level1_strassen_program(ms, fly: bool = True) -> tp.Program:
+    """Strassen's original algorithm (algos/strassen_level1.py), all seven products of a tile in one CTA.  Operand
+    sums are formed on the fly (fly=True) or read from the presum workspace (fly=False: STRASSEN_PRESUM_VIEW, a launch
+    of its own materialises them first).  Slot P accumulates m1 + m7, then m3 + m6; slot Q accumulates m4 - m5, then
+    holds m2; m1 and m4 are tapped into fp32 tiles before their slots go on accumulating:
         c0 = P + Q          c1 = m3 - (m4 - m5) + m4          c2 = m2 + m4          c3 = (m3 + m6) - m2 + m1"""
-    b = ProgramBuilder(_products_by_name(ms), fly=True)
+    b = ProgramBuilder(_products_by_name(ms), fly=fly, presum_view=STRASSEN_PRESUM_VIEW)
     b.product("m1", P)
     b.epilogue([P], [], wait=[P], release=[P], dst_kind=1, dst=WS_T1)                # tap: m1
     b.product("m4", Q)
@@ -244,6 +252,33 @@ LEVEL2_CHAIN = [
     ("m3", (1, 1, 2, 0), 0, 1, 2, -1, 3),
     ("m6", (0, 1, 0, 1), -1, 0, -1, -1, 2),
 ]
+
+
+def strassen_presum_table(ms) -> Dict[str, List[Tuple[int, int, int, int, int]]]:
+    """Per side ("a", "b"): the presums of Strassen's original algorithm in workspace order, each as
+    (view slot, quadrant 0, coefficient 0, quadrant 1, coefficient 1), taken from the operands of the DSL products."""
+    found: Dict[str, Tuple[int, int, int, int, int]] = {}
+    for m in ms:
+        for expr in (m.op1, m.op2):
+            if isinstance(expr, BinOp):
+                (c0, l0), (c1, l1) = expand_terms(expr)
+                found[expr.name] = (STRASSEN_PRESUM_VIEW[expr.name], QUADRANT_VIEW[l0.name] % 8, c0,
+                                    QUADRANT_VIEW[l1.name] % 8, c1)
+    assert set(found) == set(STRASSEN_PRESUM_VIEW)
+    order = list(STRASSEN_PRESUM_VIEW)
+    return {"a": [found[n] for n in order if n.startswith("a")], "b": [found[n] for n in order if n.startswith("b")]}
+
+
+def strassen_view_coef(ms) -> Dict[int, Tuple[int, ...]]:
+    """What every view slot holds under the presum plan of Strassen's original algorithm (for `check_program`)."""
+    out: Dict[int, Tuple[int, ...]] = {}
+    for side in strassen_presum_table(ms).values():
+        for view, q0, c0, q1, c1 in side:
+            v = [0, 0, 0, 0]
+            v[q0] += c0
+            v[q1] += c1
+            out[view] = tuple(v)
+    return out
 
 
 def operand_code(expr: Matrix) -> int:
@@ -396,6 +431,7 @@ def all_programs() -> Dict[str, tp.Program]:
     return {
         "level0": level0_program(),
         "level1_strassen": level1_strassen_program(strassen(4, 4, 4)[1]),
+        "level1_strassen_presum": level1_strassen_program(strassen(4, 4, 4)[1], fly=False),
         "level1_full_fly": level1_full_program(ms, fly=True),
         "level1_full_ws": level1_full_program(ms, fly=False),
         "level1_first": level1_first_program(ms),
@@ -426,6 +462,11 @@ def verify_programs(programs: Dict[str, tp.Program]) -> None:
     got = tp.check_program(programs["level1_strassen"], level=1)["outputs"]
     for q, part in enumerate(strassen(4, 4, 4)[0].parts):
         assert np.array_equal(bilinear_form(part), want[q]) and np.array_equal(got[q], want[q]), ("level1_strassen", q)
+    got = tp.check_program(programs["level1_strassen_presum"], level=1,
+                           view_coef=strassen_view_coef(strassen(4, 4, 4)[1]))["outputs"]
+    for q in range(4):
+        assert np.array_equal(got[q], want[q]), ("level1_strassen_presum", q)
+    assert programs["level1_strassen_presum"].needs_feed == 0
     for name in ("level1_first_early", "level1_first"):
         r1 = tp.check_program(programs[name], level=1, expect=[0])
         assert np.array_equal(r1["outputs"][0], want[0]), name
@@ -548,6 +589,15 @@ def generate_tables() -> str:
         out.append(f'  {{"{name}", sb200_program_{name}}},\n')
     out.append("};\n")
     out.append(f"#define SB200_NUM_EMITTED_PROGRAMS {len(programs)}\n")
+    from .algos.strassen_level1 import strassen
+
+    out.append("/* Presums of Strassen's original algorithm under its presum plan, per side (A, B) in workspace order: "
+               "view slot that\n   reads the presum, then result = c0 * quadrant q0 + c1 * quadrant q1. */\n")
+    out.append("static const struct sb200_presum_pair { int view, q0, c0, q1, c1; } sb200_strassen_presums[2][5] = {\n")
+    table = strassen_presum_table(strassen(4, 4, 4)[1])
+    for side in ("a", "b"):
+        out.append("  {" + ", ".join("{%d, %d, %d, %d, %d}" % row for row in table[side]) + "},\n")
+    out.append("};\n")
     _, ms = strassen_winograd(4, 4, 4)
     out.append("/* The seven level-1 groups of a level-2 run in execution order.  a, b: operand codes (0..3 raw outer "
                "quadrant, 4..7 outer presum);\n   dst, src, src2, extra_dst: outer chain buffers X0..X2 (-1 none); "

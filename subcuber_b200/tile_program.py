@@ -81,7 +81,7 @@ class ProgramError(ValueError):
     pass
 
 
-def _operand_vector(op: Operand) -> np.ndarray:
+def _operand_vector(op: Operand, view_coef: Optional[Dict[int, Sequence[int]]] = None) -> np.ndarray:
     v = np.zeros(4, dtype=np.int64)
     if not (1 <= op.nterms <= MAX_TERMS):
         raise ProgramError("operand with a bad term count")
@@ -94,15 +94,20 @@ def _operand_vector(op: Operand) -> np.ndarray:
         side = s
         if op.coef[t] not in (1, -1):
             raise ProgramError("coefficients must be +1 or -1")
-        v += op.coef[t] * np.array(VIEW_COEF[name], dtype=np.int64)
+        coef = view_coef[op.view[t]] if view_coef and op.view[t] in view_coef else VIEW_COEF[name]
+        v += op.coef[t] * np.array(coef, dtype=np.int64)
     if op.nterms == 1 and op.coef[0] != 1:
         raise ProgramError("a single-term operand is loaded by TMA and cannot carry a sign; use `negate`")
     return v
 
 
 def check_program(pg: Program, level: int, nslots: int = 2, ws_in: Optional[Dict[int, np.ndarray]] = None,
-                  expect: Optional[Sequence[int]] = None, tiles: int = 3, algebra: bool = True) -> Dict[str, object]:
+                  expect: Optional[Sequence[int]] = None, tiles: int = 3, algebra: bool = True,
+                  view_coef: Optional[Dict[int, Sequence[int]]] = None) -> Dict[str, object]:
     """Validate `pg`.  Returns {"outputs": {quadrant: 4x4 matrix}, "ws": {...}, "bubbles": n}.
+
+    view_coef: what the views hold when that is not the Strassen-Winograd assignment of VIEW_COEF (view id ->
+               coefficients over the side's four quadrants), for plans that put other presums in the view slots.
 
     ws_in: symbolic contents of workspace buffers written by an earlier launch.
     algebra: False checks the hand-over protocol only (programs tied into an outer recursion step do not produce
@@ -139,7 +144,7 @@ def check_program(pg: Program, level: int, nslots: int = 2, ws_in: Optional[Dict
                 free[slot] -= 1
             elif not busy_until_commit[slot]:
                 raise ProgramError(f"product step {s} writes slot {slot} without owning it (needs wait_free)")
-            a, b = _operand_vector(pr.a), _operand_vector(pr.b)
+            a, b = _operand_vector(pr.a, view_coef), _operand_vector(pr.b, view_coef)
             if (pr.a.view[0] >= 8) or (pr.b.view[0] < 8):
                 raise ProgramError("A operand must use A-side views and B operand B-side views")
             val = np.outer(a, b) * (-1 if pr.negate else 1)

@@ -39,7 +39,8 @@ def test_registry_rows(lib):
     assert [r.name for r in runner.kernels(dtype="half", level=1)] == [
         "blackwell_f16_sw_fused_presum", "blackwell_f16_sw_interleaved_presum",
         "blackwell_f16_sw_fused_presum_2sm", "blackwell_f16_sw_interleaved_presum_2sm",
-        "blackwell_f16_sw_merged_presum_2sm", "blackwell_f16_strassen_fused_presum", "blackwell_f16_strassen_fused_presum_2sm", "blackwell_f16_sw_auto"]
+        "blackwell_f16_sw_merged_presum_2sm", "blackwell_f16_strassen_fused_presum", "blackwell_f16_strassen_fused_presum_2sm",
+        "blackwell_f16_strassen_presum_2sm", "blackwell_f16_sw_auto"]
     assert [r.name for r in runner.kernels(dtype="f32", level=0, regex="cubic")] == [
         "blackwell_f32_cubic_128x256", "blackwell_f32_cubic_128x128", "blackwell_f32_cubic_2sm_256x256"]
 

@@ -23,8 +23,10 @@ L1_F32 = ["blackwell_f32_sw_interleaved_presum", "blackwell_f32_sw_fused_presum"
 L2_F16 = ["blackwell_f16_sw_level2", "blackwell_f16_sw_level2_2sm"]
 L2_F32 = ["blackwell_f32_sw_level2", "blackwell_f32_sw_level2_2sm"]
 # Strassen's original algorithm: the same products of blocks summed another way, checked against the same oracle
-STRASSEN_F16 = ["blackwell_f16_strassen_fused_presum", "blackwell_f16_strassen_fused_presum_2sm"]
-STRASSEN_F32 = ["blackwell_f32_strassen_fused_presum", "blackwell_f32_strassen_fused_presum_2sm"]
+STRASSEN_F16 = ["blackwell_f16_strassen_fused_presum", "blackwell_f16_strassen_fused_presum_2sm",
+                "blackwell_f16_strassen_presum_2sm"]
+STRASSEN_F32 = ["blackwell_f32_strassen_fused_presum", "blackwell_f32_strassen_fused_presum_2sm",
+                "blackwell_f32_strassen_presum_2sm"]
 # bfloat16 storage: the f16 kernels with the other 16-bit format
 BF16 = ["blackwell_bf16_cubic_128x256", "blackwell_bf16_cubic_2sm_256x256", "blackwell_bf16_sw_fused_presum_2sm",
         "blackwell_bf16_sw_interleaved_presum", "blackwell_bf16_sw_interleaved_presum_2sm",
@@ -529,6 +531,23 @@ def test_uniform_inputs_tf32(kernel, dist, oracle, cuda_device):
     err, model_err = _rel_fro(got, truth), _rel_fro(model, truth)
     assert err <= 4.0 * model_err + 1e-6, f"{err:.3e} vs TF32 model {model_err:.3e}"
     assert err < 3e-3
+
+
+@pytest.mark.parametrize("dtype", ["f16", "f32"])
+@pytest.mark.parametrize("shape", [(2048, 2048, 2048), (1001, 2568, 1160), (4096, 1536, 3072)])
+def test_strassen_presum_plan_equals_the_fused_plan(dtype, shape, cuda_device):
+    """Strassen's original algorithm on materialised presums (a launch that only forms the ten presums, then the seven
+    products) runs the tile program of the fused plan on operand values that are the same bit for bit (fp32 sum of two
+    raw values, one rounding), so the two plans agree exactly on any input."""
+    from subcuber_b200 import inputs
+
+    m, n, k = shape
+    a, b = inputs.operands(dtype, "uniform1", m, n, k, seed=21)
+    fused = _run(f"blackwell_{dtype}_strassen_fused_presum_2sm", a, b, cuda_device)
+    fast = _run(f"blackwell_{dtype}_strassen_presum_2sm", a, b, cuda_device)
+    assert np.array_equal(fused, fast), f"{np.count_nonzero(fused != fast)} elements differ"
+    again = _run(f"blackwell_{dtype}_strassen_presum_2sm", a, b, cuda_device)
+    assert np.array_equal(fast, again)
 
 
 # ----------------------------------------------------------------------------------------- full size
