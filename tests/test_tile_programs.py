@@ -85,3 +85,40 @@ def test_the_library_runs_the_generated_tables(lib):
     reads_m0 = sum(1 for i in range(second.nepilogues) for t in range(second.epilogue[i].nsrc)
                    if second.epilogue[i].src[t] == 0)
     assert reads_m0 == 1
+
+
+def test_strassen_presum_plan_tables(lib):
+    """Strassen's original algorithm on materialised presums: the generated presum table lists each two-term operand
+    sum of the DSL products once, every product operand of the program is a single view, and with the views holding
+    what the table says the program yields the four blocks of the product."""
+    import numpy as np
+
+    from subcuber_b200 import emit
+    from subcuber_b200.algos.strassen_level1 import strassen
+    from subcuber_b200.algos.strassen_winograd_level1 import strassen_winograd
+
+    c, ms = strassen(4, 4, 4)
+    table = emit.strassen_presum_table(ms)
+    assert [len(table[s]) for s in ("a", "b")] == [5, 5]
+    views = [row[0] for s in ("a", "b") for row in table[s]]
+    assert len(set(views)) == 10 and all(v < 8 for v in views[:5]) and all(v >= 8 for v in views[5:])
+    # a1 and b1 are read by no product of this algorithm on their own: their view slots carry the fifth presums
+    assert 1 in views and 9 in views
+    for side in ("a", "b"):
+        for view, q0, c0, q1, c1 in table[side]:
+            assert q0 != q1 and c0 in (1, -1) and c1 in (1, -1)
+    pg = tp.from_library("level1_strassen_presum")
+    assert pg.needs_feed == 0 and pg.nproducts == 7
+    for i in range(pg.nproducts):
+        assert pg.product[i].a.nterms == 1 and pg.product[i].b.nterms == 1
+    got = tp.check_program(pg, level=1, view_coef=emit.strassen_view_coef(ms))["outputs"]
+    want = {q: emit.bilinear_form(part) for q, part in enumerate(strassen_winograd(4, 4, 4)[0].parts)}
+    for q in range(4):
+        assert np.array_equal(got[q], want[q])
+    # without the plan's view assignment the same table is not the product (views 1 and 9 would be raw quadrants)
+    with pytest.raises(tp.ProgramError):
+        tp.check_program(pg, level=1)
+    # the table the library was built with is the generated one
+    text = emit.generate_tables()
+    for side in ("a", "b"):
+        assert "{" + ", ".join("{%d, %d, %d, %d, %d}" % row for row in table[side]) + "}" in text
