@@ -464,31 +464,79 @@ def main():
     if exchange is not None:
         a, b = exchange.last()
     e2e_steps = max(4, min(10, args.steps))
-    a_host = a.cpu().pin_memory()
-    b_host = b.cpu().pin_memory()
-    d_host = torch.empty((m, n), dtype=tdt).pin_memory()
-    pipe = runner.HostPipeline(kernel, m, n, k, tdt, device, opts)
-    for _ in range(3):
-        pipe.submit(a_host, b_host, d_host)
-    pipe.finish()
-    barrier()
     e0 = torch.cuda.Event(enable_timing=True)
     e1 = torch.cuda.Event(enable_timing=True)
-    e0.record(pipe.s_mm)   # every stream is idle here: the first copy starts after this point
-    for _ in range(e2e_steps):
-        pipe.submit(a_host, b_host, d_host)
-    pipe.join(pipe.s_mm)   # the last result has reached the host
-    e1.record(pipe.s_mm)
-    pipe.finish()
-    barrier()
+    if exchange is not None and hasattr(exchange, "feed"):
+        # several GPUs: every GPU uploads only the shards it owns (1/P of A and of B) from its pinned host memory; the
+        # exchange spreads them over NVLink under the kernels of the steps before; every GPU downloads its block of D
+        a_own, b_own = exchange.shard_views(0)
+        a_host = a_own.cpu().pin_memory()
+        b_host = b_own.cpu().pin_memory()
+        d_host = torch.empty((m, n), dtype=tdt).pin_memory()
+        d_bufs = [d, torch.empty_like(d)]
+        s_out = torch.cuda.Stream(device)
+        done_mm = [torch.cuda.Event() for _ in range(2)]
+        done_out = [torch.cuda.Event() for _ in range(2)]
+        h2d_bytes = (a_host.numel() + b_host.numel()) * es
+        exchange.start_feeding()
+
+        def e2e_step(i, after=None):
+            exchange.feed(a_host, b_host, after)
+            ai, bi = exchange.next()
+            slot = i % 2
+            stream.wait_event(done_out[slot])          # this buffer's previous result has left
+            rc = lib.sb200_gemm_opt(kernel.encode(), ai.data_ptr(), bi.data_ptr(), d_bufs[slot].data_ptr(), m, n, k,
+                                    ws.ptr, ws.nbytes, stream.cuda_stream, opts_ref)
+            if rc != 0:
+                raise runner.KernelError(kernel, rc)
+            exchange.done()
+            done_mm[slot].record(stream)
+            s_out.wait_event(done_mm[slot])
+            with torch.cuda.stream(s_out):
+                d_host.copy_(d_bufs[slot], non_blocking=True)
+                done_out[slot].record(s_out)
+
+        for ev in done_out:
+            ev.record(stream)
+        for i in range(3 + exchange.NBUF):              # the first steps still run on shards issued before
+            e2e_step(i)
+        barrier()
+        e0.record(stream)                               # every stream is idle here: the first upload waits for this
+        for i in range(e2e_steps):
+            e2e_step(i, after=e0 if i == 0 else None)
+        stream.wait_stream(s_out)                       # the last result has reached the host
+        e1.record(stream)
+        barrier()
+        check_status()
+        exchange.check_status()
+        d2h_bytes = m * n * es
+        note = ("bytes per GPU and step: every GPU uploads the shards of A and B it owns from its pinned host memory "
+                "(the exchange spreads them over NVLink) and downloads its block of D")
+    else:
+        a_host = a.cpu().pin_memory()
+        b_host = b.cpu().pin_memory()
+        d_host = torch.empty((m, n), dtype=tdt).pin_memory()
+        pipe = runner.HostPipeline(kernel, m, n, k, tdt, device, opts)
+        for _ in range(3):
+            pipe.submit(a_host, b_host, d_host)
+        pipe.finish()
+        barrier()
+        e0.record(pipe.s_mm)   # every stream is idle here: the first copy starts after this point
+        for _ in range(e2e_steps):
+            pipe.submit(a_host, b_host, d_host)
+        pipe.join(pipe.s_mm)   # the last result has reached the host
+        e1.record(pipe.s_mm)
+        pipe.finish()
+        barrier()
+        h2d_bytes, d2h_bytes = (m * k + k * n) * es, m * n * es
+        note = "bytes per GPU and step; every GPU copies the operands it multiplies from its own pinned host memory"
     e2e_ms = e0.elapsed_time(e1)
     if world > 1:
         t = torch.tensor([e2e_ms], dtype=torch.float64, device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t.item())
     e2e = {"value": flops_step * e2e_steps / (e2e_ms * 1e-3) / 1e12, "unit": UNIT,
-           "h2d_bytes_per_step": (m * k + k * n) * es, "d2h_bytes_per_step": m * n * es, "steps": e2e_steps,
-           "note": "bytes per GPU and step; every GPU copies the slabs it multiplies from its own pinned host memory"}
+           "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes, "steps": e2e_steps, "note": note}
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline and dtn == "f16" and level >= 1:

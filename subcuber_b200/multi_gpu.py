@@ -378,6 +378,12 @@ class GridExchange:
         self.issued = 0
         self.taken = 0
         self._last = None
+        self.feeding = False
+        self.fed = 0
+        self.pushed = [torch.cuda.Event() for _ in range(nbuf)]     # my pushes out of buffer j have left
+        self.uploaded = [torch.cuda.Event() for _ in range(nbuf)]   # fresh shards have reached buffer j (feeding)
+        for ev in self.pushed:
+            ev.record(torch.cuda.current_stream(device))
         torch.cuda.synchronize(device)
         dist.barrier()  # every process has mapped every buffer and zeroed its flags before the first push
 
@@ -388,6 +394,45 @@ class GridExchange:
         """Where this rank's A shard and B shard live for a step that uses buffer j (write new shard values here
         before the step's `next`: the pushes read them from here)."""
         return self.a_own[j], self.b_own[j]
+
+    def start_feeding(self) -> None:
+        """From now on every step's shards come from the caller (`feed`), e.g. from pinned host memory: each GPU
+        uploads only the 1/P of A and of B it owns, and the exchange spreads them over NVLink.  Steps whose pushes
+        are already in flight keep the shards they were issued with."""
+        if self.feeding:
+            return
+        nbuf = self.NBUF
+        with torch.cuda.device(self.device):
+            # a slab nobody shares is read by the GEMM where the shard lies: one copy per buffer, so that the upload
+            # for a later step cannot touch what a running GEMM reads
+            if not self.share_a:
+                self.a_own = [self.a_own[0].clone() for _ in range(nbuf)]
+            if not self.share_b:
+                self.b_own = [self.b_own[0].clone() for _ in range(nbuf)]
+            self.upload = torch.cuda.Stream(device=self.device)
+            for ev in self.uploaded:
+                ev.record(torch.cuda.current_stream(self.device))
+        self.feeding = True
+        self.fed = self.issued
+
+    def feed(self, a_shard: torch.Tensor, b_shard: torch.Tensor, after: Optional[torch.cuda.Event] = None) -> None:
+        """Shards of the next step that has none yet (steps are fed in order, before the `next` that starts their
+        pushes: `next` of step s starts the pushes of step s + NBUF - 1).  Host tensors should be pinned: the copies
+        are asynchronous, on a stream of their own, and wait for the GEMM and the pushes that last used the buffer
+        (and for `after`, when given)."""
+        if not self.feeding:
+            raise RuntimeError("call start_feeding() first")
+        j = self.fed % self.NBUF
+        with torch.cuda.device(self.device):
+            if after is not None:
+                self.upload.wait_event(after)
+            self.upload.wait_event(self.consumed_local[j])
+            self.upload.wait_event(self.pushed[j])
+            with torch.cuda.stream(self.upload):
+                self.a_own[j].copy_(a_shard, non_blocking=True)
+                self.b_own[j].copy_(b_shard, non_blocking=True)
+            self.uploaded[j].record(self.upload)
+        self.fed += 1
 
     def _signal(self, kind: int, buf: int, value: int, stream) -> None:
         """Raise my counter (kind, buf) in every peer's flag array to `value`, behind the work queued on `stream`."""
@@ -409,7 +454,11 @@ class GridExchange:
     def _start(self) -> None:
         s = self.issued
         j = s % self.NBUF
+        if self.feeding and self.fed <= s:
+            raise RuntimeError(f"step {s} has not been fed its shards")
         with torch.cuda.device(self.device):
+            if self.feeding:
+                self.comm.wait_event(self.uploaded[j])                    # the step's shards have arrived
             self.comm.wait_event(self.consumed_local[j])                  # my GEMM that read buffer j is over
             self._wait(1, j, s - self.NBUF + 1, self.comm)                # ... and so are the peers' (step s - NBUF)
             free = self.free_ev[j]
@@ -428,6 +477,7 @@ class GridExchange:
                         turn += 1
             for st in self.copy_streams:
                 self.comm.wait_stream(st)
+            self.pushed[j].record(self.comm)
             self._signal(0, j, s + 1, self.comm)                          # my pushes for step s have landed everywhere
         self.issued += 1
 
@@ -446,6 +496,8 @@ class GridExchange:
             arrived = torch.cuda.Event()
             arrived.record(self.arrivals)
             cur.wait_event(arrived)
+            if self.feeding:
+                cur.wait_event(self.uploaded[j])   # an unshared slab is read where the upload put it
         after.record(cur)
         self.wait_events.append((before, after))
         self.taken += 1

@@ -35,6 +35,22 @@ def main():
         # against the same kernel on private copies of the slabs this rank should hold
         want_a, want_b = multi_gpu.expected_slabs(gp, rank, "f16", dev, seed=5)
         ok = ok and torch.equal(d, runner.gemm(kernel, want_a, want_b, opts=opts))
+    # feeding mode: every rank uploads the shards it owns from pinned host memory, new values every step (the A shards
+    # scaled by a power of two, so the expected block is the same GEMM on scaled slabs, bit for bit); the two steps
+    # whose pushes were already in flight still run on the old shards
+    first_fed = ex.issued
+    scale = lambda s: (1.0, 2.0, 0.5)[s % 3] if s >= first_fed else 1.0
+    a_own, b_own = ex.shard_views(0)
+    a_host = [(a_own * c).cpu().pin_memory() for c in (1.0, 2.0, 0.5)]
+    b_host = b_own.cpu().pin_memory()
+    ex.start_feeding()
+    for step in range(5, 12):
+        ex.feed(a_host[(step + ex.NBUF - 1) % 3], b_host)     # shards of the step whose pushes this `next` starts
+        a, b = ex.next()
+        runner.gemm(kernel, a, b, d, workspace=ws, check=False, opts=opts)
+        ex.done()
+        torch.cuda.synchronize(dev)
+        ok = ok and torch.equal(d, runner.gemm(kernel, want_a * scale(step), want_b, opts=opts))
     ex.check_status()
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
