@@ -359,6 +359,7 @@ def main():
     if exchange is not None:
         exchange.check_status()
         exchange_wait_ms = exchange.wait_ms(args.steps)
+    own_elapsed_ms = elapsed_ms
     if world > 1:
         t = torch.tensor([elapsed_ms], dtype=torch.float64, device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -375,6 +376,15 @@ def main():
             per_launch[l] += ms.value
     per_launch = [x / args.steps for x in per_launch]
     lib.sb200_events_destroy(evl)
+    # several GPUs: what every rank measured on its own stream (ms per step: whole step, its launches, its waits)
+    per_rank = None
+    if world > 1:
+        mine = torch.tensor([own_elapsed_ms / args.steps, sum(per_launch), exchange_wait_ms or 0.0], dtype=torch.float64,
+                            device=device)
+        everyone = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(everyone, mine)
+        per_rank = [{"ms_per_step": round(float(t_[0]), 4), "launches_ms": round(float(t_[1]), 4),
+                     "wait_ms": round(float(t_[2]), 4)} for t_ in everyone]
     dom = max(range(launches), key=lambda i: per_launch[i])
     # algorithmic flops of a GEMM are 2MNK at every level; each of its 7 (49) products carries 1/7 (1/49) of them
     if dtn == "f64":
@@ -563,7 +573,7 @@ def main():
             "frac_of_dense_peak": value / (DENSE_PEAK[dtn] * world),
             "dense_peak": {"value": DENSE_PEAK[dtn] * world, "unit": "TFLOP/s", "source": "nominal, dense, per GPU x GPUs"},
             "cublas": cublas, "sustained": sustained, "parity": parity,
-            "exchange_wait_ms_per_step": exchange_wait_ms,
+            "exchange_wait_ms_per_step": exchange_wait_ms, "per_rank": per_rank,
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches * args.steps, "host_enqueue_ms_per_step": host_ms,
             "roofline": roofline, "cpu_baseline": cpu_baseline,
         }
