@@ -471,7 +471,11 @@ class GridExchange:
                     n_rows = shard.shape[0]
                     lo = piece * n_rows // self.PIECES
                     hi = (piece + 1) * n_rows // self.PIECES
-                    for r in sorted(dsts):
+                    # every rank starts with the peer after itself: were all of them to go through their peers in
+                    # rank order, the highest rank would be served last by everyone and wait for its slabs every step
+                    order = sorted(dsts)
+                    first = sum(1 for r in order if r < self.rank)
+                    for r in order[first:] + order[:first]:
                         with torch.cuda.stream(self.copy_streams[turn % len(self.copy_streams)]):
                             dsts[r][j][rows.start + lo:rows.start + hi].copy_(shard[lo:hi], non_blocking=True)
                         turn += 1
