@@ -422,18 +422,7 @@ __device__ __forceinline__ void presum_rect(const PresumSideJob& j, int row0, in
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       if (o[u] < 0) continue;
-      if (j.npairs > 0) {
-        // table-driven two-term presums: fp32 sum of the raw values, one rounding
-        for (int r = 0; r < j.npairs; ++r) {
-          const int q0 = j.pair_q[r][0], q1 = j.pair_q[r][1];
-          const uint4 y0 = q0 == 0 ? x0[u] : (q0 == 1 ? x1[u] : (q0 == 2 ? x2[u] : x3[u]));
-          const uint4 y1 = q1 == 0 ? x0[u] : (q1 == 1 ? x1[u] : (q1 == 2 ? x2[u] : x3[u]));
-          VecAcc<ESIZE> s(bf);
-          s.set(y0, j.pair_c[r][0]);
-          s.add(y1, j.pair_c[r][1]);
-          *reinterpret_cast<uint4*>(out + r * q + o[u]) = s.pack();
-        }
-      } else if (j.side == 0) {
+      if (j.side == 0) {
         // A side: S1 = A2 + A3, S2 = S1 - A0, A02 = A0 - A2, A1S2 = A1 - S2
         VecAcc<ESIZE> s(bf);
         s.set(x2[u], 1); s.add(x3[u], 1);                             // S1
@@ -463,9 +452,57 @@ __device__ __forceinline__ void presum_rect(const PresumSideJob& j, int row0, in
   }
 }
 
+// Table-driven two-term presums over a whole quadrant (PresumSideJob::npairs > 0): result r = c0 * quadrant q0 +
+// c1 * quadrant q1, fp32 sum of the raw values, one rounding.  A function of its own, so that the loop above stays
+// as it is for the plans that run beside products.
+template <int ESIZE>
+__device__ __forceinline__ void presum_pairs(const PresumSideJob& j, int gtid, int gthreads, bool bf) {
+  constexpr int EPV = 16 / ESIZE;
+  constexpr int U = 4;
+  const int vec_per_row = j.cols / EPV;
+  const long long total = static_cast<long long>(j.rows) * vec_per_row;
+  const long long q = static_cast<long long>(j.rows) * j.cols * ESIZE;  // bytes per result matrix
+  char* out = static_cast<char*>(j.dst);
+  for (long long v0 = gtid; v0 < total; v0 += static_cast<long long>(gthreads) * U) {
+    uint4 x[U][4];
+    long long o[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long v = v0 + static_cast<long long>(u) * gthreads;
+      o[u] = -1;
+      if (v < total) {
+        const int r = static_cast<int>(v / vec_per_row);
+        const int c = static_cast<int>(v - static_cast<long long>(r) * vec_per_row) * EPV;
+        const long long in = (r * j.ld + c) * ESIZE;
+        const bool has_r = r < j.rows2, has_c = c < j.cols2;
+        const uint4 zero = make_uint4(0, 0, 0, 0);
+        x[u][0] = ptx::ldg_nc_v4(static_cast<const char*>(j.src[0]) + in);
+        x[u][1] = has_c ? ptx::ldg_nc_v4(static_cast<const char*>(j.src[1]) + in) : zero;
+        x[u][2] = has_r ? ptx::ldg_nc_v4(static_cast<const char*>(j.src[2]) + in) : zero;
+        x[u][3] = (has_r && has_c) ? ptx::ldg_nc_v4(static_cast<const char*>(j.src[3]) + in) : zero;
+        o[u] = (static_cast<long long>(r) * j.cols + c) * ESIZE;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (o[u] < 0) continue;
+      for (int r = 0; r < j.npairs; ++r) {
+        const int q0 = j.pair_q[r][0], q1 = j.pair_q[r][1];
+        const uint4 y0 = q0 == 0 ? x[u][0] : (q0 == 1 ? x[u][1] : (q0 == 2 ? x[u][2] : x[u][3]));
+        const uint4 y1 = q1 == 0 ? x[u][0] : (q1 == 1 ? x[u][1] : (q1 == 2 ? x[u][2] : x[u][3]));
+        VecAcc<ESIZE> s(bf);
+        s.set(y0, j.pair_c[r][0]);
+        s.add(y1, j.pair_c[r][1]);
+        *reinterpret_cast<uint4*>(out + r * q + o[u]) = s.pack();
+      }
+    }
+  }
+}
+
 template <int ESIZE>
 __device__ __forceinline__ void presum_side_job(const PresumSideJob& j, int gtid, int gthreads, bool bf) {
-  presum_rect<ESIZE>(j, 0, j.rows, 0, j.cols, gtid, gthreads, bf);
+  if (j.npairs > 0) presum_pairs<ESIZE>(j, gtid, gthreads, bf);
+  else presum_rect<ESIZE>(j, 0, j.rows, 0, j.cols, gtid, gthreads, bf);
 }
 
 // One-launch plan: the presum warps of a CTA (PT threads, `ptid` among them) draw chunks until the list is exhausted.
